@@ -1,0 +1,102 @@
+/*
+ * mxq.h -- C ABI of libmxq, the sm_100a implementation of MASE's MX / block-floating-point
+ * quantizers and of the forward GEMM of its MX Linear modules.
+ *
+ * Conventions
+ *   - every pointer named x/y/codes/scales/... is DEVICE memory owned by the caller; the library never
+ *     allocates, frees or keeps device memory, and never synchronises the host with the device;
+ *   - every kernel is enqueued on `stream` (a cudaStream_t passed as void*; NULL = legacy default stream);
+ *   - log2 tables are HOST pointers to 256 bytes, copied by value into the launch;
+ *   - functions return MXQ_OK (0) or a negative MXQ_ERR_* code; nothing throws or exits.
+ *
+ * Each entry point cites the MASE function it replaces (paths inside the MASE repository).
+ */
+#ifndef MXQ_H_
+#define MXQ_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MXQ_VERSION 1
+
+/* element types of float tensors */
+#define MXQ_F32 0
+#define MXQ_BF16 1
+
+#define MXQ_OK 0
+#define MXQ_ERR_DTYPE (-1)     /* unsupported element type */
+#define MXQ_ERR_SHAPE (-2)     /* sizes out of range or not divisible as required */
+#define MXQ_ERR_FORMAT (-3)    /* unsupported (exponent, fraction) or bit width */
+#define MXQ_ERR_ALIGN (-4)     /* pointer not aligned to 16 bytes */
+#define MXQ_ERR_NULL (-5)      /* required pointer is NULL */
+#define MXQ_ERR_LAUNCH (-6)    /* the CUDA runtime reported an error at launch */
+#define MXQ_ERR_UNSUPPORTED (-7)
+#define MXQ_ERR_DEVICE (-8)    /* a kernel reported a device-side error status (bounded wait ran out) */
+
+int mxq_version(void);
+const char *mxq_error_string(int code);
+
+/*
+ * log2 tables.  The reference picks the shared exponent as ceil(log2(amax)) or floor(log2(amax)) with
+ * `torch.log2` evaluated on the host in fp32 or bf16; its rounding is observable next to powers of two.
+ * The kernels compute the exact integer result from the bits of amax and correct it with a table indexed
+ * by the biased exponent `ex` of amax (1..254):
+ *   ceil tables  (MXINT, block-fp): mantissas 1..t[ex] (23-bit units for fp32 input, 7-bit units for bf16
+ *                input) give ceil(log2(amax)) == ex-127 instead of ex-126;
+ *   floor table  (MXFP):            the top t[ex] mantissas (2^23 - t[ex] .. 2^23 - 1) give
+ *                floor(log2(amax)) == ex-126 instead of ex-127.
+ * The host-side package builds them from the host's own torch.log2.
+ */
+
+/* MXINT quantize-dequantize.  Replaces chop/nn/quantizers/mxint/mxint.py:145-171 (mxint_quantizer_sim,
+ * non-search branch) = extract_mxint_components + compose_mxint_tensor (mxint/fake.py:11-80) on a tensor
+ * already flattened so that each block is `block` consecutive elements.
+ * x: n_blocks*block elements of in_dtype; y: same count of out_dtype.  2 <= bits <= 8. */
+int mxq_mxint_fake(const void *x, void *y, int in_dtype, int out_dtype, int64_t n_blocks, int block, int bits,
+                   const uint8_t *ceil_tab_host, void *stream);
+
+/* MXINT codes.  Replaces extract_mxint_components (mxint/fake.py:11-56).  mant: int8 [n_blocks*block] in
+ * [-2^(bits-1), 2^(bits-1)-1]; scales: uint8 [n_blocks] = clamp(ceil(log2(amax)) + 127, 0, 255). */
+int mxq_mxint_extract(const void *x, int8_t *mant, uint8_t *scales, int in_dtype, int64_t n_blocks, int block,
+                      int bits, const uint8_t *ceil_tab_host, void *stream);
+
+/* Replaces compose_mxint_tensor (mxint/fake.py:59-80). */
+int mxq_mxint_compose(const int8_t *mant, const uint8_t *scales, void *y, int out_dtype, int64_t n_blocks,
+                      int block, int bits, void *stream);
+
+/* MXFP quantize-dequantize with E exponent and F fraction bits per element, E8M0 shared scale.
+ * Replaces chop/nn/quantizers/mxfp/mxfp.py:14-115 (mxfp_quantizer_sim, non-search branch) =
+ * extract_mxfp_components + compose_mxfp_tensor (mxfp/fake.py:12-104) with the element codec of
+ * _minifloat_mx/fake.py:11-149 (is_finite=True, round-to-nearest).
+ * (E,F) in {(4,3),(5,2),(2,3),(3,2),(2,1),(1,2)}. */
+int mxq_mxfp_fake(const void *x, void *y, int in_dtype, int out_dtype, int64_t n_blocks, int block, int E, int F,
+                  const uint8_t *floor_tab_host, void *stream);
+
+/* MXFP codes.  Replaces extract_mxfp_components (mxfp/fake.py:12-72).  codes: uint8 [n_blocks*block], one
+ * element per byte (sign | exponent | fraction in the low 1+E+F bits); scales: uint8 [n_blocks] (E8M0). */
+int mxq_mxfp_extract(const void *x, uint8_t *codes, uint8_t *scales, int in_dtype, int64_t n_blocks, int block,
+                     int E, int F, const uint8_t *floor_tab_host, void *stream);
+
+/* Replaces compose_mxfp_tensor (mxfp/fake.py:75-104). */
+int mxq_mxfp_compose(const uint8_t *codes, const uint8_t *scales, void *y, int out_dtype, int64_t n_blocks,
+                     int block, int E, int F, void *stream);
+
+/* Element-wise minifloat quantize-dequantize.  Replaces minifloat_quantizer_sim
+ * (_minifloat_mx/minifloat.py:12-33) for is_finite=True, round-to-nearest. */
+int mxq_minifloat_fake(const void *x, void *y, int in_dtype, int out_dtype, int64_t n, int E, int F, void *stream);
+
+/* Block floating point with tiles of `bs` consecutive elements of the last dimension (a ragged last tile is
+ * padded with zeros).  Replaces _block_fp_quantize (chop/nn/quantizers/block_fp.py:7-82) for the tilings in
+ * which a tile lies inside one row: 1-D tensors, 2-D activations, and block shapes [1, bs].
+ * x, y: rows*cols elements of `dtype`.  width = mantissa bits + sign; exponent in
+ * [-exp_bias, 2^exp_width - 1 - exp_bias]. */
+int mxq_bfp_fake(const void *x, void *y, int dtype, int64_t rows, int64_t cols, int bs, int width, int exp_width,
+                 int exp_bias, const uint8_t *ceil_tab_host, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MXQ_H_ */

@@ -1,0 +1,64 @@
+"""ctypes binding of libmxq.so, the C-ABI library declared in include/mxq.h.
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_int, c_int64, c_void_p, c_char_p
+
+_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libmxq.so")
+_lib = None
+
+# name -> argument types, exactly the prototypes of include/mxq.h
+_PROTOTYPES = {
+    "mxq_version": [],
+    "mxq_mxint_fake": [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_void_p, c_void_p],
+    "mxq_mxint_extract": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p],
+    "mxq_mxint_compose": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p],
+    "mxq_mxfp_fake": [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p],
+    "mxq_mxfp_extract": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p],
+    "mxq_mxfp_compose": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p],
+    "mxq_minifloat_fake": [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_void_p],
+    "mxq_bfp_fake": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+}
+
+
+class MxqError(RuntimeError):
+    pass
+
+
+def library_path() -> str:
+    return _PATH
+
+
+def exported_symbols() -> list[str]:
+    return sorted(_PROTOTYPES) + ["mxq_error_string"]
+
+
+def lib():
+    """The loaded library.  Raises if it has not been built (`python -m mase_b200.build`)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_PATH):
+            raise MxqError(
+                f"{_PATH} is missing: build it with `python -m mase_b200.build` (needs nvcc). "
+                "mase_b200 has no CPU or eager fallback."
+            )
+        handle = ctypes.CDLL(_PATH)
+        for name, argtypes in _PROTOTYPES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        handle.mxq_error_string.argtypes = [c_int]
+        handle.mxq_error_string.restype = c_char_p
+        _lib = handle
+    return _lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = lib().mxq_error_string(code).decode()
+        raise MxqError(f"{what} failed: {msg} (code {code})")

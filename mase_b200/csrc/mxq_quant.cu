@@ -1,0 +1,504 @@
+// Block quantizer kernels (MXINT, MXFP, minifloat, block floating point) and their C entry points.
+//
+// Fast path: the tensor is a flat run of blocks of B consecutive elements, B a power of two.  Every
+// thread owns one 16-byte vector (4 fp32 or 8 bf16 elements) per step, so a block is shared by
+// G = B / vector-length neighbouring lanes; the block maximum is found with log2(G) xor-shuffles, the
+// shared exponent is derived from its bits, and elements are encoded in registers.  Loads and stores are
+// 128-bit, fully coalesced and streaming (evict-first); a CTA handles kUnroll independent vectors per
+// thread per step to keep enough bytes in flight for HBM3e.
+//
+// Generic path: any other block size (smaller than a vector, not a power of two, wider than a warp's
+// span, or a ragged row tail for block-fp) is handled by one thread per block with scalar accesses.
+
+#include "mxq_common.cuh"
+
+namespace mxq {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+enum class Mode { kFake, kCodes };
+
+template <typename T>
+__device__ __forceinline__ T group_max(T v, int group) {
+  for (int o = 1; o < group; o <<= 1) {
+    T w = __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    v = v > w ? v : w;
+  }
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// MXINT
+// ---------------------------------------------------------------------------------------------------
+template <typename Tin, typename Tout, Mode kMode>
+__global__ void __launch_bounds__(kThreads)
+mxint_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, int8_t *__restrict__ mant, uint8_t *__restrict__ scales,
+             int64_t n_vec, int group, int bits, const __grid_constant__ Log2Tab tab) {
+  constexpr int N = Elem<Tin>::kVec;
+  const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+  const int64_t step = (int64_t)gridDim.x * kThreads * kUnroll;
+  for (int64_t base = (int64_t)blockIdx.x * kThreads * kUnroll; base < n_vec; base += step) {
+    uint4 raw[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + u * kThreads + threadIdx.x;
+      raw[u] = i < n_vec ? ld_stream(xv + i) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + u * kThreads + threadIdx.x;
+      uint32_t b[N];
+      unpack(raw[u], b);
+      float amax = 0.f;
+#pragma unroll
+      for (int k = 0; k < N; ++k) amax = fmaxf(amax, fabsf(__uint_as_float(b[k])));
+      amax = group_max(amax, group);
+      const MxintBlock p = mxint_block<Elem<Tin>::kBf16>(amax, bits, tab);
+      if (i >= n_vec) continue;
+      if constexpr (kMode == Mode::kFake) {
+        float out[N];
+#pragma unroll
+        for (int k = 0; k < N; ++k) out[k] = mxint_dequant(mxint_mant(__uint_as_float(b[k]), p), p);
+        store_vals(y, i * N, out);
+      } else {
+        uint32_t c[N];
+#pragma unroll
+        for (int k = 0; k < N; ++k) c[k] = (uint32_t)(int)mxint_mant(__uint_as_float(b[k]), p) & 0xFFu;
+        store_bytes(reinterpret_cast<uint8_t *>(mant), i * N, c);
+        if ((threadIdx.x & (group - 1)) == 0) scales[i / group] = (uint8_t)p.scale;
+      }
+    }
+  }
+}
+
+template <typename Tin, typename Tout, Mode kMode>
+__global__ void __launch_bounds__(kThreads)
+mxint_generic_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, int8_t *__restrict__ mant,
+                     uint8_t *__restrict__ scales, int64_t n_blocks, int block, int bits,
+                     const __grid_constant__ Log2Tab tab) {
+  for (int64_t blk = (int64_t)blockIdx.x * kThreads + threadIdx.x; blk < n_blocks;
+       blk += (int64_t)gridDim.x * kThreads) {
+    const Tin *xb = x + blk * block;
+    float amax = 0.f;
+    for (int k = 0; k < block; ++k) amax = fmaxf(amax, fabsf(load_scalar(xb + k)));
+    const MxintBlock p = mxint_block<Elem<Tin>::kBf16>(amax, bits, tab);
+    for (int k = 0; k < block; ++k) {
+      const float m = mxint_mant(load_scalar(xb + k), p);
+      if constexpr (kMode == Mode::kFake)
+        store_scalar(y + blk * block + k, mxint_dequant(m, p));
+      else
+        mant[blk * block + k] = (int8_t)(int)m;
+    }
+    if constexpr (kMode == Mode::kCodes) scales[blk] = (uint8_t)p.scale;
+  }
+}
+
+template <typename Tout>
+__global__ void __launch_bounds__(kThreads)
+mxint_compose_kernel(const int8_t *__restrict__ mant, const uint8_t *__restrict__ scales, Tout *__restrict__ y,
+                     int64_t n, int block, int bits) {
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads) {
+    const int k = (int)scales[i / block] - 127;
+    const float m = (float)mant[i];
+    // mant / 2**(bits-1) * 2**(scale-127); 2**128 is inf in the reference's working dtype
+    const float v = k >= 128 ? m * __int_as_float(0x7F800000) : m * pow2f(k - (bits - 1));
+    store_scalar(y + i, v);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// MXFP
+// ---------------------------------------------------------------------------------------------------
+template <typename Tin, typename Tout, Mode kMode, int E, int F>
+__global__ void __launch_bounds__(kThreads)
+mxfp_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, uint8_t *__restrict__ codes, uint8_t *__restrict__ scales,
+            int64_t n_vec, int group, const __grid_constant__ Log2Tab tab) {
+  constexpr int N = Elem<Tin>::kVec;
+  const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+  const int64_t step = (int64_t)gridDim.x * kThreads * kUnroll;
+  for (int64_t base = (int64_t)blockIdx.x * kThreads * kUnroll; base < n_vec; base += step) {
+    uint4 raw[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + u * kThreads + threadIdx.x;
+      raw[u] = i < n_vec ? ld_stream(xv + i) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + u * kThreads + threadIdx.x;
+      uint32_t b[N];
+      unpack(raw[u], b);
+      uint32_t amax = 0;
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const uint32_t a = b[k] & 0x7FFFFFFFu;
+        if ((a >> 23) == 0) b[k] = 0;  // fp32 subnormals (and -0) are flushed to +0
+        amax = max(amax, (a >> 23) == 0 ? 0u : a);
+      }
+      amax = group_max(amax, group);
+      const MxfpBlock p = mxfp_block(amax, E, tab);
+      if (i >= n_vec) continue;
+      if constexpr (kMode == Mode::kFake) {
+        float out[N];
+#pragma unroll
+        for (int k = 0; k < N; ++k) out[k] = mxfp_decode(mxfp_encode(b[k], p.sh, E, F), E, F) * p.scale_f;
+        store_vals(y, i * N, out);
+      } else {
+        uint32_t c[N];
+#pragma unroll
+        for (int k = 0; k < N; ++k) c[k] = mxfp_encode(b[k], p.sh, E, F);
+        store_bytes(codes, i * N, c);
+        if ((threadIdx.x & (group - 1)) == 0) scales[i / group] = (uint8_t)p.scale;
+      }
+    }
+  }
+}
+
+template <typename Tin, typename Tout, Mode kMode>
+__global__ void __launch_bounds__(kThreads)
+mxfp_generic_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, uint8_t *__restrict__ codes,
+                    uint8_t *__restrict__ scales, int64_t n_blocks, int block, int E, int F,
+                    const __grid_constant__ Log2Tab tab) {
+  for (int64_t blk = (int64_t)blockIdx.x * kThreads + threadIdx.x; blk < n_blocks;
+       blk += (int64_t)gridDim.x * kThreads) {
+    const Tin *xb = x + blk * block;
+    uint32_t amax = 0;
+    for (int k = 0; k < block; ++k) {
+      const uint32_t a = __float_as_uint(load_scalar(xb + k)) & 0x7FFFFFFFu;
+      amax = max(amax, (a >> 23) == 0 ? 0u : a);
+    }
+    const MxfpBlock p = mxfp_block(amax, E, tab);
+    for (int k = 0; k < block; ++k) {
+      uint32_t b = __float_as_uint(load_scalar(xb + k));
+      if (((b & 0x7FFFFFFFu) >> 23) == 0) b = 0;
+      const uint32_t c = mxfp_encode(b, p.sh, E, F);
+      if constexpr (kMode == Mode::kFake)
+        store_scalar(y + blk * block + k, mxfp_decode(c, E, F) * p.scale_f);
+      else
+        codes[blk * block + k] = (uint8_t)c;
+    }
+    if constexpr (kMode == Mode::kCodes) scales[blk] = (uint8_t)p.scale;
+  }
+}
+
+template <typename Tout>
+__global__ void __launch_bounds__(kThreads)
+mxfp_compose_kernel(const uint8_t *__restrict__ codes, const uint8_t *__restrict__ scales, Tout *__restrict__ y,
+                    int64_t n, int block, int E, int F) {
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads) {
+    const float sf = pow2f((int)scales[i / block] - 127);
+    store_scalar(y + i, mxfp_decode(codes[i], E, F) * sf);
+  }
+}
+
+// element-wise minifloat: the MXFP codec with a unit scale; input subnormals flush, sign follows x < 0
+template <typename Tin, typename Tout>
+__global__ void __launch_bounds__(kThreads)
+minifloat_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, int64_t n, int E, int F) {
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads) {
+    const uint32_t b = __float_as_uint(load_scalar(x + i));
+    uint32_t c = mxfp_encode(b & 0x7FFFFFFFu, 0, E, F);
+    if ((b >> 31) && (b & 0x7FFFFFFFu) != 0) c |= 1u << (E + F);  // x < 0, also for flushed subnormals
+    store_scalar(y + i, mxfp_decode(c, E, F));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// block floating point
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+bfp_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t n_vec, int group, int width, int exp_width, int exp_bias,
+           const __grid_constant__ Log2Tab tab) {
+  constexpr int N = Elem<T>::kVec;
+  const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+  const int64_t step = (int64_t)gridDim.x * kThreads * kUnroll;
+  for (int64_t base = (int64_t)blockIdx.x * kThreads * kUnroll; base < n_vec; base += step) {
+    uint4 raw[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + u * kThreads + threadIdx.x;
+      raw[u] = i < n_vec ? ld_stream(xv + i) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + u * kThreads + threadIdx.x;
+      uint32_t b[N];
+      unpack(raw[u], b);
+      float amax = 0.f;
+#pragma unroll
+      for (int k = 0; k < N; ++k) amax = fmaxf(amax, fabsf(__uint_as_float(b[k])));
+      amax = group_max(amax, group);
+      const BfpBlock p = bfp_block<T>(amax, width, exp_width, exp_bias, tab);
+      if (i >= n_vec) continue;
+      float out[N];
+#pragma unroll
+      for (int k = 0; k < N; ++k) out[k] = bfp_elem<T>(__uint_as_float(b[k]), p);
+      store_vals(y, i * N, out);
+    }
+  }
+}
+
+// one thread per tile; tiles never cross a row, the last tile of a row may be short
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+bfp_generic_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, int64_t cols, int bs, int width,
+                   int exp_width, int exp_bias, const __grid_constant__ Log2Tab tab) {
+  const int64_t tiles_per_row = (cols + bs - 1) / bs;
+  const int64_t n_tiles = rows * tiles_per_row;
+  for (int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x; t < n_tiles; t += (int64_t)gridDim.x * kThreads) {
+    const int64_t r = t / tiles_per_row, c0 = (t % tiles_per_row) * bs;
+    const int len = (int)min((int64_t)bs, cols - c0);
+    const T *xb = x + r * cols + c0;
+    float amax = 0.f;
+    for (int k = 0; k < len; ++k) amax = fmaxf(amax, fabsf(load_scalar(xb + k)));
+    const BfpBlock p = bfp_block<T>(amax, width, exp_width, exp_bias, tab);
+    for (int k = 0; k < len; ++k) store_scalar(y + r * cols + c0 + k, bfp_elem<T>(load_scalar(xb + k), p));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------
+static int grid_for(int64_t work_items, int per_cta) {
+  int64_t g = (work_items + per_cta - 1) / per_cta;
+  const int64_t cap = 148 * 16;  // a few waves of resident CTAs on 148 SMs; the kernels loop beyond that
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+static int check_launch() { return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH; }
+static Log2Tab load_tab(const uint8_t *host) {
+  Log2Tab t;
+  for (int i = 0; i < 256; ++i) t.t[i] = host ? host[i] : 0;
+  return t;
+}
+static bool legal_ef(int E, int F) {
+  return (E == 4 && F == 3) || (E == 5 && F == 2) || (E == 2 && F == 3) || (E == 3 && F == 2) || (E == 2 && F == 1) ||
+         (E == 1 && F == 2);
+}
+// lanes sharing one block, or 0 when the fast path does not apply
+template <typename Tin>
+static int fast_group(int block) {
+  constexpr int N = Elem<Tin>::kVec;
+  if (!is_pow2(block) || block < N || block > 32 * N) return 0;
+  return block / N;
+}
+
+template <typename Tin, typename Tout, Mode kMode>
+static int launch_mxint(const void *x, void *y, int8_t *mant, uint8_t *scales, int64_t n_blocks, int block, int bits,
+                        const Log2Tab &tab, cudaStream_t st) {
+  const int group = fast_group<Tin>(block);
+  if (group && aligned16(x) && (kMode == Mode::kCodes ? aligned16(mant) : aligned16(y))) {
+    const int64_t n_vec = n_blocks * group;
+    mxint_kernel<Tin, Tout, kMode><<<grid_for(n_vec, kThreads * kUnroll), kThreads, 0, st>>>(
+        (const Tin *)x, (Tout *)y, mant, scales, n_vec, group, bits, tab);
+  } else {
+    mxint_generic_kernel<Tin, Tout, kMode><<<grid_for(n_blocks, kThreads), kThreads, 0, st>>>(
+        (const Tin *)x, (Tout *)y, mant, scales, n_blocks, block, bits, tab);
+  }
+  return check_launch();
+}
+
+template <typename Tin, typename Tout, Mode kMode, int E, int F>
+static int launch_mxfp_ef(const void *x, void *y, uint8_t *codes, uint8_t *scales, int64_t n_blocks, int block,
+                          const Log2Tab &tab, cudaStream_t st) {
+  const int group = fast_group<Tin>(block);
+  if (group && aligned16(x) && (kMode == Mode::kCodes ? aligned16(codes) : aligned16(y))) {
+    const int64_t n_vec = n_blocks * group;
+    mxfp_kernel<Tin, Tout, kMode, E, F><<<grid_for(n_vec, kThreads * kUnroll), kThreads, 0, st>>>(
+        (const Tin *)x, (Tout *)y, codes, scales, n_vec, group, tab);
+  } else {
+    mxfp_generic_kernel<Tin, Tout, kMode><<<grid_for(n_blocks, kThreads), kThreads, 0, st>>>(
+        (const Tin *)x, (Tout *)y, codes, scales, n_blocks, block, E, F, tab);
+  }
+  return check_launch();
+}
+
+template <typename Tin, typename Tout, Mode kMode>
+static int launch_mxfp(const void *x, void *y, uint8_t *codes, uint8_t *scales, int64_t n_blocks, int block, int E,
+                       int F, const Log2Tab &tab, cudaStream_t st) {
+#define MXQ_EF(e, f) \
+  if (E == e && F == f) return launch_mxfp_ef<Tin, Tout, kMode, e, f>(x, y, codes, scales, n_blocks, block, tab, st);
+  MXQ_EF(4, 3) MXQ_EF(5, 2) MXQ_EF(2, 3) MXQ_EF(3, 2) MXQ_EF(2, 1) MXQ_EF(1, 2)
+#undef MXQ_EF
+  return MXQ_ERR_FORMAT;
+}
+
+}  // namespace mxq
+
+using namespace mxq;
+
+// dispatch on (input type, output type)
+#define MXQ_DISPATCH_IO(in_dtype, out_dtype, CALL)                                    \
+  if (in_dtype == MXQ_F32 && out_dtype == MXQ_F32) { CALL(float, float) }             \
+  if (in_dtype == MXQ_BF16 && out_dtype == MXQ_BF16) { CALL(__nv_bfloat16, __nv_bfloat16) } \
+  if (in_dtype == MXQ_F32 && out_dtype == MXQ_BF16) { CALL(float, __nv_bfloat16) }    \
+  if (in_dtype == MXQ_BF16 && out_dtype == MXQ_F32) { CALL(__nv_bfloat16, float) }    \
+  return MXQ_ERR_DTYPE;
+
+extern "C" {
+
+int mxq_version(void) { return MXQ_VERSION; }
+
+const char *mxq_error_string(int code) {
+  switch (code) {
+    case MXQ_OK: return "ok";
+    case MXQ_ERR_DTYPE: return "unsupported element type";
+    case MXQ_ERR_SHAPE: return "bad shape or size";
+    case MXQ_ERR_FORMAT: return "unsupported number format";
+    case MXQ_ERR_ALIGN: return "pointer is not 16-byte aligned";
+    case MXQ_ERR_NULL: return "null pointer";
+    case MXQ_ERR_LAUNCH: return "CUDA launch failed";
+    case MXQ_ERR_UNSUPPORTED: return "unsupported configuration";
+    case MXQ_ERR_DEVICE: return "device-side error status";
+    default: return "unknown error";
+  }
+}
+
+int mxq_mxint_fake(const void *x, void *y, int in_dtype, int out_dtype, int64_t n_blocks, int block, int bits,
+                   const uint8_t *ceil_tab_host, void *stream) {
+  if (n_blocks == 0) return MXQ_OK;
+  if (!x || !y || !ceil_tab_host) return MXQ_ERR_NULL;
+  if (n_blocks < 0 || block < 1) return MXQ_ERR_SHAPE;
+  if (bits < 2 || bits > 8) return MXQ_ERR_FORMAT;
+  const Log2Tab tab = load_tab(ceil_tab_host);
+#define CALL(TI, TO) \
+  return launch_mxint<TI, TO, Mode::kFake>(x, y, nullptr, nullptr, n_blocks, block, bits, tab, (cudaStream_t)stream);
+  MXQ_DISPATCH_IO(in_dtype, out_dtype, CALL)
+#undef CALL
+}
+
+int mxq_mxint_extract(const void *x, int8_t *mant, uint8_t *scales, int in_dtype, int64_t n_blocks, int block, int bits,
+                      const uint8_t *ceil_tab_host, void *stream) {
+  if (n_blocks == 0) return MXQ_OK;
+  if (!x || !mant || !scales || !ceil_tab_host) return MXQ_ERR_NULL;
+  if (n_blocks < 0 || block < 1) return MXQ_ERR_SHAPE;
+  if (bits < 2 || bits > 8) return MXQ_ERR_FORMAT;
+  const Log2Tab tab = load_tab(ceil_tab_host);
+  if (in_dtype == MXQ_F32)
+    return launch_mxint<float, float, Mode::kCodes>(x, nullptr, mant, scales, n_blocks, block, bits, tab,
+                                                    (cudaStream_t)stream);
+  if (in_dtype == MXQ_BF16)
+    return launch_mxint<__nv_bfloat16, float, Mode::kCodes>(x, nullptr, mant, scales, n_blocks, block, bits, tab,
+                                                            (cudaStream_t)stream);
+  return MXQ_ERR_DTYPE;
+}
+
+int mxq_mxint_compose(const int8_t *mant, const uint8_t *scales, void *y, int out_dtype, int64_t n_blocks, int block,
+                      int bits, void *stream) {
+  if (n_blocks == 0) return MXQ_OK;
+  if (!mant || !scales || !y) return MXQ_ERR_NULL;
+  if (n_blocks < 0 || block < 1) return MXQ_ERR_SHAPE;
+  if (bits < 2 || bits > 8) return MXQ_ERR_FORMAT;
+  const int64_t n = n_blocks * block;
+  const int grid = grid_for(n, kThreads);
+  if (out_dtype == MXQ_F32)
+    mxint_compose_kernel<float><<<grid, kThreads, 0, (cudaStream_t)stream>>>(mant, scales, (float *)y, n, block, bits);
+  else if (out_dtype == MXQ_BF16)
+    mxint_compose_kernel<__nv_bfloat16>
+        <<<grid, kThreads, 0, (cudaStream_t)stream>>>(mant, scales, (__nv_bfloat16 *)y, n, block, bits);
+  else
+    return MXQ_ERR_DTYPE;
+  return check_launch();
+}
+
+int mxq_mxfp_fake(const void *x, void *y, int in_dtype, int out_dtype, int64_t n_blocks, int block, int E, int F,
+                  const uint8_t *floor_tab_host, void *stream) {
+  if (n_blocks == 0) return MXQ_OK;
+  if (!x || !y || !floor_tab_host) return MXQ_ERR_NULL;
+  if (n_blocks < 0 || block < 1) return MXQ_ERR_SHAPE;
+  if (!legal_ef(E, F)) return MXQ_ERR_FORMAT;
+  const Log2Tab tab = load_tab(floor_tab_host);
+#define CALL(TI, TO) \
+  return launch_mxfp<TI, TO, Mode::kFake>(x, y, nullptr, nullptr, n_blocks, block, E, F, tab, (cudaStream_t)stream);
+  MXQ_DISPATCH_IO(in_dtype, out_dtype, CALL)
+#undef CALL
+}
+
+int mxq_mxfp_extract(const void *x, uint8_t *codes, uint8_t *scales, int in_dtype, int64_t n_blocks, int block, int E,
+                     int F, const uint8_t *floor_tab_host, void *stream) {
+  if (n_blocks == 0) return MXQ_OK;
+  if (!x || !codes || !scales || !floor_tab_host) return MXQ_ERR_NULL;
+  if (n_blocks < 0 || block < 1) return MXQ_ERR_SHAPE;
+  if (!legal_ef(E, F)) return MXQ_ERR_FORMAT;
+  const Log2Tab tab = load_tab(floor_tab_host);
+  if (in_dtype == MXQ_F32)
+    return launch_mxfp<float, float, Mode::kCodes>(x, nullptr, codes, scales, n_blocks, block, E, F, tab,
+                                                   (cudaStream_t)stream);
+  if (in_dtype == MXQ_BF16)
+    return launch_mxfp<__nv_bfloat16, float, Mode::kCodes>(x, nullptr, codes, scales, n_blocks, block, E, F, tab,
+                                                           (cudaStream_t)stream);
+  return MXQ_ERR_DTYPE;
+}
+
+int mxq_mxfp_compose(const uint8_t *codes, const uint8_t *scales, void *y, int out_dtype, int64_t n_blocks, int block,
+                     int E, int F, void *stream) {
+  if (n_blocks == 0) return MXQ_OK;
+  if (!codes || !scales || !y) return MXQ_ERR_NULL;
+  if (n_blocks < 0 || block < 1) return MXQ_ERR_SHAPE;
+  if (!legal_ef(E, F)) return MXQ_ERR_FORMAT;
+  const int64_t n = n_blocks * block;
+  const int grid = grid_for(n, kThreads);
+  if (out_dtype == MXQ_F32)
+    mxfp_compose_kernel<float><<<grid, kThreads, 0, (cudaStream_t)stream>>>(codes, scales, (float *)y, n, block, E, F);
+  else if (out_dtype == MXQ_BF16)
+    mxfp_compose_kernel<__nv_bfloat16>
+        <<<grid, kThreads, 0, (cudaStream_t)stream>>>(codes, scales, (__nv_bfloat16 *)y, n, block, E, F);
+  else
+    return MXQ_ERR_DTYPE;
+  return check_launch();
+}
+
+int mxq_minifloat_fake(const void *x, void *y, int in_dtype, int out_dtype, int64_t n, int E, int F, void *stream) {
+  if (n == 0) return MXQ_OK;
+  if (!x || !y) return MXQ_ERR_NULL;
+  if (n < 0) return MXQ_ERR_SHAPE;
+  if (E < 1 || F < 1 || E + F > 7) return MXQ_ERR_FORMAT;
+  const int grid = grid_for(n, kThreads);
+#define CALL(TI, TO)                                                                                        \
+  minifloat_kernel<TI, TO><<<grid, kThreads, 0, (cudaStream_t)stream>>>((const TI *)x, (TO *)y, n, E, F); \
+  return check_launch();
+  MXQ_DISPATCH_IO(in_dtype, out_dtype, CALL)
+#undef CALL
+}
+
+int mxq_bfp_fake(const void *x, void *y, int dtype, int64_t rows, int64_t cols, int bs, int width, int exp_width,
+                 int exp_bias, const uint8_t *ceil_tab_host, void *stream) {
+  if (rows == 0 || cols == 0) return MXQ_OK;
+  if (!x || !y || !ceil_tab_host) return MXQ_ERR_NULL;
+  if (rows < 0 || cols < 0 || bs < 1) return MXQ_ERR_SHAPE;
+  if (width < 2 || width > 24 || exp_width < 1 || exp_width > 8) return MXQ_ERR_FORMAT;
+  const Log2Tab tab = load_tab(ceil_tab_host);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bs > cols) bs = (int)cols;
+  if (dtype == MXQ_F32) {
+    const int group = fast_group<float>(bs);
+    if (group && cols % bs == 0 && aligned16(x) && aligned16(y)) {
+      const int64_t n_vec = rows * cols / 4;
+      bfp_kernel<float><<<grid_for(n_vec, kThreads * kUnroll), kThreads, 0, st>>>(
+          (const float *)x, (float *)y, n_vec, group, width, exp_width, exp_bias, tab);
+    } else {
+      bfp_generic_kernel<float><<<grid_for(rows * ((cols + bs - 1) / bs), kThreads), kThreads, 0, st>>>(
+          (const float *)x, (float *)y, rows, cols, bs, width, exp_width, exp_bias, tab);
+    }
+  } else if (dtype == MXQ_BF16) {
+    const int group = fast_group<__nv_bfloat16>(bs);
+    if (group && cols % bs == 0 && aligned16(x) && aligned16(y)) {
+      const int64_t n_vec = rows * cols / 8;
+      bfp_kernel<__nv_bfloat16><<<grid_for(n_vec, kThreads * kUnroll), kThreads, 0, st>>>(
+          (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, n_vec, group, width, exp_width, exp_bias, tab);
+    } else {
+      bfp_generic_kernel<__nv_bfloat16><<<grid_for(rows * ((cols + bs - 1) / bs), kThreads), kThreads, 0, st>>>(
+          (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, rows, cols, bs, width, exp_width, exp_bias, tab);
+    }
+  } else {
+    return MXQ_ERR_DTYPE;
+  }
+  return check_launch();
+}
+
+}  // extern "C"

@@ -1,0 +1,171 @@
+"""Quantized Linear modules with MASE's constructor, config keys and state_dict layout.
+
+Counterparts of `LinearMXFP`, `LinearMXInt` and `LinearBlockFP` in
+chop/nn/quantized/modules/linear.py (:817-895, :898-972, :199-219) and of `linearBlockFP` in
+chop/nn/quantized/functional/linear.py:220-278.  The quantize pass builds them as
+`cls(in_features, out_features, bias, device, dtype, config=...)` and then calls
+`load_state_dict(old.state_dict(), strict=False)` (chop/passes/module/module_modify_helper.py:103-176),
+which is where MX weights are quantized once; activations are quantized on every forward.
+"""
+
+from __future__ import annotations
+
+from functools import partial
+
+import torch
+from torch import Tensor
+
+from .gemm import linear_forward
+from .quantizers import block_fp_quantizer, mxfp_quantizer, mxint_quantizer
+
+
+class _LinearBase(torch.nn.Linear):
+    """chop/nn/quantized/modules/linear.py:61-83"""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, device=None, dtype=None) -> None:
+        super().__init__(in_features, out_features, bias, device, dtype)
+        self.bypass = False
+        self.pruning_masks = None
+
+
+class LinearMXFP(_LinearBase):
+    """Linear whose weight (and optionally bias) is MXFP-quantized at load time and whose input is
+    MXFP-quantized along the feature dimension on every forward.  Inference only."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=None, config=None):
+        super().__init__(in_features, out_features, bias, device, dtype)
+        assert config is not None, "config is None!"
+        self.config = config
+        self.bypass = config.get("bypass", False)
+        self.gptq = config.get("gptq", False)
+        self.clip_search = config.get("clip_search", False)
+
+    def load_state_dict(self, state_dict, strict=True, assign=False):
+        """Load pretrained weights, then quantize them in place (blocks run along in_features)."""
+        result = super().load_state_dict(state_dict, strict=strict, assign=assign)
+        if self.bypass or self.gptq:
+            return result
+        cfg = self.config
+        self.weight.data.copy_(
+            mxfp_quantizer(
+                self.weight.data,
+                block_size=cfg["weight_block_size"],
+                element_exp_bits=cfg["weight_exponent_width"],
+                element_frac_bits=cfg["weight_frac_width"],
+                block_dim=1,
+            )
+        )
+        b_block, b_exp, b_frac = cfg.get("bias_block_size"), cfg.get("bias_exponent_width"), cfg.get("bias_frac_width")
+        if self.bias is not None and b_block is not None and b_exp is not None:
+            self.bias.data.copy_(
+                mxfp_quantizer(self.bias.data, block_size=b_block, element_exp_bits=b_exp, element_frac_bits=b_frac,
+                               block_dim=0)
+            )
+        return result
+
+    @torch.no_grad()
+    def forward(self, x: Tensor) -> Tensor:
+        if self.bypass:
+            return linear_forward(x, self.weight, self.bias)
+        cfg = self.config
+        x_block, x_exp, x_frac = cfg.get("data_in_block_size"), cfg.get("data_in_exponent_width"), cfg.get("data_in_frac_width")
+        if x_block is not None and x_exp is not None:
+            x = mxfp_quantizer(x, block_size=x_block, element_exp_bits=x_exp, element_frac_bits=x_frac, block_dim=-1)
+        return linear_forward(x, self.weight, self.bias)
+
+
+class LinearMXInt(_LinearBase):
+    """Linear with MXINT weight (quantized at load time) and MXINT activations.  Inference only."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=None, config=None):
+        super().__init__(in_features, out_features, bias, device, dtype)
+        assert config is not None, "config is None!"
+        self.config = config
+        self.bypass = config.get("bypass", False)
+        self.gptq = config.get("gptq", False)
+        self.clip_search = config.get("clip_search", False)
+
+    def load_state_dict(self, state_dict, strict=True, assign=False):
+        result = super().load_state_dict(state_dict, strict=strict, assign=assign)
+        if self.bypass or self.gptq:
+            return result
+        cfg = self.config
+        self.weight.data.copy_(
+            mxint_quantizer(self.weight.data, block_size=cfg["weight_block_size"], element_bits=cfg["weight_width"],
+                            block_dim=1, quantile_search=self.clip_search)
+        )
+        b_block, b_bits = cfg.get("bias_block_size"), cfg.get("bias_width")
+        if self.bias is not None and b_block is not None and b_bits is not None:
+            self.bias.data.copy_(
+                mxint_quantizer(self.bias.data, block_size=b_block, element_bits=b_bits, block_dim=0,
+                                quantile_search=self.clip_search)
+            )
+        return result
+
+    @torch.no_grad()
+    def forward(self, x: Tensor) -> Tensor:
+        if self.bypass:
+            return linear_forward(x, self.weight, self.bias)
+        cfg = self.config
+        x_block, x_bits = cfg.get("data_in_block_size"), cfg.get("data_in_width")
+        if x_block is not None and x_bits is not None:
+            x = mxint_quantizer(x, block_size=x_block, element_bits=x_bits, block_dim=-1)
+        return linear_forward(x, self.weight, self.bias)
+
+
+def linearBlockFP(x: Tensor, weight: Tensor, bias: Tensor = None, config: dict = None) -> Tensor:
+    """Quantize x, weight and bias with block floating point on every call, then multiply
+    (chop/nn/quantized/functional/linear.py:220-278)."""
+    w_quantizer = partial(
+        block_fp_quantizer,
+        width=config["weight_width"],
+        exponent_width=config["weight_exponent_width"],
+        exponent_bias=config["weight_exponent_bias"],
+        block_size=config["weight_block_size"],
+        skip_first_dim=False,
+    )
+    x_quantizer = partial(
+        block_fp_quantizer,
+        width=config["data_in_width"],
+        exponent_width=config["data_in_exponent_width"],
+        exponent_bias=config["data_in_exponent_bias"],
+        block_size=config["data_in_block_size"],
+        skip_first_dim=config.get("data_in_skip_first_dim", True),
+    )
+    b_quantizer = partial(
+        block_fp_quantizer,
+        width=config["bias_width"],
+        exponent_width=config["bias_exponent_width"],
+        exponent_bias=config["bias_exponent_bias"],
+        block_size=config["bias_block_size"],
+        skip_first_dim=False,
+    )
+    x = x_quantizer(x)
+    weight = w_quantizer(weight)
+    bias = b_quantizer(bias) if bias is not None else None
+    return linear_forward(x, weight, bias)
+
+
+class LinearBlockFP(_LinearBase):
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=None, config=None):
+        super().__init__(in_features, out_features, bias, device, dtype)
+        assert config is not None, "config is None!"
+        self.config = config
+        self.bypass = config.get("bypass", False)
+
+    def forward(self, x: Tensor) -> Tensor:
+        if self.bypass:
+            return linear_forward(x, self.weight, self.bias)
+        return linearBlockFP(x, self.weight, self.bias, self.config)
+
+
+# entries of chop.nn.quantized.modules.quantized_module_map (nn/quantized/modules/__init__.py:241-246)
+quantized_module_map = {
+    "linear_mxfp": LinearMXFP,
+    "linear_mxint": LinearMXInt,
+    "linear_block_fp": LinearBlockFP,
+}
+# entry of chop.nn.quantized.functional.quantized_func_map (nn/quantized/functional/__init__.py:287)
+quantized_func_map = {
+    "linear_block_fp": linearBlockFP,
+}

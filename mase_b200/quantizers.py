@@ -1,0 +1,516 @@
+"""MX / block-floating-point quantizers with MASE's function signatures, running on libmxq (sm_100a).
+
+Drop-in counterparts of (paths inside the MASE repository, `src/chop/nn/quantizers/`):
+
+  mxint/mxint.py:211   mxint_quantizer            mxint/mxint.py:14   mxint_quantizer_sim
+  mxint/fake.py:11     extract_mxint_components   mxint/fake.py:59    compose_mxint_tensor
+  mxfp/mxfp.py:187     mxfp_quantizer             mxfp/mxfp.py:14     mxfp_quantizer_sim
+  mxfp/fake.py:12      extract_mxfp_components    mxfp/fake.py:75     compose_mxfp_tensor
+  _minifloat_mx/minifloat.py:12  minifloat_quantizer_sim
+  _minifloat_mx/fake.py:11,96    extract_minifloat_component / compose_minifloat_component
+  block_fp.py:111      block_fp_quantizer
+
+Same names, parameter names, defaults, return types and error behaviour.  Tensors must live on a CUDA
+device: there is no CPU path.  fp32 and bf16 inputs are supported; other dtypes raise
+NotImplementedError rather than silently computing something else.  The calibration-time options
+(`quantile_search=True`, `percentile != 1.0`, `act_tensor`) are not part of the inference path and raise
+NotImplementedError.
+"""
+
+from __future__ import annotations
+
+import functools
+from dataclasses import dataclass
+from typing import Literal
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from .log2_tables import ceil_table, floor_table
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+# ---------------------------------------------------------------------------------------------------
+# metadata classes (same fields and checks as the reference's dataclasses)
+# ---------------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class MinifloatMeta:
+    """_minifloat_mx/meta.py:11-35"""
+
+    exp_bits: int
+    frac_bits: int
+    is_finite: bool
+    round_mode: Literal["rn", "rd", "ru", "rz"]
+
+    def __post_init__(self):
+        assert self.exp_bits > 0
+        assert self.frac_bits > 0
+        assert self.exp_bits + self.frac_bits < 16
+
+    @functools.cached_property
+    def n_bits(self) -> int:
+        return self.exp_bits + self.frac_bits + 1
+
+
+@dataclass
+class MinifloatTensorMeta:
+    device: str
+    dtype: str
+    shape: tuple[int, ...]
+    meta: MinifloatMeta
+
+
+@dataclass(frozen=True)
+class MXFPMeta:
+    """mxfp/meta.py:12-59"""
+
+    block_size: int
+    scale_exp_bits: int
+    element_exp_bits: int
+    element_frac_bits: int
+    element_is_finite: bool
+    round_mode: Literal["rn", "ru", "rd", "rz"]
+
+    def __post_init__(self):
+        legal_scale_exp_bits = (8,)
+        assert self.scale_exp_bits in legal_scale_exp_bits, (
+            f"Invalid scale exponent bits: {self.scale_exp_bits}. Legal values are: {legal_scale_exp_bits}."
+        )
+        legal = ((4, 3), (5, 2), (2, 3), (3, 2), (2, 1), (1, 2))
+        ef = (self.element_exp_bits, self.element_frac_bits)
+        assert ef in legal, f"Invalid element exp/frac bits: {ef}. Legal values are: {legal}."
+
+    @functools.cached_property
+    def element_meta(self) -> MinifloatMeta:
+        return MinifloatMeta(
+            exp_bits=self.element_exp_bits,
+            frac_bits=self.element_frac_bits,
+            is_finite=self.element_is_finite,
+            round_mode=self.round_mode,
+        )
+
+
+@dataclass(frozen=True)
+class MXFPTensorMeta:
+    device: str
+    dtype: str
+    shape: tuple[int, ...]
+    block_dim: int
+    meta: MXFPMeta
+
+
+@dataclass
+class MXIntMeta:
+    """mxint/meta.py:8-23"""
+
+    block_size: int
+    scale_bits: int
+    element_bits: int
+
+
+@dataclass
+class MXIntTensorMeta:
+    device: str
+    dtype: str
+    shape: tuple[int, ...]
+    block_dim: int
+    meta: MXIntMeta
+
+
+# ---------------------------------------------------------------------------------------------------
+# helpers
+# ---------------------------------------------------------------------------------------------------
+def _require_cuda(t: Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: tensor is on '{t.device}'; mase_b200 runs on CUDA devices only (no CPU fallback)")
+
+
+def _dtype_code(dt: torch.dtype, what: str) -> int:
+    if dt not in _DT:
+        raise NotImplementedError(f"{what}: dtype {dt} is not supported (float32 and bfloat16 are)")
+    return _DT[dt]
+
+
+def _stream(t: Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _tab_ptr(tab) -> int:
+    return tab.ctypes.data
+
+
+def flatten_for_quantize(tensor: Tensor, block_dim: int) -> Tensor:
+    """Move `block_dim` last and flatten (mxfp/helpers.py:8-29)."""
+    nd = tensor.dim()
+    d = block_dim % nd
+    order = list(range(nd))
+    order.append(order.pop(d))
+    return tensor.permute(order).flatten()
+
+
+def permute_for_dequantize(flatten_tensor: Tensor, ori_shape: tuple[int, ...], block_dim: int) -> Tensor:
+    """Undo `flatten_for_quantize`; the result is a permuted view (mxfp/helpers.py:32-63)."""
+    nd = len(ori_shape)
+    d = block_dim % nd
+    moved = list(ori_shape)
+    moved.append(moved.pop(d))
+    inv = list(range(nd))
+    inv.insert(d, inv.pop(-1))
+    return flatten_tensor.reshape(moved).permute(inv)
+
+
+def _flat_contiguous(x: Tensor) -> Tensor:
+    x = x.flatten()
+    if not x.is_contiguous() or x.data_ptr() % 16:
+        x = x.contiguous()
+        if x.data_ptr() % 16:
+            x = x.clone(memory_format=torch.contiguous_format)
+    return x
+
+
+# ---------------------------------------------------------------------------------------------------
+# MXINT
+# ---------------------------------------------------------------------------------------------------
+def _mxint_fake_flat(flat: Tensor, meta: MXIntMeta, out_dtype: torch.dtype) -> Tensor:
+    B = meta.block_size
+    assert flat.numel() % B == 0, f"Input tensor size {flat.numel()} is not divisible by block size {B}."
+    if meta.scale_bits != 8:
+        raise NotImplementedError("mxint: only scale_bits=8 is supported")
+    if not 2 <= meta.element_bits <= 8:
+        raise NotImplementedError("mxint: element_bits must be between 2 and 8")
+    di = _dtype_code(flat.dtype, "mxint")
+    do = _dtype_code(out_dtype, "mxint")
+    flat = _flat_contiguous(flat)
+    y = torch.empty(flat.shape, dtype=out_dtype, device=flat.device)
+    with torch.cuda.device(flat.device):
+        rc = _lib.lib().mxq_mxint_fake(flat.data_ptr(), y.data_ptr(), di, do, flat.numel() // B, B, meta.element_bits,
+                                       _tab_ptr(ceil_table(flat.dtype)), _stream(flat))
+    _lib.check(rc, "mxq_mxint_fake")
+    return y
+
+
+def mxint_codes(x: Tensor, block_size: int, element_bits: int) -> tuple[Tensor, Tensor]:
+    """Packed MXINT codes of an already-flattened tensor: (scales uint8 [n_blocks], mantissas int8 [n_blocks, B])."""
+    _require_cuda(x, "mxint_codes")
+    B = block_size
+    assert x.numel() % B == 0, f"Input tensor size {x.numel()} is not divisible by block size {B}."
+    if not 2 <= element_bits <= 8:
+        raise NotImplementedError("mxint: element_bits must be between 2 and 8")
+    di = _dtype_code(x.dtype, "mxint")
+    flat = _flat_contiguous(x)
+    n = flat.numel() // B
+    mant = torch.empty((n, B), dtype=torch.int8, device=x.device)
+    scales = torch.empty((n,), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().mxq_mxint_extract(flat.data_ptr(), mant.data_ptr(), scales.data_ptr(), di, n, B, element_bits,
+                                          _tab_ptr(ceil_table(x.dtype)), _stream(x))
+    _lib.check(rc, "mxq_mxint_extract")
+    return scales, mant
+
+
+def extract_mxint_components(x: Tensor, mxint_meta: MXIntMeta, percentile: float = 1.0) -> tuple[Tensor, Tensor]:
+    """(scale [n_blocks,1], mantissa [n_blocks,B]), both integer-valued tensors of x.dtype (mxint/fake.py:11-56)."""
+    _require_cuda(x, "extract_mxint_components")
+    if percentile != 1.0:
+        raise NotImplementedError("percentile clipping is a calibration-time option and is not provided")
+    if mxint_meta.scale_bits != 8:
+        raise NotImplementedError("mxint: only scale_bits=8 is supported")
+    scales, mant = mxint_codes(x, mxint_meta.block_size, mxint_meta.element_bits)
+    return scales.view(-1, 1).to(x.dtype), mant.to(x.dtype)
+
+
+def compose_mxint_tensor(shared_scales: Tensor, elements: Tensor, mxint_meta: MXIntMeta) -> Tensor:
+    """elements / 2**(bits-1) * 2**(scale-127), shape [n_blocks, B], dtype of `elements` (mxint/fake.py:59-80)."""
+    _require_cuda(elements, "compose_mxint_tensor")
+    do = _dtype_code(elements.dtype, "mxint")
+    B = mxint_meta.block_size
+    mant = elements.to(torch.int8).contiguous()
+    sc = shared_scales.to(torch.uint8).contiguous()
+    y = torch.empty(elements.shape, dtype=elements.dtype, device=elements.device)
+    with torch.cuda.device(elements.device):
+        rc = _lib.lib().mxq_mxint_compose(mant.data_ptr(), sc.data_ptr(), y.data_ptr(), do, mant.numel() // B, B,
+                                          mxint_meta.element_bits, _stream(elements))
+    _lib.check(rc, "mxq_mxint_compose")
+    return y
+
+
+def mxint_quantizer_sim(
+    tensor: Tensor,
+    block_dim: int,
+    mxint_meta: MXIntMeta,
+    act_tensor: Tensor | None = None,
+    dtype: torch.dtype | None = None,
+    quantile_search: bool = False,
+    cali_batch_size: int = 32,
+) -> Tensor:
+    """Quantize-dequantize along `block_dim` (mxint/mxint.py:14-171, non-search branch)."""
+    _require_cuda(tensor, "mxint_quantizer_sim")
+    if quantile_search or act_tensor is not None:
+        raise NotImplementedError("quantile_search / act_tensor are calibration-time options and are not provided")
+    ori_shape = tuple(tensor.shape)
+    ndim = len(ori_shape)
+    assert block_dim < ndim and block_dim >= -ndim
+    flat = flatten_for_quantize(tensor, block_dim)
+    y = _mxint_fake_flat(flat, mxint_meta, dtype or tensor.dtype)
+    return permute_for_dequantize(y, ori_shape, block_dim)
+
+
+class MXIntQuantize(torch.autograd.Function):
+    """Straight-through estimator around the quantizer (mxint/mxint.py:179-208)."""
+
+    @staticmethod
+    def forward(ctx, x, block_size, element_bits, block_dim, scale_bits, quantile_search):
+        meta = MXIntMeta(block_size=block_size, scale_bits=scale_bits, element_bits=element_bits)
+        return mxint_quantizer_sim(tensor=x, block_dim=block_dim, mxint_meta=meta, quantile_search=quantile_search)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return grad_output.clone(), None, None, None, None, None
+
+
+def mxint_quantizer(
+    x: Tensor,
+    block_size: int,
+    element_bits: int,
+    block_dim: int = -1,
+    scale_bits: int = 8,
+    quantile_search: bool = False,
+) -> Tensor:
+    """MXINT fake quantization, same interface as chop.nn.quantizers.mxint_quantizer (mxint/mxint.py:211-251)."""
+    return MXIntQuantize.apply(x, block_size, element_bits, block_dim, scale_bits, quantile_search)
+
+
+# ---------------------------------------------------------------------------------------------------
+# MXFP
+# ---------------------------------------------------------------------------------------------------
+def _check_mxfp_meta(meta: MXFPMeta) -> None:
+    if not meta.element_is_finite or meta.round_mode != "rn":
+        raise NotImplementedError("mxfp: only element_is_finite=True with round_mode='rn' is provided "
+                                  "(what chop's mxfp_quantizer hard-codes)")
+
+
+def extract_mxfp_components(tensor: Tensor, mxfp_meta: MXFPMeta, percentile: float = 1.0) -> tuple[Tensor, Tensor]:
+    """(scales uint8 [n_blocks,1], elements uint8 [n_blocks,B]) (mxfp/fake.py:12-72)."""
+    _require_cuda(tensor, "extract_mxfp_components")
+    if percentile != 1.0:
+        raise NotImplementedError("percentile clipping is a calibration-time option and is not provided")
+    _check_mxfp_meta(mxfp_meta)
+    B = mxfp_meta.block_size
+    assert tensor.numel() % B == 0
+    di = _dtype_code(tensor.dtype, "mxfp")
+    flat = _flat_contiguous(tensor)
+    n = flat.numel() // B
+    codes = torch.empty((n, B), dtype=torch.uint8, device=tensor.device)
+    scales = torch.empty((n, 1), dtype=torch.uint8, device=tensor.device)
+    with torch.cuda.device(tensor.device):
+        rc = _lib.lib().mxq_mxfp_extract(flat.data_ptr(), codes.data_ptr(), scales.data_ptr(), di, n, B,
+                                         mxfp_meta.element_exp_bits, mxfp_meta.element_frac_bits,
+                                         _tab_ptr(floor_table()), _stream(tensor))
+    _lib.check(rc, "mxq_mxfp_extract")
+    return scales, codes
+
+
+def compose_mxfp_tensor(scales: Tensor, elements: Tensor, mxfp_meta: MXFPMeta, output_dtype: torch.dtype) -> Tensor:
+    """Flat dequantized tensor of `output_dtype` (mxfp/fake.py:75-104)."""
+    assert scales.dtype == torch.uint8
+    assert elements.dtype == torch.uint8
+    _require_cuda(elements, "compose_mxfp_tensor")
+    do = _dtype_code(output_dtype, "mxfp")
+    B = mxfp_meta.block_size
+    elements = elements.contiguous()
+    scales = scales.contiguous()
+    y = torch.empty((elements.numel(),), dtype=output_dtype, device=elements.device)
+    with torch.cuda.device(elements.device):
+        rc = _lib.lib().mxq_mxfp_compose(elements.data_ptr(), scales.data_ptr(), y.data_ptr(), do,
+                                         elements.numel() // B, B, mxfp_meta.element_exp_bits,
+                                         mxfp_meta.element_frac_bits, _stream(elements))
+    _lib.check(rc, "mxq_mxfp_compose")
+    return y
+
+
+def _mxfp_fake_flat(flat: Tensor, meta: MXFPMeta, out_dtype: torch.dtype) -> Tensor:
+    _check_mxfp_meta(meta)
+    B = meta.block_size
+    assert flat.numel() % B == 0
+    di = _dtype_code(flat.dtype, "mxfp")
+    do = _dtype_code(out_dtype, "mxfp")
+    flat = _flat_contiguous(flat)
+    y = torch.empty(flat.shape, dtype=out_dtype, device=flat.device)
+    with torch.cuda.device(flat.device):
+        rc = _lib.lib().mxq_mxfp_fake(flat.data_ptr(), y.data_ptr(), di, do, flat.numel() // B, B,
+                                      meta.element_exp_bits, meta.element_frac_bits, _tab_ptr(floor_table()),
+                                      _stream(flat))
+    _lib.check(rc, "mxq_mxfp_fake")
+    return y
+
+
+def mxfp_quantizer_sim(
+    tensor: Tensor,
+    block_dim: int,
+    mxfp_meta: MXFPMeta,
+    act_tensor: Tensor | None = None,
+    dtype: torch.dtype | None = None,
+    quantile_search: bool = False,
+    cali_batch_size: int = 32,
+) -> Tensor:
+    """Quantize-dequantize along `block_dim` (mxfp/mxfp.py:14-115, non-search branch)."""
+    _require_cuda(tensor, "mxfp_quantizer_sim")
+    if quantile_search or act_tensor is not None:
+        raise NotImplementedError("quantile_search / act_tensor are calibration-time options and are not provided")
+    ori_shape = tuple(tensor.shape)
+    ndim = len(ori_shape)
+    assert block_dim < ndim and block_dim >= -ndim
+    flat = flatten_for_quantize(tensor, block_dim)
+    y = _mxfp_fake_flat(flat, mxfp_meta, dtype or tensor.dtype)
+    return permute_for_dequantize(y, ori_shape, block_dim)
+
+
+class MXFPQuantize(torch.autograd.Function):
+    """Straight-through estimator around the quantizer (mxfp/mxfp.py:151-184)."""
+
+    @staticmethod
+    def forward(ctx, x, block_size, element_exp_bits, element_frac_bits, block_dim, scale_exp_bits, quantile_search):
+        meta = MXFPMeta(
+            block_size=block_size,
+            scale_exp_bits=scale_exp_bits,
+            element_exp_bits=element_exp_bits,
+            element_frac_bits=element_frac_bits,
+            element_is_finite=True,
+            round_mode="rn",
+        )
+        return mxfp_quantizer_sim(tensor=x, block_dim=block_dim, mxfp_meta=meta, quantile_search=quantile_search)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return grad_output.clone(), None, None, None, None, None, None
+
+
+def mxfp_quantizer(
+    x: Tensor,
+    block_size: int,
+    element_exp_bits: int,
+    element_frac_bits: int,
+    block_dim: int = -1,
+    scale_exp_bits: int = 8,
+    quantile_search: bool = False,
+) -> Tensor:
+    """MXFP fake quantization, same interface as chop.nn.quantizers.mxfp_quantizer (mxfp/mxfp.py:187-230)."""
+    return MXFPQuantize.apply(x, block_size, element_exp_bits, element_frac_bits, block_dim, scale_exp_bits,
+                              quantile_search)
+
+
+# ---------------------------------------------------------------------------------------------------
+# element-wise minifloat
+# ---------------------------------------------------------------------------------------------------
+def minifloat_quantizer_sim(tensor: Tensor, minifloat_meta: MinifloatMeta, output_dtype: torch.dtype | None = None) -> Tensor:
+    """Element-wise quantize-dequantize (_minifloat_mx/minifloat.py:12-33)."""
+    _require_cuda(tensor, "minifloat_quantizer_sim")
+    if not minifloat_meta.is_finite or minifloat_meta.round_mode != "rn":
+        raise NotImplementedError("minifloat: only is_finite=True with round_mode='rn' is provided")
+    if minifloat_meta.exp_bits + minifloat_meta.frac_bits > 7:
+        raise NotImplementedError("minifloat: at most 8 bits per element")
+    out_dtype = output_dtype or tensor.dtype
+    di = _dtype_code(tensor.dtype, "minifloat")
+    do = _dtype_code(out_dtype, "minifloat")
+    x = tensor.contiguous()
+    y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().mxq_minifloat_fake(x.data_ptr(), y.data_ptr(), di, do, x.numel(), minifloat_meta.exp_bits,
+                                           minifloat_meta.frac_bits, _stream(x))
+    _lib.check(rc, "mxq_minifloat_fake")
+    return y
+
+
+# ---------------------------------------------------------------------------------------------------
+# block floating point
+# ---------------------------------------------------------------------------------------------------
+def _infer_block_shape(x_shape: list[int], block_shape: list[int]) -> list[int]:
+    """Right-align block_shape with x_shape, -1 / oversize entries take the whole dim (utils.py:_infer_block_shape)."""
+    nd = len(x_shape)
+    if len(block_shape) >= nd:
+        inferred = list(block_shape[-nd:])
+    else:
+        inferred = [-1] * (nd - len(block_shape)) + list(block_shape)
+    return [x_shape[i] if inferred[i] == -1 or inferred[i] > x_shape[i] else inferred[i] for i in range(nd)]
+
+
+def _bfp_row_tile(shape: tuple[int, ...], block_size: list[int], skip_first_dim: bool) -> int:
+    """Tile length along the last dim if every tile lies within one row, else raises."""
+    nd = len(shape)
+    if nd == 1:
+        assert skip_first_dim is False, "skip_first_dim must be False for bias to be blocked"
+        tile = _infer_block_shape(list(shape), block_size)
+    elif nd == 2:
+        ref_shape = [1, shape[1]] if skip_first_dim else list(shape)
+        tile = _infer_block_shape(ref_shape, block_size)
+    elif nd == 3:
+        if not skip_first_dim:
+            raise NotImplementedError("block 3d weight is not supported.")
+        tile = _infer_block_shape([1, *shape[1:]], block_size)
+    else:
+        raise RuntimeError(f"Unsupported x.ndim = {nd}")
+    # dims other than the last must have extent-1 tiles (or the dim itself has extent 1)
+    for d in range(nd - 1):
+        extent = 1 if (d == 0 and skip_first_dim and nd > 1) else shape[d]
+        if tile[d] != 1 and extent != 1:
+            raise NotImplementedError(
+                f"block_fp: tile {tile} spans several rows of a tensor of shape {tuple(shape)}; only tiles of consecutive "
+                "elements of the last dimension are provided"
+            )
+    return tile[-1]
+
+
+def _block_fp_quantize(x: Tensor, width=12, exponent_width=8, exponent_bias=None, block_size=[16], skip_first_dim=True):
+    _require_cuda(x, "block_fp_quantizer")
+    if isinstance(block_size, int):
+        block_size = [block_size]
+    dt = _dtype_code(x.dtype, "block_fp")
+    if exponent_bias in (None, "none", "None"):
+        exponent_bias = 2 ** (exponent_width - 1) - 1
+    if x.numel() == 0:
+        return x.clone()
+    bs = _bfp_row_tile(tuple(x.shape), list(block_size), skip_first_dim)
+    xc = x.contiguous()
+    cols = xc.shape[-1]
+    rows = xc.numel() // cols
+    y = torch.empty_like(xc)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().mxq_bfp_fake(xc.data_ptr(), y.data_ptr(), dt, rows, cols, bs, width, exponent_width,
+                                     int(exponent_bias), _tab_ptr(ceil_table(x.dtype)), _stream(x))
+    _lib.check(rc, "mxq_bfp_fake")
+    return y
+
+
+class BlockFPQuantize(torch.autograd.Function):
+    """Straight-through estimator (block_fp.py:85-108)."""
+
+    @staticmethod
+    def forward(ctx, x, width=12, exponent_width=8, exponent_bias=None, block_size=[16], skip_first_dim=True):
+        return _block_fp_quantize(x, width, exponent_width, exponent_bias, block_size, skip_first_dim)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return grad_output.clone(), None, None, None, None, None
+
+
+def block_fp_quantizer(
+    x: Tensor,
+    width: int = 12,
+    exponent_width: int = 8,
+    exponent_bias: int = None,
+    block_size: list[int] = [16],
+    skip_first_dim: bool = True,
+):
+    """Block floating point (MSFP) fake quantization, interface of chop.nn.quantizers.block_fp_quantizer
+    (block_fp.py:111-142): one shared exponent per tile, sign-magnitude mantissas of `width-1` bits."""
+    return BlockFPQuantize.apply(x, width, exponent_width, exponent_bias, block_size, skip_first_dim)
+
+
+# entries of chop.nn.quantizers.quantizer_map (nn/quantizers/__init__.py:14-28) provided here
+quantizer_map = {
+    "mxfp": mxfp_quantizer,
+    "mxint": mxint_quantizer,
+    "block_fp": block_fp_quantizer,
+}

@@ -1,0 +1,130 @@
+"""The CPU oracle against vectors produced by the MASE reference itself (tests/golden/make_golden.py)."""
+
+import pytest
+import torch
+
+from conftest import assert_bits_equal
+from oracle import mx_oracle as O
+
+
+def _cases(golden, kind):
+    return [c for c in golden.cases if c["kind"] == kind]
+
+
+def test_fixture_inventory(golden):
+    kinds = {c["kind"] for c in golden.cases}
+    assert kinds == {"mxint", "mxfp", "minifloat", "bfp", "blockdim", "linear"}
+    assert len(golden.cases) >= 200
+
+
+def test_mxint_oracle_matches_reference(golden):
+    for c in _cases(golden, "mxint"):
+        x = golden.tensor(c["input"] + "/x")
+        sc, m = O.mxint_extract(x.flatten(), c["block"], c["bits"])
+        assert_bits_equal(sc, golden.tensor(c["tag"] + "/scale"), c["tag"] + " scale")
+        assert_bits_equal(m, golden.tensor(c["tag"] + "/mant"), c["tag"] + " mant")
+        assert_bits_equal(O.mxint_fake(x, c["block"], c["bits"]), golden.tensor(c["tag"] + "/fake"), c["tag"] + " fake")
+
+
+def test_mxfp_oracle_matches_reference(golden):
+    for c in _cases(golden, "mxfp"):
+        x = golden.tensor(c["input"] + "/x")
+        sc, co = O.mxfp_extract(x.flatten(), c["block"], c["E"], c["F"])
+        assert_bits_equal(sc, golden.tensor(c["tag"] + "/scale"), c["tag"] + " scale")
+        assert_bits_equal(co, golden.tensor(c["tag"] + "/codes"), c["tag"] + " codes")
+        assert_bits_equal(O.mxfp_fake(x, c["block"], c["E"], c["F"]), golden.tensor(c["tag"] + "/fake"), c["tag"] + " fake")
+
+
+def test_minifloat_oracle_matches_reference(golden):
+    for c in _cases(golden, "minifloat"):
+        x = golden.tensor(c["input"] + "/x")
+        assert_bits_equal(O.minifloat_fake(x, c["E"], c["F"]), golden.tensor(c["tag"] + "/fake"), c["tag"])
+
+
+def test_bfp_oracle_matches_reference(golden):
+    for c in _cases(golden, "bfp"):
+        x = golden.tensor(c["input"] + "/x")
+        y = O.bfp_fake_rows(x, c["width"], c["exponent_width"], c["exponent_bias"], c["block_size"][-1])
+        assert_bits_equal(y, golden.tensor(c["tag"] + "/fake"), c["tag"])
+
+
+def test_block_dim_oracle_matches_reference(golden):
+    for c in _cases(golden, "blockdim"):
+        dt, bd, blk = c["dtype"], c["block_dim"], c["block"]
+        x = golden.tensor(f"blockdim/{dt}/x")
+        assert_bits_equal(O.mxint_fake(x, blk, 8, bd).contiguous(), golden.tensor(f"blockdim/{dt}/mxint_d{bd}/fake"), f"mxint d{bd}")
+        assert_bits_equal(O.mxfp_fake(x, blk, 4, 3, bd).contiguous(), golden.tensor(f"blockdim/{dt}/mxfp_d{bd}/fake"), f"mxfp d{bd}")
+
+
+def test_known_answers_e4m3():
+    """The encoder quirks, as values at block scale 2**0 (block maximum 256 -> shared exponent 0)."""
+    x = torch.zeros(32)
+    vals = [256.0, 1.97, 3.97, 7.9, 480.0, 500.0, 2.0**-7, 1.5 * 2.0**-7]
+    x[: len(vals)] = torch.tensor(vals)
+    sc, co = O.mxfp_extract(x, 32, 4, 3)
+    assert int(sc) == 127
+    assert co[0, : len(vals)].tolist() == [0x78, 0x38, 0x48, 0x48, 0x7F, 0x78, 0x00, 0x06]
+    y = O.mxfp_fake(x, 32, 4, 3)
+    assert y[: len(vals)].tolist() == [256.0, 1.0, 4.0, 4.0, 480.0, 256.0, 0.0, 1.5 * 2.0**-7]
+
+
+def test_known_answers_mxint_saturation():
+    x = torch.zeros(32)
+    x[:3] = torch.tensor([1.0, -1.0, 0.5])
+    sc, m = O.mxint_extract(x, 32, 8)
+    assert int(sc) == 127 and m[0, :3].tolist() == [127.0, -128.0, 64.0]
+    xb = torch.zeros(32, dtype=torch.bfloat16)
+    xb[0] = 16.125  # log2(16.125) = 4.011 rounds to 4.0 in bf16: the exponent stays 4 and the maximum clips
+    sc, m = O.mxint_extract(xb, 32, 8)
+    assert int(sc) == 131 and float(m[0, 0]) == 127.0
+    sc, m = O.mxint_extract(xb.float(), 32, 8)  # in fp32 the logarithm is not an integer: exponent 5
+    assert int(sc) == 132 and float(m[0, 0]) == 64.0
+
+
+def test_linear_oracle_matches_reference(golden):
+    """Weights quantized like load_state_dict does; forward vs the reference's own output."""
+    for c in _cases(golden, "linear"):
+        dt, tag, cfg = c["dtype"], c["tag"], c["config"]
+        x = golden.tensor(f"linear/{dt}/x")
+        w = golden.tensor(f"linear/{dt}/w")
+        b = golden.tensor(f"linear/{dt}/b")
+        w_ref, b_ref, y_ref = golden.tensor(tag + "/w_q"), golden.tensor(tag + "/b_q"), golden.tensor(tag + "/y")
+        if c["cls"] == "LinearMXFP":
+            wq = O.mxfp_fake(w, cfg["weight_block_size"], cfg["weight_exponent_width"], cfg["weight_frac_width"], 1)
+            bq = b
+            if "bias_block_size" in cfg:
+                bq = O.mxfp_fake(b, cfg["bias_block_size"], cfg["bias_exponent_width"], cfg["bias_frac_width"], 0)
+            y = O.linear_mxfp(x, wq, bq, cfg)
+        elif c["cls"] == "LinearMXInt":
+            wq, bq = O.mxint_fake(w, cfg["weight_block_size"], cfg["weight_width"], 1), b
+            y = O.linear_mxint(x, wq, bq, cfg)
+        else:
+            wq, bq = w, b
+            y = O.linear_block_fp(x, w, b, cfg)
+        if c["cls"] != "LinearBlockFP":
+            assert_bits_equal(wq.contiguous(), w_ref, tag + " w_q")
+            assert_bits_equal(bq.contiguous(), b_ref, tag + " b_q")
+        # the reference output is in x.dtype from the library GEMM; the oracle accumulates in fp32
+        err = (y - y_ref.float()).abs().max() / y_ref.float().abs().max()
+        tol = 1e-5 if dt == "fp32" else 8e-3  # bf16 output rounding: half an ulp = 2**-9 relative
+        assert float(err) <= tol, f"{tag}: {float(err)}"
+
+
+@pytest.mark.skipif(not __import__("os").path.isdir("/root/reference/src/chop"), reason="no MASE checkout")
+def test_oracle_vs_live_reference_random():
+    """Where a MASE checkout is present, compare on fresh random data as well (larger than the fixtures)."""
+    import sys, os
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    import make_golden
+
+    make_golden.import_reference("/root/reference/src/chop")
+    import chop.nn.quantizers as q
+
+    g = torch.Generator().manual_seed(2024)
+    x = torch.randn(256, 512, generator=g) * torch.exp2(torch.randint(-20, 20, (256, 1), generator=g).float())
+    for dt in (torch.float32, torch.bfloat16):
+        xd = x.to(dt)
+        assert_bits_equal(O.mxint_fake(xd, 32, 8), q.mxint_quantizer(xd, 32, 8), "mxint")
+        assert_bits_equal(O.mxfp_fake(xd, 32, 4, 3), q.mxfp_quantizer(xd, 32, 4, 3), "mxfp e4m3")
+        assert_bits_equal(O.mxfp_fake(xd, 32, 2, 1), q.mxfp_quantizer(xd, 32, 2, 1), "mxfp e2m1")
+        assert_bits_equal(O.bfp_fake_rows(xd, 8, 8, 127, 32), q.block_fp_quantizer(xd, 8, 8, 127, [1, 32], True), "bfp")
