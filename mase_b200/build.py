@@ -57,7 +57,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 print(" ".join(cmd), flush=True)
             subprocess.run(cmd, check=True)
         objs.append(obj)
-    cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-lcudart"]
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB_PATH, *objs, "-lcudart"]
     subprocess.run(cmd, check=True)
     return LIB_PATH
 

@@ -110,11 +110,43 @@ mxint_compose_kernel(const int8_t *__restrict__ mant, const uint8_t *__restrict_
 // ---------------------------------------------------------------------------------------------------
 // MXFP
 // ---------------------------------------------------------------------------------------------------
+// Fast path of the MXFP element codec.
+//
+// With K = (biased exponent of the block maximum) - (2**E - 1), an element whose biased fp32 exponent is ex has
+// the minifloat exponent code ye = ex - K.  When K >= 1 and every element of the vector has ye >= 1 (no
+// subnormal code, no underflow, no flushed input), quantize-dequantize reduces to rounding |x| to F fraction
+// bits (half to even, after dropping the low 8 fp32 mantissa bits) with the block scale cancelling out, except
+// that a fraction carry is lost when ye is odd (the reference ORs the carry into the exponent field): then the
+// result is 2**e instead of 2**(e+1).  That is a handful of integer operations on the bit patterns; for bf16
+// tensors two elements are processed per 32-bit register.  Everything else takes the general element codec.
+template <int F>
+__device__ __forceinline__ uint32_t mxfp_round_pair(uint32_t a2, uint32_t kodd2) {
+  constexpr uint32_t kHalf2 = ((1u << (6 - F)) - 1u) * 0x00010001u;
+  constexpr uint32_t kMask2 = ((0xFFFFu << (7 - F)) & 0xFFFFu) * 0x00010001u;
+  const uint32_t lsb2 = (a2 >> (7 - F)) & 0x00010001u;
+  uint32_t y2 = (a2 + kHalf2 + lsb2) & kMask2;                   // no carry crosses bit 15: a2 < 0x7F80 per half
+  y2 -= (y2 ^ a2) & (a2 ^ kodd2) & 0x00800080u;                  // exponent lsb flipped (carry) and ye odd
+  return y2;
+}
+template <int F>
+__device__ __forceinline__ uint32_t mxfp_round_one(uint32_t at, uint32_t kodd) {
+  constexpr uint32_t kHalf = (1u << (22 - F)) - 1u;
+  constexpr uint32_t kMask = ~((1u << (23 - F)) - 1u);
+  const uint32_t lsb = (at >> (23 - F)) & 1u;
+  uint32_t y = (at + kHalf + lsb) & kMask;
+  y -= (y ^ at) & (at ^ kodd) & 0x00800000u;
+  return y;
+}
+
 template <typename Tin, typename Tout, Mode kMode, int E, int F>
 __global__ void __launch_bounds__(kThreads)
 mxfp_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, uint8_t *__restrict__ codes, uint8_t *__restrict__ scales,
             int64_t n_vec, int group, const __grid_constant__ Log2Tab tab) {
   constexpr int N = Elem<Tin>::kVec;
+  constexpr bool kBf16In = Elem<Tin>::kBf16;
+  constexpr int kTop = (1 << E) - 1;
+  constexpr int kBias = (1 << (E - 1)) - 1;
+  constexpr int kEmax = kTop - kBias;
   const uint4 *xv = reinterpret_cast<const uint4 *>(x);
   const int64_t step = (int64_t)gridDim.x * kThreads * kUnroll;
   for (int64_t base = (int64_t)blockIdx.x * kThreads * kUnroll; base < n_vec; base += step) {
@@ -127,29 +159,112 @@ mxfp_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, uint8_t *__restrict
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t i = base + u * kThreads + threadIdx.x;
-      uint32_t b[N];
-      unpack(raw[u], b);
-      uint32_t amax = 0;
-#pragma unroll
-      for (int k = 0; k < N; ++k) {
-        const uint32_t a = b[k] & 0x7FFFFFFFu;
-        if ((a >> 23) == 0) b[k] = 0;  // fp32 subnormals (and -0) are flushed to +0
-        amax = max(amax, (a >> 23) == 0 ? 0u : a);
-      }
-      amax = group_max(amax, group);
-      const MxfpBlock p = mxfp_block(amax, E, tab);
-      if (i >= n_vec) continue;
-      if constexpr (kMode == Mode::kFake) {
-        float out[N];
-#pragma unroll
-        for (int k = 0; k < N; ++k) out[k] = mxfp_decode(mxfp_encode(b[k], p.sh, E, F), E, F) * p.scale_f;
-        store_vals(y, i * N, out);
+      const uint32_t r[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+      // ---- block maximum of |x| as an fp32 bit pattern (0 when every element is zero or an fp32 subnormal) ----
+      uint32_t a[4], amax;
+      if constexpr (kBf16In) {
+        __nv_bfloat162 m2 = __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&(a[0] = r[0] & 0x7FFF7FFFu)),
+                                    *reinterpret_cast<const __nv_bfloat162 *>(&(a[1] = r[1] & 0x7FFF7FFFu)));
+        m2 = __hmax2(m2, __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&(a[2] = r[2] & 0x7FFF7FFFu)),
+                                 *reinterpret_cast<const __nv_bfloat162 *>(&(a[3] = r[3] & 0x7FFF7FFFu))));
+        const uint32_t mb = *reinterpret_cast<uint32_t *>(&m2);
+        const uint32_t m = group_max(max(mb & 0xFFFFu, mb >> 16), group);
+        amax = (m >> 7) ? (m << 16) : 0u;
       } else {
-        uint32_t c[N];
 #pragma unroll
-        for (int k = 0; k < N; ++k) c[k] = mxfp_encode(b[k], p.sh, E, F);
-        store_bytes(codes, i * N, c);
-        if ((threadIdx.x & (group - 1)) == 0) scales[i / group] = (uint8_t)p.scale;
+        for (int k = 0; k < 4; ++k) a[k] = r[k] & 0x7FFFFFFFu;
+        const uint32_t m = group_max(max(max(a[0], a[1]), max(a[2], a[3])), group);
+        amax = (m >> 23) ? m : 0u;
+      }
+      if (i >= n_vec) continue;
+      const int exm = (int)(amax >> 23);
+      int up = 0;  // host log2 rounds up to the next integer for fp32 maxima a few ulps below a power of two
+      if constexpr (!kBf16In) {
+        const uint32_t man = amax & 0x7FFFFFu;
+        if (man >= 0x7FFF00u) up = (0x7FFFFFu - man) < tab.t[exm] ? 1 : 0;
+      }
+      const int K = exm + up - kTop;
+      bool fast = K >= 1;
+      uint32_t yq[N];  // rounded |x| as fp32 bit patterns (bf16 input: two bf16 patterns per word in yq[0..3])
+      if constexpr (kBf16In) {
+        const uint32_t t1 = (uint32_t)((K + 1) << 7) * 0x00010001u;
+        const __nv_bfloat162 t1v = *reinterpret_cast<const __nv_bfloat162 *>(&t1);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) fast = fast && __hbge2(*reinterpret_cast<const __nv_bfloat162 *>(&a[k]), t1v);
+        if (fast) {
+          const uint32_t kodd2 = (K & 1) ? 0x00800080u : 0u;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) yq[k] = mxfp_round_pair<F>(a[k], kodd2);
+        }
+      } else {
+        const uint32_t t1 = (uint32_t)(K + 1) << 23;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) fast = fast && a[k] >= t1;
+        if (fast) {
+          const uint32_t kodd = (K & 1) ? 0x00800000u : 0u;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) yq[k] = mxfp_round_one<F>(a[k] & 0x7FFFFF00u, kodd);
+        }
+      }
+      if (fast) {
+        if constexpr (kMode == Mode::kFake) {
+          if constexpr (kBf16In && Elem<Tout>::kBf16) {
+            st_stream(reinterpret_cast<uint4 *>(y) + i,
+                      make_uint4(yq[0] | (r[0] & 0x80008000u), yq[1] | (r[1] & 0x80008000u),
+                                 yq[2] | (r[2] & 0x80008000u), yq[3] | (r[3] & 0x80008000u)));
+          } else {
+            float out[N];
+            if constexpr (kBf16In) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint32_t v = yq[k] | (r[k] & 0x80008000u);
+                out[2 * k] = __uint_as_float(v << 16), out[2 * k + 1] = __uint_as_float(v & 0xFFFF0000u);
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) out[k] = __uint_as_float(yq[k] | (r[k] & 0x80000000u));
+            }
+            store_vals(y, i * N, out);
+          }
+        } else {
+          // code = sign | ((ye << F) | f) with ye = ex - K: the rounded pattern shifted down, minus K << F
+          if constexpr (kBf16In) {
+            uint32_t c2[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              c2[k] = ((yq[k] >> (7 - F)) - (uint32_t)(K << F) * 0x00010001u) |
+                      ((r[k] >> (15 - (E + F))) & ((1u << (E + F)) * 0x00010001u));
+            __stcs(reinterpret_cast<uint2 *>(codes + i * N),
+                   make_uint2(__byte_perm(c2[0], c2[1], 0x6420), __byte_perm(c2[2], c2[3], 0x6420)));
+          } else {
+            uint32_t c[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              c[k] = ((yq[k] >> (23 - F)) - (uint32_t)(K << F)) | ((r[k] >> (31 - (E + F))) & (1u << (E + F)));
+            store_bytes(codes, i * N, c);
+          }
+          if ((threadIdx.x & (group - 1)) == 0) scales[i / group] = (uint8_t)(exm + up - kEmax);
+        }
+      } else {
+        // ---- general path: subnormal / underflowing / flushed elements, all-zero blocks, clamped scales ----
+        uint32_t b[N];
+        unpack(raw[u], b);
+#pragma unroll
+        for (int k = 0; k < N; ++k)
+          if (((b[k] & 0x7FFFFFFFu) >> 23) == 0) b[k] = 0;  // fp32 subnormals and -0 are flushed to +0
+        const MxfpBlock p = mxfp_block(amax, E, tab);
+        if constexpr (kMode == Mode::kFake) {
+          float out[N];
+#pragma unroll
+          for (int k = 0; k < N; ++k) out[k] = mxfp_decode(mxfp_encode(b[k], p.sh, E, F), E, F) * p.scale_f;
+          store_vals(y, i * N, out);
+        } else {
+          uint32_t c[N];
+#pragma unroll
+          for (int k = 0; k < N; ++k) c[k] = mxfp_encode(b[k], p.sh, E, F);
+          store_bytes(codes, i * N, c);
+          if ((threadIdx.x & (group - 1)) == 0) scales[i / group] = (uint8_t)p.scale;
+        }
       }
     }
   }
@@ -207,13 +322,23 @@ minifloat_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, int64_t n, int
 // ---------------------------------------------------------------------------------------------------
 // block floating point
 // ---------------------------------------------------------------------------------------------------
+// Fast path of block floating point: when the tile exponent e leaves 2**(mb-e) and 2**(e-mb) in the normal
+// fp32 range and every element is either exactly zero or large enough that the reference's "+1e-9" and its
+// "close to zero" pass-through cannot matter (bf16: |x| >= 2**-21; fp32: |x| > 1e-8, where the addition is kept),
+// the result is sign(x) * min(rint(val * 2**(mb-e)), hi) * 2**(e-mb).  Other vectors take bfp_elem().
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 bfp_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t n_vec, int group, int width, int exp_width, int exp_bias,
            const __grid_constant__ Log2Tab tab) {
   constexpr int N = Elem<T>::kVec;
+  constexpr bool kBf16 = Elem<T>::kBf16;
   const uint4 *xv = reinterpret_cast<const uint4 *>(x);
   const int64_t step = (int64_t)gridDim.x * kThreads * kUnroll;
+  const int mb = width - 1;
+  const int e_lo = -exp_bias, e_hi = (1 << exp_width) - 1 - exp_bias;
+  const float hi = round_to<T>((float)((1 << mb) - 1));
+  // smallest |x| bit pattern that stays on the fast path, minus one (so that 0 - 1 wraps and passes too)
+  const uint32_t thr_m1 = kBf16 ? ((uint32_t)(127 - 21) << 23) - 1u : __float_as_uint(1e-8f);
   for (int64_t base = (int64_t)blockIdx.x * kThreads * kUnroll; base < n_vec; base += step) {
     uint4 raw[kUnroll];
 #pragma unroll
@@ -230,11 +355,30 @@ bfp_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t n_vec, int group,
 #pragma unroll
       for (int k = 0; k < N; ++k) amax = fmaxf(amax, fabsf(__uint_as_float(b[k])));
       amax = group_max(amax, group);
-      const BfpBlock p = bfp_block<T>(amax, width, exp_width, exp_bias, tab);
       if (i >= n_vec) continue;
-      float out[N];
+      int e = 0;
+      bool fast = (__float_as_uint(amax) >> 23) != 0;
+      if (fast) {
+        e = min(max(ceil_log2_ref<kBf16>(amax, tab), e_lo), e_hi);
+        fast = e <= 127 && e >= mb - 28 && mb <= 16;
+      }
 #pragma unroll
-      for (int k = 0; k < N; ++k) out[k] = bfp_elem<T>(__uint_as_float(b[k]), p);
+      for (int k = 0; k < N; ++k) fast = fast && ((b[k] & 0x7FFFFFFFu) - 1u) >= thr_m1;
+      float out[N];
+      if (fast) {
+        const float c1 = __int_as_float((mb - e + 127) << 23), c2 = __int_as_float((e - mb + 127) << 23);
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          const float xf = __uint_as_float(b[k]);
+          const float val = kBf16 ? fabsf(xf) : fabsf(xf) + 1e-9f;
+          const float q = fminf(rintf(val * c1), hi) * c2;
+          out[k] = copysignf(q, xf + 0.f);  // x = -0 gives +0, a negative x that rounds to zero gives -0
+        }
+      } else {
+        const BfpBlock p = bfp_block<T>(amax, width, exp_width, exp_bias, tab);
+#pragma unroll
+        for (int k = 0; k < N; ++k) out[k] = bfp_elem<T>(__uint_as_float(b[k]), p);
+      }
       store_vals(y, i * N, out);
     }
   }

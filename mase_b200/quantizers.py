@@ -134,11 +134,54 @@ def _dtype_code(dt: torch.dtype, what: str) -> int:
 
 
 def _stream(t: Tensor) -> int:
-    return torch.cuda.current_stream(t.device).cuda_stream
+    return torch._C._cuda_getCurrentRawStream(t.device.index)
 
 
-def _tab_ptr(tab) -> int:
-    return tab.ctypes.data
+class _on_device:
+    """Makes the tensor's device current for the launch; a no-op when it already is (the common case)."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, t: Tensor):
+        self.idx = t.device.index
+
+    def __enter__(self):
+        self.prev = torch.cuda.current_device()
+        if self.prev != self.idx:
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev != self.idx:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+def _is_last_dim_contiguous(t: Tensor, block_dim: int) -> bool:
+    return (block_dim % t.dim()) == t.dim() - 1 and t.is_contiguous()
+
+
+_TAB_PTRS: dict = {}
+
+
+def _ceil_tab_ptr(dtype: torch.dtype) -> int:
+    """Host address of the ceil(log2) table for tensors of `dtype` (the arrays are cached for the process)."""
+    p = _TAB_PTRS.get(dtype)
+    if p is None:
+        p = _TAB_PTRS[dtype] = ceil_table(dtype).ctypes.data
+    return p
+
+
+def _floor_tab_ptr() -> int:
+    p = _TAB_PTRS.get("floor")
+    if p is None:
+        p = _TAB_PTRS["floor"] = floor_table().ctypes.data
+    return p
+
+
+@functools.lru_cache(maxsize=None)
+def _mxfp_meta(block_size, scale_exp_bits, element_exp_bits, element_frac_bits):
+    return MXFPMeta(block_size=block_size, scale_exp_bits=scale_exp_bits, element_exp_bits=element_exp_bits,
+                    element_frac_bits=element_frac_bits, element_is_finite=True, round_mode="rn")
 
 
 def flatten_for_quantize(tensor: Tensor, block_dim: int) -> Tensor:
@@ -162,7 +205,8 @@ def permute_for_dequantize(flatten_tensor: Tensor, ori_shape: tuple[int, ...], b
 
 
 def _flat_contiguous(x: Tensor) -> Tensor:
-    x = x.flatten()
+    if x.dim() != 1:
+        x = x.flatten()
     if not x.is_contiguous() or x.data_ptr() % 16:
         x = x.contiguous()
         if x.data_ptr() % 16:
@@ -184,9 +228,9 @@ def _mxint_fake_flat(flat: Tensor, meta: MXIntMeta, out_dtype: torch.dtype) -> T
     do = _dtype_code(out_dtype, "mxint")
     flat = _flat_contiguous(flat)
     y = torch.empty(flat.shape, dtype=out_dtype, device=flat.device)
-    with torch.cuda.device(flat.device):
+    with _on_device(flat):
         rc = _lib.lib().mxq_mxint_fake(flat.data_ptr(), y.data_ptr(), di, do, flat.numel() // B, B, meta.element_bits,
-                                       _tab_ptr(ceil_table(flat.dtype)), _stream(flat))
+                                       _ceil_tab_ptr(flat.dtype), _stream(flat))
     _lib.check(rc, "mxq_mxint_fake")
     return y
 
@@ -203,9 +247,9 @@ def mxint_codes(x: Tensor, block_size: int, element_bits: int) -> tuple[Tensor, 
     n = flat.numel() // B
     mant = torch.empty((n, B), dtype=torch.int8, device=x.device)
     scales = torch.empty((n,), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x):
         rc = _lib.lib().mxq_mxint_extract(flat.data_ptr(), mant.data_ptr(), scales.data_ptr(), di, n, B, element_bits,
-                                          _tab_ptr(ceil_table(x.dtype)), _stream(x))
+                                          _ceil_tab_ptr(x.dtype), _stream(x))
     _lib.check(rc, "mxq_mxint_extract")
     return scales, mant
 
@@ -218,7 +262,9 @@ def extract_mxint_components(x: Tensor, mxint_meta: MXIntMeta, percentile: float
     if mxint_meta.scale_bits != 8:
         raise NotImplementedError("mxint: only scale_bits=8 is supported")
     scales, mant = mxint_codes(x, mxint_meta.block_size, mxint_meta.element_bits)
-    return scales.view(-1, 1).to(x.dtype), mant.to(x.dtype)
+    # the reference keeps mantissas as floats, where a small negative value rounds to -0.0
+    mant_f = torch.copysign(mant.to(x.dtype), x.reshape(mant.shape))
+    return scales.view(-1, 1).to(x.dtype), mant_f
 
 
 def compose_mxint_tensor(shared_scales: Tensor, elements: Tensor, mxint_meta: MXIntMeta) -> Tensor:
@@ -229,11 +275,11 @@ def compose_mxint_tensor(shared_scales: Tensor, elements: Tensor, mxint_meta: MX
     mant = elements.to(torch.int8).contiguous()
     sc = shared_scales.to(torch.uint8).contiguous()
     y = torch.empty(elements.shape, dtype=elements.dtype, device=elements.device)
-    with torch.cuda.device(elements.device):
+    with _on_device(elements):
         rc = _lib.lib().mxq_mxint_compose(mant.data_ptr(), sc.data_ptr(), y.data_ptr(), do, mant.numel() // B, B,
                                           mxint_meta.element_bits, _stream(elements))
     _lib.check(rc, "mxq_mxint_compose")
-    return y
+    return torch.copysign(y, elements)  # int8 codes cannot carry the sign of a -0.0 mantissa
 
 
 def mxint_quantizer_sim(
@@ -252,6 +298,8 @@ def mxint_quantizer_sim(
     ori_shape = tuple(tensor.shape)
     ndim = len(ori_shape)
     assert block_dim < ndim and block_dim >= -ndim
+    if _is_last_dim_contiguous(tensor, block_dim):  # no permutation needed: the tensor already is a run of blocks
+        return _mxint_fake_flat(tensor.view(-1), mxint_meta, dtype or tensor.dtype).view(ori_shape)
     flat = flatten_for_quantize(tensor, block_dim)
     y = _mxint_fake_flat(flat, mxint_meta, dtype or tensor.dtype)
     return permute_for_dequantize(y, ori_shape, block_dim)
@@ -279,6 +327,9 @@ def mxint_quantizer(
     quantile_search: bool = False,
 ) -> Tensor:
     """MXINT fake quantization, same interface as chop.nn.quantizers.mxint_quantizer (mxint/mxint.py:211-251)."""
+    if not (x.requires_grad and torch.is_grad_enabled()):  # nothing to differentiate: skip the autograd wrapper
+        meta = MXIntMeta(block_size=block_size, scale_bits=scale_bits, element_bits=element_bits)
+        return mxint_quantizer_sim(tensor=x, block_dim=block_dim, mxint_meta=meta, quantile_search=quantile_search)
     return MXIntQuantize.apply(x, block_size, element_bits, block_dim, scale_bits, quantile_search)
 
 
@@ -304,10 +355,10 @@ def extract_mxfp_components(tensor: Tensor, mxfp_meta: MXFPMeta, percentile: flo
     n = flat.numel() // B
     codes = torch.empty((n, B), dtype=torch.uint8, device=tensor.device)
     scales = torch.empty((n, 1), dtype=torch.uint8, device=tensor.device)
-    with torch.cuda.device(tensor.device):
+    with _on_device(tensor):
         rc = _lib.lib().mxq_mxfp_extract(flat.data_ptr(), codes.data_ptr(), scales.data_ptr(), di, n, B,
                                          mxfp_meta.element_exp_bits, mxfp_meta.element_frac_bits,
-                                         _tab_ptr(floor_table()), _stream(tensor))
+                                         _floor_tab_ptr(), _stream(tensor))
     _lib.check(rc, "mxq_mxfp_extract")
     return scales, codes
 
@@ -322,7 +373,7 @@ def compose_mxfp_tensor(scales: Tensor, elements: Tensor, mxfp_meta: MXFPMeta, o
     elements = elements.contiguous()
     scales = scales.contiguous()
     y = torch.empty((elements.numel(),), dtype=output_dtype, device=elements.device)
-    with torch.cuda.device(elements.device):
+    with _on_device(elements):
         rc = _lib.lib().mxq_mxfp_compose(elements.data_ptr(), scales.data_ptr(), y.data_ptr(), do,
                                          elements.numel() // B, B, mxfp_meta.element_exp_bits,
                                          mxfp_meta.element_frac_bits, _stream(elements))
@@ -338,9 +389,9 @@ def _mxfp_fake_flat(flat: Tensor, meta: MXFPMeta, out_dtype: torch.dtype) -> Ten
     do = _dtype_code(out_dtype, "mxfp")
     flat = _flat_contiguous(flat)
     y = torch.empty(flat.shape, dtype=out_dtype, device=flat.device)
-    with torch.cuda.device(flat.device):
+    with _on_device(flat):
         rc = _lib.lib().mxq_mxfp_fake(flat.data_ptr(), y.data_ptr(), di, do, flat.numel() // B, B,
-                                      meta.element_exp_bits, meta.element_frac_bits, _tab_ptr(floor_table()),
+                                      meta.element_exp_bits, meta.element_frac_bits, _floor_tab_ptr(),
                                       _stream(flat))
     _lib.check(rc, "mxq_mxfp_fake")
     return y
@@ -362,6 +413,8 @@ def mxfp_quantizer_sim(
     ori_shape = tuple(tensor.shape)
     ndim = len(ori_shape)
     assert block_dim < ndim and block_dim >= -ndim
+    if _is_last_dim_contiguous(tensor, block_dim):  # no permutation needed: the tensor already is a run of blocks
+        return _mxfp_fake_flat(tensor.view(-1), mxfp_meta, dtype or tensor.dtype).view(ori_shape)
     flat = flatten_for_quantize(tensor, block_dim)
     y = _mxfp_fake_flat(flat, mxfp_meta, dtype or tensor.dtype)
     return permute_for_dequantize(y, ori_shape, block_dim)
@@ -397,6 +450,9 @@ def mxfp_quantizer(
     quantile_search: bool = False,
 ) -> Tensor:
     """MXFP fake quantization, same interface as chop.nn.quantizers.mxfp_quantizer (mxfp/mxfp.py:187-230)."""
+    if not (x.requires_grad and torch.is_grad_enabled()):  # nothing to differentiate: skip the autograd wrapper
+        meta = _mxfp_meta(block_size, scale_exp_bits, element_exp_bits, element_frac_bits)
+        return mxfp_quantizer_sim(tensor=x, block_dim=block_dim, mxfp_meta=meta, quantile_search=quantile_search)
     return MXFPQuantize.apply(x, block_size, element_exp_bits, element_frac_bits, block_dim, scale_exp_bits,
                               quantile_search)
 
@@ -416,7 +472,7 @@ def minifloat_quantizer_sim(tensor: Tensor, minifloat_meta: MinifloatMeta, outpu
     do = _dtype_code(out_dtype, "minifloat")
     x = tensor.contiguous()
     y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x):
         rc = _lib.lib().mxq_minifloat_fake(x.data_ptr(), y.data_ptr(), di, do, x.numel(), minifloat_meta.exp_bits,
                                            minifloat_meta.frac_bits, _stream(x))
     _lib.check(rc, "mxq_minifloat_fake")
@@ -476,9 +532,9 @@ def _block_fp_quantize(x: Tensor, width=12, exponent_width=8, exponent_bias=None
     cols = xc.shape[-1]
     rows = xc.numel() // cols
     y = torch.empty_like(xc)
-    with torch.cuda.device(x.device):
+    with _on_device(x):
         rc = _lib.lib().mxq_bfp_fake(xc.data_ptr(), y.data_ptr(), dt, rows, cols, bs, width, exponent_width,
-                                     int(exponent_bias), _tab_ptr(ceil_table(x.dtype)), _stream(x))
+                                     int(exponent_bias), _ceil_tab_ptr(x.dtype), _stream(x))
     _lib.check(rc, "mxq_bfp_fake")
     return y
 
@@ -505,6 +561,8 @@ def block_fp_quantizer(
 ):
     """Block floating point (MSFP) fake quantization, interface of chop.nn.quantizers.block_fp_quantizer
     (block_fp.py:111-142): one shared exponent per tile, sign-magnitude mantissas of `width-1` bits."""
+    if not (x.requires_grad and torch.is_grad_enabled()):
+        return _block_fp_quantize(x, width, exponent_width, exponent_bias, block_size, skip_first_dim)
     return BlockFPQuantize.apply(x, width, exponent_width, exponent_bias, block_size, skip_first_dim)
 
 

@@ -1,0 +1,126 @@
+"""CPU-only checks: the C-ABI library loads and exports what include/mxq.h declares, host-side helpers."""
+
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import mase_b200 as mb
+from mase_b200 import _lib, build, log2_tables, quantizers
+from oracle import mx_oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def library():
+    build.build()
+    return _lib.lib()
+
+
+def test_library_exports_every_declared_symbol(library):
+    header = open(os.path.join(ROOT, "include", "mxq.h")).read()
+    declared = set(re.findall(r"\b(mxq_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations parsed"
+    for name in declared:
+        assert hasattr(library, name), f"{name} declared in include/mxq.h but not exported"
+    assert declared == set(_lib.exported_symbols()), "ctypes prototypes and header disagree"
+    assert library.mxq_version() == 1
+    assert library.mxq_error_string(-4) == b"pointer is not 16-byte aligned"
+
+
+def test_argument_validation_without_gpu(library):
+    """Bad arguments are rejected before anything is launched."""
+    tab = (ctypes.c_uint8 * 256)()
+    assert library.mxq_mxint_fake(None, None, 0, 0, 4, 32, 8, tab, None) == -5
+    assert library.mxq_mxint_fake(16, 16, 0, 0, -1, 32, 8, tab, None) == -2
+    assert library.mxq_mxint_fake(16, 16, 0, 0, 4, 32, 9, tab, None) == -3
+    assert library.mxq_mxfp_fake(16, 16, 0, 0, 4, 32, 3, 3, tab, None) == -3
+    assert library.mxq_mxfp_fake(16, 16, 7, 0, 4, 32, 4, 3, tab, None) == -1
+    assert library.mxq_mxfp_fake(16, 16, 0, 0, 0, 32, 4, 3, tab, None) == 0  # empty: nothing to do
+    assert library.mxq_bfp_fake(16, 16, 0, 4, 64, 32, 40, 8, 127, tab, None) == -3
+
+
+def test_missing_library_is_loud(monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "_PATH", "/nonexistent/libmxq.so")
+    with pytest.raises(_lib.MxqError):
+        _lib.lib()
+
+
+def test_cpu_tensors_are_rejected():
+    for call in (
+        lambda: mb.mxint_quantizer(torch.randn(2, 32), 32, 8),
+        lambda: mb.mxfp_quantizer(torch.randn(2, 32), 32, 4, 3),
+        lambda: mb.block_fp_quantizer(torch.randn(2, 32), 8, 8, 127, [1, 32]),
+        lambda: mb.minifloat_quantizer_sim(torch.randn(2, 32), mb.MinifloatMeta(4, 3, True, "rn")),
+    ):
+        with pytest.raises(RuntimeError, match="CUDA"):
+            call()
+
+
+def test_log2_tables_reproduce_host_log2():
+    """Applying the tables to the exact integer log2 equals torch.log2 + ceil/floor for random and edge values."""
+    g = torch.Generator().manual_seed(0)
+    ex = torch.randint(1, 255, (200000,), generator=g, dtype=torch.int32)
+    near = torch.randint(0, 64, (200000,), generator=g, dtype=torch.int32)
+    far = torch.randint(0, 1 << 23, (200000,), generator=g, dtype=torch.int32)
+    for man in (near, (1 << 23) - 1 - near, far):
+        x = ((ex << 23) | man).view(torch.float32)
+        ct = torch.from_numpy(log2_tables.ceil_table(torch.float32).astype(np.int32))
+        got = ex - 127 + (man > ct[ex.long()]).int()
+        assert torch.equal(got, torch.log2(x).ceil().int())
+        ft = torch.from_numpy(log2_tables.floor_table().astype(np.int32))
+        got = ex - 127 + (((1 << 23) - 1 - man) < ft[ex.long()]).int()
+        assert torch.equal(got, torch.log2(x).floor().int())
+    # bf16: exhaustive over all positive normal values
+    bits = torch.arange(1 << 7, 255 << 7, dtype=torch.int32)
+    xb = bits.to(torch.int16).view(torch.bfloat16)
+    bt = torch.from_numpy(log2_tables.ceil_table(torch.bfloat16).astype(np.int32))
+    got = (bits >> 7) - 127 + ((bits & 0x7F) > bt[(bits >> 7).long()]).int()
+    assert torch.equal(got, torch.log2(xb).ceil().int())
+
+
+def test_permute_helpers_match_oracle():
+    x = torch.arange(2 * 3 * 4 * 5).reshape(2, 3, 4, 5)
+    for d in (-1, 0, 1, 2, 3, -3):
+        flat = quantizers.flatten_for_quantize(x, d)
+        assert torch.equal(flat, O.flatten_blocks(x, d))
+        back = quantizers.permute_for_dequantize(flat, tuple(x.shape), d)
+        assert torch.equal(back, x)
+
+
+def test_bfp_tile_inference():
+    t = quantizers._bfp_row_tile
+    assert t((64, 128), [1, 16], True) == 16
+    assert t((64, 128), [16], True) == 16          # 2-D activation: first dim is always 1
+    assert t((64, 128), [8, 16], True) == 16
+    assert t((64, 128), [1, 16], False) == 16
+    assert t((64, 128), [1, 256], False) == 128    # oversize tile takes the whole row
+    assert t((96,), [16], False) == 16
+    assert t((4, 7, 40), [1, 16], True) == 16
+    assert t((1, 128), [16], False) == 16
+    with pytest.raises(NotImplementedError):
+        t((64, 128), [16], False)                   # [64,16] tile
+    with pytest.raises(NotImplementedError):
+        t((4, 7, 40), [16], True)                   # [1,7,16] tile
+    with pytest.raises(NotImplementedError):
+        t((4, 7, 40), [1, 16], False)
+    with pytest.raises(RuntimeError):
+        t((2, 2, 2, 2), [16], True)
+    with pytest.raises(AssertionError):
+        t((96,), [16], True)
+
+
+def test_meta_classes_validate_like_reference():
+    with pytest.raises(AssertionError):
+        mb.MXFPMeta(32, 8, 3, 3, True, "rn")
+    with pytest.raises(AssertionError):
+        mb.MXFPMeta(32, 4, 4, 3, True, "rn")
+    m = mb.MXFPMeta(32, 8, 4, 3, True, "rn")
+    assert m.element_meta.n_bits == 8
+    assert set(mb.quantizer_map) == {"mxfp", "mxint", "block_fp"}
+    assert set(mb.quantized_module_map) == {"linear_mxfp", "linear_mxint", "linear_block_fp"}
