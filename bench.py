@@ -42,7 +42,7 @@ CPU_SAMPLE_ROWS = 2048
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per element (read + write) of the fake-quant kernel from an ncu capture of a smaller tensor of the
 # same kernel (profiles/); None until measured.  Scales linearly with the element count.
-NCU_DRAM_BYTES_PER_ELEM = None
+NCU_DRAM_BYTES_PER_ELEM = 3.65
 
 
 def measured_peaks() -> tuple[float, str]:
