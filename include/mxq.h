@@ -96,6 +96,39 @@ int mxq_minifloat_fake(const void *x, void *y, int in_dtype, int out_dtype, int6
 int mxq_bfp_fake(const void *x, void *y, int dtype, int64_t rows, int64_t cols, int bs, int width, int exp_width,
                  int exp_bias, const uint8_t *ceil_tab_host, void *stream);
 
+/*
+ * Forward GEMM of the quantized Linear modules: D[M,N] = A[M,K] * B[N,K]^T (+ bias[N]), fp32 accumulation on the
+ * tcgen05 tensor cores.  Replaces the `F.linear(x, self.weight, self.bias)` at the end of LinearMXFP.forward,
+ * LinearMXInt.forward (chop/nn/quantized/modules/linear.py:895, :972) and linearBlockFP
+ * (chop/nn/quantized/functional/linear.py:278).
+ *
+ * `status` is an optional device int (zero it once): a kernel whose bounded waits run out stores a non-zero code
+ * there instead of hanging; the caller reads it when it next synchronises.
+ */
+
+/* Operands that already hold quantized values in bf16 (exact for every MX / block-fp format with <= 8 significant
+ * bits) or fp32 (multiplied as tf32: exact for up to 11 significant bits).  A: [M,K], B: [N,K], row-major,
+ * 16-byte aligned rows (K % 8 == 0 for bf16, K % 4 == 0 for fp32).  D: [M,N] of out_dtype. */
+int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int in_dtype, int out_dtype, int bias_dtype,
+                   int64_t M, int64_t N, int64_t K, int *status, void *stream);
+
+/* Size in bytes of the scale array that mxq_mxfp_pack_mma writes for a [rows, k] operand. */
+int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k);
+
+/* Quantize a [rows, k] matrix to MXFP (E, F) with blocks of 32 along k -- the same codes and scales as
+ * extract_mxfp_components (chop/nn/quantizers/mxfp/fake.py:12-72) -- and store them as tensor-core operands:
+ * hardware E4M3 bytes [rows, k] plus E8M0 scales in 512-byte chunks per 128 rows x 128 columns.  E <= 4, F <= 3.
+ * A block that holds the reference's top E4M3 code (480, NaN in hardware) is stored one binade lower with its
+ * scale raised by one. */
+int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k, int E,
+                      int F, const uint8_t *floor_tab_host, void *stream);
+
+/* Block-scaled GEMM on operands produced by mxq_mxfp_pack_mma (kind::mxf8f6f4, one E8M0 scale per 32 elements of
+ * K).  Replaces quantize-activations + F.linear of LinearMXFP.forward (chop/nn/quantized/modules/linear.py:877-895). */
+int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_codes, const uint8_t *b_scales,
+                  void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status,
+                  void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,513 @@
+// D[M,N] = A[M,K] * B[N,K]^T (+ bias[N]) on the 5th-generation tensor cores of sm_100a.
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0 (one lane)  TMA producer: 128-byte-swizzled K-major tiles of A (128 rows) and B (BN rows) and, for the
+//                      block-scaled kind, the E8M0 scale chunks, into a 4-stage shared-memory ring (mbarrier
+//                      transaction counts signal arrival);
+//   warp 1 (one lane)  MMA issuer: tcgen05.mma (cta_group::1, M=128, N=BN, 32 bytes of K per instruction) with fp32
+//                      accumulators in tensor memory; tcgen05.commit releases ring slots and publishes finished
+//                      accumulators;
+//   warps 2..5         epilogue: tcgen05.ld the accumulator (each warp owns the 32 TMEM lanes of its quarter), add
+//                      the bias, convert and store to global memory.
+// Kinds: bf16 x bf16 (kind::f16), fp32 x fp32 rounded to tf32 (kind::tf32) and MXFP8 E4M3 x E4M3 with one E8M0
+// scale per 32 elements of K (kind::mxf8f6f4.block_scale).  The dense kinds double-buffer the accumulator
+// (2 x 256 TMEM columns) so that the epilogue of a tile overlaps the main loop of the next one; the block-scaled
+// kind needs TMEM columns for the scale factors and uses a single accumulator.
+//
+// No thread-block clusters and no multicast loads are used.  Every wait on an mbarrier is bounded: when it runs
+// out the CTA raises an abort flag, records an error code in the caller's status word, waits (bounded) for its own
+// bulk copies in flight, frees its tensor memory and returns.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "mxq.h"
+
+namespace mxq {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kRowBytes = 128;            // bytes of K per row per stage = one 128B swizzle atom
+constexpr int kTmemCols = 512;
+constexpr unsigned long long kTimeoutNs = 1000000000ull;  // 1 s per wait
+
+enum Kind { kBf16 = 0, kTf32 = 1, kMxf8 = 2 };
+
+// error codes written to the status word
+constexpr int kErrProducerWait = 1, kErrMmaWaitFull = 2, kErrMmaWaitAcc = 3, kErrEpilogueWait = 4;
+
+// ---- PTX wrappers -----------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out of time).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0xFFu) == 0) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > kTimeoutNs) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// shared-memory matrix descriptor: K-major tile of rows x 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// descriptor of a 32 x 16-byte scale-factor chunk (no swizzle, 8-row groups 128 bytes apart)
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+template <int kKind>
+__device__ __forceinline__ void umma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc, uint32_t sfa,
+                                     uint32_t sfb) {
+  if constexpr (kKind == kBf16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc)
+        : "memory");
+  } else if constexpr (kKind == kTf32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(acc)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// instruction descriptor: fp32 accumulate, K-major A and B, M = 128, N = BN
+template <int kKind, int BN>
+__device__ __forceinline__ uint32_t make_idesc() {
+  uint32_t d = ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  if constexpr (kKind == kBf16) d |= (1u << 4) | (1u << 7) | (1u << 10);   // D fp32, A bf16, B bf16
+  if constexpr (kKind == kTf32) d |= (1u << 4) | (2u << 7) | (2u << 10);   // D fp32, A tf32, B tf32
+  if constexpr (kKind == kMxf8) d |= (0u << 7) | (0u << 10) | (1u << 23);  // A, B E4M3; scales E8M0
+  return d;
+}
+
+template <int BN, bool kScaled>
+struct Layout {
+  static constexpr int kA = BM * kRowBytes;
+  static constexpr int kB = BN * kRowBytes;
+  static constexpr int kSfa = kScaled ? 512 : 0;
+  static constexpr int kSfb = kScaled ? (BN / 128) * 512 : 0;
+  static constexpr int kAB = kA + kB;                   // operand tiles of one stage; a multiple of 1024 bytes
+  static constexpr int kSf = kSfa + kSfb;               // scale chunks of one stage
+  static constexpr int kStage = kAB + kSf;              // bytes that arrive per stage (the transaction count)
+  static constexpr int kSfBase = kStages * kAB;         // scale chunks live after all operand tiles
+  static constexpr int kBarriers = kStages * kStage;    // full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+  static constexpr int kTotal = kBarriers + 16 * 8 + 16 + 1024;  // + tmem slot, abort flag, alignment slack
+};
+
+struct Params {
+  const uint8_t *sfa;   // scale factors of A in 512-byte chunks [rows/128][k/128] (block-scaled kind only)
+  const uint8_t *sfb;
+  void *d;
+  const void *bias;
+  int *status;
+  int M, N, K;          // K in elements
+  int k_chunks;         // ceil(K * element_size / 128)
+  int out_bf16;         // output element type: 1 bf16, 0 fp32
+  int bias_bf16;        // bias element type
+};
+
+template <int kKind, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  constexpr bool kScaled = kKind == kMxf8;
+  constexpr int kAccStages = kScaled ? 1 : (2 * BN <= kTmemCols ? 2 : 1);
+  constexpr int kSfCol = kAccStages * BN;        // first TMEM column of the scale factors
+  constexpr int kSfColsPerStage = 4 + 4 * (BN / 128);
+  using L = Layout<BN, kScaled>;
+  constexpr int kElem = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
+  constexpr int kBlockK = kRowBytes / kElem;      // elements of K per stage
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t bar_base = s_base + L::kBarriers;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kBarriers + 16 * 8);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kBarriers + 16 * 8 + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), 1), mbar_init(empty_bar(s), 1);
+    for (int a = 0; a < 2; ++a) mbar_init(acc_full_bar(a), 1), mbar_init(acc_empty_bar(a), 4);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer ----------------
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t used = 0, last_phase = 0;  // per-stage bit masks for the exit path
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
+        for (int kc = 0; kc < p.k_chunks; ++kc) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = s_base + stage * L::kAB, sb = sa + L::kA;
+          const uint32_t ssf = s_base + L::kSfBase + stage * L::kSf;
+          mbar_expect_tx(full_bar(stage), L::kStage);
+          tma_load_2d(sa, &map_a, full_bar(stage), kc * kBlockK, m_blk * BM);
+          tma_load_2d(sb, &map_b, full_bar(stage), kc * kBlockK, n_blk * BN);
+          if constexpr (kScaled) {
+            bulk_load_1d(ssf, p.sfa + ((size_t)m_blk * p.k_chunks + kc) * 512, 512, full_bar(stage));
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)
+              bulk_load_1d(ssf + 512 + 512 * j, p.sfb + ((size_t)(n_blk * (BN / 128) + j) * p.k_chunks + kc) * 512, 512,
+                           full_bar(stage));
+          }
+          used |= 1u << stage;
+          last_phase = (last_phase & ~(1u << stage)) | (phase << stage);
+          if (++stage == kStages) stage = 0, phase ^= 1u;
+        }
+      }
+      if (*abort_flag) {
+        // let the copies that were already issued land before the CTA gives up its shared memory
+        for (int s = 0; s < kStages; ++s) {
+          if (!((used >> s) & 1u)) continue;
+          const unsigned long long t0 = global_ns();
+          while (!mbar_try_wait(full_bar(s), (last_phase >> s) & 1u) && global_ns() - t0 < 20000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ----------------
+      const uint32_t idesc = make_idesc<kKind, BN>();
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local % kAccStages;
+        const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kc = 0; kc < p.k_chunks; ++kc) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kErrMmaWaitFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = s_base + stage * L::kAB, sb = sa + L::kA;
+          const uint64_t da = desc_sw128(sa), db = desc_sw128(sb);
+          uint32_t sfa_t = 0, sfb_t = 0;
+          if constexpr (kScaled) {
+            const uint32_t ssf = s_base + L::kSfBase + stage * L::kSf;
+            sfa_t = tmem_base + (uint32_t)(kSfCol + stage * kSfColsPerStage);
+            sfb_t = sfa_t + 4;
+            tc_cp_sf(sfa_t, desc_sf(ssf));
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) tc_cp_sf(sfb_t + 4 * j, desc_sf(ssf + 512 + 512 * j));
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // 32 bytes of K per instruction: advance the start-address field (16-byte units) inside the swizzle atom
+            uint32_t id = idesc;
+            if constexpr (kScaled) id |= ((uint32_t)k << 29) | ((uint32_t)k << 4);  // byte k of each scale word
+            umma<kKind>(d_tmem, da + 2u * k, db + 2u * k, id, (kc | k) != 0 ? 1u : 0u, sfa_t, sfb_t);
+          }
+          tc_commit(empty_bar(stage));  // arrives when the MMAs that read this slot have completed
+          if (++stage == kStages) stage = 0, phase ^= 1u;
+        }
+        if (ok) tc_commit(acc_full_bar(acc));
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quarter = warp & 3;  // TMEM lanes [32 * quarter, +32) are the ones this warp may read
+    int local = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+      const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
+      const int acc = local % kAccStages;
+      const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
+      if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait)) break;
+      tc_fence_after();
+      const int row = m_blk * BM + quarter * 32 + lane;
+      const int n0 = n_blk * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        if (n0 + c >= p.N) break;  // uniform across the warp
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c), v);
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = n0 + c + j;
+            float b = 0.f;
+            if (n < p.N)
+              b = p.bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.bias)[n])
+                              : reinterpret_cast<const float *>(p.bias)[n];
+            v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
+          }
+        }
+        if (row < p.M) {
+          const bool full = n0 + c + 32 <= p.N;
+          if (p.out_bf16) {
+            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.d) + (size_t)row * p.N + n0 + c;
+            if (full && (p.N & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * t]), __uint_as_float(v[j + 2 * t + 1]));
+                  w[t] = *reinterpret_cast<uint32_t *>(&h);
+                }
+                *reinterpret_cast<uint4 *>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            } else {
+              for (int j = 0; j < 32 && n0 + c + j < p.N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            }
+          } else {
+            float *dst = reinterpret_cast<float *>(p.d) + (size_t)row * p.N + n0 + c;
+            if (full && (p.N & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4 *>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+              for (int j = 0; j < 32 && n0 + c + j < p.N; ++j) dst[j] = __uint_as_float(v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// tensor map of a K-major matrix [rows, k] with boxes of box_rows x 128 bytes, 128-byte swizzle, zero fill
+static int make_map(CUtensorMap *map, const void *ptr, int kind, int64_t rows, int64_t k, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return MXQ_ERR_UNSUPPORTED;
+  const int es = kind == kBf16 ? 2 : (kind == kTf32 ? 4 : 1);
+  const CUtensorMapDataType dt = kind == kBf16  ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : kind == kTf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k * es};
+  cuuint32_t box[2] = {(cuuint32_t)(kRowBytes / es), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_LAUNCH;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int kKind, int BN>
+static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
+                  int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, cudaStream_t st) {
+  using L = Layout<BN, kKind == kMxf8>;
+  constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, kKind, M, K, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, b, kKind, N, K, BN);
+  if (rc) return rc;
+  Params p;
+  p.sfa = sfa, p.sfb = sfb, p.d = d, p.bias = bias, p.status = status;
+  p.M = (int)M, p.N = (int)N, p.K = (int)K;
+  p.k_chunks = (int)((K * es + kRowBytes - 1) / kRowBytes);
+  p.out_bf16 = out_dtype == MXQ_BF16, p.bias_bf16 = bias_dtype == MXQ_BF16;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
+        cudaSuccess)
+      return MXQ_ERR_LAUNCH;
+    attr_set = true;
+  }
+  const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  umma_gemm_kernel<kKind, BN><<<grid, kThreads, L::kTotal, st>>>(ma, mb, p);
+  return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
+}
+
+}  // namespace gemm
+}  // namespace mxq
+
+using namespace mxq::gemm;
+
+extern "C" {
+
+int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k) {
+  if (rows < 0 || k < 0) return MXQ_ERR_SHAPE;
+  const int64_t row_chunks = ((rows + 255) / 256) * 2;  // padded to whole 256-row tiles
+  const int64_t k_chunks = (k + 127) / 128;
+  return row_chunks * k_chunks * 512;
+}
+
+int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int in_dtype, int out_dtype, int bias_dtype,
+                   int64_t M, int64_t N, int64_t K, int *status, void *stream) {
+  if (M == 0 || N == 0) return MXQ_OK;
+  if (!a || !b || !d) return MXQ_ERR_NULL;
+  if (M < 0 || N < 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return MXQ_ERR_SHAPE;
+  if (out_dtype != MXQ_F32 && out_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
+  if (bias && bias_dtype != MXQ_F32 && bias_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d)) & 15u)
+    return MXQ_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (in_dtype == MXQ_BF16) {
+    if (K % 8) return MXQ_ERR_SHAPE;  // rows must be 16-byte multiples for the tensor map
+    return launch<kBf16, 256>(a, b, nullptr, nullptr, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+  }
+  if (in_dtype == MXQ_F32) {
+    if (K % 4) return MXQ_ERR_SHAPE;
+    return launch<kTf32, 256>(a, b, nullptr, nullptr, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+  }
+  return MXQ_ERR_DTYPE;
+}
+
+int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_codes, const uint8_t *b_scales,
+                  void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status,
+                  void *stream) {
+  if (M == 0 || N == 0) return MXQ_OK;
+  if (!a_codes || !a_scales || !b_codes || !b_scales || !d) return MXQ_ERR_NULL;
+  if (M < 0 || N < 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || K % 32) return MXQ_ERR_SHAPE;
+  if (out_dtype != MXQ_F32 && out_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
+  if (bias && bias_dtype != MXQ_F32 && bias_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
+  if ((reinterpret_cast<uintptr_t>(a_codes) | reinterpret_cast<uintptr_t>(b_codes) | reinterpret_cast<uintptr_t>(d) |
+       reinterpret_cast<uintptr_t>(a_scales) | reinterpret_cast<uintptr_t>(b_scales)) & 15u)
+    return MXQ_ERR_ALIGN;
+  return launch<kMxf8, 256>(a_codes, b_codes, a_scales, b_scales, d, bias, out_dtype, bias_dtype, M, N, K, status,
+                            (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -10,6 +10,8 @@
 // Generic path: any other block size (smaller than a vector, not a power of two, wider than a warp's
 // span, or a ragged row tail for block-fp) is handled by one thread per block with scalar accesses.
 
+#include <cuda_fp8.h>
+
 #include "mxq_common.cuh"
 
 namespace mxq {
@@ -266,6 +268,124 @@ mxfp_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, uint8_t *__restrict
           if ((threadIdx.x & (group - 1)) == 0) scales[i / group] = (uint8_t)p.scale;
         }
       }
+    }
+  }
+}
+
+// Operands for the block-scaled tensor-core GEMM: blocks of 32 along K of a [rows, K] matrix.
+//   codes  : one hardware E4M3 byte per element, row-major [rows, K];
+//   scales : E8M0 bytes in chunks of 512 bytes per (128 rows x 128 columns of K), chunk (r/128, k/128) at
+//            ((r/128) * ceil(K/128) + k/128) * 512, byte (r%32)*16 + ((r%128)/32)*4 + (k%128)/32 inside a chunk --
+//            the arrangement tcgen05.cp (32x128b.warpx4) moves into tensor memory unchanged.
+// Every element keeps the exact value of the reference's (E, F) code times its scale: minifloat formats with
+// E <= 4 and F <= 3 are subsets of E4M3.  One exception: the reference's E4M3 uses the top code (480) as a
+// number, which is NaN to the hardware.  A block that contains it is stored one binade lower with its scale
+// raised by one; only elements of the two lowest binades of such a block can round (by at most 2**-16 of the
+// block maximum).
+template <typename Tin, int E, int F>
+__global__ void __launch_bounds__(kThreads)
+mxfp_pack_mma_kernel(const Tin *__restrict__ x, uint8_t *__restrict__ codes, uint8_t *__restrict__ scales, int64_t n_vec,
+                     int64_t k_elems, int64_t k_chunks, const __grid_constant__ Log2Tab tab) {
+  constexpr int N = Elem<Tin>::kVec;
+  constexpr bool kBf16In = Elem<Tin>::kBf16;
+  constexpr int kGroup = 32 / N;
+  constexpr int kTop = (1 << E) - 1;
+  constexpr int kBias = (1 << (E - 1)) - 1;
+  constexpr int kEmax = kTop - kBias;
+  const uint4 *xv = reinterpret_cast<const uint4 *>(x);
+  const int64_t step = (int64_t)gridDim.x * kThreads;
+  // whole warps iterate together (the bound is rounded up), so the shuffles below are always convergent
+  const int64_t n_round = (n_vec + 31) & ~(int64_t)31;
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n_round; i += step) {
+    const uint4 raw = i < n_vec ? ld_stream(xv + i) : make_uint4(0, 0, 0, 0);
+    const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t a[4], amax;
+    if constexpr (kBf16In) {
+      uint32_t m = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        a[k] = r[k] & 0x7FFF7FFFu;
+        m = max(m, max(a[k] & 0xFFFFu, a[k] >> 16));
+      }
+      m = group_max(m, kGroup);
+      amax = (m >> 7) ? (m << 16) : 0u;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) a[k] = r[k] & 0x7FFFFFFFu;
+      const uint32_t m = group_max(max(max(a[0], a[1]), max(a[2], a[3])), kGroup);
+      amax = (m >> 23) ? m : 0u;
+    }
+    const int exm = (int)(amax >> 23);
+    int up = 0;
+    if constexpr (!kBf16In) {
+      const uint32_t man = amax & 0x7FFFFFu;
+      if (man >= 0x7FFF00u) up = (0x7FFFFFu - man) < tab.t[exm] ? 1 : 0;
+    }
+    const int K = exm + up - kTop;
+    bool fast = K >= 1;
+    if constexpr (kBf16In) {
+      const uint32_t t1 = (uint32_t)((K + 1) << 7) * 0x00010001u;
+      const __nv_bfloat162 t1v = *reinterpret_cast<const __nv_bfloat162 *>(&t1);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) fast = fast && __hbge2(*reinterpret_cast<const __nv_bfloat162 *>(&a[k]), t1v);
+    } else {
+      const uint32_t t1 = (uint32_t)(K + 1) << 23;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) fast = fast && a[k] >= t1;
+    }
+    float v[N];  // element values in units of the block scale
+    int scale;
+    if (fast) {
+      const int sh = exm + up - 127 - kEmax;
+      scale = sh + 127;
+      const uint32_t shb = (uint32_t)sh << 23;
+      if constexpr (kBf16In) {
+        const uint32_t kodd2 = (K & 1) ? 0x00800080u : 0u;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t w = mxfp_round_pair<F>(a[k], kodd2) | (r[k] & 0x80008000u);
+          v[2 * k] = __uint_as_float((w << 16) - shb), v[2 * k + 1] = __uint_as_float((w & 0xFFFF0000u) - shb);
+        }
+      } else {
+        const uint32_t kodd = (K & 1) ? 0x00800000u : 0u;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          v[k] = __uint_as_float((mxfp_round_one<F>(a[k] & 0x7FFFFF00u, kodd) | (r[k] & 0x80000000u)) - shb);
+      }
+    } else {
+      uint32_t b[N];
+      unpack(raw, b);
+      const MxfpBlock p = mxfp_block(amax, E, tab);
+      scale = p.scale;
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        if (((b[k] & 0x7FFFFFFFu) >> 23) == 0) b[k] = 0;
+        v[k] = mxfp_decode(mxfp_encode(b[k], p.sh, E, F), E, F);
+      }
+    }
+    if constexpr (E == 4 && F == 3) {
+      int top = 0;
+#pragma unroll
+      for (int k = 0; k < N; ++k) top |= fabsf(v[k]) > 448.f ? 1 : 0;
+      for (int o = 1; o < kGroup; o <<= 1) top |= __shfl_xor_sync(0xFFFFFFFFu, top, o);
+      if (top) {
+        scale += 1;
+#pragma unroll
+        for (int k = 0; k < N; ++k) v[k] *= 0.5f;
+      }
+    }
+    if (i >= n_vec) continue;
+    uint32_t c[N];
+#pragma unroll
+    for (int k = 0; k < N; k += 2) {
+      const uint32_t two = __nv_cvt_float2_to_fp8x2(make_float2(v[k], v[k + 1]), __NV_SATFINITE, __NV_E4M3);
+      c[k] = two & 0xFFu, c[k + 1] = two >> 8;
+    }
+    store_bytes(codes, i * N, c);
+    if ((threadIdx.x & (kGroup - 1)) == 0) {
+      const int64_t e0 = i * N, row = e0 / k_elems, kb = (e0 % k_elems) >> 5;
+      scales[((row >> 7) * k_chunks + (kb >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kb & 3)] =
+          (uint8_t)scale;
     }
   }
 }
@@ -577,6 +697,37 @@ int mxq_mxfp_extract(const void *x, uint8_t *codes, uint8_t *scales, int in_dtyp
     return launch_mxfp<__nv_bfloat16, float, Mode::kCodes>(x, nullptr, codes, scales, n_blocks, block, E, F, tab,
                                                            (cudaStream_t)stream);
   return MXQ_ERR_DTYPE;
+}
+
+int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k, int E, int F,
+                      const uint8_t *floor_tab_host, void *stream) {
+  if (rows == 0 || k == 0) return MXQ_OK;
+  if (!x || !codes || !scales_mma || !floor_tab_host) return MXQ_ERR_NULL;
+  if (rows < 0 || k < 0 || k % 32) return MXQ_ERR_SHAPE;
+  if (!legal_ef(E, F) || E > 4 || F > 3) return MXQ_ERR_FORMAT;
+  if (!aligned16(x) || !aligned16(codes)) return MXQ_ERR_ALIGN;
+  const Log2Tab tab = load_tab(floor_tab_host);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t k_chunks = (k + 127) / 128;
+  const int64_t sf_bytes = ((rows + 255) / 256) * 2 * k_chunks * 512;
+  if (cudaMemsetAsync(scales_mma, 0, sf_bytes, st) != cudaSuccess) return MXQ_ERR_LAUNCH;  // padding reads as 2**-127
+#define MXQ_PACK(TI, e, f)                                                                                      \
+  if (E == e && F == f) {                                                                                       \
+    const int64_t n_vec = rows * k / Elem<TI>::kVec;                                                            \
+    mxfp_pack_mma_kernel<TI, e, f><<<grid_for(n_vec, kThreads), kThreads, 0, st>>>((const TI *)x, codes, scales_mma, \
+                                                                                  n_vec, k, k_chunks, tab);     \
+    return check_launch();                                                                                      \
+  }
+  if (in_dtype == MXQ_F32) {
+    MXQ_PACK(float, 4, 3) MXQ_PACK(float, 2, 3) MXQ_PACK(float, 3, 2) MXQ_PACK(float, 2, 1) MXQ_PACK(float, 1, 2)
+  } else if (in_dtype == MXQ_BF16) {
+    MXQ_PACK(__nv_bfloat16, 4, 3) MXQ_PACK(__nv_bfloat16, 2, 3) MXQ_PACK(__nv_bfloat16, 3, 2)
+    MXQ_PACK(__nv_bfloat16, 2, 1) MXQ_PACK(__nv_bfloat16, 1, 2)
+  } else {
+    return MXQ_ERR_DTYPE;
+  }
+#undef MXQ_PACK
+  return MXQ_ERR_FORMAT;
 }
 
 int mxq_mxfp_compose(const uint8_t *codes, const uint8_t *scales, void *y, int out_dtype, int64_t n_blocks, int block,

@@ -1,18 +1,155 @@
-"""y = x @ W^T (+ bias) for operands that already hold quantized values.
+"""Forward GEMM of the quantized Linear modules on the tcgen05 tensor cores (libmxq, include/mxq.h).
 
-The operands of the quantized Linear modules are fake-quantized tensors: every value is a minifloat /
-integer mantissa times a power of two and is exactly representable in bf16 (and fp32), so products are
-exact and only the fp32 accumulation order differs from the reference's `F.linear`
-(chop/nn/quantized/modules/linear.py:895, :972).
+`linear_forward(x, weight, bias)` replaces the `F.linear` at the end of LinearMXFP / LinearMXInt / linearBlockFP
+(chop/nn/quantized/modules/linear.py:895, :972; chop/nn/quantized/functional/linear.py:278).  Its operands already
+hold quantized values: every value is a small-significand number times a power of two, exactly representable in
+bf16 (and in tf32 for fp32 tensors), so products are exact and only the fp32 accumulation order differs from the
+reference.
+
+`MXOperand` / `mx_linear` are the block-scaled path: the operands stay as E4M3 codes with one E8M0 scale per 32
+elements of K and are multiplied by `tcgen05.mma.kind::mxf8f6f4.block_scale`.
 """
 
 from __future__ import annotations
 
+import os
+from dataclasses import dataclass
+
 import torch
 from torch import Tensor
 
+from . import _lib
+from .quantizers import _DT, _floor_tab_ptr, _on_device, _require_cuda, _stream
+
+_STATUS: dict[int, Tensor] = {}
+_CHECK_EVERY_CALL = os.environ.get("MXQ_CHECK_STATUS", "0") == "1"
+
+_STATUS_TEXT = {
+    1: "TMA producer: wait for a free shared-memory slot ran out",
+    2: "MMA issuer: wait for an operand tile ran out",
+    3: "MMA issuer: wait for a free accumulator ran out",
+    4: "epilogue: wait for a finished accumulator ran out",
+}
+
+
+def _status(device: torch.device) -> Tensor:
+    t = _STATUS.get(device.index)
+    if t is None:
+        t = _STATUS[device.index] = torch.zeros(1, dtype=torch.int32, device=device)
+    return t
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if a GEMM kernel on `device` reported that one of its bounded waits ran out."""
+    devices = list(_STATUS) if device is None else [torch.device(device).index or 0]
+    for idx in devices:
+        t = _STATUS.get(idx)
+        if t is None:
+            continue
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise _lib.MxqError(f"GEMM kernel on cuda:{idx} gave up: {_STATUS_TEXT.get(code, code)}")
+
+
+def _bias_args(bias: Tensor | None):
+    if bias is None:
+        return None, 0
+    if bias.dtype not in _DT:
+        raise NotImplementedError(f"bias dtype {bias.dtype} is not supported")
+    return bias.contiguous(), _DT[bias.dtype]
+
 
 def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None) -> Tensor:
-    if not x.is_cuda:
-        raise RuntimeError("mase_b200 runs on CUDA devices only (no CPU fallback)")
-    return torch.nn.functional.linear(x, weight, bias)
+    """x[..., K] @ weight[N, K]^T + bias, output in x.dtype; bf16 operands use kind::f16, fp32 operands kind::tf32."""
+    _require_cuda(x, "linear_forward")
+    if x.dtype != weight.dtype:
+        raise RuntimeError(f"expected input and weight to have the same dtype, got {x.dtype} and {weight.dtype}")
+    if x.dtype not in _DT:
+        raise NotImplementedError(f"linear_forward: dtype {x.dtype} is not supported (float32 and bfloat16 are)")
+    N, K = weight.shape
+    if x.shape[-1] != K:
+        raise RuntimeError(f"mat1 and mat2 shapes cannot be multiplied ({tuple(x.shape)} and {K}x{N})")
+    lead = x.shape[:-1]
+    a = x.reshape(-1, K)
+    if not a.is_contiguous() or a.data_ptr() % 16:
+        a = a.contiguous().clone() if a.data_ptr() % 16 else a.contiguous()
+    w = weight if weight.is_contiguous() else weight.contiguous()
+    M = a.shape[0]
+    need = 8 if x.dtype == torch.bfloat16 else 4
+    if K % need:
+        # rows must be multiples of 16 bytes for the tensor maps: pad K with zeros (contributes nothing)
+        pad = need - K % need
+        a = torch.nn.functional.pad(a, (0, pad))
+        w = torch.nn.functional.pad(w, (0, pad))
+        K += pad
+    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    b, bdt = _bias_args(bias)
+    st = _status(x.device)
+    with _on_device(x):
+        rc = _lib.lib().mxq_gemm_dense(a.data_ptr(), w.data_ptr(), out.data_ptr(), 0 if b is None else b.data_ptr(),
+                                       _DT[x.dtype], _DT[x.dtype], bdt, M, N, K, st.data_ptr(), _stream(x))
+    _lib.check(rc, "mxq_gemm_dense")
+    if _CHECK_EVERY_CALL:
+        check_status(x.device)
+    return out.reshape(*lead, N)
+
+
+@dataclass
+class MXOperand:
+    """A [rows, K] matrix as tensor-core operands: hardware E4M3 bytes and E8M0 scales in the MMA chunk layout."""
+
+    codes: Tensor   # uint8 [rows, K]
+    scales: Tensor  # uint8 [mxq_mma_scale_bytes(rows, K)]
+    rows: int
+    k: int
+
+
+def mma_supported(exp_bits: int, frac_bits: int, block_size: int, k: int) -> bool:
+    """Formats the block-scaled GEMM can take: every value must be an E4M3 number, blocks of 32 along K."""
+    return block_size == 32 and exp_bits <= 4 and frac_bits <= 3 and k % 32 == 0
+
+
+def pack_mx_operand(x: Tensor, exp_bits: int, frac_bits: int) -> MXOperand:
+    """MXFP(exp_bits, frac_bits), block 32 along the last dim, of a 2-D tensor, stored for the tensor cores."""
+    _require_cuda(x, "pack_mx_operand")
+    if x.dtype not in _DT:
+        raise NotImplementedError(f"pack_mx_operand: dtype {x.dtype} is not supported")
+    assert x.dim() == 2
+    rows, k = x.shape
+    if not mma_supported(exp_bits, frac_bits, 32, k):
+        raise NotImplementedError("block-scaled operands need E <= 4, F <= 3 and K divisible by 32")
+    xc = x.contiguous()
+    if xc.data_ptr() % 16:
+        xc = xc.clone()
+    lib = _lib.lib()
+    codes = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((int(lib.mxq_mma_scale_bytes(rows, k)),), dtype=torch.uint8, device=x.device)
+    with _on_device(x):
+        rc = lib.mxq_mxfp_pack_mma(xc.data_ptr(), codes.data_ptr(), scales.data_ptr(), _DT[x.dtype], rows, k, exp_bits,
+                                   frac_bits, _floor_tab_ptr(), _stream(x))
+    _lib.check(rc, "mxq_mxfp_pack_mma")
+    return MXOperand(codes, scales, rows, k)
+
+
+def mx_gemm(a: MXOperand, b: MXOperand, bias: Tensor | None, out_dtype: torch.dtype) -> Tensor:
+    """[a.rows, b.rows] = a @ b^T (+ bias) with block-scaled MXFP8 tensor-core MMAs, fp32 accumulation."""
+    assert a.k == b.k
+    out = torch.empty((a.rows, b.rows), dtype=out_dtype, device=a.codes.device)
+    bb, bdt = _bias_args(bias)
+    st = _status(a.codes.device)
+    with _on_device(a.codes):
+        rc = _lib.lib().mxq_gemm_mxf8(a.codes.data_ptr(), a.scales.data_ptr(), b.codes.data_ptr(), b.scales.data_ptr(),
+                                      out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[out_dtype], bdt, a.rows,
+                                      b.rows, a.k, st.data_ptr(), _stream(a.codes))
+    _lib.check(rc, "mxq_gemm_mxf8")
+    if _CHECK_EVERY_CALL:
+        check_status(a.codes.device)
+    return out
+
+
+def mx_linear(x: Tensor, weight: MXOperand, bias: Tensor | None, exp_bits: int, frac_bits: int) -> Tensor:
+    """Quantize x[..., K] to MXFP(exp_bits, frac_bits) along K and multiply with a packed weight."""
+    lead = x.shape[:-1]
+    a = pack_mx_operand(x.reshape(-1, x.shape[-1]), exp_bits, frac_bits)
+    return mx_gemm(a, weight, bias, x.dtype).reshape(*lead, weight.rows)

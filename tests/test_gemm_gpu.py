@@ -1,0 +1,107 @@
+"""Tensor-core GEMMs (through the C ABI) against fp32 references built from the oracle-quantized operands."""
+
+import pytest
+import torch
+
+import mase_b200 as mb
+from mase_b200 import gemm, synthetic
+from oracle import mx_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+REL_TOL = 1e-3  # max |err| / max |ref|, the bar for fp32 accumulation-order differences
+
+
+def rel_err(y, ref):
+    return float((y.float().cpu() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+
+
+def quantized_operands(M, K, N, seed, dtype):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    x[:, :: max(1, K // 7)] *= 30
+    w = torch.randn(N, K, generator=g) * 0.02
+    xq = O.mxfp_fake(x.to(dtype), 32, 4, 3) if K % 32 == 0 else O.mxint_fake(x.to(dtype), 8, 8)
+    wq = O.mxfp_fake(w.to(dtype), 32, 4, 3) if K % 32 == 0 else O.mxint_fake(w.to(dtype), 8, 8)
+    return xq, wq
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 256), (128, 256, 256), (256, 512, 512), (1, 128, 256), (77, 192, 384),
+                                   (300, 4096, 1000), (128, 72, 256), (2048, 1024, 4096)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_dense_gemm_matches_fp32_reference(shape, dtype):
+    M, K, N = shape
+    xq, wq = quantized_operands(M, K, N, seed=M + K + N, dtype=dtype)
+    ref = xq.float() @ wq.float().t()
+    y = gemm.linear_forward(xq.to(DEV), wq.to(DEV), None)
+    gemm.check_status()
+    assert y.dtype == dtype and y.shape == (M, N)
+    tol = REL_TOL if dtype == torch.float32 else 4e-3  # bf16 output rounding: half an ulp = 2**-9 of the value
+    assert rel_err(y, ref) <= tol
+    if dtype == torch.bfloat16:  # at most one bf16 ulp from the rounded fp32 reference
+        ulp = (y.float().cpu() - ref.bfloat16().float()).abs() / ref.abs().clamp_min(1e-6)
+        big = ref.abs() > 1e-3 * ref.abs().max()
+        assert float(ulp[big].max()) <= 2.0 ** -7
+
+
+def test_dense_gemm_bias_and_leading_dims():
+    g = torch.Generator().manual_seed(5)
+    x = O.mxint_fake(torch.randn(2, 3, 40, 128, generator=g).bfloat16(), 32, 8)
+    w = O.mxint_fake((torch.randn(96, 128, generator=g) * 0.05).bfloat16(), 32, 8)
+    b = torch.randn(96, generator=g).bfloat16()
+    ref = torch.nn.functional.linear(x.float(), w.float(), b.float())
+    y = gemm.linear_forward(x.to(DEV), w.to(DEV), b.to(DEV))
+    gemm.check_status()
+    assert y.shape == (2, 3, 40, 96)
+    assert rel_err(y, ref) <= 4e-3
+    y32 = gemm.linear_forward(x.float().to(DEV), w.float().to(DEV), b.float().to(DEV))
+    assert rel_err(y32, ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 256), (128, 512, 256), (256, 4096, 512), (1, 4096, 4096), (16, 4096, 4096),
+                                   (200, 1024, 640), (2048, 4096, 4096)])
+def test_mxf8_gemm_matches_oracle(shape):
+    """Block-scaled GEMM of MXFP8-quantized activations and weights vs fp32 GEMM of the oracle's fake-quant values."""
+    M, K, N = shape
+    x, w = synthetic.linear_operands(M, K, N, seed=2)
+    ref = O.mxfp_fake(x, 32, 4, 3).float() @ O.mxfp_fake(w, 32, 4, 3, 1).float().t()
+    wp = gemm.pack_mx_operand(w.to(DEV), 4, 3)
+    y = gemm.mx_linear(x.to(DEV), wp, None, 4, 3)
+    gemm.check_status()
+    assert y.shape == (M, N) and y.dtype == torch.bfloat16
+    assert rel_err(y, ref) <= 4e-3
+    xp = gemm.pack_mx_operand(x.to(DEV), 4, 3)
+    y32 = gemm.mx_gemm(xp, wp, None, torch.float32)
+    gemm.check_status()
+    assert rel_err(y32, ref) <= REL_TOL
+
+
+def test_mxf8_pack_round_trip():
+    """Packed codes * scales reproduce the oracle's fake-quant values (up to the documented re-encoding of blocks
+    that hold the reference's top E4M3 code)."""
+    x, _ = synthetic.linear_operands(300, 1024, 32, seed=2)
+    op = gemm.pack_mx_operand(x.to(DEV), 4, 3)
+    codes = op.codes.cpu().view(torch.float8_e4m3fn).float()
+    sc = op.scales.cpu()
+    rows, k = 300, 1024
+    r = torch.arange(rows).view(-1, 1)
+    kb = torch.arange(k // 32).view(1, -1)
+    idx = ((r // 128) * ((k + 127) // 128) + kb // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + (kb % 4)
+    s = sc[idx.flatten()].view(rows, k // 32).float() - 127
+    y = (codes.view(rows, k // 32, 32) * torch.exp2(s).unsqueeze(-1)).view(rows, k)
+    ref = O.mxfp_fake(x, 32, 4, 3).float()
+    assert not torch.isnan(codes).any()
+    blockmax = ref.view(rows, -1, 32).abs().amax(-1, keepdim=True).clamp_min(1e-30)
+    err = ((y - ref).view(rows, -1, 32).abs() / blockmax).max()
+    assert float(err) <= 2.0 ** -15
+    assert float((y != ref).float().mean()) < 1e-3
+
+
+def test_mxfp4_weight_mxfp8_activation():
+    M, K, N = 256, 1024, 512
+    x, w = synthetic.linear_operands(M, K, N, seed=4)
+    ref = O.mxfp_fake(x, 32, 4, 3).float() @ O.mxfp_fake(w, 32, 2, 1, 1).float().t()
+    wp = gemm.pack_mx_operand(w.to(DEV), 2, 1)
+    y = gemm.mx_gemm(gemm.pack_mx_operand(x.to(DEV), 4, 3), wp, None, torch.float32)
+    gemm.check_status()
+    assert rel_err(y, ref) <= REL_TOL
