@@ -235,6 +235,38 @@ def extras(device, x) -> dict:
         xx = synthetic.student_t3(*shape, seed=1).to(device)
         g = quick_gbs(lambda: mb.mxfp_quantizer(xx, 32, 4, 3), xx.numel() * 4, calls=50)
         out[f"mxfp8_bf16_{shape[0]}x{shape[1]}_us"] = xx.numel() * 4 / g / 1e3
+    out["linear_mxfp8_4096x4096"] = linear_extras(device)
+    return out
+
+
+def linear_extras(device) -> dict:
+    """MXFP8 Linear forward 4096 -> 4096 (bf16, no bias): activation quantization + block-scaled tcgen05 GEMM."""
+    import mase_b200 as mb
+    from mase_b200 import gemm, synthetic
+
+    K = N = 4096
+    cfg = {"weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3,
+           "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    out = {}
+    layer = None
+    for M in (1, 16, 128, 2048, 8192):
+        x, w = synthetic.linear_operands(M, K, N, seed=2)
+        x = x.to(device)
+        if layer is None:
+            layer = mb.LinearMXFP(K, N, bias=False, device=device, dtype=torch.bfloat16, config=cfg)
+            layer.load_state_dict({"weight": w.to(device)}, strict=False)
+        flops = 2.0 * M * N * K
+        calls = 20 if M >= 2048 else 50
+        t_fwd = 1.0 / quick_gbs(lambda: layer(x), 1, calls=calls) / 1e9   # seconds per call
+        xp = gemm.pack_mx_operand(x, 4, 3)
+        wp = layer._packed_weight()
+        t_gemm = 1.0 / quick_gbs(lambda: gemm.mx_gemm(xp, wp, None, torch.bfloat16), 1, calls=calls) / 1e9
+        xq = mb.mxfp_quantizer(x, 32, 4, 3)
+        t_dense = 1.0 / quick_gbs(lambda: gemm.linear_forward(xq, layer.weight, None), 1, calls=calls) / 1e9
+        out[f"M{M}"] = {"forward_us": t_fwd * 1e6, "forward_TFLOPs": flops / t_fwd / 1e12,
+                        "gemm_only_us": t_gemm * 1e6, "gemm_only_TFLOPs": flops / t_gemm / 1e12,
+                        "bf16_gemm_of_fake_quant_us": t_dense * 1e6, "bf16_gemm_TFLOPs": flops / t_dense / 1e12}
+    gemm.check_status()
     return out
 
 

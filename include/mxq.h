@@ -129,6 +129,15 @@ int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t
                   void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status,
                   void *stream);
 
+/* LinearMXFP.forward in one call (chop/nn/quantized/modules/linear.py:877-895): quantize x[M,K] to MXFP(E,F),
+ * block 32 along K, into `workspace` (scratch owned by the caller, 256-byte aligned, at least
+ * mxq_mx_linear_workspace_bytes(M, K) bytes), then D = x_q * W_q^T (+ bias) with the block-scaled GEMM.
+ * w_codes / w_scales come from mxq_mxfp_pack_mma on the [N,K] weight. */
+int64_t mxq_mx_linear_workspace_bytes(int64_t M, int64_t K);
+int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d, const void *bias,
+                  int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
+                  const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

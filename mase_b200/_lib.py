@@ -28,6 +28,9 @@ _PROTOTYPES = {
     "mxq_mxfp_pack_mma": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p],
     "mxq_gemm_mxf8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
                       c_int64, c_void_p, c_void_p],
+    "mxq_mx_linear_workspace_bytes": [c_int64, c_int64],
+    "mxq_mx_linear": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64,
+                      c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
     "mxq_bfp_fake": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
 }
 
@@ -57,7 +60,7 @@ def lib():
         for name, argtypes in _PROTOTYPES.items():
             fn = getattr(handle, name)
             fn.argtypes = argtypes
-            fn.restype = c_int64 if name == "mxq_mma_scale_bytes" else c_int
+            fn.restype = c_int64 if name.endswith("_bytes") else c_int
         handle.mxq_error_string.argtypes = [c_int]
         handle.mxq_error_string.restype = c_char_p
         _lib = handle

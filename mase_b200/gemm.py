@@ -149,7 +149,29 @@ def mx_gemm(a: MXOperand, b: MXOperand, bias: Tensor | None, out_dtype: torch.dt
 
 
 def mx_linear(x: Tensor, weight: MXOperand, bias: Tensor | None, exp_bits: int, frac_bits: int) -> Tensor:
-    """Quantize x[..., K] to MXFP(exp_bits, frac_bits) along K and multiply with a packed weight."""
+    """Quantize x[..., K] to MXFP(exp_bits, frac_bits) along K and multiply with a packed weight (one C call;
+    the packed activations live in a scratch tensor allocated here)."""
+    _require_cuda(x, "mx_linear")
+    if x.dtype not in _DT:
+        raise NotImplementedError(f"mx_linear: dtype {x.dtype} is not supported")
+    K = x.shape[-1]
+    assert K == weight.k
     lead = x.shape[:-1]
-    a = pack_mx_operand(x.reshape(-1, x.shape[-1]), exp_bits, frac_bits)
-    return mx_gemm(a, weight, bias, x.dtype).reshape(*lead, weight.rows)
+    a = x.reshape(-1, K)
+    if not a.is_contiguous() or a.data_ptr() % 16:
+        a = a.contiguous().clone() if a.data_ptr() % 16 else a.contiguous()
+    M, N = a.shape[0], weight.rows
+    lib = _lib.lib()
+    ws_bytes = int(lib.mxq_mx_linear_workspace_bytes(M, K))
+    ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=x.device)
+    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    bb, bdt = _bias_args(bias)
+    st = _status(x.device)
+    with _on_device(x):
+        rc = lib.mxq_mx_linear(a.data_ptr(), _DT[x.dtype], weight.codes.data_ptr(), weight.scales.data_ptr(),
+                               out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[x.dtype], bdt, M, N, K, exp_bits,
+                               frac_bits, _floor_tab_ptr(), ws.data_ptr(), ws_bytes, st.data_ptr(), _stream(x))
+    _lib.check(rc, "mxq_mx_linear")
+    if _CHECK_EVERY_CALL:
+        check_status(x.device)
+    return out.reshape(*lead, N)

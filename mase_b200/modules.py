@@ -15,7 +15,7 @@ from functools import partial
 import torch
 from torch import Tensor
 
-from .gemm import linear_forward
+from .gemm import MXOperand, linear_forward, mma_supported, mx_linear, pack_mx_operand
 from .quantizers import block_fp_quantizer, mxfp_quantizer, mxint_quantizer
 
 
@@ -46,6 +46,7 @@ class LinearMXFP(_LinearBase):
         if self.bypass or self.gptq:
             return result
         cfg = self.config
+        self._pack_weight_for_tensor_cores()  # from the unquantized weight: quantizing twice is not idempotent
         self.weight.data.copy_(
             mxfp_quantizer(
                 self.weight.data,
@@ -63,6 +64,37 @@ class LinearMXFP(_LinearBase):
             )
         return result
 
+    def _pack_weight_for_tensor_cores(self) -> None:
+        """Keep the weight's MXFP codes and scales as block-scaled MMA operands next to the fake-quantized
+        `weight` (which stays in the state_dict exactly as the reference stores it).  Only when both the weight
+        and the activation format fit the block-scaled MMA; otherwise forward multiplies the fake-quantized
+        tensors.  The copy is tied to the parameter's version counter: an in-place update of `weight` after
+        loading makes forward fall back to the fake-quantized tensors."""
+        cfg = self.config
+        self._mx_weight_version = None
+        for name in ("_mx_w_codes", "_mx_w_scales"):
+            if name in self._buffers:
+                del self._buffers[name]
+        w = self.weight.data
+        x_block, x_exp, x_frac = cfg.get("data_in_block_size"), cfg.get("data_in_exponent_width"), cfg.get("data_in_frac_width")
+        if not w.is_cuda or x_block is None or x_exp is None or x_frac is None:
+            return
+        if not (mma_supported(cfg["weight_exponent_width"], cfg["weight_frac_width"], cfg["weight_block_size"], w.shape[1])
+                and mma_supported(x_exp, x_frac, x_block, w.shape[1])):
+            return
+        op = pack_mx_operand(w, cfg["weight_exponent_width"], cfg["weight_frac_width"])
+        self.register_buffer("_mx_w_codes", op.codes, persistent=False)
+        self.register_buffer("_mx_w_scales", op.scales, persistent=False)
+        self._mx_weight_version = self.weight._version
+
+    def _packed_weight(self) -> MXOperand | None:
+        codes = self._buffers.get("_mx_w_codes")
+        if codes is None or getattr(self, "_mx_weight_version", None) != self.weight._version:
+            return None
+        if codes.device != self.weight.device:
+            return None
+        return MXOperand(codes, self._buffers["_mx_w_scales"], codes.shape[0], codes.shape[1])
+
     @torch.no_grad()
     def forward(self, x: Tensor) -> Tensor:
         if self.bypass:
@@ -70,6 +102,11 @@ class LinearMXFP(_LinearBase):
         cfg = self.config
         x_block, x_exp, x_frac = cfg.get("data_in_block_size"), cfg.get("data_in_exponent_width"), cfg.get("data_in_frac_width")
         if x_block is not None and x_exp is not None:
+            packed = self._packed_weight()
+            if packed is not None and x.is_cuda and x.dtype == self.weight.dtype:
+                # activations are quantized straight into tensor-core operands; same codes and scales as
+                # mxfp_quantizer, multiplied by tcgen05 block-scaled MMAs
+                return mx_linear(x, packed, self.bias, x_exp, x_frac)
             x = mxfp_quantizer(x, block_size=x_block, element_exp_bits=x_exp, element_frac_bits=x_frac, block_dim=-1)
         return linear_forward(x, self.weight, self.bias)
 

@@ -1,0 +1,116 @@
+"""Quantized Linear modules on the GPU against the reference's golden outputs and the CPU oracle."""
+
+import copy
+
+import pytest
+import torch
+
+import mase_b200 as mb
+from mase_b200 import gemm, synthetic
+from conftest import assert_bits_equal
+from oracle import mx_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+CLASSES = {"LinearMXFP": mb.LinearMXFP, "LinearMXInt": mb.LinearMXInt, "LinearBlockFP": mb.LinearBlockFP}
+
+
+def rel_err(y, ref):
+    return float((y.float().cpu() - ref.float()).abs().max() / ref.float().abs().max())
+
+
+def test_linear_modules_match_reference_golden(golden):
+    """Same constructor + load_state_dict route as the quantize pass; weights bit-exact, outputs within tolerance."""
+    for c in [c for c in golden.cases if c["kind"] == "linear"]:
+        dt, tag, cfg = c["dtype"], c["tag"], c["config"]
+        dtype = torch.float32 if dt == "fp32" else torch.bfloat16
+        x = golden.tensor(f"linear/{dt}/x").to(DEV)
+        state = {"weight": golden.tensor(f"linear/{dt}/w").to(DEV), "bias": golden.tensor(f"linear/{dt}/b").to(DEV)}
+        layer = CLASSES[c["cls"]](c["K"], c["N"], bias=True, device=DEV, dtype=dtype, config=dict(cfg))
+        layer.load_state_dict(copy.deepcopy(state), strict=False)
+        if c["cls"] != "LinearBlockFP":
+            assert_bits_equal(layer.weight.data, golden.tensor(tag + "/w_q"), tag + " w_q")
+            assert_bits_equal(layer.bias.data, golden.tensor(tag + "/b_q"), tag + " b_q")
+        y = layer(x)
+        gemm.check_status()
+        y_ref = golden.tensor(tag + "/y")
+        assert y.dtype == y_ref.dtype and y.shape == y_ref.shape
+        # the reference output went through the CPU library GEMM in x.dtype; compare within accumulation tolerance
+        tol = 1e-3 if dt == "fp32" else 8e-3
+        assert rel_err(y, y_ref) <= tol, tag
+
+
+@pytest.mark.parametrize("M", [1, 16, 128, 2048])
+def test_config3_linear_mxfp8_vs_oracle(M):
+    """MXFP8 Linear 4096 -> 4096, bf16, no bias (seed 2); fp32 GEMM of oracle-quantized operands is the reference."""
+    K = N = 4096
+    x, w = synthetic.linear_operands(M, K, N, seed=2)
+    cfg = {"weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3,
+           "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    layer = mb.LinearMXFP(K, N, bias=False, device=DEV, dtype=torch.bfloat16, config=cfg)
+    layer.load_state_dict({"weight": w.to(DEV)}, strict=False)
+    wq = O.mxfp_fake(w, 32, 4, 3, 1)
+    assert_bits_equal(layer.weight.data, wq, "weight")
+    assert layer._packed_weight() is not None  # the block-scaled tensor-core path is the one that runs
+    y = layer(x.to(DEV))
+    gemm.check_status()
+    ref = O.linear_mxfp(x, wq, None, cfg)
+    assert rel_err(y, ref) <= 4e-3  # bf16 output: half an ulp is 2**-9 of the value
+    # the fake-quantized fallback (dense bf16 MMA) agrees with the block-scaled path
+    y2 = gemm.linear_forward(mb.mxfp_quantizer(x.to(DEV), 32, 4, 3), layer.weight, None)
+    assert rel_err(y2, ref) <= 4e-3
+    assert rel_err(y, y2.cpu()) <= 4e-3
+
+
+def test_mixed_precision_layer_linears():
+    """The Linear children of the Llama-style layer: MXINT8 W+A projections, MXFP4-weight / MXFP8-activation FFN."""
+    g = torch.Generator().manual_seed(3)
+    h, ffn, tokens = 512, 1376, 96
+    x = torch.randn(tokens, h, generator=g).bfloat16()
+    int_cfg = {"weight_block_size": 32, "weight_width": 8, "data_in_block_size": 32, "data_in_width": 8}
+    ffn_cfg = {"weight_block_size": 32, "weight_exponent_width": 2, "weight_frac_width": 1,
+               "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    wq = (torch.randn(h, h, generator=g) * 0.02).bfloat16()
+    q = mb.LinearMXInt(h, h, bias=False, device=DEV, dtype=torch.bfloat16, config=int_cfg)
+    q.load_state_dict({"weight": wq.to(DEV)}, strict=False)
+    ref = O.linear_mxint(x, O.mxint_fake(wq, 32, 8, 1), None, int_cfg)
+    assert rel_err(q(x.to(DEV)), ref) <= 4e-3
+    wu = (torch.randn(ffn, h, generator=g) * 0.02).bfloat16()
+    up = mb.LinearMXFP(h, ffn, bias=False, device=DEV, dtype=torch.bfloat16, config=ffn_cfg)
+    up.load_state_dict({"weight": wu.to(DEV)}, strict=False)
+    assert up._packed_weight() is not None
+    ref = O.linear_mxfp(x, O.mxfp_fake(wu, 32, 2, 1, 1), None, ffn_cfg)
+    assert rel_err(up(x.to(DEV)), ref) <= 4e-3
+    wd = (torch.randn(h, ffn, generator=g) * 0.02).bfloat16()
+    down = mb.LinearMXFP(ffn, h, bias=False, device=DEV, dtype=torch.bfloat16, config=ffn_cfg)
+    down.load_state_dict({"weight": wd.to(DEV)}, strict=False)
+    xa = torch.randn(tokens, ffn, generator=g).bfloat16()
+    ref = O.linear_mxfp(xa, O.mxfp_fake(wd, 32, 2, 1, 1), None, ffn_cfg)
+    assert rel_err(down(xa.to(DEV)), ref) <= 4e-3
+    gemm.check_status()
+
+
+def test_bypass_and_unloaded_weights():
+    cfg = {"weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3,
+           "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(64, 256, generator=g).bfloat16()
+    w = (torch.randn(128, 256, generator=g) * 0.05).bfloat16()
+    # weights copied without load_state_dict (the FX-pass route): stay unquantized, activations are quantized
+    layer = mb.LinearMXFP(256, 128, bias=False, device=DEV, dtype=torch.bfloat16, config=dict(cfg))
+    with torch.no_grad():
+        layer.weight.copy_(w.to(DEV))
+    assert layer._packed_weight() is None
+    ref = O.mxfp_fake(x, 32, 4, 3).float() @ w.float().t()
+    assert rel_err(layer(x.to(DEV)), ref) <= 4e-3
+    by = mb.LinearMXFP(256, 128, bias=False, device=DEV, dtype=torch.bfloat16, config=dict(cfg, bypass=True))
+    by.load_state_dict({"weight": w.to(DEV)}, strict=False)
+    assert_bits_equal(by.weight.data, w, "bypass keeps the weight")
+    assert rel_err(by(x.to(DEV)), x.float() @ w.float().t()) <= 4e-3
+    # an in-place update after loading invalidates the packed copy
+    layer.load_state_dict({"weight": w.to(DEV)}, strict=False)
+    assert layer._packed_weight() is not None
+    with torch.no_grad():
+        layer.weight.mul_(2.0)
+    assert layer._packed_weight() is None
+    gemm.check_status()
