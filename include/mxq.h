@@ -35,6 +35,7 @@ extern "C" {
 #define MXQ_ERR_LAUNCH (-6)    /* the CUDA runtime reported an error at launch */
 #define MXQ_ERR_UNSUPPORTED (-7)
 #define MXQ_ERR_DEVICE (-8)    /* a kernel reported a device-side error status (bounded wait ran out) */
+#define MXQ_ERR_TOO_LARGE (-9) /* problem needs more scratch than MXQ_STATIC_SCRATCH_BYTES (mxq_mx_linear_static) */
 
 int mxq_version(void);
 const char *mxq_error_string(int code);
@@ -137,6 +138,30 @@ int64_t mxq_mx_linear_workspace_bytes(int64_t M, int64_t K);
 int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d, const void *bias,
                   int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
                   const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status, void *stream);
+
+/* Allocation-free variant of mxq_mx_linear.  It has no counterpart in the reference.
+ *
+ * Some callers are not in a position to hand over scratch memory: code that runs where the allocator must not be
+ * touched (inside a serving loop with a frozen memory pool, in a plugin that only receives input and output
+ * buffers from its host application, or in a process whose device memory is fully pre-partitioned), for whom a
+ * cudaMalloc -- or a caching allocator falling back to one -- is either forbidden or an unpredictable stall.  For
+ * them the packed activations go into a fixed array that is part of the library's device image:
+ * MXQ_STATIC_SCRATCH_BYTES (40 MiB) on every GPU that loads the library, held until the process exits.
+ *
+ *   - needs mxq_mx_linear_workspace_bytes(M, K) <= MXQ_STATIC_SCRATCH_BYTES (e.g. M = 8192, K = 4096 fits); larger
+ *     problems return MXQ_ERR_TOO_LARGE and must use mxq_mx_linear with their own workspace;
+ *   - calls no cudaMalloc / cudaFree and no allocating library routine; inputs and the output are the caller's;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current) and caches it: make that first call with the right device current and before any stream capture;
+ *   - every call on a device shares the one array.  A call only reads scratch bytes it has written itself (it
+ *     zeroes the scale region and overwrites the code region it uses), so leftovers of earlier calls are harmless,
+ *     but two calls that overlap in time on the same GPU (different streams or threads) race on it and corrupt
+ *     each other's result: serialise them.
+ * Arguments and results are otherwise those of mxq_mx_linear. */
+#define MXQ_STATIC_SCRATCH_BYTES (40u << 20)
+int mxq_mx_linear_static(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d,
+                         const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
+                         const uint8_t *floor_tab_host, int *status, void *stream);
 
 #ifdef __cplusplus
 }

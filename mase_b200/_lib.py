@@ -31,6 +31,8 @@ _PROTOTYPES = {
     "mxq_mx_linear_workspace_bytes": [c_int64, c_int64],
     "mxq_mx_linear": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64,
                       c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
+    "mxq_mx_linear_static": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
+                             c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "mxq_bfp_fake": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
 }
 

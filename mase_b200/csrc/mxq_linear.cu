@@ -7,7 +7,31 @@
 
 #include "mxq.h"
 
+#include <mutex>
+
 static inline int64_t align256(int64_t v) { return (v + 255) & ~(int64_t)255; }
+
+// Scratch for mxq_mx_linear_static.  The array lives in the device image of this library: every GPU that loads
+// libmxq holds MXQ_STATIC_SCRATCH_BYTES of its memory from the first use of the library until the process exits.
+// In host code the name below is only a handle for cudaGetSymbolAddress, never a pointer a kernel may be given.
+static __device__ __align__(256) uint8_t g_static_scratch[MXQ_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device, looked up once per device.
+static int static_scratch_address(uint8_t **out) {
+  constexpr int kMaxDevices = 64;
+  static uint8_t *cached[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return MXQ_ERR_LAUNCH;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void *ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return MXQ_ERR_LAUNCH;
+    cached[dev] = static_cast<uint8_t *>(ptr);
+  }
+  *out = cached[dev];
+  return MXQ_OK;
+}
 
 extern "C" {
 
@@ -32,6 +56,22 @@ int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uin
   int rc = mxq_mxfp_pack_mma(x, a_codes, a_scales, in_dtype, M, K, E, F, floor_tab_host, stream);
   if (rc != MXQ_OK) return rc;
   return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, d, bias, out_dtype, bias_dtype, M, N, K, status, stream);
+}
+
+int mxq_mx_linear_static(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d,
+                         const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
+                         const uint8_t *floor_tab_host, int *status, void *stream) {
+  if (M == 0 || N == 0) return MXQ_OK;
+  const int64_t need = mxq_mx_linear_workspace_bytes(M, K);
+  if (need < 0) return (int)need;
+  if (need > (int64_t)MXQ_STATIC_SCRATCH_BYTES) return MXQ_ERR_TOO_LARGE;
+  uint8_t *scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);  // first call on a device resolves the symbol's address
+  if (rc != MXQ_OK) return rc;
+  // every byte of the scratch that is read is written first by this call: the pack step zeroes the scale region and
+  // overwrites M*K code bytes, so whatever an earlier call left behind is never consumed
+  return mxq_mx_linear(x, in_dtype, w_codes, w_scales, d, bias, out_dtype, bias_dtype, M, N, K, E, F, floor_tab_host,
+                       scratch, MXQ_STATIC_SCRATCH_BYTES, status, stream);
 }
 
 }  // extern "C"

@@ -619,6 +619,7 @@ const char *mxq_error_string(int code) {
     case MXQ_ERR_LAUNCH: return "CUDA launch failed";
     case MXQ_ERR_UNSUPPORTED: return "unsupported configuration";
     case MXQ_ERR_DEVICE: return "device-side error status";
+    case MXQ_ERR_TOO_LARGE: return "problem exceeds the built-in scratch of mxq_mx_linear_static (MXQ_STATIC_SCRATCH_BYTES)";
     default: return "unknown error";
   }
 }
