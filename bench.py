@@ -270,6 +270,51 @@ def linear_extras(device) -> dict:
     return out
 
 
+def tp_stack_extras(device, rank: int, world: int) -> dict:
+    """Tensor-parallel Linear stack at the 70B shape: hidden 8192, FFN 28672, 4 gated-MLP layers, M = 8192 tokens,
+    MXFP4 (E2M1) weights / MXFP8 (E4M3) activations, gate/up column parallel, down row parallel with an fp32
+    all-reduce.  Strong scaling (total work fixed); every rank runs it."""
+    import torch.distributed as dist
+
+    import mase_b200 as mb
+    from mase_b200 import gemm, tp as tpmod
+
+    hidden, ffn, layers, M = 8192, 28672, 4, 8192
+    cfg = {"weight_block_size": 32, "weight_exponent_width": 2, "weight_frac_width": 1,
+           "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    tp = tpmod.TPGroup(rank, world, None)
+    gen = torch.Generator(device=device).manual_seed(4)
+    stack = []
+    for _ in range(layers):
+        mods = []
+        for (n, k, mode) in ((ffn, hidden, "column"), (ffn, hidden, "column"), (hidden, ffn, "row")):
+            # every rank draws the same full weight (same seed) and keeps its shard
+            w = (torch.randn(n, k, generator=gen, device=device) * 0.02).to(torch.bfloat16)
+            kw = {"chunks": 4} if mode == "row" and world > 1 else {}
+            mods.append(tpmod.build_tp_linear(mb.LinearMXFP, w, None, cfg, mode, tp, device=device, **kw))
+            del w
+        stack.append(tpmod.TPGatedMLP(*mods))
+    x0 = torch.randn(M, hidden, generator=gen, device=device).to(torch.bfloat16)
+
+    def step():
+        x = x0
+        for layer in stack:
+            x = layer(x)
+        return x
+
+    for _ in range(2):
+        step()
+    steps = 3
+    sec = time_region(step, steps, world, device)
+    gemm.check_status()
+    flops = layers * 3 * 2.0 * M * hidden * ffn
+    del stack
+    torch.cuda.empty_cache()
+    return {"config": "4 x (gate, up: 8192->28672 column; down: 28672->8192 row + all-reduce), M=8192, W E2M1 / A E4M3",
+            "ms_per_step": sec / steps * 1e3, "TFLOPs_aggregate": flops * steps / sec / 1e12, "n_gpus": world,
+            "scaling": "strong"}
+
+
 def run_ours(args) -> None:
     import torch.distributed as dist
 
@@ -339,6 +384,13 @@ def run_ours(args) -> None:
     ok = torch.equal(hy[:rows_c].view(torch.int16), state["y"][:rows_c].cpu().view(torch.int16))
     clocks = sampler.stop()
     del hx, hy, dbuf
+    tp_extra = None
+    if not args.no_extra:
+        state.clear()
+        del x
+        torch.cuda.empty_cache()
+        tp_extra = tp_stack_extras(device, rank, world)
+        x = synthetic.device_student_t3(ROWS, COLS, seed=1 + rank, device=device)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
@@ -350,6 +402,8 @@ def run_ours(args) -> None:
         cpu = {"value": CPU_SAMPLE_ROWS * COLS * BYTES_PER_ELEM / cpu_sec / 1e9, "unit": "GB/s", "cores": cores,
                "kind": "port", "sample": f"{CPU_SAMPLE_ROWS} of {ROWS} rows, one pass"}
         extra = extras(device, x) if not args.no_extra else {}
+        if tp_extra is not None:
+            extra["tp_linear_stack_70b_shape"] = tp_extra
         print(json.dumps({
             "metric": "mx_quant_dequant_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True,

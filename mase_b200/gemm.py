@@ -60,8 +60,9 @@ def _bias_args(bias: Tensor | None):
     return bias.contiguous(), _DT[bias.dtype]
 
 
-def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None) -> Tensor:
-    """x[..., K] @ weight[N, K]^T + bias, output in x.dtype; bf16 operands use kind::f16, fp32 operands kind::tf32."""
+def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None, out_dtype: torch.dtype | None = None) -> Tensor:
+    """x[..., K] @ weight[N, K]^T + bias, output in x.dtype (or `out_dtype`); bf16 operands use kind::f16, fp32
+    operands kind::tf32."""
     _require_cuda(x, "linear_forward")
     if x.dtype != weight.dtype:
         raise RuntimeError(f"expected input and weight to have the same dtype, got {x.dtype} and {weight.dtype}")
@@ -83,12 +84,12 @@ def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None) -> Tensor:
         a = torch.nn.functional.pad(a, (0, pad))
         w = torch.nn.functional.pad(w, (0, pad))
         K += pad
-    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
     b, bdt = _bias_args(bias)
     st = _status(x.device)
     with _on_device(x):
         rc = _lib.lib().mxq_gemm_dense(a.data_ptr(), w.data_ptr(), out.data_ptr(), 0 if b is None else b.data_ptr(),
-                                       _DT[x.dtype], _DT[x.dtype], bdt, M, N, K, st.data_ptr(), _stream(x))
+                                       _DT[x.dtype], _DT[out.dtype], bdt, M, N, K, st.data_ptr(), _stream(x))
     _lib.check(rc, "mxq_gemm_dense")
     if _CHECK_EVERY_CALL:
         check_status(x.device)
@@ -148,7 +149,8 @@ def mx_gemm(a: MXOperand, b: MXOperand, bias: Tensor | None, out_dtype: torch.dt
     return out
 
 
-def mx_linear(x: Tensor, weight: MXOperand, bias: Tensor | None, exp_bits: int, frac_bits: int) -> Tensor:
+def mx_linear(x: Tensor, weight: MXOperand, bias: Tensor | None, exp_bits: int, frac_bits: int,
+              out_dtype: torch.dtype | None = None) -> Tensor:
     """Quantize x[..., K] to MXFP(exp_bits, frac_bits) along K and multiply with a packed weight (one C call;
     the packed activations live in a scratch tensor allocated here)."""
     _require_cuda(x, "mx_linear")
@@ -164,12 +166,12 @@ def mx_linear(x: Tensor, weight: MXOperand, bias: Tensor | None, exp_bits: int, 
     lib = _lib.lib()
     ws_bytes = int(lib.mxq_mx_linear_workspace_bytes(M, K))
     ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=x.device)
-    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
     bb, bdt = _bias_args(bias)
     st = _status(x.device)
     with _on_device(x):
         rc = lib.mxq_mx_linear(a.data_ptr(), _DT[x.dtype], weight.codes.data_ptr(), weight.scales.data_ptr(),
-                               out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[x.dtype], bdt, M, N, K, exp_bits,
+                               out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[out.dtype], bdt, M, N, K, exp_bits,
                                frac_bits, _floor_tab_ptr(), ws.data_ptr(), ws_bytes, st.data_ptr(), _stream(x))
     _lib.check(rc, "mxq_mx_linear")
     if _CHECK_EVERY_CALL:

@@ -22,6 +22,10 @@ from .quantizers import block_fp_quantizer, mxfp_quantizer, mxint_quantizer
 class _LinearBase(torch.nn.Linear):
     """chop/nn/quantized/modules/linear.py:61-83"""
 
+    # dtype of the forward result; None = the input's dtype like the reference.  The row-parallel wrapper asks for
+    # float32 partial sums so that the cross-GPU reduction happens before the only rounding to the output dtype.
+    output_dtype = None
+
     def __init__(self, in_features: int, out_features: int, bias: bool = False, device=None, dtype=None) -> None:
         super().__init__(in_features, out_features, bias, device, dtype)
         self.bypass = False
@@ -98,7 +102,7 @@ class LinearMXFP(_LinearBase):
     @torch.no_grad()
     def forward(self, x: Tensor) -> Tensor:
         if self.bypass:
-            return linear_forward(x, self.weight, self.bias)
+            return linear_forward(x, self.weight, self.bias, self.output_dtype)
         cfg = self.config
         x_block, x_exp, x_frac = cfg.get("data_in_block_size"), cfg.get("data_in_exponent_width"), cfg.get("data_in_frac_width")
         if x_block is not None and x_exp is not None:
@@ -106,9 +110,9 @@ class LinearMXFP(_LinearBase):
             if packed is not None and x.is_cuda and x.dtype == self.weight.dtype:
                 # activations are quantized straight into tensor-core operands; same codes and scales as
                 # mxfp_quantizer, multiplied by tcgen05 block-scaled MMAs
-                return mx_linear(x, packed, self.bias, x_exp, x_frac)
+                return mx_linear(x, packed, self.bias, x_exp, x_frac, self.output_dtype)
             x = mxfp_quantizer(x, block_size=x_block, element_exp_bits=x_exp, element_frac_bits=x_frac, block_dim=-1)
-        return linear_forward(x, self.weight, self.bias)
+        return linear_forward(x, self.weight, self.bias, self.output_dtype)
 
 
 class LinearMXInt(_LinearBase):
@@ -142,15 +146,15 @@ class LinearMXInt(_LinearBase):
     @torch.no_grad()
     def forward(self, x: Tensor) -> Tensor:
         if self.bypass:
-            return linear_forward(x, self.weight, self.bias)
+            return linear_forward(x, self.weight, self.bias, self.output_dtype)
         cfg = self.config
         x_block, x_bits = cfg.get("data_in_block_size"), cfg.get("data_in_width")
         if x_block is not None and x_bits is not None:
             x = mxint_quantizer(x, block_size=x_block, element_bits=x_bits, block_dim=-1)
-        return linear_forward(x, self.weight, self.bias)
+        return linear_forward(x, self.weight, self.bias, self.output_dtype)
 
 
-def linearBlockFP(x: Tensor, weight: Tensor, bias: Tensor = None, config: dict = None) -> Tensor:
+def linearBlockFP(x: Tensor, weight: Tensor, bias: Tensor = None, config: dict = None, out_dtype=None) -> Tensor:
     """Quantize x, weight and bias with block floating point on every call, then multiply
     (chop/nn/quantized/functional/linear.py:220-278)."""
     w_quantizer = partial(
@@ -180,7 +184,7 @@ def linearBlockFP(x: Tensor, weight: Tensor, bias: Tensor = None, config: dict =
     x = x_quantizer(x)
     weight = w_quantizer(weight)
     bias = b_quantizer(bias) if bias is not None else None
-    return linear_forward(x, weight, bias)
+    return linear_forward(x, weight, bias, out_dtype)
 
 
 class LinearBlockFP(_LinearBase):
@@ -192,8 +196,8 @@ class LinearBlockFP(_LinearBase):
 
     def forward(self, x: Tensor) -> Tensor:
         if self.bypass:
-            return linear_forward(x, self.weight, self.bias)
-        return linearBlockFP(x, self.weight, self.bias, self.config)
+            return linear_forward(x, self.weight, self.bias, self.output_dtype)
+        return linearBlockFP(x, self.weight, self.bias, self.config, self.output_dtype)
 
 
 # entries of chop.nn.quantized.modules.quantized_module_map (nn/quantized/modules/__init__.py:241-246)
