@@ -418,6 +418,49 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+def run_linear(args) -> None:
+    """`--workload linear`: MXFP8 Linear forward 4096 -> 4096 at M = --m (single GPU), one JSON line.  Used for the
+    tensor-core roofline and for profiler captures of the GEMM and activation-pack kernels."""
+    import mase_b200 as mb
+    from mase_b200 import gemm, synthetic
+
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    M, K, N = args.m, 4096, 4096
+    cfg = {"weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3,
+           "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    x, w = synthetic.linear_operands(M, K, N, seed=2)
+    x = x.to(device)
+    layer = mb.LinearMXFP(K, N, bias=False, device=device, dtype=torch.bfloat16, config=cfg)
+    layer.load_state_dict({"weight": w.to(device)}, strict=False)
+    for _ in range(max(args.warmup, 3)):
+        layer(x)
+    sec = time_region(lambda: layer(x), args.steps, 1, device)
+    xp = gemm.pack_mx_operand(x, 4, 3)
+    wp = layer._packed_weight()
+    sec_gemm = time_region(lambda: gemm.mx_gemm(xp, wp, None, torch.bfloat16), args.steps, 1, device)
+    gemm.check_status()
+    flops = 2.0 * M * N * K
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            bf16_peak, src = float(json.load(fh)["bf16_tflops"]), "2 x measured bf16 cuBLAS burst"
+    except Exception:
+        bf16_peak, src = 1590.0, "2 x fallback bf16"
+    peak = 2.0 * bf16_peak
+    ach = flops * args.steps / sec_gemm / 1e12
+    print(json.dumps({
+        "metric": "mx_linear_forward_TFLOPs", "value": flops * args.steps / sec / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": sec / args.steps * 1e3,
+        "higher_is_better": True, "dtype": "mxfp8 (E4M3 x E4M3, E8M0 scales), fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"LinearMXFP 4096->4096 forward, M={M}, bf16 in/out, W and A MXFP8 block 32"},
+        "gpu_launches": 3 * args.steps,
+        "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                     "peak_source": src + " (no block-scaled FP8 entry in MEASURED_PEAKS.json; nominal 4500)",
+                     "kernel": "mxq::gemm::umma_gemm_kernel<mxf8,256>", "traffic": None},
+        "gemm_only_ms": sec_gemm / args.steps * 1e3,
+    }))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -427,7 +470,13 @@ def main() -> None:
     ap.add_argument("--no-extra", action="store_true", help="skip the untimed extra measurements")
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the [rows, 8192] tensor (default: the full workload)")
     ap.add_argument("--kernel-only", action="store_true", help="only the device-resident timed region (for profilers)")
+    ap.add_argument("--workload", default="quant", choices=["quant", "linear"],
+                    help="quant: the headline quantizer benchmark; linear: MXFP8 Linear forward (profiling aid)")
+    ap.add_argument("--m", type=int, default=8192, help="tokens for --workload linear")
     args = ap.parse_args()
+    if args.workload == "linear" and args.impl == "ours":
+        run_linear(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -95,6 +95,11 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -169,7 +174,8 @@ struct Layout {
   static constexpr int kSf = kSfa + kSfb;               // scale chunks of one stage
   static constexpr int kStage = kAB + kSf;              // bytes that arrive per stage (the transaction count)
   static constexpr int kSfBase = kStages * kAB;         // scale chunks live after all operand tiles
-  static constexpr int kBarriers = kStages * kStage;    // full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+  static constexpr int kStaging = (kStages * kStage + 1023) & ~1023;  // epilogue: 4 warps x 2 buffers x 2048 bytes
+  static constexpr int kBarriers = kStaging + 4 * 4096;  // full[kStages], empty[kStages], acc_full[2], acc_empty[2]
   static constexpr int kTotal = kBarriers + 16 * 8 + 16 + 1024;  // + tmem slot, abort flag, alignment slack
 };
 
@@ -183,11 +189,13 @@ struct Params {
   int k_chunks;         // ceil(K * element_size / 128)
   int out_bf16;         // output element type: 1 bf16, 0 fp32
   int bias_bf16;        // bias element type
+  int tma_store;        // output rows are 16-byte multiples: the epilogue writes through TMA stores
 };
 
 template <int kKind, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_d, const Params p) {
   constexpr bool kScaled = kKind == kMxf8;
   constexpr int kAccStages = kScaled ? 1 : (2 * BN <= kTmemCols ? 2 : 1);
   constexpr int kSfCol = kAccStages * BN;        // first TMEM column of the scale factors
@@ -234,6 +242,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // ---------------- TMA producer ----------------
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
       int stage = 0;
       uint32_t phase = 0;
       uint32_t used = 0, last_phase = 0;  // per-stage bit masks for the exit path
@@ -318,7 +327,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
+    // Each warp drains the 32 TMEM lanes (= 32 tile rows) of its quarter in chunks of 32 columns.  A chunk is
+    // converted, written to a 64-byte-swizzled staging buffer in shared memory (32 rows x 64 bytes, two buffers per
+    // warp) and handed to a TMA store, which writes whole lines and clips at the matrix edges.  Output matrices
+    // whose rows are not 16-byte multiples take direct predicated stores instead.
     const int quarter = warp & 3;  // TMEM lanes [32 * quarter, +32) are the ones this warp may read
+    uint8_t *stage_buf = smem + L::kStaging + (warp - 2) * 4096;
+    int buf = 0;
     int local = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
       const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
@@ -326,7 +341,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait)) break;
       tc_fence_after();
-      const int row = m_blk * BM + quarter * 32 + lane;
+      const int row0 = m_blk * BM + quarter * 32;
       const int n0 = n_blk * BN;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
@@ -344,31 +359,57 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
           }
         }
-        if (row < p.M) {
-          const bool full = n0 + c + 32 <= p.N;
+        if (p.tma_store) {
           if (p.out_bf16) {
-            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.d) + (size_t)row * p.N + n0 + c;
-            if (full && (p.N & 7) == 0) {
+            uint32_t w[16];
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint32_t w[4];
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * t]), __uint_as_float(v[j + 2 * t + 1]));
-                  w[t] = *reinterpret_cast<uint32_t *>(&h);
-                }
-                *reinterpret_cast<uint4 *>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-            } else {
-              for (int j = 0; j < 32 && n0 + c + j < p.N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            for (int t = 0; t < 16; ++t) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * t]), __uint_as_float(v[2 * t + 1]));
+              w[t] = *reinterpret_cast<uint32_t *>(&h);
             }
-          } else {
-            float *dst = reinterpret_cast<float *>(p.d) + (size_t)row * p.N + n0 + c;
-            if (full && (p.N & 3) == 0) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            uint8_t *dst = stage_buf + buf * 2048 + lane * 64;
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4 *>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-              for (int j = 0; j < 32 && n0 + c + j < p.N; ++j) dst[j] = __uint_as_float(v[j]);
+            for (int t = 0; t < 4; ++t)  // 16-byte chunk t of this row lands at chunk t ^ ((row >> 1) & 3)
+              *reinterpret_cast<uint4 *>(dst + ((t ^ ((lane >> 1) & 3)) << 4)) =
+                  make_uint4(w[4 * t], w[4 * t + 1], w[4 * t + 2], w[4 * t + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&map_d, smem_u32(stage_buf + buf * 2048), n0 + c, row0);
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            buf ^= 1;
+          } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {  // fp32: two boxes of 16 columns (64 bytes per row) per chunk
+              if (n0 + c + 16 * h >= p.N) break;
+              if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+              __syncwarp();
+              uint8_t *dst = stage_buf + buf * 2048 + lane * 64;
+#pragma unroll
+              for (int t = 0; t < 4; ++t)
+                *reinterpret_cast<uint4 *>(dst + ((t ^ ((lane >> 1) & 3)) << 4)) =
+                    make_uint4(v[16 * h + 4 * t], v[16 * h + 4 * t + 1], v[16 * h + 4 * t + 2], v[16 * h + 4 * t + 3]);
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&map_d, smem_u32(stage_buf + buf * 2048), n0 + c + 16 * h, row0);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              }
+              buf ^= 1;
+            }
+          }
+        } else if (row0 + lane < p.M) {
+          const size_t off = (size_t)(row0 + lane) * p.N + n0 + c;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (n0 + c + j < p.N) {
+              if (p.out_bf16)
+                reinterpret_cast<__nv_bfloat16 *>(p.d)[off + j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+              else
+                reinterpret_cast<float *>(p.d)[off + j] = __uint_as_float(v[j]);
             }
           }
         }
@@ -377,6 +418,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(acc));
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores done before the CTA exits
   }
 
   tc_fence_before();
@@ -421,6 +463,21 @@ static int make_map(CUtensorMap *map, const void *ptr, int kind, int64_t rows, i
   return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
+// tensor map of the output [rows, n] for stores of 32-row x 64-byte boxes, 64-byte swizzle
+static int make_store_map(CUtensorMap *map, void *ptr, bool bf16, int64_t rows, int64_t n) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return MXQ_ERR_UNSUPPORTED;
+  const int es = bf16 ? 2 : 4;
+  cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)n * es};
+  cuuint32_t box[2] = {(cuuint32_t)(64 / es), 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_LAUNCH;
+}
+
 static int sm_count() {
   static int n = 0;
   if (!n) {
@@ -437,16 +494,24 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
                   int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, cudaStream_t st) {
   using L = Layout<BN, kKind == kMxf8>;
   constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, md;
   int rc = make_map(&ma, a, kKind, M, K, BM);
   if (rc) return rc;
   rc = make_map(&mb, b, kKind, N, K, BN);
   if (rc) return rc;
+  const bool out_bf16 = out_dtype == MXQ_BF16;
+  const bool tma_store = (N * (out_bf16 ? 2 : 4)) % 16 == 0;
+  if (tma_store) {
+    rc = make_store_map(&md, d, out_bf16, M, N);
+    if (rc) return rc;
+  } else {
+    md = ma;  // unused by the kernel
+  }
   Params p;
   p.sfa = sfa, p.sfb = sfb, p.d = d, p.bias = bias, p.status = status;
   p.M = (int)M, p.N = (int)N, p.K = (int)K;
   p.k_chunks = (int)((K * es + kRowBytes - 1) / kRowBytes);
-  p.out_bf16 = out_dtype == MXQ_BF16, p.bias_bf16 = bias_dtype == MXQ_BF16;
+  p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
@@ -456,7 +521,7 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   }
   const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  umma_gemm_kernel<kKind, BN><<<grid, kThreads, L::kTotal, st>>>(ma, mb, p);
+  umma_gemm_kernel<kKind, BN><<<grid, kThreads, L::kTotal, st>>>(ma, mb, md, p);
   return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 

@@ -285,107 +285,152 @@ mxfp_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, uint8_t *__restrict
 template <typename Tin, int E, int F>
 __global__ void __launch_bounds__(kThreads)
 mxfp_pack_mma_kernel(const Tin *__restrict__ x, uint8_t *__restrict__ codes, uint8_t *__restrict__ scales, int64_t n_vec,
-                     int64_t k_elems, int64_t k_chunks, const __grid_constant__ Log2Tab tab) {
+                     uint32_t vec_per_row, int64_t k_chunks, const __grid_constant__ Log2Tab tab) {
   constexpr int N = Elem<Tin>::kVec;
   constexpr bool kBf16In = Elem<Tin>::kBf16;
   constexpr int kGroup = 32 / N;
   constexpr int kTop = (1 << E) - 1;
   constexpr int kBias = (1 << (E - 1)) - 1;
   constexpr int kEmax = kTop - kBias;
+  constexpr int kU = 2;
   const uint4 *xv = reinterpret_cast<const uint4 *>(x);
-  const int64_t step = (int64_t)gridDim.x * kThreads;
-  // whole warps iterate together (the bound is rounded up), so the shuffles below are always convergent
-  const int64_t n_round = (n_vec + 31) & ~(int64_t)31;
-  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n_round; i += step) {
-    const uint4 raw = i < n_vec ? ld_stream(xv + i) : make_uint4(0, 0, 0, 0);
-    const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
-    uint32_t a[4], amax;
-    if constexpr (kBf16In) {
-      uint32_t m = 0;
+  const int64_t step = (int64_t)gridDim.x * kThreads * kU;
+  for (int64_t base = (int64_t)blockIdx.x * kThreads * kU; base < n_vec; base += step) {
+    uint4 raws[kU];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        a[k] = r[k] & 0x7FFF7FFFu;
-        m = max(m, max(a[k] & 0xFFFFu, a[k] >> 16));
-      }
-      m = group_max(m, kGroup);
-      amax = (m >> 7) ? (m << 16) : 0u;
-    } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) a[k] = r[k] & 0x7FFFFFFFu;
-      const uint32_t m = group_max(max(max(a[0], a[1]), max(a[2], a[3])), kGroup);
-      amax = (m >> 23) ? m : 0u;
+    for (int u = 0; u < kU; ++u) {
+      const int64_t i = base + u * kThreads + threadIdx.x;
+      raws[u] = i < n_vec ? ld_stream(xv + i) : make_uint4(0, 0, 0, 0);
     }
-    const int exm = (int)(amax >> 23);
-    int up = 0;
-    if constexpr (!kBf16In) {
-      const uint32_t man = amax & 0x7FFFFFu;
-      if (man >= 0x7FFF00u) up = (0x7FFFFFu - man) < tab.t[exm] ? 1 : 0;
-    }
-    const int K = exm + up - kTop;
-    bool fast = K >= 1;
-    if constexpr (kBf16In) {
-      const uint32_t t1 = (uint32_t)((K + 1) << 7) * 0x00010001u;
-      const __nv_bfloat162 t1v = *reinterpret_cast<const __nv_bfloat162 *>(&t1);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) fast = fast && __hbge2(*reinterpret_cast<const __nv_bfloat162 *>(&a[k]), t1v);
-    } else {
-      const uint32_t t1 = (uint32_t)(K + 1) << 23;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) fast = fast && a[k] >= t1;
-    }
-    float v[N];  // element values in units of the block scale
-    int scale;
-    if (fast) {
-      const int sh = exm + up - 127 - kEmax;
-      scale = sh + 127;
-      const uint32_t shb = (uint32_t)sh << 23;
+    for (int u = 0; u < kU; ++u) {
+      const int64_t i = base + u * kThreads + threadIdx.x;
+      const uint4 raw = raws[u];
+      const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t a[4], amax;
       if constexpr (kBf16In) {
-        const uint32_t kodd2 = (K & 1) ? 0x00800080u : 0u;
+        __nv_bfloat162 m2 = __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&(a[0] = r[0] & 0x7FFF7FFFu)),
+                                    *reinterpret_cast<const __nv_bfloat162 *>(&(a[1] = r[1] & 0x7FFF7FFFu)));
+        m2 = __hmax2(m2, __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&(a[2] = r[2] & 0x7FFF7FFFu)),
+                                 *reinterpret_cast<const __nv_bfloat162 *>(&(a[3] = r[3] & 0x7FFF7FFFu))));
+        const uint32_t mb = *reinterpret_cast<uint32_t *>(&m2);
+        const uint32_t m = group_max(max(mb & 0xFFFFu, mb >> 16), kGroup);
+        amax = (m >> 7) ? (m << 16) : 0u;
+      } else {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint32_t w = mxfp_round_pair<F>(a[k], kodd2) | (r[k] & 0x80008000u);
-          v[2 * k] = __uint_as_float((w << 16) - shb), v[2 * k + 1] = __uint_as_float((w & 0xFFFF0000u) - shb);
+        for (int k = 0; k < 4; ++k) a[k] = r[k] & 0x7FFFFFFFu;
+        const uint32_t m = group_max(max(max(a[0], a[1]), max(a[2], a[3])), kGroup);
+        amax = (m >> 23) ? m : 0u;
+      }
+      const int exm = (int)(amax >> 23);
+      int up = 0;
+      if constexpr (!kBf16In) {
+        const uint32_t man = amax & 0x7FFFFFu;
+        if (man >= 0x7FFF00u) up = (0x7FFFFFu - man) < tab.t[exm] ? 1 : 0;
+      }
+      const int K = exm + up - kTop;
+      const uint32_t kodd = (K & 1) ? 0x00800000u : 0u;
+      bool fast = K >= 1;
+      if constexpr (kBf16In) {
+        const uint32_t t1 = (uint32_t)((K + 1) << 7) * 0x00010001u;
+        const __nv_bfloat162 t1v = *reinterpret_cast<const __nv_bfloat162 *>(&t1);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) fast = fast && __hbge2(*reinterpret_cast<const __nv_bfloat162 *>(&a[k]), t1v);
+      } else {
+        const uint32_t t1 = (uint32_t)(K + 1) << 23;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) fast = fast && a[k] >= t1;
+      }
+      int sh, scale;
+      if (K >= 1) {
+        sh = exm + up - 127 - kEmax, scale = sh + 127;
+      } else {
+        const MxfpBlock p = mxfp_block(amax, E, tab);
+        sh = p.sh, scale = p.scale;
+      }
+      // pass 1: the reference's rounding; note whether an element lands on the top E4M3 code (exponent code 15,
+      // fraction 7), which any element of the top binade can do, not only the block maximum
+      uint32_t yq[4];     // fast path: rounded |x| patterns (bf16: two per word)
+      uint32_t cw[N];     // general path: reference codes
+      int top = 0;
+      if (fast) {
+        if constexpr (kBf16In) {
+          const uint32_t kodd2 = kodd ? 0x00800080u : 0u;
+          const uint32_t t16 = (((uint32_t)exm << 7) | (7u << 4)) * 0x00010001u;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            yq[k] = mxfp_round_pair<F>(a[k], kodd2);
+            if constexpr (E == 4 && F == 3) {
+              const uint32_t z = yq[k] ^ t16;  // a zero halfword = that element is the top code
+              top |= (int)(((z - 0x00010001u) & ~z & 0x80008000u) != 0);
+            }
+          }
+        } else {
+          const uint32_t t32 = ((uint32_t)exm << 23) | (7u << 20);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            yq[k] = mxfp_round_one<F>(a[k] & 0x7FFFFF00u, kodd);
+            if constexpr (E == 4 && F == 3) top |= (int)(yq[k] == t32);
+          }
+        }
+        if (up) top = 0;  // the maximum was assigned exponent code 14: nothing reaches code 15
+      } else {
+        uint32_t b[N];
+        unpack(raw, b);
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          if (((b[k] & 0x7FFFFFFFu) >> 23) == 0) b[k] = 0;
+          cw[k] = mxfp_encode(b[k], sh, E, F);
+          if constexpr (E == 4 && F == 3) top |= (int)((cw[k] & 0x7Fu) == 0x7Fu);
+        }
+      }
+      if constexpr (E == 4 && F == 3) {
+        for (int o = 1; o < kGroup; o <<= 1) top |= __shfl_xor_sync(0xFFFFFFFFu, top, o);
+      }
+      if (i >= n_vec) continue;  // after the shuffles: every lane of the warp takes part in them
+      // pass 2: values in units of the (possibly raised) scale, converted to hardware E4M3
+      uint32_t c2[N / 2];  // two E4M3 bytes per word (low 16 bits)
+      if (fast) {
+        const uint32_t shb = (uint32_t)(sh + top) << 23;  // division by the scale = exponent subtraction
+        if constexpr (kBf16In) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t w = yq[k] | (r[k] & 0x80008000u);
+            c2[k] = __nv_cvt_float2_to_fp8x2(make_float2(__uint_as_float((w << 16) - shb),
+                                                         __uint_as_float((w & 0xFFFF0000u) - shb)),
+                                             __NV_SATFINITE, __NV_E4M3);
+          }
+        } else {
+          float v[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) v[k] = __uint_as_float((yq[k] | (r[k] & 0x80000000u)) - shb);
+          c2[0] = __nv_cvt_float2_to_fp8x2(make_float2(v[0], v[1]), __NV_SATFINITE, __NV_E4M3);
+          c2[1] = __nv_cvt_float2_to_fp8x2(make_float2(v[2], v[3]), __NV_SATFINITE, __NV_E4M3);
         }
       } else {
-        const uint32_t kodd = (K & 1) ? 0x00800000u : 0u;
+        const float half = top ? 0.5f : 1.f;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          v[k] = __uint_as_float((mxfp_round_one<F>(a[k] & 0x7FFFFF00u, kodd) | (r[k] & 0x80000000u)) - shb);
+        for (int k = 0; k < N; k += 2)
+          c2[k / 2] = __nv_cvt_float2_to_fp8x2(
+              make_float2(mxfp_decode(cw[k], E, F) * half, mxfp_decode(cw[k + 1], E, F) * half), __NV_SATFINITE, __NV_E4M3);
       }
-    } else {
-      uint32_t b[N];
-      unpack(raw, b);
-      const MxfpBlock p = mxfp_block(amax, E, tab);
-      scale = p.scale;
-#pragma unroll
-      for (int k = 0; k < N; ++k) {
-        if (((b[k] & 0x7FFFFFFFu) >> 23) == 0) b[k] = 0;
-        v[k] = mxfp_decode(mxfp_encode(b[k], p.sh, E, F), E, F);
+      if constexpr (kBf16In)
+        __stcs(reinterpret_cast<uint2 *>(codes + i * N),
+               make_uint2(__byte_perm(c2[0], c2[1], 0x5410), __byte_perm(c2[2], c2[3], 0x5410)));
+      else
+        __stcs(reinterpret_cast<uint32_t *>(codes + i * N), __byte_perm(c2[0], c2[1], 0x5410));
+      if ((threadIdx.x & (kGroup - 1)) == 0) {
+        int64_t row, vcol;
+        if (n_vec <= 0xFFFFFFFFll) {
+          const uint32_t iu = (uint32_t)i;
+          row = iu / vec_per_row, vcol = iu - (uint32_t)row * vec_per_row;
+        } else {
+          row = i / vec_per_row, vcol = i - row * vec_per_row;
+        }
+        const int64_t kb = (vcol * N) >> 5;
+        scales[((row >> 7) * k_chunks + (kb >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kb & 3)] =
+            (uint8_t)(scale + top);
       }
-    }
-    if constexpr (E == 4 && F == 3) {
-      int top = 0;
-#pragma unroll
-      for (int k = 0; k < N; ++k) top |= fabsf(v[k]) > 448.f ? 1 : 0;
-      for (int o = 1; o < kGroup; o <<= 1) top |= __shfl_xor_sync(0xFFFFFFFFu, top, o);
-      if (top) {
-        scale += 1;
-#pragma unroll
-        for (int k = 0; k < N; ++k) v[k] *= 0.5f;
-      }
-    }
-    if (i >= n_vec) continue;
-    uint32_t c[N];
-#pragma unroll
-    for (int k = 0; k < N; k += 2) {
-      const uint32_t two = __nv_cvt_float2_to_fp8x2(make_float2(v[k], v[k + 1]), __NV_SATFINITE, __NV_E4M3);
-      c[k] = two & 0xFFu, c[k + 1] = two >> 8;
-    }
-    store_bytes(codes, i * N, c);
-    if ((threadIdx.x & (kGroup - 1)) == 0) {
-      const int64_t e0 = i * N, row = e0 / k_elems, kb = (e0 % k_elems) >> 5;
-      scales[((row >> 7) * k_chunks + (kb >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kb & 3)] =
-          (uint8_t)scale;
     }
   }
 }
@@ -715,8 +760,8 @@ int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in
 #define MXQ_PACK(TI, e, f)                                                                                      \
   if (E == e && F == f) {                                                                                       \
     const int64_t n_vec = rows * k / Elem<TI>::kVec;                                                            \
-    mxfp_pack_mma_kernel<TI, e, f><<<grid_for(n_vec, kThreads), kThreads, 0, st>>>((const TI *)x, codes, scales_mma, \
-                                                                                  n_vec, k, k_chunks, tab);     \
+    mxfp_pack_mma_kernel<TI, e, f><<<grid_for(n_vec, kThreads * 2), kThreads, 0, st>>>(                         \
+        (const TI *)x, codes, scales_mma, n_vec, (uint32_t)(k / Elem<TI>::kVec), k_chunks, tab);                \
     return check_launch();                                                                                      \
   }
   if (in_dtype == MXQ_F32) {
