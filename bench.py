@@ -263,7 +263,14 @@ def linear_extras(device) -> dict:
         t_gemm = 1.0 / quick_gbs(lambda: gemm.mx_gemm(xp, wp, None, torch.bfloat16), 1, calls=calls) / 1e9
         xq = mb.mxfp_quantizer(x, 32, 4, 3)
         t_dense = 1.0 / quick_gbs(lambda: gemm.linear_forward(xq, layer.weight, None), 1, calls=calls) / 1e9
+        # the same forward replayed from a CUDA graph: device time without the per-call host work
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            layer(x)
+        t_graph = 1.0 / quick_gbs(graph.replay, 1, calls=calls) / 1e9
+        del graph
         out[f"M{M}"] = {"forward_us": t_fwd * 1e6, "forward_TFLOPs": flops / t_fwd / 1e12,
+                        "forward_cuda_graph_us": t_graph * 1e6, "forward_cuda_graph_TFLOPs": flops / t_graph / 1e12,
                         "gemm_only_us": t_gemm * 1e6, "gemm_only_TFLOPs": flops / t_gemm / 1e12,
                         "bf16_gemm_of_fake_quant_us": t_dense * 1e6, "bf16_gemm_TFLOPs": flops / t_dense / 1e12}
     gemm.check_status()

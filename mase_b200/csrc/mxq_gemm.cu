@@ -29,7 +29,7 @@ namespace mxq {
 namespace gemm {
 
 constexpr int BM = 128;
-constexpr int kStages = 4;
+constexpr int kMaxStages = 4;
 constexpr int kThreads = 192;
 constexpr int kRowBytes = 128;            // bytes of K per row per stage = one 128B swizzle atom
 constexpr int kTmemCols = 512;
@@ -151,7 +151,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+// Wait for the outstanding tcgen05.ld.  The registers of `r` only hold data after the wait, which the compiler cannot
+// know: the empty statements re-define them after the (volatile, hence ordered) wait so that no use is hoisted above it.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                    "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :: "memory");
+  asm volatile("" : "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]),
+                    "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]),
+                    "+r"(r[31])
+               :: "memory");
 }
 
 // instruction descriptor: fp32 accumulate, K-major A and B, M = 128, N = BN
@@ -164,18 +175,24 @@ __device__ __forceinline__ uint32_t make_idesc() {
   return d;
 }
 
+// Operand ring of 4 stages and 2 store boxes per epilogue warp.  (A 3-stage ring with a store staging area for a
+// whole tile was measured slower for the block-scaled kind: the main loop is limited by how fast operand tiles
+// arrive from L2, so ring depth matters more than a shorter epilogue.)
 template <int BN, bool kScaled>
 struct Layout {
+  static constexpr int kStages = 4;
+  static constexpr int kStoreBufs = 2;  // 2048-byte store boxes per epilogue warp
   static constexpr int kA = BM * kRowBytes;
   static constexpr int kB = BN * kRowBytes;
   static constexpr int kSfa = kScaled ? 512 : 0;
-  static constexpr int kSfb = kScaled ? (BN / 128) * 512 : 0;
+  static constexpr int kSfbChunks = (BN + 127) / 128;    // 128-row scale chunks that cover the BN rows of a B tile
+  static constexpr int kSfb = kScaled ? kSfbChunks * 512 : 0;
   static constexpr int kAB = kA + kB;                   // operand tiles of one stage; a multiple of 1024 bytes
   static constexpr int kSf = kSfa + kSfb;               // scale chunks of one stage
   static constexpr int kStage = kAB + kSf;              // bytes that arrive per stage (the transaction count)
   static constexpr int kSfBase = kStages * kAB;         // scale chunks live after all operand tiles
-  static constexpr int kStaging = (kStages * kStage + 1023) & ~1023;  // epilogue: 4 warps x 2 buffers x 2048 bytes
-  static constexpr int kBarriers = kStaging + 4 * 4096;  // full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+  static constexpr int kStaging = (kStages * kStage + 1023) & ~1023;  // epilogue: 4 warps x kStoreBufs x 2048 bytes
+  static constexpr int kBarriers = kStaging + 4 * kStoreBufs * 2048;  // full[], empty[], acc_full[2], acc_empty[2]
   static constexpr int kTotal = kBarriers + 16 * 8 + 16 + 1024;  // + tmem slot, abort flag, alignment slack
 };
 
@@ -197,10 +214,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_d, const Params p) {
   constexpr bool kScaled = kKind == kMxf8;
-  constexpr int kAccStages = kScaled ? 1 : (2 * BN <= kTmemCols ? 2 : 1);
+  constexpr int kSfbChunks = (BN + 127) / 128;
+  constexpr int kSfColsPerStage = 4 + 4 * kSfbChunks;
+  // two accumulators when they fit next to the scale-factor columns (always for the dense kinds)
+  constexpr int kAccStages = 2 * BN + (kScaled ? kMaxStages * kSfColsPerStage : 0) <= kTmemCols ? 2 : 1;
   constexpr int kSfCol = kAccStages * BN;        // first TMEM column of the scale factors
-  constexpr int kSfColsPerStage = 4 + 4 * (BN / 128);
   using L = Layout<BN, kScaled>;
+  constexpr int kStages = L::kStages;
+  constexpr int kStoreBufs = L::kStoreBufs;
   constexpr int kElem = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
   constexpr int kBlockK = kRowBytes / kElem;      // elements of K per stage
 
@@ -209,9 +230,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const uint32_t s_base = smem_u32(smem);
   const uint32_t bar_base = s_base + L::kBarriers;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
-  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kBarriers + 16 * 8);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kBarriers + 16 * 8 + 8);
 
@@ -262,8 +283,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if constexpr (kScaled) {
             bulk_load_1d(ssf, p.sfa + ((size_t)m_blk * p.k_chunks + kc) * 512, 512, full_bar(stage));
 #pragma unroll
-            for (int j = 0; j < BN / 128; ++j)
-              bulk_load_1d(ssf + 512 + 512 * j, p.sfb + ((size_t)(n_blk * (BN / 128) + j) * p.k_chunks + kc) * 512, 512,
+            for (int j = 0; j < kSfbChunks; ++j)
+              bulk_load_1d(ssf + 512 + 512 * j, p.sfb + ((size_t)((n_blk * BN) / 128 + j) * p.k_chunks + kc) * 512, 512,
                            full_bar(stage));
           }
           used |= 1u << stage;
@@ -295,6 +316,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        // a B tile narrower than a 128-row scale chunk starts at one of the chunk's four 32-row TMEM columns
+        const uint32_t sfb_col = (uint32_t)((((tile % tiles_n) * BN) & 127) >> 5);
         for (int kc = 0; kc < p.k_chunks; ++kc) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kErrMmaWaitFull)) {
             ok = false;
@@ -310,14 +333,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             sfb_t = sfa_t + 4;
             tc_cp_sf(sfa_t, desc_sf(ssf));
 #pragma unroll
-            for (int j = 0; j < BN / 128; ++j) tc_cp_sf(sfb_t + 4 * j, desc_sf(ssf + 512 + 512 * j));
+            for (int j = 0; j < kSfbChunks; ++j) tc_cp_sf(sfb_t + 4 * j, desc_sf(ssf + 512 + 512 * j));
           }
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             // 32 bytes of K per instruction: advance the start-address field (16-byte units) inside the swizzle atom
             uint32_t id = idesc;
             if constexpr (kScaled) id |= ((uint32_t)k << 29) | ((uint32_t)k << 4);  // byte k of each scale word
-            umma<kKind>(d_tmem, da + 2u * k, db + 2u * k, id, (kc | k) != 0 ? 1u : 0u, sfa_t, sfb_t);
+            umma<kKind>(d_tmem, da + 2u * k, db + 2u * k, id, (kc | k) != 0 ? 1u : 0u, sfa_t, sfb_t + sfb_col);
           }
           tc_commit(empty_bar(stage));  // arrives when the MMAs that read this slot have completed
           if (++stage == kStages) stage = 0, phase ^= 1u;
@@ -332,7 +355,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // warp) and handed to a TMA store, which writes whole lines and clips at the matrix edges.  Output matrices
     // whose rows are not 16-byte multiples take direct predicated stores instead.
     const int quarter = warp & 3;  // TMEM lanes [32 * quarter, +32) are the ones this warp may read
-    uint8_t *stage_buf = smem + L::kStaging + (warp - 2) * 4096;
+    uint8_t *stage_buf = smem + L::kStaging + (warp - 2) * (kStoreBufs * 2048);
     int buf = 0;
     int local = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
@@ -343,11 +366,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_after();
       const int row0 = m_blk * BM + quarter * 32;
       const int n0 = n_blk * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      // two chunks in flight: the TMEM load of chunk c+1 is issued before chunk c is converted and stored
+      const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      uint32_t vv[2][32];
+      tmem_ld32(t_acc, vv[0]);
+      tmem_ld_wait(vv[0]);
+#pragma unroll
+      for (int ci = 0; ci < BN / 32; ++ci) {
+        const int c = ci * 32;
         if (n0 + c >= p.N) break;  // uniform across the warp
-        uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c), v);
+        uint32_t(&v)[32] = vv[ci & 1];
+        if (ci + 1 < BN / 32 && n0 + c + 32 < p.N) tmem_ld32(t_acc + (uint32_t)(c + 32), vv[(ci + 1) & 1]);
         if (p.bias != nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -367,7 +396,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * t]), __uint_as_float(v[2 * t + 1]));
               w[t] = *reinterpret_cast<uint32_t *>(&h);
             }
-            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStoreBufs - 1) : "memory");
             __syncwarp();
             uint8_t *dst = stage_buf + buf * 2048 + lane * 64;
 #pragma unroll
@@ -380,12 +409,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               tma_store_2d(&map_d, smem_u32(stage_buf + buf * 2048), n0 + c, row0);
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
-            buf ^= 1;
+            buf = (buf + 1) % kStoreBufs;
           } else {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {  // fp32: two boxes of 16 columns (64 bytes per row) per chunk
               if (n0 + c + 16 * h >= p.N) break;
-              if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+              if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStoreBufs - 1) : "memory");
               __syncwarp();
               uint8_t *dst = stage_buf + buf * 2048 + lane * 64;
 #pragma unroll
@@ -398,7 +427,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tma_store_2d(&map_d, smem_u32(stage_buf + buf * 2048), n0 + c + 16 * h, row0);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
               }
-              buf ^= 1;
+              buf = (buf + 1) % kStoreBufs;
             }
           }
         } else if (row0 + lane < p.M) {
@@ -413,6 +442,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
         }
+        tmem_ld_wait(vv[(ci + 1) & 1]);
       }
       tc_fence_before();
       __syncwarp();
@@ -525,6 +555,24 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
+// Tile width: 256 columns when that already gives every SM a tile; narrower tiles for small problems (few rows of
+// activations against a large weight are bound by streaming the weight, which needs many SMs pulling at once).
+template <int kKind>
+static int launch_any(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
+                      int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, cudaStream_t st) {
+  const int64_t tiles_m = (M + BM - 1) / BM;
+  const int sms = sm_count();
+  if (tiles_m * ((N + 255) / 256) * 2 > sms || N <= 64)
+    return launch<kKind, 256>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+  // The block-scaled MMA takes its B scales from TMEM columns whose offset inside a 128-row chunk must be even
+  // (0 or 2), so its narrowest tile is 64 columns; the dense kinds go down to 32.
+  if (kKind == kMxf8 || tiles_m * ((N + 63) / 64) * 2 > sms || N <= 32)
+    return launch<kKind, 64>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+  if constexpr (kKind != kMxf8)
+    return launch<kKind, 32>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+  return MXQ_ERR_UNSUPPORTED;
+}
+
 }  // namespace gemm
 }  // namespace mxq
 
@@ -551,11 +599,11 @@ int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int 
   cudaStream_t st = (cudaStream_t)stream;
   if (in_dtype == MXQ_BF16) {
     if (K % 8) return MXQ_ERR_SHAPE;  // rows must be 16-byte multiples for the tensor map
-    return launch<kBf16, 256>(a, b, nullptr, nullptr, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+    return launch_any<kBf16>(a, b, nullptr, nullptr, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
   }
   if (in_dtype == MXQ_F32) {
     if (K % 4) return MXQ_ERR_SHAPE;
-    return launch<kTf32, 256>(a, b, nullptr, nullptr, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+    return launch_any<kTf32>(a, b, nullptr, nullptr, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
   }
   return MXQ_ERR_DTYPE;
 }
@@ -571,7 +619,7 @@ int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t
   if ((reinterpret_cast<uintptr_t>(a_codes) | reinterpret_cast<uintptr_t>(b_codes) | reinterpret_cast<uintptr_t>(d) |
        reinterpret_cast<uintptr_t>(a_scales) | reinterpret_cast<uintptr_t>(b_scales)) & 15u)
     return MXQ_ERR_ALIGN;
-  return launch<kMxf8, 256>(a_codes, b_codes, a_scales, b_scales, d, bias, out_dtype, bias_dtype, M, N, K, status,
+  return launch_any<kMxf8>(a_codes, b_codes, a_scales, b_scales, d, bias, out_dtype, bias_dtype, M, N, K, status,
                             (cudaStream_t)stream);
 }
 

@@ -330,16 +330,19 @@ mxfp_pack_mma_kernel(const Tin *__restrict__ x, uint8_t *__restrict__ codes, uin
       }
       const int K = exm + up - kTop;
       const uint32_t kodd = (K & 1) ? 0x00800000u : 0u;
-      bool fast = K >= 1;
+      // `fast`: the block's scale is not clamped, elements with exponent code >= 2 are handled on bit patterns.
+      // `clean`: every element of this vector is such an element; the others are patched one by one afterwards.
+      const bool fast = K >= 1;
+      const uint32_t t1_32 = (uint32_t)(K + 2) << 23;  // smallest |x| pattern with exponent code >= 2
+      bool clean = true;
       if constexpr (kBf16In) {
-        const uint32_t t1 = (uint32_t)((K + 1) << 7) * 0x00010001u;
+        const uint32_t t1 = (uint32_t)((K + 2) << 7) * 0x00010001u;
         const __nv_bfloat162 t1v = *reinterpret_cast<const __nv_bfloat162 *>(&t1);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) fast = fast && __hbge2(*reinterpret_cast<const __nv_bfloat162 *>(&a[k]), t1v);
+        for (int k = 0; k < 4; ++k) clean = clean && __hbge2(*reinterpret_cast<const __nv_bfloat162 *>(&a[k]), t1v);
       } else {
-        const uint32_t t1 = (uint32_t)(K + 1) << 23;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) fast = fast && a[k] >= t1;
+        for (int k = 0; k < 4; ++k) clean = clean && a[k] >= t1_32;
       }
       int sh, scale;
       if (K >= 1) {
@@ -348,32 +351,32 @@ mxfp_pack_mma_kernel(const Tin *__restrict__ x, uint8_t *__restrict__ codes, uin
         const MxfpBlock p = mxfp_block(amax, E, tab);
         sh = p.sh, scale = p.scale;
       }
-      // pass 1: the reference's rounding; note whether an element lands on the top E4M3 code (exponent code 15,
-      // fraction 7), which any element of the top binade can do, not only the block maximum
+      // pass 1: the reference's rounding.  Nothing rounds above the top code (a carry out of the top binade is lost),
+      // so a block holds the top E4M3 code (exponent code 15, fraction 7 -- any element of the top binade can land
+      // on it, not only the maximum) iff the largest rounded pattern of the block equals it.
       uint32_t yq[4];     // fast path: rounded |x| patterns (bf16: two per word)
       uint32_t cw[N];     // general path: reference codes
-      int top = 0;
+      uint32_t ymax = 0;  // largest rounded pattern (fast) or largest code magnitude moved to the same scale (general)
       if (fast) {
         if constexpr (kBf16In) {
           const uint32_t kodd2 = kodd ? 0x00800080u : 0u;
-          const uint32_t t16 = (((uint32_t)exm << 7) | (7u << 4)) * 0x00010001u;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            yq[k] = mxfp_round_pair<F>(a[k], kodd2);
-            if constexpr (E == 4 && F == 3) {
-              const uint32_t z = yq[k] ^ t16;  // a zero halfword = that element is the top code
-              top |= (int)(((z - 0x00010001u) & ~z & 0x80008000u) != 0);
-            }
+          for (int k = 0; k < 4; ++k) yq[k] = mxfp_round_pair<F>(a[k], kodd2);
+          if constexpr (E == 4 && F == 3) {
+            __nv_bfloat162 mx = __hmax2(__hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&yq[0]),
+                                                *reinterpret_cast<const __nv_bfloat162 *>(&yq[1])),
+                                        __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&yq[2]),
+                                                *reinterpret_cast<const __nv_bfloat162 *>(&yq[3])));
+            const uint32_t mxb = *reinterpret_cast<uint32_t *>(&mx);
+            ymax = max(mxb & 0xFFFFu, mxb >> 16) == (((uint32_t)exm << 7) | (7u << 4)) ? 1u : 0u;
           }
         } else {
-          const uint32_t t32 = ((uint32_t)exm << 23) | (7u << 20);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            yq[k] = mxfp_round_one<F>(a[k] & 0x7FFFFF00u, kodd);
-            if constexpr (E == 4 && F == 3) top |= (int)(yq[k] == t32);
-          }
+          for (int k = 0; k < 4; ++k) yq[k] = mxfp_round_one<F>(a[k] & 0x7FFFFF00u, kodd);
+          if constexpr (E == 4 && F == 3)
+            ymax = max(max(yq[0], yq[1]), max(yq[2], yq[3])) == (((uint32_t)exm << 23) | (7u << 20)) ? 1u : 0u;
         }
-        if (up) top = 0;  // the maximum was assigned exponent code 14: nothing reaches code 15
+        if (up) ymax = 0;  // the maximum was assigned exponent code 14: nothing reaches code 15
       } else {
         uint32_t b[N];
         unpack(raw, b);
@@ -381,31 +384,48 @@ mxfp_pack_mma_kernel(const Tin *__restrict__ x, uint8_t *__restrict__ codes, uin
         for (int k = 0; k < N; ++k) {
           if (((b[k] & 0x7FFFFFFFu) >> 23) == 0) b[k] = 0;
           cw[k] = mxfp_encode(b[k], sh, E, F);
-          if constexpr (E == 4 && F == 3) top |= (int)((cw[k] & 0x7Fu) == 0x7Fu);
+          if constexpr (E == 4 && F == 3) ymax |= (cw[k] & 0x7Fu) == 0x7Fu ? 1u : 0u;
         }
       }
+      int top = (int)ymax;
       if constexpr (E == 4 && F == 3) {
         for (int o = 1; o < kGroup; o <<= 1) top |= __shfl_xor_sync(0xFFFFFFFFu, top, o);
       }
       if (i >= n_vec) continue;  // after the shuffles: every lane of the warp takes part in them
-      // pass 2: values in units of the (possibly raised) scale, converted to hardware E4M3
+      // pass 2: hardware E4M3 bytes.  With exponent codes >= 2 everywhere the byte is sign | (exponent code, fraction)
+      // re-biased to E4M3 -- read straight off the rounded pattern -- and raising the scale by one just lowers the
+      // exponent code by one.  The general path goes through the value and the hardware conversion.
       uint32_t c2[N / 2];  // two E4M3 bytes per word (low 16 bits)
       if (fast) {
-        const uint32_t shb = (uint32_t)(sh + top) << 23;  // division by the scale = exponent subtraction
+        const uint32_t kh = (uint32_t)(K + kBias - 7 + top) << 3;  // pattern exponent -> E4M3 exponent code
         if constexpr (kBf16In) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint32_t w = yq[k] | (r[k] & 0x80008000u);
-            c2[k] = __nv_cvt_float2_to_fp8x2(make_float2(__uint_as_float((w << 16) - shb),
-                                                         __uint_as_float((w & 0xFFFF0000u) - shb)),
-                                             __NV_SATFINITE, __NV_E4M3);
+            // bit 15 of each half absorbs the borrow of an element that is too small for this path (patched below)
+            const uint32_t m2 = ((((yq[k] >> 4) | 0x80008000u) - kh * 0x00010001u) & 0x007F007Fu) | ((r[k] >> 8) & 0x00800080u);
+            c2[k] = __byte_perm(m2, 0, 0x4420);  // bytes 0 and 2 -> low 16 bits
           }
         } else {
-          float v[4];
+          uint32_t m[4];
 #pragma unroll
-          for (int k = 0; k < 4; ++k) v[k] = __uint_as_float((yq[k] | (r[k] & 0x80000000u)) - shb);
-          c2[0] = __nv_cvt_float2_to_fp8x2(make_float2(v[0], v[1]), __NV_SATFINITE, __NV_E4M3);
-          c2[1] = __nv_cvt_float2_to_fp8x2(make_float2(v[2], v[3]), __NV_SATFINITE, __NV_E4M3);
+          for (int k = 0; k < 4; ++k) m[k] = (((yq[k] >> 20) - kh) & 0x7Fu) | ((r[k] >> 24) & 0x80u);
+          c2[0] = m[0] | (m[1] << 8), c2[1] = m[2] | (m[3] << 8);
+        }
+        if (!clean) {
+          // elements below exponent code 2 (subnormal codes, underflow, zeros): the reference's element codec, then
+          // the exact value (halved if the scale was raised) through the hardware conversion
+          uint32_t b[N];
+          unpack(raw, b);
+          const float half = top ? 0.5f : 1.f;
+#pragma unroll
+          for (int k = 0; k < N; ++k) {
+            if ((b[k] & 0x7FFFFFFFu) < t1_32) {
+              const uint32_t bb = ((b[k] & 0x7FFFFFFFu) >> 23) == 0 ? 0u : b[k];
+              const float v = mxfp_decode(mxfp_encode(bb, sh, E, F), E, F) * half;
+              const uint32_t byte = __nv_cvt_float2_to_fp8x2(make_float2(v, 0.f), __NV_SATFINITE, __NV_E4M3) & 0xFFu;
+              c2[k / 2] = (k & 1) ? ((c2[k / 2] & 0x00FFu) | (byte << 8)) : ((c2[k / 2] & 0xFF00u) | byte);
+            }
+          }
         }
       } else {
         const float half = top ? 0.5f : 1.f;

@@ -27,7 +27,7 @@ def quantized_operands(M, K, N, seed, dtype):
 
 
 @pytest.mark.parametrize("shape", [(128, 64, 256), (128, 256, 256), (256, 512, 512), (1, 128, 256), (77, 192, 384),
-                                   (300, 4096, 1000), (128, 72, 256), (2048, 1024, 4096)])
+                                   (300, 4096, 1000), (128, 72, 256), (2048, 1024, 4096), (256, 512, 4096), (16, 1024, 4096)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_dense_gemm_matches_fp32_reference(shape, dtype):
     M, K, N = shape
@@ -59,7 +59,7 @@ def test_dense_gemm_bias_and_leading_dims():
 
 
 @pytest.mark.parametrize("shape", [(128, 128, 256), (128, 512, 256), (256, 4096, 512), (1, 4096, 4096), (16, 4096, 4096),
-                                   (200, 1024, 640), (2048, 4096, 4096)])
+                                   (200, 1024, 640), (2048, 4096, 4096), (256, 512, 4096), (128, 4096, 4096)])
 def test_mxf8_gemm_matches_oracle(shape):
     """Block-scaled GEMM of MXFP8-quantized activations and weights vs fp32 GEMM of the oracle's fake-quant values."""
     M, K, N = shape
