@@ -114,3 +114,27 @@ def test_bypass_and_unloaded_weights():
         layer.weight.mul_(2.0)
     assert layer._packed_weight() is None
     gemm.check_status()
+
+
+def test_large_m_with_bias_vs_oracle():
+    """Several waves of tiles, a ragged last 128-row panel and a bias."""
+    M, K, N = 4736 + 77, 512, 4096
+    x, w = synthetic.linear_operands(M, K, N, seed=12)
+    g = torch.Generator().manual_seed(12)
+    b = torch.randn(N, generator=g).bfloat16()
+    cfg = {"weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3,
+           "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    layer = mb.LinearMXFP(K, N, bias=True, device=DEV, dtype=torch.bfloat16, config=cfg)
+    layer.load_state_dict({"weight": w.to(DEV), "bias": b.to(DEV)}, strict=False)
+    xd = x.to(DEV)
+    y1 = layer(xd)
+    y2 = layer(xd)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert torch.equal(y1, y2)
+    ref = O.linear_mxfp(x, O.mxfp_fake(w, 32, 4, 3, 1), b, cfg)
+    assert rel_err(y1, ref) <= 4e-3
+    # same result as the two-kernel path on one stream
+    xp = gemm.pack_mx_operand(xd, 4, 3)
+    y3 = gemm.mx_gemm(xp, layer._packed_weight(), layer.bias, torch.bfloat16)
+    assert torch.equal(y1, y3)
