@@ -217,8 +217,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   constexpr int kSfbChunks = (BN + 127) / 128;
   constexpr int kSfColsPerStage = 4 + 4 * kSfbChunks;
   // two accumulators when they fit next to the scale-factor columns (always for the dense kinds)
-  constexpr int kAccStages = 2 * BN + (kScaled ? kMaxStages * kSfColsPerStage : 0) <= kTmemCols ? 2 : 1;
-  constexpr int kSfCol = kAccStages * BN;        // first TMEM column of the scale factors
+  // Two accumulators of BN columns when they fit next to the scale-factor columns (always for the dense kinds).
+  // The block-scaled 256-column tile does not fit twice (2 x 256 + 48 > 512): its two accumulators overlap by 64
+  // columns -- [0, 256) and [192, 448), scale factors from column 448 -- and the epilogue drains the shared 64
+  // columns first and says so on its own barrier, so that the next tile's MMAs wait for a quarter of the epilogue
+  // instead of all of it.
+  constexpr bool kOverlap = kScaled && BN == 256;
+  constexpr int kAccStages =
+      kOverlap || 2 * BN + (kScaled ? kMaxStages * kSfColsPerStage : 0) <= kTmemCols ? 2 : 1;
+  constexpr int kAccStride = kOverlap ? 192 : BN;  // first column of accumulator 1
+  constexpr int kSfCol = kOverlap ? 448 : kAccStages * BN;  // first TMEM column of the scale factors
   using L = Layout<BN, kScaled>;
   constexpr int kStages = L::kStages;
   constexpr int kStoreBufs = L::kStoreBufs;
@@ -233,6 +241,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
   auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
+  const uint32_t overlap_bar = bar_base + 8u * (2 * kMaxStages + 4);  // shared accumulator columns drained
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kBarriers + 16 * 8);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kBarriers + 16 * 8 + 8);
 
@@ -243,6 +252,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), 1), mbar_init(empty_bar(s), 1);
     for (int a = 0; a < 2; ++a) mbar_init(acc_full_bar(a), 1), mbar_init(acc_empty_bar(a), 4);
+    mbar_init(overlap_bar, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -314,8 +324,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int acc = local % kAccStages;
         const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
+        if constexpr (kOverlap) {  // the previous tile's epilogue has read the columns both accumulators share
+          if (local > 0 &&
+              !mbar_wait(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc))
+            break;
+        }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccStride);
         // a B tile narrower than a 128-row scale chunk starts at one of the chunk's four 32-row TMEM columns
         const uint32_t sfb_col = (uint32_t)((((tile % tiles_n) * BN) & 127) >> 5);
         for (int kc = 0; kc < p.k_chunks; ++kc) {
@@ -367,16 +382,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int row0 = m_blk * BM + quarter * 32;
       const int n0 = n_blk * BN;
       // two chunks in flight: the TMEM load of chunk c+1 is issued before chunk c is converted and stored
-      const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride);
+      // chunk order: with overlapping accumulators the 64 shared columns go first (the last two chunks of
+      // accumulator 0, the first two of accumulator 1)
+      const int first = kOverlap && acc == 0 ? BN / 32 - 2 : 0;
       uint32_t vv[2][32];
-      tmem_ld32(t_acc, vv[0]);
+      tmem_ld32(t_acc + (uint32_t)(first * 32), vv[0]);
       tmem_ld_wait(vv[0]);
 #pragma unroll
       for (int ci = 0; ci < BN / 32; ++ci) {
-        const int c = ci * 32;
-        if (n0 + c >= p.N) break;  // uniform across the warp
+        const int c = ((ci + first) % (BN / 32)) * 32;
+        const bool active = n0 + c < p.N;  // uniform across the warp; chunks past the edge are read but not stored
         uint32_t(&v)[32] = vv[ci & 1];
-        if (ci + 1 < BN / 32 && n0 + c + 32 < p.N) tmem_ld32(t_acc + (uint32_t)(c + 32), vv[(ci + 1) & 1]);
+        if (ci + 1 < BN / 32) tmem_ld32(t_acc + (uint32_t)(((ci + 1 + first) % (BN / 32)) * 32), vv[(ci + 1) & 1]);
         if (p.bias != nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -388,7 +406,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
           }
         }
-        if (p.tma_store) {
+        if (!active) {
+          // nothing to store
+        } else if (p.tma_store) {
           if (p.out_bf16) {
             uint32_t w[16];
 #pragma unroll
@@ -443,6 +463,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
         tmem_ld_wait(vv[(ci + 1) & 1]);
+        if constexpr (kOverlap) {
+          if (ci == 0) {  // chunks 0 and 1 of this order -- the shared columns -- are in registers now
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(overlap_bar);
+          }
+        }
       }
       tc_fence_before();
       __syncwarp();
