@@ -97,6 +97,13 @@ int mxq_minifloat_fake(const void *x, void *y, int in_dtype, int out_dtype, int6
 int mxq_bfp_fake(const void *x, void *y, int dtype, int64_t rows, int64_t cols, int bs, int width, int exp_width,
                  int exp_bias, const uint8_t *ceil_tab_host, void *stream);
 
+/* Block floating point with two-dimensional tiles of bh x bw over the last two dimensions of x[batch, rows, cols]
+ * (ragged edges are zero padding).  Replaces _block_fp_quantize (chop/nn/quantizers/block_fp.py:7-82) for the tilings
+ * that go through F.unfold / F.fold: 2-D weights with skip_first_dim=False (chop/nn/quantizers/utils.py:228-276) and
+ * 3-D activations (utils.py:278-323).  A result of -0.0 is returned as +0.0, as after the reference's fold. */
+int mxq_bfp_fake_tiles(const void *x, void *y, int dtype, int64_t batch, int64_t rows, int64_t cols, int bh, int bw,
+                       int width, int exp_width, int exp_bias, const uint8_t *ceil_tab_host, void *stream);
+
 /*
  * Forward GEMM of the quantized Linear modules: D[M,N] = A[M,K] * B[N,K]^T (+ bias[N]), fp32 accumulation on the
  * tcgen05 tensor cores.  Replaces the `F.linear(x, self.weight, self.bias)` at the end of LinearMXFP.forward,

@@ -33,6 +33,8 @@ _PROTOTYPES = {
                       c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
     "mxq_mx_linear_static": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
                              c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "mxq_bfp_fake_tiles": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p, c_void_p],
     "mxq_bfp_fake": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
 }
 

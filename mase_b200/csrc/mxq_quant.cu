@@ -411,6 +411,52 @@ bfp_generic_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, int
   }
 }
 
+// Tiles of bh x bw over the last two dimensions of x[batch, rows, cols] (ragged edges count as zero padding).
+// A group of G threads owns one tile: a warp for tiles of up to 2048 elements, a whole CTA above that.  Pass 1 finds
+// the tile maximum, pass 2 re-reads the tile (from L1/L2) and applies the element-wise restatement of the reference.
+template <typename T, int G>
+__global__ void __launch_bounds__(kThreads)
+bfp_tile_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t batch, int rows, int cols, int bh, int bw, int width,
+                int exp_width, int exp_bias, const __grid_constant__ Log2Tab tab) {
+  __shared__ float warp_max[kThreads / 32];
+  const int tiles_r = (rows + bh - 1) / bh, tiles_c = (cols + bw - 1) / bw;
+  const int64_t n_tiles = batch * tiles_r * tiles_c;
+  const int groups_per_cta = kThreads / G;
+  const int g = threadIdx.x / G, t = threadIdx.x % G;
+  for (int64_t tile0 = (int64_t)blockIdx.x * groups_per_cta; tile0 < n_tiles; tile0 += (int64_t)gridDim.x * groups_per_cta) {
+    const int64_t tile = tile0 + g;
+    const bool live = tile < n_tiles;
+    int64_t b = 0;
+    int r0 = 0, c0 = 0, vh = 0, vw = 1;
+    if (live) {
+      b = tile / (tiles_r * tiles_c);
+      const int rem = (int)(tile - b * (tiles_r * tiles_c));
+      r0 = (rem / tiles_c) * bh, c0 = (rem % tiles_c) * bw;
+      vh = min(bh, rows - r0), vw = min(bw, cols - c0);
+    }
+    const T *xt = x + (b * rows + r0) * (int64_t)cols + c0;
+    T *yt = y + (b * rows + r0) * (int64_t)cols + c0;
+    const int n = vh * vw;
+    float amax = 0.f;
+    for (int e = t; e < n; e += G) amax = fmaxf(amax, fabsf(load_scalar(xt + (int64_t)(e / vw) * cols + e % vw)));
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if constexpr (G > 32) {
+      __syncthreads();  // previous iteration's readers are done
+      if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+      __syncthreads();
+      amax = 0.f;
+#pragma unroll
+      for (int w = 0; w < kThreads / 32; ++w) amax = fmaxf(amax, warp_max[w]);
+    }
+    const BfpBlock p = bfp_block<T>(amax, width, exp_width, exp_bias, tab);
+    for (int e = t; e < n; e += G) {
+      const int64_t off = (int64_t)(e / vw) * cols + e % vw;
+      // the reference folds tiles back by adding them into zeros: -0.0 comes out as +0.0
+      store_scalar(yt + off, bfp_elem<T>(load_scalar(xt + off), p) + 0.f);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------
@@ -683,6 +729,37 @@ int mxq_bfp_fake(const void *x, void *y, int dtype, int64_t rows, int64_t cols, 
   } else {
     return MXQ_ERR_DTYPE;
   }
+  return check_launch();
+}
+
+int mxq_bfp_fake_tiles(const void *x, void *y, int dtype, int64_t batch, int64_t rows, int64_t cols, int bh, int bw,
+                       int width, int exp_width, int exp_bias, const uint8_t *ceil_tab_host, void *stream) {
+  if (batch == 0 || rows == 0 || cols == 0) return MXQ_OK;
+  if (!x || !y || !ceil_tab_host) return MXQ_ERR_NULL;
+  if (batch < 0 || rows < 0 || cols < 0 || rows > INT32_MAX || cols > INT32_MAX || bh < 1 || bw < 1) return MXQ_ERR_SHAPE;
+  if (width < 2 || width > 24 || exp_width < 1 || exp_width > 8) return MXQ_ERR_FORMAT;
+  if (bh > rows) bh = (int)rows;
+  if (bw > cols) bw = (int)cols;
+  const Log2Tab tab = load_tab(ceil_tab_host);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t n_tiles = batch * ((rows + bh - 1) / bh) * ((cols + bw - 1) / bw);
+  const bool small = (int64_t)bh * bw <= 2048;
+  const int grid = grid_for(n_tiles, small ? kThreads / 32 : 1);
+#define MXQ_TILES(T)                                                                                            \
+  if (small)                                                                                                    \
+    bfp_tile_kernel<T, 32><<<grid, kThreads, 0, st>>>((const T *)x, (T *)y, batch, (int)rows, (int)cols, bh, bw, \
+                                                      width, exp_width, exp_bias, tab);                         \
+  else                                                                                                          \
+    bfp_tile_kernel<T, kThreads><<<grid, kThreads, 0, st>>>((const T *)x, (T *)y, batch, (int)rows, (int)cols, bh, \
+                                                            bw, width, exp_width, exp_bias, tab);
+  if (dtype == MXQ_F32) {
+    MXQ_TILES(float)
+  } else if (dtype == MXQ_BF16) {
+    MXQ_TILES(__nv_bfloat16)
+  } else {
+    return MXQ_ERR_DTYPE;
+  }
+#undef MXQ_TILES
   return check_launch();
 }
 

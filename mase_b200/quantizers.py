@@ -492,30 +492,24 @@ def _infer_block_shape(x_shape: list[int], block_shape: list[int]) -> list[int]:
     return [x_shape[i] if inferred[i] == -1 or inferred[i] > x_shape[i] else inferred[i] for i in range(nd)]
 
 
-def _bfp_row_tile(shape: tuple[int, ...], block_size: list[int], skip_first_dim: bool) -> int:
-    """Tile length along the last dim if every tile lies within one row, else raises."""
+def _bfp_tile(shape: tuple[int, ...], block_size: list[int], skip_first_dim: bool) -> tuple[int, int]:
+    """(tile rows, tile columns) over the last two dims, following the reference's `block` dispatch
+    (chop/nn/quantizers/utils.py:486-514): 1-D bias, 2-D activation (first dim never blocked), 2-D weight,
+    3-D activation.  Tile rows == 1 means tiles of consecutive elements of the last dimension."""
     nd = len(shape)
     if nd == 1:
         assert skip_first_dim is False, "skip_first_dim must be False for bias to be blocked"
-        tile = _infer_block_shape(list(shape), block_size)
-    elif nd == 2:
+        return 1, _infer_block_shape(list(shape), block_size)[0]
+    if nd == 2:
         ref_shape = [1, shape[1]] if skip_first_dim else list(shape)
         tile = _infer_block_shape(ref_shape, block_size)
-    elif nd == 3:
+        return tile[0], tile[1]
+    if nd == 3:
         if not skip_first_dim:
             raise NotImplementedError("block 3d weight is not supported.")
         tile = _infer_block_shape([1, *shape[1:]], block_size)
-    else:
-        raise RuntimeError(f"Unsupported x.ndim = {nd}")
-    # dims other than the last must have extent-1 tiles (or the dim itself has extent 1)
-    for d in range(nd - 1):
-        extent = 1 if (d == 0 and skip_first_dim and nd > 1) else shape[d]
-        if tile[d] != 1 and extent != 1:
-            raise NotImplementedError(
-                f"block_fp: tile {tile} spans several rows of a tensor of shape {tuple(shape)}; only tiles of consecutive "
-                "elements of the last dimension are provided"
-            )
-    return tile[-1]
+        return tile[1], tile[2]
+    raise RuntimeError(f"Unsupported x.ndim = {nd}")
 
 
 def _block_fp_quantize(x: Tensor, width=12, exponent_width=8, exponent_bias=None, block_size=[16], skip_first_dim=True):
@@ -525,17 +519,25 @@ def _block_fp_quantize(x: Tensor, width=12, exponent_width=8, exponent_bias=None
     dt = _dtype_code(x.dtype, "block_fp")
     if exponent_bias in (None, "none", "None"):
         exponent_bias = 2 ** (exponent_width - 1) - 1
+    bh, bw = _bfp_tile(tuple(x.shape), list(block_size), skip_first_dim)
     if x.numel() == 0:
         return x.clone()
-    bs = _bfp_row_tile(tuple(x.shape), list(block_size), skip_first_dim)
     xc = x.contiguous()
     cols = xc.shape[-1]
-    rows = xc.numel() // cols
     y = torch.empty_like(xc)
+    lib = _lib.lib()
     with _on_device(x):
-        rc = _lib.lib().mxq_bfp_fake(xc.data_ptr(), y.data_ptr(), dt, rows, cols, bs, width, exponent_width,
-                                     int(exponent_bias), _ceil_tab_ptr(x.dtype), _stream(x))
-    _lib.check(rc, "mxq_bfp_fake")
+        if bh == 1 or x.dim() == 1 or xc.shape[-2] == 1:
+            # tiles of consecutive elements of the last dimension
+            rc = lib.mxq_bfp_fake(xc.data_ptr(), y.data_ptr(), dt, xc.numel() // cols, cols, bw, width, exponent_width,
+                                  int(exponent_bias), _ceil_tab_ptr(x.dtype), _stream(x))
+            what = "mxq_bfp_fake"
+        else:
+            rows = xc.shape[-2]
+            rc = lib.mxq_bfp_fake_tiles(xc.data_ptr(), y.data_ptr(), dt, xc.numel() // (rows * cols), rows, cols, bh, bw,
+                                        width, exponent_width, int(exponent_bias), _ceil_tab_ptr(x.dtype), _stream(x))
+            what = "mxq_bfp_fake_tiles"
+    _lib.check(rc, what)
     return y
 
 

@@ -267,6 +267,25 @@ def bfp_fake_rows(x: Tensor, width: int, exponent_width: int, exponent_bias, bs:
     return out.reshape(shape)
 
 
+def bfp_fake_tiles(x: Tensor, width: int, exponent_width: int, exponent_bias, bh: int, bw: int) -> Tensor:
+    """Block floating point with tiles of bh x bw over the last two dimensions (2-D weights with
+    `skip_first_dim=False`, 3-D activations: utils.py:_block_2d_weight / _block_3d_activation).  Ragged edges
+    are padded with zeros at the end of each dimension.  The reference reassembles the tiles with F.fold, which
+    adds them into a zero tensor, so a -0.0 result becomes +0.0 on this route."""
+    shape = x.shape
+    R, C = shape[-2], shape[-1]
+    bh, bw = min(bh, R), min(bw, C)
+    x3 = x.reshape(-1, R, C)
+    B = x3.shape[0]
+    pr, pc = (-R) % bh, (-C) % bw
+    xp = torch.nn.functional.pad(x3, (0, pc, 0, pr))
+    Rp, Cp = R + pr, C + pc
+    tiles = xp.reshape(B, Rp // bh, bh, Cp // bw, bw).permute(0, 1, 3, 2, 4).reshape(-1, bh * bw)
+    yt = bfp_fake_rows(tiles, width, exponent_width, exponent_bias, bh * bw)
+    y = yt.reshape(B, Rp // bh, Cp // bw, bh, bw).permute(0, 1, 3, 2, 4).reshape(B, Rp, Cp)[:, :R, :C]
+    return (y + torch.zeros_like(y)).reshape(shape)  # -0.0 + 0.0 = +0.0, as after F.fold
+
+
 # --------------------------------------------------------------------------------------------------
 # quantized Linear forward (quantized/modules/linear.py:877-895, 956-972; functional/linear.py:220-278)
 # --------------------------------------------------------------------------------------------------

@@ -157,6 +157,20 @@ def main(root: str) -> None:
                 index.append({"kind": "bfp", "input": key, "tag": tag, "width": width, "exponent_width": ew,
                               "exponent_bias": eb, "block_size": bs, "skip_first_dim": skip})
 
+    # block floating point with tiles that span rows (2-D weights, 3-D activations: the unfold / fold route)
+    g = torch.Generator().manual_seed(55)
+    for tname, shape, bs, skip in (("w64x96_b16", (64, 96), [16], False), ("w70x100_b16x32", (70, 100), [16, 32], False),
+                                   ("a3x20x40_b16", (3, 20, 40), [16], True), ("a2x33x50_b8x8", (2, 33, 50), [8, 8], True)):
+        xt = torch.randn(*shape, generator=g) * torch.exp2(torch.randint(-12, 6, shape, generator=g).float())
+        xt.view(-1)[::7] = 0
+        for dt_name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+            x = xt.to(dt)
+            arrays[f"bfp_tiles/{tname}/{dt_name}/x"] = bits(x)
+            for width in (8, 12):
+                arrays[f"bfp_tiles/{tname}/{dt_name}/w{width}/fake"] = bits(q.block_fp_quantizer(x, width, 8, 127, bs, skip))
+            index.append({"kind": "bfp_tiles", "name": tname, "dtype": dt_name, "shape": list(shape), "block_size": bs,
+                          "skip_first_dim": skip, "widths": [8, 12]})
+
     # block_dim other than the last, on a 3-D tensor
     g = torch.Generator().manual_seed(99)
     x3 = torch.randn(6, 64, 10, generator=g)

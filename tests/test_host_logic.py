@@ -94,19 +94,18 @@ def test_permute_helpers_match_oracle():
 
 
 def test_bfp_tile_inference():
-    t = quantizers._bfp_row_tile
-    assert t((64, 128), [1, 16], True) == 16
-    assert t((64, 128), [16], True) == 16          # 2-D activation: first dim is always 1
-    assert t((64, 128), [8, 16], True) == 16
-    assert t((64, 128), [1, 16], False) == 16
-    assert t((64, 128), [1, 256], False) == 128    # oversize tile takes the whole row
-    assert t((96,), [16], False) == 16
-    assert t((4, 7, 40), [1, 16], True) == 16
-    assert t((1, 128), [16], False) == 16
-    with pytest.raises(NotImplementedError):
-        t((64, 128), [16], False)                   # [64,16] tile
-    with pytest.raises(NotImplementedError):
-        t((4, 7, 40), [16], True)                   # [1,7,16] tile
+    t = quantizers._bfp_tile
+    assert t((64, 128), [1, 16], True) == (1, 16)
+    assert t((64, 128), [16], True) == (1, 16)          # 2-D activation: first dim is never blocked
+    assert t((64, 128), [8, 16], True) == (1, 16)
+    assert t((64, 128), [1, 16], False) == (1, 16)
+    assert t((64, 128), [1, 256], False) == (1, 128)    # oversize tile takes the whole row
+    assert t((64, 128), [16], False) == (64, 16)        # 2-D weight, one entry: whole columns of 16
+    assert t((64, 128), [16, 32], False) == (16, 32)
+    assert t((96,), [16], False) == (1, 16)
+    assert t((4, 7, 40), [1, 16], True) == (1, 16)
+    assert t((4, 7, 40), [16], True) == (7, 16)         # 3-D activation, one entry: all tokens x 16 features
+    assert t((4, 7, 40), [4, 16], True) == (4, 16)
     with pytest.raises(NotImplementedError):
         t((4, 7, 40), [1, 16], False)
     with pytest.raises(RuntimeError):

@@ -13,7 +13,7 @@ def _cases(golden, kind):
 
 def test_fixture_inventory(golden):
     kinds = {c["kind"] for c in golden.cases}
-    assert kinds == {"mxint", "mxfp", "minifloat", "bfp", "blockdim", "linear"}
+    assert kinds == {"mxint", "mxfp", "minifloat", "bfp", "bfp_tiles", "blockdim", "linear"}
     assert len(golden.cases) >= 200
 
 
@@ -46,6 +46,17 @@ def test_bfp_oracle_matches_reference(golden):
         x = golden.tensor(c["input"] + "/x")
         y = O.bfp_fake_rows(x, c["width"], c["exponent_width"], c["exponent_bias"], c["block_size"][-1])
         assert_bits_equal(y, golden.tensor(c["tag"] + "/fake"), c["tag"])
+
+
+def test_bfp_tiles_oracle_matches_reference(golden):
+    from mase_b200.quantizers import _bfp_tile
+
+    for c in _cases(golden, "bfp_tiles"):
+        x = golden.tensor(f"bfp_tiles/{c['name']}/{c['dtype']}/x")
+        bh, bw = _bfp_tile(tuple(c["shape"]), c["block_size"], c["skip_first_dim"])
+        for width in c["widths"]:
+            ref = golden.tensor(f"bfp_tiles/{c['name']}/{c['dtype']}/w{width}/fake")
+            assert_bits_equal(O.bfp_fake_tiles(x, width, 8, 127, bh, bw), ref, f"{c['name']} w{width}", signed_zero=False)
 
 
 def test_block_dim_oracle_matches_reference(golden):

@@ -56,6 +56,15 @@ def test_bfp_golden(golden):
         assert_bits_equal(y, golden.tensor(c["tag"] + "/fake"), c["tag"])
 
 
+def test_bfp_tiles_golden(golden):
+    for c in _cases(golden, "bfp_tiles"):
+        x = golden.tensor(f"bfp_tiles/{c['name']}/{c['dtype']}/x").to(DEV)
+        for width in c["widths"]:
+            ref = golden.tensor(f"bfp_tiles/{c['name']}/{c['dtype']}/w{width}/fake")
+            y = mb.block_fp_quantizer(x, width, 8, 127, c["block_size"], c["skip_first_dim"])
+            assert_bits_equal(y, ref, f"{c['name']} w{width}", signed_zero=False)
+
+
 def test_block_dim_golden(golden):
     for c in _cases(golden, "blockdim"):
         dt, bd, blk = c["dtype"], c["block_dim"], c["block"]
@@ -182,7 +191,7 @@ def test_errors_and_unsupported():
     with pytest.raises(AssertionError):
         mb.mxfp_quantizer(torch.randn(4, 32, device=DEV), 32, 3, 3)
     with pytest.raises(NotImplementedError):
-        mb.block_fp_quantizer(torch.randn(64, 64, device=DEV), 8, 8, 127, [16], False)  # [64,16] tile spans rows
+        mb.block_fp_quantizer(torch.randn(2, 8, 64, device=DEV), 8, 8, 127, [16], False)  # 3-D weights: as the reference
 
 
 def test_output_dtype_and_autograd():
@@ -226,3 +235,20 @@ def test_full_size_properties():
     assert_bits_equal(yi[idx], O.mxint_fake(xs, 32, 8), "sampled rows mxint8")
     yb = mb.block_fp_quantizer(x, 8, 8, 127, [1, 32], True)
     assert_bits_equal(yb[idx], O.bfp_fake_rows(xs, 8, 8, 127, 32), "sampled rows bfp")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_block_fp_two_dimensional_tiles_vs_oracle(dtype):
+    """Tiles that span rows: 2-D weights with skip_first_dim=False and 3-D activations (the reference's unfold/fold
+    route; signed zeros come out positive there)."""
+    g = torch.Generator().manual_seed(21)
+    cases = [((64, 96), [16], False, 64, 16), ((64, 96), [16, 16], False, 16, 16), ((70, 100), [16, 32], False, 16, 32),
+             ((300, 40), [8], False, 300, 8), ((3, 20, 40), [16], True, 20, 16), ((2, 33, 50), [8, 8], True, 8, 8),
+             ((4096, 64), [16], False, 4096, 16)]
+    for shape, bs, skip, bh, bw in cases:
+        x = torch.randn(*shape, generator=g) * torch.exp2(torch.randint(-12, 6, shape, generator=g).float())
+        x.view(-1)[::7] = 0
+        x = x.to(dtype)
+        for width, ew, eb in ((8, 8, 127), (7, 8, 127), (12, 8, None)):
+            y = mb.block_fp_quantizer(x.to(DEV), width, ew, eb, bs, skip)
+            assert_bits_equal(y, O.bfp_fake_tiles(x, width, ew, eb, bh, bw), f"{shape} {bs} w{width}", signed_zero=False)
