@@ -297,29 +297,31 @@ def tp_stack_extras(device, rank: int, world: int) -> dict:
         for (n, k, mode) in ((ffn, hidden, "column"), (ffn, hidden, "column"), (hidden, ffn, "row")):
             # every rank draws the same full weight (same seed) and keeps its shard
             w = (torch.randn(n, k, generator=gen, device=device) * 0.02).to(torch.bfloat16)
-            kw = {"chunks": 4} if mode == "row" and world > 1 else {}
+            kw = {"reduce": "scatter_gather"} if mode == "row" else {}
             mods.append(tpmod.build_tp_linear(mb.LinearMXFP, w, None, cfg, mode, tp, device=device, **kw))
             del w
         stack.append(tpmod.TPGatedMLP(*mods))
     x0 = torch.randn(M, hidden, generator=gen, device=device).to(torch.bfloat16)
 
-    def step():
-        x = x0
-        for layer in stack:
-            x = layer(x)
-        return x
+    results = {}
+    for micro in ((1,) if world == 1 else (1, 2)):
+        def step():
+            return tpmod.run_mlp_stack(stack, x0, micro_batches=micro)
 
-    for _ in range(2):
-        step()
-    steps = 3
-    sec = time_region(step, steps, world, device)
+        for _ in range(2):
+            step()
+        steps = 3
+        results[micro] = time_region(step, steps, world, device) / steps
     gemm.check_status()
+    micro, sec_step = min(results.items(), key=lambda kv: kv[1])
     flops = layers * 3 * 2.0 * M * hidden * ffn
     del stack
     torch.cuda.empty_cache()
     return {"config": "4 x (gate, up: 8192->28672 column; down: 28672->8192 row + all-reduce), M=8192, W E2M1 / A E4M3",
-            "ms_per_step": sec / steps * 1e3, "TFLOPs_aggregate": flops * steps / sec / 1e12, "n_gpus": world,
-            "scaling": "strong"}
+            "ms_per_step": sec_step * 1e3, "TFLOPs_aggregate": flops / sec_step / 1e12, "n_gpus": world,
+            "scaling": "strong", "micro_batches": micro,
+            "ms_per_step_by_micro_batches": {str(k): v * 1e3 for k, v in results.items()},
+            "reduction": "fp32 reduce-scatter + bf16 all-gather on a side stream"}
 
 
 def run_ours(args) -> None:

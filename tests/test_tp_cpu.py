@@ -50,9 +50,13 @@ def _worker(rank, world, port, results):
         ref = ref_mlp(x)
         gate = tpmod.ColumnParallelLinear(OracleLinearMXFP(tpmod.shard_linear_weight(wg, "column", tp), CFG), tp)
         up = tpmod.ColumnParallelLinear(OracleLinearMXFP(tpmod.shard_linear_weight(wu, "column", tp), CFG), tp)
-        down = tpmod.RowParallelLinear(OracleLinearMXFP(tpmod.shard_linear_weight(wd, "row", tp), CFG), tp, bias, chunks=3)
-        y = tpmod.TPGatedMLP(gate, up, down)(x)
+        down = tpmod.RowParallelLinear(OracleLinearMXFP(tpmod.shard_linear_weight(wd, "row", tp), CFG), tp, bias)
+        mlp = tpmod.TPGatedMLP(gate, up, down)
+        y = mlp(x)
         err = float((y.float() - ref.float()).abs().max() / ref.float().abs().max())
+        # micro-batched stack runner gives the same rows
+        y2 = tpmod.run_mlp_stack([mlp], x, micro_batches=2)
+        err = max(err, float((y2.float() - ref.float()).abs().max() / ref.float().abs().max()))
         # column-parallel output gathered back equals the unsharded layer bit for bit
         full = tpmod.ColumnParallelLinear(OracleLinearMXFP(tpmod.shard_linear_weight(wg, "column", tp), CFG), tp,
                                           gather_output=True)(x)

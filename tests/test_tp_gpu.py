@@ -34,10 +34,12 @@ def _worker(rank, world, port, results):
         mlp = tpmod.TPGatedMLP(
             tpmod.build_tp_linear(mb.LinearMXFP, wg, None, CFG, "column", tp, device=dev),
             tpmod.build_tp_linear(mb.LinearMXFP, wu, None, CFG, "column", tp, device=dev),
-            tpmod.build_tp_linear(mb.LinearMXFP, wd, None, CFG, "row", tp, device=dev, chunks=2),
+            tpmod.build_tp_linear(mb.LinearMXFP, wd, None, CFG, "row", tp, device=dev, reduce="scatter_gather"),
         )
         y = mlp(x.to(dev))
+        y2 = tpmod.run_mlp_stack([mlp], x.to(dev), micro_batches=2)
         torch.cuda.synchronize()
+        assert torch.equal(y, y2)
         gemm.check_status()
         if rank == 0:
             q = lambda w: O.mxfp_fake(w, 32, 2, 1, 1)
