@@ -120,6 +120,12 @@ int mxq_bfp_fake_tiles(const void *x, void *y, int dtype, int64_t batch, int64_t
 int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int in_dtype, int out_dtype, int bias_dtype,
                    int64_t M, int64_t N, int64_t K, int *status, void *stream);
 
+/* The GEMM kernels are persistent: one CTA per SM, each holding nearly all of the SM's shared memory, so a kernel
+ * of another stream (an NCCL collective, say) cannot start on an SM until a GEMM CTA leaves it.  This process-wide
+ * knob caps the CTAs of later GEMM launches (0 = use every SM) so that such a kernel finds free SMs; it returns
+ * the previous value.  No counterpart in the reference. */
+int mxq_gemm_set_max_ctas(int max_ctas);
+
 /* Size in bytes of the scale array that mxq_mxfp_pack_mma writes for a [rows, k] operand. */
 int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k);
 

@@ -535,6 +535,10 @@ static int make_store_map(CUtensorMap *map, void *ptr, bool bf16, int64_t rows, 
   return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
+// Upper bound on the CTAs (= SMs) a GEMM launch occupies; 0 = all of them.  Process-wide, set through
+// mxq_gemm_set_max_ctas by callers that want to keep SMs free for a concurrent collective.
+static int g_max_ctas = 0;
+
 static int sm_count() {
   static int n = 0;
   if (!n) {
@@ -577,7 +581,8 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
     attr_set = true;
   }
   const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (g_max_ctas > 0 && grid > g_max_ctas) grid = g_max_ctas;
   umma_gemm_kernel<kKind, BN><<<grid, kThreads, L::kTotal, st>>>(ma, mb, md, p);
   return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
@@ -606,6 +611,12 @@ static int launch_any(const void *a, const void *b, const uint8_t *sfa, const ui
 using namespace mxq::gemm;
 
 extern "C" {
+
+int mxq_gemm_set_max_ctas(int max_ctas) {
+  const int prev = g_max_ctas;
+  g_max_ctas = max_ctas > 0 ? max_ctas : 0;
+  return prev;
+}
 
 int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k) {
   if (rows < 0 || k < 0) return MXQ_ERR_SHAPE;

@@ -205,15 +205,35 @@ class TPGatedMLP(nn.Module):
         return self.down(self.hidden(x))
 
 
-def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1) -> Tensor:
+def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, comm_sms: int = 16) -> Tensor:
     """x -> layer_1 -> ... -> layer_L.  With micro_batches > 1 the rows are split and the cross-GPU reduction of one
-    micro-batch (side stream) overlaps the GEMMs of the next one, within and across layers."""
+    micro-batch (side stream) overlaps the GEMMs of the next one, within and across layers.  The GEMM kernels are
+    persistent and fill every SM, so while the pipeline runs they are capped to leave `comm_sms` SMs to the
+    collective kernels (otherwise those only start when a GEMM ends and nothing overlaps)."""
     if micro_batches <= 1 or x.shape[0] < micro_batches or not hasattr(layers[0].down, "start"):
         for layer in layers:
             x = layer(x)
         return x
-    parts = list(x.chunk(micro_batches, dim=0))
-    for layer in layers:
-        handles = [layer.down.start(layer.hidden(p)) for p in parts]   # reductions are in flight while later parts compute
-        parts = [layer.down.finish(h) for h in handles]
-    return torch.cat(parts, dim=0)
+    prev = None
+    if x.is_cuda and comm_sms > 0:
+        from . import _lib
+
+        sms = torch.cuda.get_device_properties(x.device).multi_processor_count
+        prev = _lib.lib().mxq_gemm_set_max_ctas(max(1, sms - comm_sms))
+    try:
+        parts = list(x.chunk(micro_batches, dim=0))
+        handles = [None] * len(parts)
+        prev_layer = None
+        for layer in layers:
+            for i in range(len(parts)):
+                # a part waits only for its own reduction of the previous layer; the other parts' reductions stay
+                # in flight underneath this part's GEMMs
+                inp = parts[i] if prev_layer is None else prev_layer.down.finish(handles[i])
+                handles[i] = layer.down.start(layer.hidden(inp))
+            prev_layer = layer
+        return torch.cat([prev_layer.down.finish(h) for h in handles], dim=0)
+    finally:
+        if prev is not None:
+            from . import _lib
+
+            _lib.lib().mxq_gemm_set_max_ctas(prev)
