@@ -205,7 +205,7 @@ class TPGatedMLP(nn.Module):
         return self.down(self.hidden(x))
 
 
-def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, comm_sms: int = 16) -> Tensor:
+def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, comm_sms: int = 32) -> Tensor:
     """x -> layer_1 -> ... -> layer_L.  With micro_batches > 1 the rows are split and the cross-GPU reduction of one
     micro-batch (side stream) overlaps the GEMMs of the next one, within and across layers.  The GEMM kernels are
     persistent and fill every SM, so while the pipeline runs they are capped to leave `comm_sms` SMs to the
