@@ -1,0 +1,53 @@
+"""`mase_b200.patch` against a real MASE checkout (skipped where none is mounted): the map entries that the quantize
+pass reads are replaced, and the pass then builds this package's classes."""
+
+import os
+import sys
+
+import pytest
+import torch
+
+import mase_b200 as mb
+
+CHOP = "/root/reference/src/chop"
+pytestmark = pytest.mark.skipif(not os.path.isdir(CHOP), reason="no MASE checkout")
+
+
+@pytest.fixture(scope="module")
+def chop_modules():
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    import make_golden
+
+    make_golden.import_reference(CHOP)
+    import chop.nn.quantizers as q
+    import chop.nn.quantized.modules as qm
+    from chop.passes.module.transforms.quantize.quantize import quantize_module_transform_pass
+
+    saved = (dict(q.quantizer_map), dict(qm.quantized_module_map))
+    yield q, qm, quantize_module_transform_pass
+    q.quantizer_map.update(saved[0])
+    qm.quantized_module_map.update(saved[1])
+
+
+def test_patch_replaces_the_entries_the_pass_reads(chop_modules):
+    q, qm, run_pass = chop_modules
+    done = mb.patch()
+    assert q.quantizer_map["mxfp"] is mb.mxfp_quantizer
+    assert q.quantizer_map["mxint"] is mb.mxint_quantizer
+    assert q.quantizer_map["block_fp"] is mb.block_fp_quantizer
+    assert qm.quantized_module_map["linear_mxfp"] is mb.LinearMXFP
+    assert qm.quantized_module_map["linear_mxint"] is mb.LinearMXInt
+    assert qm.quantized_module_map["linear_block_fp"] is mb.LinearBlockFP
+    assert any("quantized_module_map" in d for d in done)
+
+    # the unmodified pass now instantiates this package's class and calls its load_state_dict, which refuses CPU
+    # tensors (there is no CPU fallback); with bypass the swap completes on the CPU
+    model = torch.nn.Sequential(torch.nn.Linear(64, 32), torch.nn.ReLU(), torch.nn.Linear(32, 8))
+    cfg = {"name": "mxfp", "weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3,
+           "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    with pytest.raises(RuntimeError, match="CUDA"):
+        run_pass(model, {"by": "type", "linear": {"config": dict(cfg)}})
+    model = torch.nn.Sequential(torch.nn.Linear(64, 32), torch.nn.ReLU(), torch.nn.Linear(32, 8))
+    out, _ = run_pass(model, {"by": "type", "linear": {"config": dict(cfg, bypass=True)}})
+    assert isinstance(out[0], mb.LinearMXFP) and isinstance(out[2], mb.LinearMXFP)
+    assert out[0].config["weight_exponent_width"] == 4
