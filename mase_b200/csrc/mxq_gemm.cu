@@ -180,9 +180,7 @@ __device__ __forceinline__ uint32_t make_idesc() {
 // arrive from L2, so ring depth matters more than a shorter epilogue.)
 template <int BN, bool kScaled>
 struct Layout {
-  // narrow tiles serve small, latency-bound problems (a few rows against a large weight): a deeper ring keeps more
-  // of the weight stream in flight per SM
-  static constexpr int kStages = BN <= 64 ? 8 : 4;
+  static constexpr int kStages = 4;
   static constexpr int kStoreBufs = 2;  // 2048-byte store boxes per epilogue warp
   static constexpr int kA = BM * kRowBytes;
   static constexpr int kB = BN * kRowBytes;
@@ -225,11 +223,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   // columns first and says so on its own barrier, so that the next tile's MMAs wait for a quarter of the epilogue
   // instead of all of it.
   constexpr bool kOverlap = kScaled && BN == 256;
-  // Narrow tiles: MMAs into one accumulator form a dependent chain, and a 128 x 64 x 32-byte MMA is far shorter than
-  // the latency of that chain, so a narrow tile spreads its K chunks round-robin over kSplit accumulators (summed by
-  // the epilogue), which shortens the chain kSplit times.
-  constexpr int kSplit = BN <= 64 ? 4 : 1;
-  constexpr int kAccCols = kSplit * BN;            // TMEM columns of one accumulator stage
+  constexpr int kAccCols = BN;                     // TMEM columns of one accumulator stage
   constexpr int kAccStages =
       kOverlap || 2 * kAccCols + (kScaled ? kMaxStages * kSfColsPerStage : 0) <= kTmemCols ? 2 : 1;
   constexpr int kAccStride = kOverlap ? 192 : kAccCols;  // first column of accumulator stage 1
@@ -362,9 +356,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // 32 bytes of K per instruction: advance the start-address field (16-byte units) inside the swizzle atom
             uint32_t id = idesc;
             if constexpr (kScaled) id |= ((uint32_t)k << 29) | ((uint32_t)k << 4);  // byte k of each scale word
-            // accumulator kc % kSplit; its first MMA of the tile overwrites, the others accumulate
-            umma<kKind>(d_tmem + (uint32_t)((kc % kSplit) * BN), da + 2u * k, db + 2u * k, id,
-                        (kc >= kSplit || k != 0) ? 1u : 0u, sfa_t, sfb_t + sfb_col);
+            umma<kKind>(d_tmem, da + 2u * k, db + 2u * k, id, (kc | k) != 0 ? 1u : 0u, sfa_t, sfb_t + sfb_col);
           }
           tc_commit(empty_bar(stage));  // arrives when the MMAs that read this slot have completed
           if (++stage == kStages) stage = 0, phase ^= 1u;
@@ -404,18 +396,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const bool active = n0 + c < p.N;  // uniform across the warp; chunks past the edge are read but not stored
         uint32_t(&v)[32] = vv[ci & 1];
         if (ci + 1 < BN / 32) tmem_ld32(t_acc + (uint32_t)(((ci + 1 + first) % (BN / 32)) * 32), vv[(ci + 1) & 1]);
-        if constexpr (kSplit > 1) {  // add the other partial accumulators of this tile
-#pragma unroll
-          for (int a = 1; a < kSplit; ++a) {
-            if (a < p.k_chunks) {
-              uint32_t tt[32];
-              tmem_ld32(t_acc + (uint32_t)(a * BN + c), tt);
-              tmem_ld_wait(tt);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(tt[j]));
-            }
-          }
-        }
         if (p.bias != nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {

@@ -35,6 +35,65 @@ __device__ __forceinline__ uint32_t mxfp_round_pair(uint32_t a2, uint32_t kodd2)
   y2 -= (y2 ^ a2) & (a2 ^ kodd2) & 0x00800080u;                  // exponent lsb flipped (carry) and ye odd
   return y2;
 }
+// The same on vectors that also hold elements with ye <= 0 (subnormal codes and underflow), still with K >= 1 and no
+// inf / nan.  With lo = the pattern of 2**(K - 127):
+//   ye == 0 : the F-bit rounded fraction f is stored as (f | 2**F) >> 1, or as 0 when f == 0: the output keeps the
+//             element's exponent and the rounded fraction with its last bit cleared; a carry out of the binade gives
+//             lo itself (the OR loses it), and f == 0 <=> |x| <= lo + half an F-bit step gives zero;
+//   ye <  0 : zero.
+// The sign survives unless the input is flushed (biased exponent 0, -0.0 included) or x / 2**sh rounds to zero in
+// fp32, i.e. for |x| patterns from `tmin` up.  The three thresholds become per-element masks with one packed bf16
+// comparison each.
+struct SubThresholds2 {
+  __nv_bfloat162 t1, thr, tmin;  // first normal pattern, first pattern that does not round to zero, sign threshold
+};
+template <int E, int F>
+__device__ __forceinline__ SubThresholds2 sub_thresholds2(int K) {
+  constexpr int kBias = (1 << (E - 1)) - 1;
+  const uint32_t lo = (uint32_t)K << 7;
+  const uint32_t t1 = (lo + 0x80u) * 0x00010001u;
+  const uint32_t thr = (lo + (1u << (6 - F)) + 1u) * 0x00010001u;
+  const uint32_t tmin = (uint32_t)max(0x80, ((K + kBias - 150) << 7) + 1) * 0x00010001u;
+  SubThresholds2 t;
+  t.t1 = *reinterpret_cast<const __nv_bfloat162 *>(&t1);
+  t.thr = *reinterpret_cast<const __nv_bfloat162 *>(&thr);
+  t.tmin = *reinterpret_cast<const __nv_bfloat162 *>(&tmin);
+  return t;
+}
+// r2 = two raw bf16 elements; returns the two quantize-dequantized elements, signs included
+template <int F>
+__device__ __forceinline__ uint32_t mxfp_round_pair_sub(uint32_t r2, uint32_t kodd2, const SubThresholds2 &t) {
+  constexpr uint32_t kHalf2 = ((1u << (6 - F)) - 1u) * 0x00010001u;
+  constexpr uint32_t kMask2 = ((0xFFFFu << (7 - F)) & 0xFFFFu) * 0x00010001u;
+  constexpr uint32_t kLsb2 = (1u << (7 - F)) * 0x00010001u;
+  const uint32_t a2 = r2 & 0x7FFF7FFFu;
+  const __nv_bfloat162 av = *reinterpret_cast<const __nv_bfloat162 *>(&a2);
+  const uint32_t normal = __hge2_mask(av, t.t1);
+  const uint32_t nonzero = __hge2_mask(av, t.thr);
+  const uint32_t signed_ = __hge2_mask(av, t.tmin);
+  const uint32_t lsb2 = (a2 >> (7 - F)) & 0x00010001u;
+  uint32_t y2 = (a2 + kHalf2 + lsb2) & kMask2;
+  y2 -= (y2 ^ a2) & 0x00800080u & ((a2 ^ kodd2) | ~normal);  // carry lost: ye odd, or ye == 0
+  y2 &= ~(kLsb2 & ~normal);
+  return (y2 & nonzero) | (r2 & signed_ & 0x80008000u);
+}
+// fp32 version; `b` = raw bits, K as above
+template <int E, int F>
+__device__ __forceinline__ uint32_t mxfp_round_one_sub(uint32_t b, int K) {
+  constexpr int kBias = (1 << (E - 1)) - 1;
+  constexpr uint32_t kHalf = (1u << (22 - F)) - 1u;
+  constexpr uint32_t kMask = ~((1u << (23 - F)) - 1u);
+  const uint32_t a = b & 0x7FFFFFFFu, at = a & 0x7FFFFF00u;
+  const uint32_t lo = (uint32_t)K << 23;
+  const bool normal = a >= lo + 0x00800000u;
+  const uint32_t lsb = (at >> (23 - F)) & 1u;
+  uint32_t y = (at + kHalf + lsb) & kMask;
+  y -= (y ^ at) & 0x00800000u & (normal ? (at ^ ((uint32_t)K << 23)) : 0xFFFFFFFFu);
+  if (!normal) y &= ~(1u << (23 - F));
+  if (a < lo + (1u << (22 - F)) + 0x100u) y = 0;
+  if (a >= (uint32_t)max(0x00800000, ((K + kBias - 150) << 23) + 1)) y |= b & 0x80000000u;
+  return y;
+}
 template <int F>
 __device__ __forceinline__ uint32_t mxfp_round_one(uint32_t at, uint32_t kodd) {
   constexpr uint32_t kHalf = (1u << (22 - F)) - 1u;

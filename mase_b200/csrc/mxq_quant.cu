@@ -148,45 +148,67 @@ mxfp_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, uint8_t *__restrict
         if (man >= 0x7FFF00u) up = (0x7FFFFFu - man) < tab.t[exm] ? 1 : 0;
       }
       const int K = exm + up - kTop;
-      bool fast = K >= 1;
+      // `fast`: every element has a normal code (ye >= 1).  `sub`: some have subnormal codes or underflow, and the
+      // vector still avoids clamped scales and inf / nan; fake-quantization then stays on the bit patterns too.
+      // Narrow-exponent formats (E <= 3) meet small codes in almost every vector and skip the first test.
+      constexpr bool kSubPath = kMode == Mode::kFake;
+      constexpr bool kTryFast = !kSubPath || E >= 4;
+      bool fast = kTryFast && K >= 1;
+      const bool sub = kSubPath && K >= 1 && exm != 255;
       uint32_t yq[N];  // rounded |x| as fp32 bit patterns (bf16 input: two bf16 patterns per word in yq[0..3])
       if constexpr (kBf16In) {
-        const uint32_t t1 = (uint32_t)((K + 1) << 7) * 0x00010001u;
-        const __nv_bfloat162 t1v = *reinterpret_cast<const __nv_bfloat162 *>(&t1);
+        if constexpr (kTryFast) {
+          const uint32_t t1 = (uint32_t)((K + 1) << 7) * 0x00010001u;
+          const __nv_bfloat162 t1v = *reinterpret_cast<const __nv_bfloat162 *>(&t1);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) fast = fast && __hbge2(*reinterpret_cast<const __nv_bfloat162 *>(&a[k]), t1v);
+          for (int k = 0; k < 4; ++k) fast = fast && __hbge2(*reinterpret_cast<const __nv_bfloat162 *>(&a[k]), t1v);
+        }
+        const uint32_t kodd2 = (K & 1) ? 0x00800080u : 0u;
         if (fast) {
-          const uint32_t kodd2 = (K & 1) ? 0x00800080u : 0u;
 #pragma unroll
           for (int k = 0; k < 4; ++k) yq[k] = mxfp_round_pair<F>(a[k], kodd2);
+          if constexpr (kSubPath) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) yq[k] |= r[k] & 0x80008000u;
+          }
+        } else if (sub) {
+          const SubThresholds2 th = sub_thresholds2<E, F>(K);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) yq[k] = mxfp_round_pair_sub<F>(r[k], kodd2, th);
         }
       } else {
-        const uint32_t t1 = (uint32_t)(K + 1) << 23;
+        if constexpr (kTryFast) {
+          const uint32_t t1 = (uint32_t)(K + 1) << 23;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) fast = fast && a[k] >= t1;
+          for (int k = 0; k < 4; ++k) fast = fast && a[k] >= t1;
+        }
         if (fast) {
           const uint32_t kodd = (K & 1) ? 0x00800000u : 0u;
 #pragma unroll
           for (int k = 0; k < 4; ++k) yq[k] = mxfp_round_one<F>(a[k] & 0x7FFFFF00u, kodd);
+          if constexpr (kSubPath) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) yq[k] |= r[k] & 0x80000000u;
+          }
+        } else if (sub) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) yq[k] = mxfp_round_one_sub<E, F>(r[k], K);
         }
       }
-      if (fast) {
-        if constexpr (kMode == Mode::kFake) {
+      if (fast || sub) {
+        if constexpr (kMode == Mode::kFake) {  // yq holds the signed results
           if constexpr (kBf16In && Elem<Tout>::kBf16) {
-            st_stream(reinterpret_cast<uint4 *>(y) + i,
-                      make_uint4(yq[0] | (r[0] & 0x80008000u), yq[1] | (r[1] & 0x80008000u),
-                                 yq[2] | (r[2] & 0x80008000u), yq[3] | (r[3] & 0x80008000u)));
+            st_stream(reinterpret_cast<uint4 *>(y) + i, make_uint4(yq[0], yq[1], yq[2], yq[3]));
           } else {
             float out[N];
             if constexpr (kBf16In) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                const uint32_t v = yq[k] | (r[k] & 0x80008000u);
-                out[2 * k] = __uint_as_float(v << 16), out[2 * k + 1] = __uint_as_float(v & 0xFFFF0000u);
+                out[2 * k] = __uint_as_float(yq[k] << 16), out[2 * k + 1] = __uint_as_float(yq[k] & 0xFFFF0000u);
               }
             } else {
 #pragma unroll
-              for (int k = 0; k < 4; ++k) out[k] = __uint_as_float(yq[k] | (r[k] & 0x80000000u));
+              for (int k = 0; k < 4; ++k) out[k] = __uint_as_float(yq[k]);
             }
             store_vals(y, i * N, out);
           }

@@ -138,3 +138,24 @@ def test_large_m_with_bias_vs_oracle():
     xp = gemm.pack_mx_operand(xd, 4, 3)
     y3 = gemm.mx_gemm(xp, layer._packed_weight(), layer.bias, torch.bfloat16)
     assert torch.equal(y1, y3)
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (16, 4096, 4096), (128, 2048, 1024), (100, 1024, 1000), (7, 8192, 512)])
+def test_small_m_with_bias_vs_oracle(shape):
+    """At most 128 rows (narrow tiles), bias, ragged N, bf16 and fp32 outputs; results are repeatable."""
+    M, K, N = shape
+    x, w = synthetic.linear_operands(M, K, N, seed=31)
+    g = torch.Generator().manual_seed(31)
+    b = torch.randn(N, generator=g).bfloat16()
+    cfg = {"weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3,
+           "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    layer = mb.LinearMXFP(K, N, bias=True, device=DEV, dtype=torch.bfloat16, config=cfg)
+    layer.load_state_dict({"weight": w.to(DEV), "bias": b.to(DEV)}, strict=False)
+    y1 = layer(x.to(DEV))
+    y2 = layer(x.to(DEV))
+    gemm.check_status()
+    assert torch.equal(y1, y2)
+    ref = O.linear_mxfp(x, O.mxfp_fake(w, 32, 4, 3, 1), b, cfg)
+    assert rel_err(y1, ref) <= 4e-3
+    layer.output_dtype = torch.float32
+    assert rel_err(layer(x.to(DEV)), ref) <= 1e-3

@@ -124,6 +124,33 @@ def test_wide_dynamic_range_vs_oracle(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_mxfp_small_codes_exhaustive_vs_oracle(dtype):
+    """Every bf16 mantissa (fp32: the same plus ulp neighbours) in the binades around the subnormal code range,
+    both signs, odd and even block exponents, next to a block maximum; plus ReLU-sparse data with exact zeros."""
+    man = torch.arange(128, dtype=torch.int32) << 16
+    vals = []
+    for e in range(-34, 2):
+        bits = ((127 + e) << 23) + man
+        if dtype == torch.float32:
+            bits = torch.cat([bits, bits + 1, bits - 1, bits + 0x80, bits + 0xFF, bits + 0x100, bits + 0x7FFF, bits + 0x8000])
+        vals.append(bits.view(torch.float32))
+    v = torch.cat(vals)
+    v = torch.cat([v, -v])
+    pad = (-v.numel()) % 31
+    v = torch.cat([v, v[:pad]]).view(-1, 31)
+    blocks = []
+    for top in (1.0, 1.75, 2.0, 3.5):  # block maxima in two adjacent binades: odd and even shared exponents
+        blocks.append(torch.cat([torch.full((v.shape[0], 1), top), v], dim=1))
+    x = torch.cat(blocks).to(dtype)
+    g = torch.Generator().manual_seed(23)
+    sparse = torch.randn(256, 1024, generator=g).relu().to(dtype)
+    for t in (x, sparse, -sparse):
+        td = t.to(DEV)
+        for E, F in ((4, 3), (2, 1), (5, 2), (3, 2), (2, 3), (1, 2)):
+            assert_bits_equal(mb.mxfp_quantizer(td, 32, E, F), O.mxfp_fake(t, 32, E, F), f"mxfp e{E}m{F}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_power_of_two_neighbourhoods_vs_oracle(dtype):
     """Block maxima within +-64 ulps of every power of two: exercises the log2 rounding tables."""
     e = torch.arange(-126, 127).float()
