@@ -115,58 +115,36 @@ __device__ __forceinline__ uint32_t mxfp_round_one(uint32_t at, uint32_t kodd) {
 // raised by one; only elements of the two lowest binades of such a block can round (by at most 2**-16 of the
 // block maximum).
 //
-// pack_vector handles one 16-byte vector (8 bf16 or 4 fp32 elements); a block of 32 is shared by 32 / N neighbouring
-// lanes, so it must be called by all 32 lanes of a warp together (lanes without data pass zeros).  It returns the
-// vector's E4M3 bytes (two per word of c2, low 16 bits) and the block's E8M0 scale.
-template <typename Tin, int E, int F>
-__device__ __forceinline__ void pack_vector(const uint4 &raw, const Log2Tab &tab, uint32_t (&c2)[Elem<Tin>::kVec / 2],
-                                            int &scale_out) {
-  constexpr int N = Elem<Tin>::kVec;
-  constexpr bool kBf16In = Elem<Tin>::kBf16;
-  constexpr int kGroup = 32 / N;
+// pack_f32 handles one 16-byte vector of 4 fp32 elements; a block of 32 is shared by 8 neighbouring lanes, so it must
+// be called by all 32 lanes of a warp together (lanes without data pass zeros).  It returns the vector's four E4M3
+// bytes and the block's E8M0 scale.
+template <int E, int F>
+__device__ __forceinline__ uint32_t pack_f32(const uint4 &raw, const Log2Tab &tab, int &scale_out) {
+  constexpr int kGroup = 8;
   constexpr int kTop = (1 << E) - 1;
   constexpr int kBias = (1 << (E - 1)) - 1;
   constexpr int kEmax = kTop - kBias;
   const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
-  uint32_t a[4], amax;
-  if constexpr (kBf16In) {
-    __nv_bfloat162 m2 = __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&(a[0] = r[0] & 0x7FFF7FFFu)),
-                                *reinterpret_cast<const __nv_bfloat162 *>(&(a[1] = r[1] & 0x7FFF7FFFu)));
-    m2 = __hmax2(m2, __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&(a[2] = r[2] & 0x7FFF7FFFu)),
-                             *reinterpret_cast<const __nv_bfloat162 *>(&(a[3] = r[3] & 0x7FFF7FFFu))));
-    const uint32_t mb = *reinterpret_cast<uint32_t *>(&m2);
-    const uint32_t m = group_max(max(mb & 0xFFFFu, mb >> 16), kGroup);
-    amax = (m >> 7) ? (m << 16) : 0u;
-  } else {
+  uint32_t a[4];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) a[k] = r[k] & 0x7FFFFFFFu;
-    const uint32_t m = group_max(max(max(a[0], a[1]), max(a[2], a[3])), kGroup);
-    amax = (m >> 23) ? m : 0u;
-  }
+  for (int k = 0; k < 4; ++k) a[k] = r[k] & 0x7FFFFFFFu;
+  const uint32_t m = group_max(max(max(a[0], a[1]), max(a[2], a[3])), kGroup);
+  const uint32_t amax = (m >> 23) ? m : 0u;
   const int exm = (int)(amax >> 23);
   int up = 0;
-  if constexpr (!kBf16In) {
-    const uint32_t man = amax & 0x7FFFFFu;
-    if (man >= 0x7FFF00u) up = (0x7FFFFFu - man) < tab.t[exm] ? 1 : 0;
-  }
+  const uint32_t man = amax & 0x7FFFFFu;
+  if (man >= 0x7FFF00u) up = (0x7FFFFFu - man) < tab.t[exm] ? 1 : 0;
   const int K = exm + up - kTop;
   const uint32_t kodd = (K & 1) ? 0x00800000u : 0u;
   // `fast`: the block's scale is not clamped, elements with exponent code >= 2 are handled on bit patterns.
   // `clean`: every element of this vector is such an element; the others are patched one by one afterwards.
   const bool fast = K >= 1;
-  const uint32_t t1_32 = (uint32_t)(K + 2) << 23;  // smallest |x| pattern with exponent code >= 2
+  const uint32_t t1 = (uint32_t)(K + 2) << 23;  // smallest |x| pattern with exponent code >= 2
   bool clean = true;
-  if constexpr (kBf16In) {
-    const uint32_t t1 = (uint32_t)((K + 2) << 7) * 0x00010001u;
-    const __nv_bfloat162 t1v = *reinterpret_cast<const __nv_bfloat162 *>(&t1);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) clean = clean && __hbge2(*reinterpret_cast<const __nv_bfloat162 *>(&a[k]), t1v);
-  } else {
-#pragma unroll
-    for (int k = 0; k < 4; ++k) clean = clean && a[k] >= t1_32;
-  }
+  for (int k = 0; k < 4; ++k) clean = clean && a[k] >= t1;
   int sh, scale;
-  if (K >= 1) {
+  if (fast) {
     sh = exm + up - 127 - kEmax, scale = sh + 127;
   } else {
     const MxfpBlock p = mxfp_block(amax, E, tab);
@@ -175,85 +153,210 @@ __device__ __forceinline__ void pack_vector(const uint4 &raw, const Log2Tab &tab
   // pass 1: the reference's rounding.  Nothing rounds above the top code (a carry out of the top binade is lost),
   // so a block holds the top E4M3 code (exponent code 15, fraction 7 -- any element of the top binade can land
   // on it, not only the maximum) iff the largest rounded pattern of the block equals it.
-  uint32_t yq[4];     // fast path: rounded |x| patterns (bf16: two per word)
-  uint32_t cw[N];     // general path: reference codes
-  uint32_t ymax = 0;  // largest rounded pattern (fast) or largest code magnitude moved to the same scale (general)
+  uint32_t yq[4];  // fast path: rounded |x| patterns
+  uint32_t cw[4];  // general path: reference codes
+  int top = 0;
   if (fast) {
-    if constexpr (kBf16In) {
-      const uint32_t kodd2 = kodd ? 0x00800080u : 0u;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) yq[k] = mxfp_round_pair<F>(a[k], kodd2);
-      if constexpr (E == 4 && F == 3) {
-        __nv_bfloat162 mx = __hmax2(__hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&yq[0]),
-                                            *reinterpret_cast<const __nv_bfloat162 *>(&yq[1])),
-                                    __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&yq[2]),
-                                            *reinterpret_cast<const __nv_bfloat162 *>(&yq[3])));
-        const uint32_t mxb = *reinterpret_cast<uint32_t *>(&mx);
-        ymax = max(mxb & 0xFFFFu, mxb >> 16) == (((uint32_t)exm << 7) | (7u << 4)) ? 1u : 0u;
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) yq[k] = mxfp_round_one<F>(a[k] & 0x7FFFFF00u, kodd);
-      if constexpr (E == 4 && F == 3)
-        ymax = max(max(yq[0], yq[1]), max(yq[2], yq[3])) == (((uint32_t)exm << 23) | (7u << 20)) ? 1u : 0u;
-    }
-    if (up) ymax = 0;  // the maximum was assigned exponent code 14: nothing reaches code 15
+    for (int k = 0; k < 4; ++k) yq[k] = mxfp_round_one<F>(a[k] & 0x7FFFFF00u, kodd);
+    if constexpr (E == 4 && F == 3)
+      top = max(max(yq[0], yq[1]), max(yq[2], yq[3])) == (((uint32_t)exm << 23) | (7u << 20)) ? 1 : 0;
+    if (up) top = 0;  // the maximum was assigned exponent code 14: nothing reaches code 15
   } else {
-    uint32_t b[N];
-    unpack(raw, b);
 #pragma unroll
-    for (int k = 0; k < N; ++k) {
-      if (((b[k] & 0x7FFFFFFFu) >> 23) == 0) b[k] = 0;
-      cw[k] = mxfp_encode(b[k], sh, E, F);
-      if constexpr (E == 4 && F == 3) ymax |= (cw[k] & 0x7Fu) == 0x7Fu ? 1u : 0u;
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t b = (a[k] >> 23) == 0 ? 0u : r[k];
+      cw[k] = mxfp_encode(b, sh, E, F);
+      if constexpr (E == 4 && F == 3) top |= (cw[k] & 0x7Fu) == 0x7Fu ? 1 : 0;
     }
   }
-  int top = (int)ymax;
   if constexpr (E == 4 && F == 3) {
     for (int o = 1; o < kGroup; o <<= 1) top |= __shfl_xor_sync(0xFFFFFFFFu, top, o);
   }
   // pass 2: hardware E4M3 bytes.  With exponent codes >= 2 everywhere the byte is sign | (exponent code, fraction)
   // re-biased to E4M3 -- read straight off the rounded pattern -- and raising the scale by one just lowers the
   // exponent code by one.  The general path goes through the value and the hardware conversion.
+  const float half = top ? 0.5f : 1.f;
+  uint32_t bytes[4];
   if (fast) {
     const uint32_t kh = (uint32_t)(K + kBias - 7 + top) << 3;  // pattern exponent -> E4M3 exponent code
-    if constexpr (kBf16In) {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        // bit 15 of each half absorbs the borrow of an element that is too small for this path (patched below)
-        const uint32_t m2 = ((((yq[k] >> 4) | 0x80008000u) - kh * 0x00010001u) & 0x007F007Fu) | ((r[k] >> 8) & 0x00800080u);
-        c2[k] = __byte_perm(m2, 0, 0x4420);  // bytes 0 and 2 -> low 16 bits
-      }
-    } else {
-      uint32_t m[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) m[k] = (((yq[k] >> 20) - kh) & 0x7Fu) | ((r[k] >> 24) & 0x80u);
-      c2[0] = m[0] | (m[1] << 8), c2[1] = m[2] | (m[3] << 8);
-    }
+    for (int k = 0; k < 4; ++k) bytes[k] = (((yq[k] >> 20) - kh) & 0x7Fu) | ((r[k] >> 24) & 0x80u);
     if (!clean) {
       // elements below exponent code 2 (subnormal codes, underflow, zeros): the reference's element codec, then
       // the exact value (halved if the scale was raised) through the hardware conversion
-      uint32_t b[N];
-      unpack(raw, b);
-      const float half = top ? 0.5f : 1.f;
 #pragma unroll
-      for (int k = 0; k < N; ++k) {
-        if ((b[k] & 0x7FFFFFFFu) < t1_32) {
-          const uint32_t bb = ((b[k] & 0x7FFFFFFFu) >> 23) == 0 ? 0u : b[k];
+      for (int k = 0; k < 4; ++k) {
+        if (a[k] < t1) {
+          const uint32_t bb = (a[k] >> 23) == 0 ? 0u : r[k];
           const float v = mxfp_decode(mxfp_encode(bb, sh, E, F), E, F) * half;
-          const uint32_t byte = __nv_cvt_float2_to_fp8x2(make_float2(v, 0.f), __NV_SATFINITE, __NV_E4M3) & 0xFFu;
-          c2[k / 2] = (k & 1) ? ((c2[k / 2] & 0x00FFu) | (byte << 8)) : ((c2[k / 2] & 0xFF00u) | byte);
+          bytes[k] = __nv_cvt_float2_to_fp8x2(make_float2(v, 0.f), __NV_SATFINITE, __NV_E4M3) & 0xFFu;
         }
       }
     }
   } else {
-    const float half = top ? 0.5f : 1.f;
 #pragma unroll
-    for (int k = 0; k < N; k += 2)
-      c2[k / 2] = __nv_cvt_float2_to_fp8x2(
+    for (int k = 0; k < 4; k += 2) {
+      const uint32_t two = __nv_cvt_float2_to_fp8x2(
           make_float2(mxfp_decode(cw[k], E, F) * half, mxfp_decode(cw[k + 1], E, F) * half), __NV_SATFINITE, __NV_E4M3);
+      bytes[k] = two & 0xFFu, bytes[k + 1] = (two >> 8) & 0xFFu;
+    }
   }
   scale_out = scale + top;
+  return bytes[0] | (bytes[1] << 8) | (bytes[2] << 16) | (bytes[3] << 24);
+}
+
+// Rare paths of pack_bf16, kept out of line so that the common path stays small.
+//
+// patch_small_bf16: elements below exponent code 2 (subnormal codes, underflow, zeros) of a block on the fast path:
+// the reference's element codec, then the exact value (halved if the scale was raised) through the hardware
+// conversion.  r = the 8 input words, bytes = two E4M3 bytes per word in bytes 1 and 3.
+struct Words8 {
+  uint32_t w[8];
+};
+template <int E, int F>
+__device__ __noinline__ Words8 patch_small_bf16(Words8 rr, Words8 out, int K, int sh, int top) {
+  const uint32_t(&r)[8] = rr.w;
+  uint32_t(&bytes)[8] = out.w;
+  const float half = top ? 0.5f : 1.f;
+  const uint32_t t1 = (uint32_t)(K + 2) << 23;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t b = h ? (r[k] & 0xFFFF0000u) : (r[k] << 16);
+      if ((b & 0x7FFFFFFFu) < t1) {
+        const uint32_t bb = ((b & 0x7FFFFFFFu) >> 23) == 0 ? 0u : b;
+        const float val = mxfp_decode(mxfp_encode(bb, sh, E, F), E, F) * half;
+        const uint32_t byte = __nv_cvt_float2_to_fp8x2(make_float2(val, 0.f), __NV_SATFINITE, __NV_E4M3) & 0xFFu;
+        bytes[k] = h ? ((bytes[k] & 0x00FFFFFFu) | (byte << 24)) : ((bytes[k] & 0xFFFF00FFu) | (byte << 8));
+      }
+    }
+  }
+  return out;
+}
+// pack_general_bf16: blocks with a clamped scale, inf / nan or only zeros; called by both lanes of a block (one
+// shuffle inside).  Returns the bytes and, in *scale_out, the E8M0 scale.
+template <int E, int F>
+__device__ __noinline__ Words8 pack_general_bf16(Words8 rr, uint32_t amax, const Log2Tab &tab, int *scale_out) {
+  const uint32_t(&r)[8] = rr.w;
+  Words8 out;
+  uint32_t(&bytes)[8] = out.w;
+  const MxfpBlock p = mxfp_block(amax, E, tab);
+  uint32_t cw[16];
+  int top = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t b = h ? (r[k] & 0xFFFF0000u) : (r[k] << 16);
+      cw[2 * k + h] = mxfp_encode(((b & 0x7FFFFFFFu) >> 23) == 0 ? 0u : b, p.sh, E, F);
+      if constexpr (E == 4 && F == 3) top |= (cw[2 * k + h] & 0x7Fu) == 0x7Fu ? 1 : 0;
+    }
+  }
+  if constexpr (E == 4 && F == 3) top |= __shfl_xor_sync(0xFFFFFFFFu, top, 1);
+  const float half = top ? 0.5f : 1.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const uint32_t two = __nv_cvt_float2_to_fp8x2(
+        make_float2(mxfp_decode(cw[2 * k], E, F) * half, mxfp_decode(cw[2 * k + 1], E, F) * half), __NV_SATFINITE,
+        __NV_E4M3);
+    bytes[k] = ((two & 0xFFu) << 8) | ((two & 0xFF00u) << 16);
+  }
+  *scale_out = p.scale + top;
+  return out;
+}
+
+// pack_bf16 handles 16 consecutive bf16 elements (two 16-byte vectors, half a block of 32) per lane; the two lanes
+// of a block exchange their maxima, so all 32 lanes of a warp call it together (lanes without data pass zeros).
+// It returns the 16 E4M3 bytes and the block's E8M0 scale.
+//
+// Integer issue slots are the scarce resource here, so the work that can run on the floating-point pipes does:
+//   * rounding |x| to F fraction bits, half to even: with p = the element's own power of two (sign and exponent
+//     bits of x), t = fma(p, 2**(7-F), x) has its last bit at the F-th fraction bit of x and the fma rounds there;
+//     fma(p, -2**(7-F), t) then subtracts the offset exactly.  The sign rides along.  (Checked against the integer
+//     formula for every bf16 pattern.)
+//   * the block maximum, the "every element has an exponent code >= 2" test and the search for the top code use
+//     packed bf16 max / compare instructions with |x| operands.
+template <int E, int F>
+__device__ __forceinline__ uint4 pack_bf16(const uint4 &raw0, const uint4 &raw1, const Log2Tab &tab, int &scale_out) {
+  constexpr int kTop = (1 << E) - 1;
+  constexpr int kBias = (1 << (E - 1)) - 1;
+  constexpr int kEmax = kTop - kBias;
+  const Words8 rr = {{raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w}};
+  const uint32_t(&r)[8] = rr.w;
+  __nv_bfloat162 v[8], av[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    v[k] = *reinterpret_cast<const __nv_bfloat162 *>(&r[k]);
+    av[k] = __hmax2(v[k], __hneg2(v[k]));  // |x| on the floating-point pipe
+  }
+  const __nv_bfloat162 m2 = __hmax2(__hmax2(__hmax2(av[0], av[1]), __hmax2(av[2], av[3])),
+                                    __hmax2(__hmax2(av[4], av[5]), __hmax2(av[6], av[7])));
+  const uint32_t mb = *reinterpret_cast<const uint32_t *>(&m2);
+  uint32_t m = max(mb & 0xFFFFu, mb >> 16);
+  m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+  const int exm = (int)(m >> 7);                      // 0: every element is zero or flushed
+  const uint32_t amax = exm ? (m << 16) : 0u;
+  const int K = exm - kTop;
+  // `fast`: the scale is not clamped, no inf / nan, and the rounding offset 2**(e + 7 - F) stays finite
+  const bool fast = K >= 1 && exm <= 240;
+  const uint32_t t1 = (uint32_t)((K + 2) << 7) * 0x00010001u;  // smallest |x| pattern with exponent code >= 2
+  const __nv_bfloat162 t1v = *reinterpret_cast<const __nv_bfloat162 *>(&t1);
+  Words8 out;
+  uint32_t(&bytes)[8] = out.w;  // two E4M3 bytes per word, in bytes 1 and 3
+  int top = 0;
+  if (fast) {
+    bool clean = true;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) clean = clean && __hbge2(av[k], t1v);
+    const uint32_t kodd2 = (K & 1) ? 0x00800080u : 0u;
+    constexpr uint32_t kOff = (uint32_t)((127 + 7 - F) << 7) * 0x00010001u;  // 2**(7-F), both halves
+    const __nv_bfloat162 off = *reinterpret_cast<const __nv_bfloat162 *>(&kOff);
+    const __nv_bfloat162 noff = __hneg2(off);
+    uint32_t yq[8];  // rounded patterns, signs included
+    bool none_top = true;
+    const uint32_t topw = (((uint32_t)exm << 7) | (7u << 4)) * 0x00010001u;
+    const __nv_bfloat162 topv = *reinterpret_cast<const __nv_bfloat162 *>(&topw);
+    const __nv_bfloat162 ntopv = __hneg2(topv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t pw = r[k] & 0xFF80FF80u;
+      const __nv_bfloat162 p = *reinterpret_cast<const __nv_bfloat162 *>(&pw);
+      const __nv_bfloat162 y = __hfma2(p, noff, __hfma2(p, off, v[k]));
+      yq[k] = *reinterpret_cast<const uint32_t *>(&y);
+      yq[k] -= (yq[k] ^ r[k]) & (r[k] ^ kodd2) & 0x00800080u;  // exponent lsb flipped (carry) and code exponent odd
+      // a carry out of the top binade is lost, so nothing rounds above the top code: the block holds it iff some
+      // rounded pattern equals it (any element of the top binade can land there, not only the maximum)
+      if constexpr (E == 4 && F == 3) {
+        const __nv_bfloat162 yv = *reinterpret_cast<const __nv_bfloat162 *>(&yq[k]);
+        none_top = none_top && __hbne2(yv, topv) && __hbne2(yv, ntopv);
+      }
+    }
+    if constexpr (E == 4 && F == 3) {
+      top = none_top ? 0 : 1;
+      top |= __shfl_xor_sync(0xFFFFFFFFu, top, 1);
+    }
+    // sign | (exponent code, fraction) re-biased to E4M3, read off the rounded pattern; a raised scale (top code
+    // present) lowers every exponent code by one.  One multiply-add per pair of elements: the pattern times 16 puts
+    // (low four exponent bits, top three fraction bits) of the two elements into bits 8..14 and 24..30, the addend
+    // subtracts the exponent offset from both fields at once.  Bit 23 of the addend is a guard: an element too small
+    // for this path (patched below) makes its field borrow, and the guard absorbs the borrow of the low element
+    // before it reaches the high one.  Bits 15 and 31 are still the signs of the input.
+    const uint32_t koff = (uint32_t)(K + kBias - 7 + top);
+    const uint32_t addend = (1u << 23) - (koff << 11) - (koff << 27);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t e = yq[k] * 16u + addend;
+      bytes[k] = (e & 0x7F007F00u) | (r[k] & ~0x7F007F00u);  // bytes 1 and 3
+    }
+    if (!clean) out = patch_small_bf16<E, F>(rr, out, K, exm - 127 - kEmax, top);
+    scale_out = exm - kEmax + top;
+  } else {
+    out = pack_general_bf16<E, F>(rr, amax, tab, &scale_out);
+  }
+  return make_uint4(__byte_perm(bytes[0], bytes[1], 0x7531), __byte_perm(bytes[2], bytes[3], 0x7531),
+                    __byte_perm(bytes[4], bytes[5], 0x7531), __byte_perm(bytes[6], bytes[7], 0x7531));
 }
 
 }  // namespace mxq

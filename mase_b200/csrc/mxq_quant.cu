@@ -256,13 +256,17 @@ mxfp_kernel(const Tin *__restrict__ x, Tout *__restrict__ y, uint8_t *__restrict
   }
 }
 
-template <typename Tin, int E, int F>
+// byte offset of the E8M0 scale of (row, block kb of 32 along K) in the tensor-core scale layout
+template <typename I>
+__device__ __forceinline__ I mma_scale_offset(I row, I kb, I k_chunks) {
+  return ((row >> 7) * k_chunks + (kb >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kb & 3);
+}
+
+// fp32 tensors: one 16-byte vector (4 elements) per lane and step, 8 lanes per block
+template <int E, int F>
 __global__ void __launch_bounds__(kThreads)
-mxfp_pack_mma_kernel(const Tin *__restrict__ x, uint8_t *__restrict__ codes, uint8_t *__restrict__ scales, int64_t n_vec,
-                     uint32_t vec_per_row, int64_t k_chunks, const __grid_constant__ Log2Tab tab) {
-  constexpr int N = Elem<Tin>::kVec;
-  constexpr bool kBf16In = Elem<Tin>::kBf16;
-  constexpr int kGroup = 32 / N;
+mxfp_pack_mma_f32_kernel(const float *__restrict__ x, uint8_t *__restrict__ codes, uint8_t *__restrict__ scales,
+                         int64_t n_vec, uint32_t vec_per_row, int64_t k_chunks, const __grid_constant__ Log2Tab tab) {
   constexpr int kU = 2;
   const uint4 *xv = reinterpret_cast<const uint4 *>(x);
   const int64_t step = (int64_t)gridDim.x * kThreads * kU;
@@ -276,28 +280,82 @@ mxfp_pack_mma_kernel(const Tin *__restrict__ x, uint8_t *__restrict__ codes, uin
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
       const int64_t i = base + u * kThreads + threadIdx.x;
-      uint32_t c2[N / 2];
       int scale;
-      pack_vector<Tin, E, F>(raws[u], tab, c2, scale);  // every lane of the warp takes part (shuffles inside)
+      const uint32_t c4 = pack_f32<E, F>(raws[u], tab, scale);  // every lane of the warp takes part (shuffles inside)
       if (i >= n_vec) continue;
-      if constexpr (kBf16In)
-        __stcs(reinterpret_cast<uint2 *>(codes + i * N),
-               make_uint2(__byte_perm(c2[0], c2[1], 0x5410), __byte_perm(c2[2], c2[3], 0x5410)));
-      else
-        __stcs(reinterpret_cast<uint32_t *>(codes + i * N), __byte_perm(c2[0], c2[1], 0x5410));
-      if ((threadIdx.x & (kGroup - 1)) == 0) {
-        int64_t row, vcol;
-        if (n_vec <= 0xFFFFFFFFll) {
-          const uint32_t iu = (uint32_t)i;
-          row = iu / vec_per_row, vcol = iu - (uint32_t)row * vec_per_row;
-        } else {
-          row = i / vec_per_row, vcol = i - row * vec_per_row;
-        }
-        const int64_t kb = (vcol * N) >> 5;
-        scales[((row >> 7) * k_chunks + (kb >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kb & 3)] =
-            (uint8_t)scale;
+      __stcs(reinterpret_cast<uint32_t *>(codes + i * 4), c4);
+      if ((threadIdx.x & 7) == 0) {
+        const int64_t row = i / vec_per_row, vcol = i - row * vec_per_row;
+        scales[mma_scale_offset<int64_t>(row, vcol >> 3, k_chunks)] = (uint8_t)scale;
       }
     }
+  }
+}
+
+// bf16 tensors: 32 bytes (16 elements, half a block) per lane and step.  The position of a unit in the matrix is
+// carried along by additions: `jump` = (rows, units) to add per kThreads units, `stride` = the same per grid step.
+struct UnitStep {
+  uint32_t rows, units;
+};
+template <bool kWide>
+__device__ __forceinline__ void load_unit(const __nv_bfloat16 *x, int64_t unit, uint4 &lo, uint4 &hi) {
+  if constexpr (kWide) {  // one 32-byte load (the pointer is 32-byte aligned)
+    asm volatile("ld.global.cs.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(x + unit * 16));
+  } else {
+    const uint4 *p = reinterpret_cast<const uint4 *>(x) + unit * 2;
+    lo = ld_stream(p), hi = ld_stream(p + 1);
+  }
+}
+// I = uint32_t when unit indices and scale offsets fit in 32 bits (the usual case), else int64_t.
+template <int E, int F, bool kWide, typename I>
+__global__ void __launch_bounds__(kThreads, 4)
+mxfp_pack_mma_bf16_kernel(const __nv_bfloat16 *__restrict__ x, uint8_t *__restrict__ codes,
+                          uint8_t *__restrict__ scales, int64_t n_unit64, uint32_t unit_per_row, int64_t k_chunks,
+                          UnitStep jump, UnitStep stride, const __grid_constant__ Log2Tab tab) {
+  constexpr int kU = 2;
+  const I n_unit = (I)n_unit64;
+  const I step = (I)gridDim.x * kThreads * kU;
+  I base = (I)blockIdx.x * kThreads * kU;
+  // (row, unit in row) of this lane's first unit
+  I row;
+  uint32_t col;
+  {
+    const I j = base + threadIdx.x;
+    if (j <= (I)0x7FFFFFFF) {
+      const uint32_t q = (uint32_t)j / unit_per_row;
+      row = q, col = (uint32_t)j - q * unit_per_row;
+    } else {
+      row = j / unit_per_row, col = (uint32_t)(j - row * unit_per_row);
+    }
+  }
+  for (; base < n_unit; base += step) {
+    uint4 raws[kU][2];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const I j = base + u * kThreads + threadIdx.x;
+      if (j < n_unit)
+        load_unit<kWide>(x, (int64_t)j, raws[u][0], raws[u][1]);
+      else
+        raws[u][0] = raws[u][1] = make_uint4(0, 0, 0, 0);
+    }
+    I r = row;
+    uint32_t c = col;
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const I j = base + u * kThreads + threadIdx.x;
+      int scale;
+      const uint4 c16 = pack_bf16<E, F>(raws[u][0], raws[u][1], tab, scale);  // all lanes take part (shuffle inside)
+      if (j < n_unit) {
+        __stcs(reinterpret_cast<uint4 *>(codes) + j, c16);
+        if ((threadIdx.x & 1) == 0) scales[mma_scale_offset<I>(r, (I)(c >> 1), (I)k_chunks)] = (uint8_t)scale;
+      }
+      c += jump.units, r += jump.rows;
+      if (c >= unit_per_row) c -= unit_per_row, ++r;
+    }
+    col += stride.units, row += stride.rows;
+    if (col >= unit_per_row) col -= unit_per_row, ++row;
   }
 }
 
@@ -668,23 +726,47 @@ int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t k_chunks = (k + 127) / 128;
   const int64_t sf_bytes = ((rows + 255) / 256) * 2 * k_chunks * 512;
-  if (cudaMemsetAsync(scales_mma, 0, sf_bytes, st) != cudaSuccess) return MXQ_ERR_LAUNCH;  // padding reads as 2**-127
-#define MXQ_PACK(TI, e, f)                                                                                      \
-  if (E == e && F == f) {                                                                                       \
-    const int64_t n_vec = rows * k / Elem<TI>::kVec;                                                            \
-    mxfp_pack_mma_kernel<TI, e, f><<<grid_for(n_vec, kThreads * 2), kThreads, 0, st>>>(                         \
-        (const TI *)x, codes, scales_mma, n_vec, (uint32_t)(k / Elem<TI>::kVec), k_chunks, tab);                \
-    return check_launch();                                                                                      \
-  }
+  // padding (rows up to a multiple of 256, K up to a multiple of 128) reads as 2**-127; without padding every byte is written
+  if ((rows % 256 || k % 128) && cudaMemsetAsync(scales_mma, 0, sf_bytes, st) != cudaSuccess) return MXQ_ERR_LAUNCH;
   if (in_dtype == MXQ_F32) {
-    MXQ_PACK(float, 4, 3) MXQ_PACK(float, 2, 3) MXQ_PACK(float, 3, 2) MXQ_PACK(float, 2, 1) MXQ_PACK(float, 1, 2)
+    const int64_t n_vec = rows * k / 4;
+#define MXQ_PACK(e, f)                                                                                  \
+  if (E == e && F == f) {                                                                               \
+    mxfp_pack_mma_f32_kernel<e, f><<<grid_for(n_vec, kThreads * 2), kThreads, 0, st>>>(                 \
+        (const float *)x, codes, scales_mma, n_vec, (uint32_t)(k / 4), k_chunks, tab);                  \
+    return check_launch();                                                                              \
+  }
+    MXQ_PACK(4, 3) MXQ_PACK(2, 3) MXQ_PACK(3, 2) MXQ_PACK(2, 1) MXQ_PACK(1, 2)
+#undef MXQ_PACK
   } else if (in_dtype == MXQ_BF16) {
-    MXQ_PACK(__nv_bfloat16, 4, 3) MXQ_PACK(__nv_bfloat16, 2, 3) MXQ_PACK(__nv_bfloat16, 3, 2)
-    MXQ_PACK(__nv_bfloat16, 2, 1) MXQ_PACK(__nv_bfloat16, 1, 2)
+    const int64_t n_unit = rows * k / 16;
+    const uint32_t upr = (uint32_t)(k / 16);
+    const int grid = grid_for(n_unit, kThreads * 2);
+    const int64_t step = (int64_t)grid * kThreads * 2;
+    const UnitStep jump = {(uint32_t)(kThreads / upr), (uint32_t)(kThreads % upr)};
+    const UnitStep stride = {(uint32_t)(step / upr), (uint32_t)(step % upr)};
+    const bool wide = (reinterpret_cast<uintptr_t>(x) & 31) == 0;
+    // 32-bit indices: unit numbers (with a grid step of headroom) and scale offsets stay below 2**31
+    const bool small = n_unit + step < (1ll << 31) && sf_bytes < (1ll << 31);
+#define MXQ_PACK_ARGS (const __nv_bfloat16 *)x, codes, scales_mma, n_unit, upr, k_chunks, jump, stride, tab
+#define MXQ_PACK(e, f)                                                                                     \
+  if (E == e && F == f) {                                                                                  \
+    if (wide && small)                                                                                     \
+      mxfp_pack_mma_bf16_kernel<e, f, true, uint32_t><<<grid, kThreads, 0, st>>>(MXQ_PACK_ARGS);           \
+    else if (wide)                                                                                         \
+      mxfp_pack_mma_bf16_kernel<e, f, true, int64_t><<<grid, kThreads, 0, st>>>(MXQ_PACK_ARGS);            \
+    else if (small)                                                                                        \
+      mxfp_pack_mma_bf16_kernel<e, f, false, uint32_t><<<grid, kThreads, 0, st>>>(MXQ_PACK_ARGS);          \
+    else                                                                                                   \
+      mxfp_pack_mma_bf16_kernel<e, f, false, int64_t><<<grid, kThreads, 0, st>>>(MXQ_PACK_ARGS);           \
+    return check_launch();                                                                                 \
+  }
+    MXQ_PACK(4, 3) MXQ_PACK(2, 3) MXQ_PACK(3, 2) MXQ_PACK(2, 1) MXQ_PACK(1, 2)
   } else {
     return MXQ_ERR_DTYPE;
   }
 #undef MXQ_PACK
+#undef MXQ_PACK_ARGS
   return MXQ_ERR_FORMAT;
 }
 
