@@ -126,6 +126,14 @@ int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int 
  * the previous value.  No counterpart in the reference. */
 int mxq_gemm_set_max_ctas(int max_ctas);
 
+/* Tile scheme of mxq_gemm_mxf8 / mxq_mx_linear for problems of more than 128 rows and columns.
+ *   0  one CTA per 128 x 256 tile (tcgen05 cta_group::1);
+ *   1  CTA pairs on 256 x 256 tiles (thread-block clusters of two, tcgen05 cta_group::2) when such tiles fill the
+ *      GPU: each SM reads half of the B tile from its shared memory, which is what limits the single-CTA kernel;
+ *   2  CTA pairs for every such problem, however small (for tests).
+ * Process-wide; returns the previous value.  No reference counterpart. */
+int mxq_gemm_set_pair_mode(int mode);
+
 /* Size in bytes of the scale array that mxq_mxfp_pack_mma writes for a [rows, k] operand. */
 int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k);
 

@@ -209,9 +209,110 @@ struct Params {
   int tma_store;        // output rows are 16-byte multiples: the epilogue writes through TMA stores
 };
 
+// Epilogue of one tile for one warp: drains the warp's 32 TMEM lanes (= 32 tile rows starting at row0) of the
+// accumulator at t_acc in chunks of 32 columns, starting with chunk `first`.  A chunk is converted, written to a
+// 64-byte-swizzled staging buffer in shared memory (32 rows x 64 bytes, kStoreBufs buffers per warp) and handed to a
+// TMA store, which writes whole lines and clips at the matrix edges; output matrices whose rows are not 16-byte
+// multiples take direct predicated stores.  With overlapping accumulators `shared_columns_read` is called (lane 0)
+// once the first two chunks -- the columns both accumulators share -- are in registers.
+template <int BN, bool kOverlap, int kStoreBufs, typename F>
+__device__ __forceinline__ void drain_accumulator(const Params &p, const CUtensorMap *map_d, uint32_t t_acc, int first,
+                                                  int row0, int n0, int lane, uint8_t *stage_buf, int &buf,
+                                                  F shared_columns_read) {
+  // two chunks in flight: the TMEM load of chunk c+1 is issued before chunk c is converted and stored
+  // chunk order: with overlapping accumulators the 64 shared columns go first (the last two chunks of
+  // accumulator 0, the first two of accumulator 1)
+  uint32_t vv[2][32];
+  tmem_ld32(t_acc + (uint32_t)(first * 32), vv[0]);
+  tmem_ld_wait(vv[0]);
+#pragma unroll
+  for (int ci = 0; ci < BN / 32; ++ci) {
+    const int c = ((ci + first) % (BN / 32)) * 32;
+    const bool active = n0 + c < p.N;  // uniform across the warp; chunks past the edge are read but not stored
+    uint32_t(&v)[32] = vv[ci & 1];
+    if (ci + 1 < BN / 32) tmem_ld32(t_acc + (uint32_t)(((ci + 1 + first) % (BN / 32)) * 32), vv[(ci + 1) & 1]);
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int n = n0 + c + j;
+        float b = 0.f;
+        if (n < p.N)
+          b = p.bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.bias)[n])
+                          : reinterpret_cast<const float *>(p.bias)[n];
+        v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
+      }
+    }
+    if (!active) {
+      // nothing to store
+    } else if (p.tma_store) {
+      if (p.out_bf16) {
+        uint32_t w[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * t]), __uint_as_float(v[2 * t + 1]));
+          w[t] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStoreBufs - 1) : "memory");
+        __syncwarp();
+        uint8_t *dst = stage_buf + buf * 2048 + lane * 64;
+#pragma unroll
+        for (int t = 0; t < 4; ++t)  // 16-byte chunk t of this row lands at chunk t ^ ((row >> 1) & 3)
+          *reinterpret_cast<uint4 *>(dst + ((t ^ ((lane >> 1) & 3)) << 4)) =
+              make_uint4(w[4 * t], w[4 * t + 1], w[4 * t + 2], w[4 * t + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(map_d, smem_u32(stage_buf + buf * 2048), n0 + c, row0);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        buf = (buf + 1) % kStoreBufs;
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {  // fp32: two boxes of 16 columns (64 bytes per row) per chunk
+          if (n0 + c + 16 * h >= p.N) break;
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStoreBufs - 1) : "memory");
+          __syncwarp();
+          uint8_t *dst = stage_buf + buf * 2048 + lane * 64;
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            *reinterpret_cast<uint4 *>(dst + ((t ^ ((lane >> 1) & 3)) << 4)) =
+                make_uint4(v[16 * h + 4 * t], v[16 * h + 4 * t + 1], v[16 * h + 4 * t + 2], v[16 * h + 4 * t + 3]);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(map_d, smem_u32(stage_buf + buf * 2048), n0 + c + 16 * h, row0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          buf = (buf + 1) % kStoreBufs;
+        }
+      }
+    } else if (row0 + lane < p.M) {
+      const size_t off = (size_t)(row0 + lane) * p.N + n0 + c;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (n0 + c + j < p.N) {
+          if (p.out_bf16)
+            reinterpret_cast<__nv_bfloat16 *>(p.d)[off + j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+          else
+            reinterpret_cast<float *>(p.d)[off + j] = __uint_as_float(v[j]);
+        }
+      }
+    }
+    tmem_ld_wait(vv[(ci + 1) & 1]);
+    if constexpr (kOverlap) {
+      if (ci == 0) {  // chunks 0 and 1 of this order -- the shared columns -- are in registers now
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) shared_columns_read();
+      }
+    }
+  }
+}
+
 template <int kKind, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                  const __grid_constant__ CUtensorMap map_d, const Params p) {
   constexpr bool kScaled = kKind == kMxf8;
   constexpr int kSfbChunks = (BN + 127) / 128;
@@ -269,46 +370,53 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // The producer and the MMA issuer are single instruction streams: a lone warp issues a dependent instruction
+  // every few cycles, so what their loops cost per K chunk is their instruction count.  Both keep running
+  // addresses instead of recomputing them, and the producer spreads its copies over lanes.
   if (warp == 0) {
-    if (lane == 0) {
-      // ---------------- TMA producer ----------------
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
+    // ---------------- TMA producer: one lane per copy of a ring slot ----------------
+    // lane 0: A tile, lane 1: B tile, lane 2: A scale chunk, lanes 3..: B scale chunks (block-scaled kind)
+    constexpr int kCopies = kScaled ? 3 + kSfbChunks : 2;
+    if (lane < kCopies) {
+      const CUtensorMap *map = lane == 0 ? &map_a : lane == 1 ? &map_b : lane == 2 ? &map_sfa : &map_sfb;
+      asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+      if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
+      const bool is_sf = lane >= 2;
+      // destination inside ring slot 0, and the distance between slots
+      const uint32_t dst0 = is_sf ? s_base + L::kSfBase + (lane - 2) * 512 : s_base + (lane == 1 ? L::kA : 0);
+      const uint32_t dst_step = is_sf ? L::kSf : L::kAB;
+      const int dc0 = is_sf ? 0 : kBlockK, dc1 = is_sf ? 1 : 0;  // coordinate step per K chunk
+      uint32_t dst = dst0, full = full_bar(0), empty = empty_bar(0);
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t used = 0, last_phase = 0;  // per-stage bit masks for the exit path
+      int issued = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
+        int c0 = 0;
+        int c1 = lane == 0   ? m_blk * BM
+                 : lane == 1 ? n_blk * BN
+                 : lane == 2 ? m_blk * p.k_chunks
+                             : ((n_blk * BN) / 128 + (lane - 3)) * p.k_chunks;
         for (int kc = 0; kc < p.k_chunks; ++kc) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) {
+          if (!mbar_wait(empty, phase ^ 1u, abort_flag, p.status, kErrProducerWait)) {
             ok = false;
             break;
           }
-          const uint32_t sa = s_base + stage * L::kAB, sb = sa + L::kA;
-          const uint32_t ssf = s_base + L::kSfBase + stage * L::kSf;
-          mbar_expect_tx(full_bar(stage), L::kStage);
-          tma_load_2d(sa, &map_a, full_bar(stage), kc * kBlockK, m_blk * BM);
-          tma_load_2d(sb, &map_b, full_bar(stage), kc * kBlockK, n_blk * BN);
-          if constexpr (kScaled) {
-            bulk_load_1d(ssf, p.sfa + ((size_t)m_blk * p.k_chunks + kc) * 512, 512, full_bar(stage));
-#pragma unroll
-            for (int j = 0; j < kSfbChunks; ++j)
-              bulk_load_1d(ssf + 512 + 512 * j, p.sfb + ((size_t)((n_blk * BN) / 128 + j) * p.k_chunks + kc) * 512, 512,
-                           full_bar(stage));
-          }
-          used |= 1u << stage;
-          last_phase = (last_phase & ~(1u << stage)) | (phase << stage);
-          if (++stage == kStages) stage = 0, phase ^= 1u;
+          if (lane == 0) mbar_expect_tx(full, L::kStage);
+          tma_load_2d(dst, map, full, c0, c1);
+          c0 += dc0, c1 += dc1;
+          dst += dst_step, full += 8, empty += 8, ++issued;
+          if (++stage == kStages) stage = 0, phase ^= 1u, dst = dst0, full = full_bar(0), empty = empty_bar(0);
         }
       }
-      if (*abort_flag) {
+      if (*abort_flag && lane == 0) {
         // let the copies that were already issued land before the CTA gives up its shared memory
-        for (int s = 0; s < kStages; ++s) {
-          if (!((used >> s) & 1u)) continue;
+        for (int s = 0; s < kStages && s < issued; ++s) {
+          const int last = (issued - 1 - s) / kStages;  // index of the last fill of slot (issued - 1 - s) % kStages
           const unsigned long long t0 = global_ns();
-          while (!mbar_try_wait(full_bar(s), (last_phase >> s) & 1u) && global_ns() - t0 < 20000000ull) {
+          while (!mbar_try_wait(full_bar((issued - 1 - s) % kStages), (uint32_t)last & 1u) &&
+                 global_ns() - t0 < 20000000ull) {
           }
         }
       }
@@ -317,6 +425,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (lane == 0) {
       // ---------------- MMA issuer ----------------
       const uint32_t idesc = make_idesc<kKind, BN>();
+      uint32_t idk[4];  // per 32 bytes of K: byte k of each scale word
+#pragma unroll
+      for (int k = 0; k < 4; ++k) idk[k] = kScaled ? idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4) : idesc;
+      // running operand descriptors (the start-address field counts 16-byte units), barriers and TMEM columns
+      constexpr uint32_t kDescStep = L::kAB >> 4, kSfDescStep = L::kSf >> 4;
+      const uint64_t da0 = desc_sw128(s_base), db0 = desc_sw128(s_base + L::kA);
+      const uint64_t dsf0 = desc_sf(s_base + L::kSfBase);
+      uint64_t da = da0, db = db0, dsf = dsf0;
+      uint32_t sf_t = tmem_base + (uint32_t)kSfCol;
+      uint32_t full = full_bar(0), empty = empty_bar(0);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -334,32 +452,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccStride);
         // a B tile narrower than a 128-row scale chunk starts at one of the chunk's four 32-row TMEM columns
         const uint32_t sfb_col = (uint32_t)((((tile % tiles_n) * BN) & 127) >> 5);
+        uint32_t accumulate = 0;  // the tile's first MMA overwrites the accumulator
         for (int kc = 0; kc < p.k_chunks; ++kc) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kErrMmaWaitFull)) {
+          if (!mbar_wait(full, phase, abort_flag, p.status, kErrMmaWaitFull)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = s_base + stage * L::kAB, sb = sa + L::kA;
-          const uint64_t da = desc_sw128(sa), db = desc_sw128(sb);
-          uint32_t sfa_t = 0, sfb_t = 0;
           if constexpr (kScaled) {
-            const uint32_t ssf = s_base + L::kSfBase + stage * L::kSf;
-            sfa_t = tmem_base + (uint32_t)(kSfCol + stage * kSfColsPerStage);
-            sfb_t = sfa_t + 4;
-            tc_cp_sf(sfa_t, desc_sf(ssf));
+            tc_cp_sf(sf_t, dsf);
 #pragma unroll
-            for (int j = 0; j < kSfbChunks; ++j) tc_cp_sf(sfb_t + 4 * j, desc_sf(ssf + 512 + 512 * j));
+            for (int j = 0; j < kSfbChunks; ++j) tc_cp_sf(sf_t + 4 + 4 * j, dsf + 32u * (j + 1));  // 512 bytes on
           }
+          // 32 bytes of K per instruction: advance the start-address field inside the swizzle atom
+          umma<kKind>(d_tmem, da, db, idk[0], accumulate, sf_t, sf_t + 4 + sfb_col);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            // 32 bytes of K per instruction: advance the start-address field (16-byte units) inside the swizzle atom
-            uint32_t id = idesc;
-            if constexpr (kScaled) id |= ((uint32_t)k << 29) | ((uint32_t)k << 4);  // byte k of each scale word
-            umma<kKind>(d_tmem, da + 2u * k, db + 2u * k, id, (kc | k) != 0 ? 1u : 0u, sfa_t, sfb_t + sfb_col);
+          for (int k = 1; k < 4; ++k) umma<kKind>(d_tmem, da + 2u * k, db + 2u * k, idk[k], 1u, sf_t, sf_t + 4 + sfb_col);
+          accumulate = 1;
+          tc_commit(empty);  // arrives when the MMAs that read this slot have completed
+          da += kDescStep, db += kDescStep, dsf += kSfDescStep, sf_t += kSfColsPerStage, full += 8, empty += 8;
+          if (++stage == kStages) {
+            stage = 0, phase ^= 1u;
+            da = da0, db = db0, dsf = dsf0, sf_t = tmem_base + (uint32_t)kSfCol, full = full_bar(0), empty = empty_bar(0);
           }
-          tc_commit(empty_bar(stage));  // arrives when the MMAs that read this slot have completed
-          if (++stage == kStages) stage = 0, phase ^= 1u;
         }
         if (ok) tc_commit(acc_full_bar(acc));
       }
@@ -380,98 +495,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait)) break;
       tc_fence_after();
-      const int row0 = m_blk * BM + quarter * 32;
-      const int n0 = n_blk * BN;
-      // two chunks in flight: the TMEM load of chunk c+1 is issued before chunk c is converted and stored
-      const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride);
-      // chunk order: with overlapping accumulators the 64 shared columns go first (the last two chunks of
-      // accumulator 0, the first two of accumulator 1)
-      const int first = kOverlap && acc == 0 ? BN / 32 - 2 : 0;
-      uint32_t vv[2][32];
-      tmem_ld32(t_acc + (uint32_t)(first * 32), vv[0]);
-      tmem_ld_wait(vv[0]);
-#pragma unroll
-      for (int ci = 0; ci < BN / 32; ++ci) {
-        const int c = ((ci + first) % (BN / 32)) * 32;
-        const bool active = n0 + c < p.N;  // uniform across the warp; chunks past the edge are read but not stored
-        uint32_t(&v)[32] = vv[ci & 1];
-        if (ci + 1 < BN / 32) tmem_ld32(t_acc + (uint32_t)(((ci + 1 + first) % (BN / 32)) * 32), vv[(ci + 1) & 1]);
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int n = n0 + c + j;
-            float b = 0.f;
-            if (n < p.N)
-              b = p.bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.bias)[n])
-                              : reinterpret_cast<const float *>(p.bias)[n];
-            v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
-          }
-        }
-        if (!active) {
-          // nothing to store
-        } else if (p.tma_store) {
-          if (p.out_bf16) {
-            uint32_t w[16];
-#pragma unroll
-            for (int t = 0; t < 16; ++t) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * t]), __uint_as_float(v[2 * t + 1]));
-              w[t] = *reinterpret_cast<uint32_t *>(&h);
-            }
-            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStoreBufs - 1) : "memory");
-            __syncwarp();
-            uint8_t *dst = stage_buf + buf * 2048 + lane * 64;
-#pragma unroll
-            for (int t = 0; t < 4; ++t)  // 16-byte chunk t of this row lands at chunk t ^ ((row >> 1) & 3)
-              *reinterpret_cast<uint4 *>(dst + ((t ^ ((lane >> 1) & 3)) << 4)) =
-                  make_uint4(w[4 * t], w[4 * t + 1], w[4 * t + 2], w[4 * t + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&map_d, smem_u32(stage_buf + buf * 2048), n0 + c, row0);
-              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            }
-            buf = (buf + 1) % kStoreBufs;
-          } else {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {  // fp32: two boxes of 16 columns (64 bytes per row) per chunk
-              if (n0 + c + 16 * h >= p.N) break;
-              if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStoreBufs - 1) : "memory");
-              __syncwarp();
-              uint8_t *dst = stage_buf + buf * 2048 + lane * 64;
-#pragma unroll
-              for (int t = 0; t < 4; ++t)
-                *reinterpret_cast<uint4 *>(dst + ((t ^ ((lane >> 1) & 3)) << 4)) =
-                    make_uint4(v[16 * h + 4 * t], v[16 * h + 4 * t + 1], v[16 * h + 4 * t + 2], v[16 * h + 4 * t + 3]);
-              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-              __syncwarp();
-              if (lane == 0) {
-                tma_store_2d(&map_d, smem_u32(stage_buf + buf * 2048), n0 + c + 16 * h, row0);
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-              }
-              buf = (buf + 1) % kStoreBufs;
-            }
-          }
-        } else if (row0 + lane < p.M) {
-          const size_t off = (size_t)(row0 + lane) * p.N + n0 + c;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (n0 + c + j < p.N) {
-              if (p.out_bf16)
-                reinterpret_cast<__nv_bfloat16 *>(p.d)[off + j] = __float2bfloat16_rn(__uint_as_float(v[j]));
-              else
-                reinterpret_cast<float *>(p.d)[off + j] = __uint_as_float(v[j]);
-            }
-          }
-        }
-        tmem_ld_wait(vv[(ci + 1) & 1]);
-        if constexpr (kOverlap) {
-          if (ci == 0) {  // chunks 0 and 1 of this order -- the shared columns -- are in registers now
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(overlap_bar);
-          }
-        }
-      }
+      drain_accumulator<BN, kOverlap, kStoreBufs>(
+          p, &map_d, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride),
+          kOverlap && acc == 0 ? BN / 32 - 2 : 0, m_blk * BM + quarter * 32, n_blk * BN, lane, stage_buf, buf,
+          [&] { mbar_arrive(overlap_bar); });
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(acc));
@@ -481,6 +508,266 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// =====================================================================================================================
+// Block-scaled GEMM on CTA pairs (tcgen05 cta_group::2).
+//
+// Two CTAs of a cluster share a 256 x 256 output tile.  CTA r of the pair holds 128 rows of A (rows m0 + 128 r ...)
+// and 128 rows of B (columns n0 + 128 r ... of the output) in its shared memory and accumulates its 128 x 256 half
+// of the tile in its own tensor memory; one thread of the leader CTA (rank 0) issues M = 256 MMAs that run on both
+// SMs, each reading its A rows and its half of B locally.  Per SM and MMA that is 8 KB of operand reads from shared
+// memory instead of 12 KB for a lone CTA, and 32 KB instead of 48 KB per ring slot, which buys a 6-slot ring.
+//
+// Synchronisation (every wait bounded as in the single-CTA kernel):
+//   full[s]      leader's barrier.  The leader's producer arrives with the byte count of BOTH CTAs' slot s; all loads
+//                of both CTAs (cta_group::2 form of the TMA load, no multicast) complete on it.
+//   empty[s]     one per CTA; the leader commits the MMAs of slot s to its own and to the peer's barrier.
+//   acc_full[a]  one per CTA, committed the same way when a tile's MMAs are done.
+//   acc_empty[a], overlap: leader's barriers; the epilogue warps of both CTAs arrive (the peer's remotely).
+// Scale factors: each CTA loads the chunk of its own A rows and both chunks of the tile's B columns;
+// tcgen05.cp.cta_group::2 moves them from each CTA's shared memory into that CTA's tensor memory.
+// Both CTAs allocate all 512 TMEM columns, so their accumulator and scale addresses agree (checked at start-up).
+// A cluster barrier before the CTAs free their tensor memory keeps each alive while the other may still touch its
+// barriers or read its half of B.
+// =====================================================================================================================
+constexpr int kErrPairTmem = 5;
+
+struct PairLayout {
+  static constexpr int kStages = 6;
+  static constexpr int kStoreBufs = 2;
+  static constexpr int kA = BM * kRowBytes;            // this CTA's 128 rows of A
+  static constexpr int kB = 128 * kRowBytes;           // this CTA's 128 rows of B
+  static constexpr int kAB = kA + kB;
+  static constexpr int kSf = 512 + 2 * 512;            // own A chunk, both B chunks
+  static constexpr int kStageTx = 2 * (kAB + kSf);     // bytes of both CTAs that complete on the leader's barrier
+  static constexpr int kSfBase = kStages * kAB;
+  static constexpr int kStaging = (kStages * (kAB + kSf) + 1023) & ~1023;
+  static constexpr int kBarriers = kStaging + 4 * kStoreBufs * 2048;
+  static constexpr int kTotal = kBarriers + 32 * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_cluster_u32(uint32_t cluster_addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+// TMA load of a CTA pair: the data lands in this CTA's shared memory, the bytes complete on `bar`, which may be a
+// barrier of the peer CTA (shared::cluster address)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+// the MMAs issued so far by this thread arrive on `bar` (shared::cluster address, either CTA of the pair) when done
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc, uint32_t sfa,
+                                          uint32_t sfb) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(acc)
+      : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                      const __grid_constant__ CUtensorMap map_d, const Params p) {
+  using L = PairLayout;
+  constexpr int BN = 256;
+  constexpr int kStages = L::kStages;
+  constexpr int kStoreBufs = L::kStoreBufs;
+  constexpr int kAccStride = 192;  // accumulators [0, 256) and [192, 448), scale factors from column 448
+  constexpr int kSfCol = 448;
+  constexpr int kSfSlots = 4;      // TMEM scale-factor slots of 12 columns, used round-robin per K chunk
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t bar_base = s_base + L::kBarriers;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
+  const uint32_t overlap_bar = bar_base + 8u * (2 * kMaxStages + 4);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kBarriers + 32 * 8);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kBarriers + 32 * 8 + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();  // 0 = leader
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int tiles_m = (p.M + 255) / 256, tiles_n = (p.N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), 1), mbar_init(empty_bar(s), 1);
+    for (int a = 0; a < 2; ++a) mbar_init(acc_full_bar(a), 1), mbar_init(acc_empty_bar(a), 8);
+    mbar_init(overlap_bar, 8);  // 4 epilogue warps in each CTA
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // both CTAs' barriers are initialised and both tensor-memory addresses are published
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // the MMAs address both CTAs' tensor memory with one address: the two allocations must coincide
+  if (ld_cluster_u32(map_to_cta(smem_u32(tmem_slot), rank ^ 1u)) != tmem_base) {
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kErrPairTmem);
+  } else if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer (both CTAs) ----------------
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfa) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfb) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t used = 0, last_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+        const int m_blk = (tile / tiles_n) * 2 + (int)rank;      // 128-row block of A and of the A scales
+        const int n_blk = (tile % tiles_n) * 2;                  // first of the tile's two 128-column blocks
+        for (int kc = 0; kc < p.k_chunks; ++kc) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = s_base + stage * L::kAB, sb = sa + L::kA;
+          const uint32_t ssf = s_base + L::kSfBase + stage * L::kSf;
+          const uint32_t bar = map_to_cta(full_bar(stage), 0);
+          if (leader) mbar_expect_tx(full_bar(stage), L::kStageTx);
+          tma_load_2d_pair(sa, &map_a, bar, kc * kRowBytes, m_blk * BM);
+          tma_load_2d_pair(sb, &map_b, bar, kc * kRowBytes, (n_blk + (int)rank) * 128);
+          tma_load_2d_pair(ssf, &map_sfa, bar, 0, m_blk * p.k_chunks + kc);
+          tma_load_2d_pair(ssf + 512, &map_sfb, bar, 0, n_blk * p.k_chunks + kc);
+          tma_load_2d_pair(ssf + 1024, &map_sfb, bar, 0, (n_blk + 1) * p.k_chunks + kc);
+          used |= 1u << stage;
+          last_phase = (last_phase & ~(1u << stage)) | (phase << stage);
+          if (++stage == kStages) stage = 0, phase ^= 1u;
+        }
+      }
+      if (*abort_flag && leader) {
+        // let the copies that were already issued land before the CTAs give up their shared memory
+        for (int s = 0; s < kStages; ++s) {
+          if (!((used >> s) & 1u)) continue;
+          const unsigned long long t0 = global_ns();
+          while (!mbar_try_wait(full_bar(s), (last_phase >> s) & 1u) && global_ns() - t0 < 20000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ---------------- MMA issuer (leader only) ----------------
+      // M = 256 (both CTAs), N = 256, E4M3 x E4M3, E8M0 scales
+      const uint32_t idesc = ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24) | (1u << 23);
+      const uint32_t peer = rank ^ 1u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      uint32_t chunk = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
+        if (local > 0 && !mbar_wait(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc))
+          break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccStride);
+        for (int kc = 0; kc < p.k_chunks; ++kc, ++chunk) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kErrMmaWaitFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = s_base + stage * L::kAB, sb = sa + L::kA;
+          const uint64_t da = desc_sw128(sa), db = desc_sw128(sb);
+          const uint32_t ssf = s_base + L::kSfBase + stage * L::kSf;
+          const uint32_t sfa_t = tmem_base + (uint32_t)(kSfCol + (chunk % kSfSlots) * 12), sfb_t = sfa_t + 4;
+          tc_cp_sf_pair(sfa_t, desc_sf(ssf));
+          tc_cp_sf_pair(sfb_t, desc_sf(ssf + 512));
+          tc_cp_sf_pair(sfb_t + 4, desc_sf(ssf + 1024));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t id = idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4);  // byte k of each scale word
+            umma_pair(d_tmem, da + 2u * k, db + 2u * k, id, (kc | k) != 0 ? 1u : 0u, sfa_t, sfb_t);
+          }
+          // both CTAs' slot s is free once these MMAs have completed
+          tc_commit_pair(map_to_cta(empty_bar(stage), rank));
+          tc_commit_pair(map_to_cta(empty_bar(stage), peer));
+          if (++stage == kStages) stage = 0, phase ^= 1u;
+        }
+        if (ok) {
+          tc_commit_pair(map_to_cta(acc_full_bar(acc), rank));
+          tc_commit_pair(map_to_cta(acc_full_bar(acc), peer));
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5 of both CTAs): this CTA's 128 rows of the tile ----------------
+    const int quarter = warp & 3;
+    uint8_t *stage_buf = smem + L::kStaging + (warp - 2) * (kStoreBufs * 2048);
+    const uint32_t lead_overlap = map_to_cta(overlap_bar, 0);
+    int buf = 0;
+    int local = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++local) {
+      const int m_blk = (tile / tiles_n) * 2 + (int)rank, n_blk = tile % tiles_n;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+      if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait)) break;
+      tc_fence_after();
+      drain_accumulator<BN, true, kStoreBufs>(
+          p, &map_d, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride), acc == 0 ? BN / 32 - 2 : 0,
+          m_blk * BM + quarter * 32, n_blk * BN, lane, stage_buf, buf, [&] { mbar_arrive_cluster(lead_overlap); });
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(acc), 0));
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores done before the CTA exits
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // neither CTA frees tensor memory or exits while the other may still use it
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
@@ -536,6 +823,20 @@ static int make_store_map(CUtensorMap *map, void *ptr, bool bf16, int64_t rows, 
   return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
+// tensor map over scale-factor chunks: [chunks, 512 bytes] as rows of 128 32-bit words, one chunk per box
+static int make_sf_map(CUtensorMap *map, const void *ptr, int64_t chunks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return MXQ_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {128, (cuuint64_t)chunks};
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {128, 1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_LAUNCH;
+}
+
 // Upper bound on the CTAs (= SMs) a GEMM launch occupies; 0 = all of them.  Process-wide, set through
 // mxq_gemm_set_max_ctas by callers that want to keep SMs free for a concurrent collective.
 static int g_max_ctas = 0;
@@ -574,6 +875,13 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   p.M = (int)M, p.N = (int)N, p.K = (int)K;
   p.k_chunks = (int)((K * es + kRowBytes - 1) / kRowBytes);
   p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
+  CUtensorMap msa = ma, msb = ma;  // unused by the dense kinds
+  if constexpr (kKind == kMxf8) {
+    rc = make_sf_map(&msa, sfa, ((M + 255) / 256) * 2 * p.k_chunks);
+    if (rc) return rc;
+    rc = make_sf_map(&msb, sfb, ((N + 255) / 256) * 2 * p.k_chunks);
+    if (rc) return rc;
+  }
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
@@ -584,9 +892,57 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (g_max_ctas > 0 && grid > g_max_ctas) grid = g_max_ctas;
-  umma_gemm_kernel<kKind, BN><<<grid, kThreads, L::kTotal, st>>>(ma, mb, md, p);
+  umma_gemm_kernel<kKind, BN><<<grid, kThreads, L::kTotal, st>>>(ma, mb, msa, msb, md, p);
   return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
+
+// Block-scaled GEMM on CTA pairs; the scale buffers are padded to whole 256-row tiles (mxq_mma_scale_bytes).
+static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
+                       int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, cudaStream_t st) {
+  using L = PairLayout;
+  CUtensorMap ma, mb, msa, msb, md;
+  int rc = make_map(&ma, a, kMxf8, M, K, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, b, kMxf8, N, K, 128);
+  if (rc) return rc;
+  const int64_t k_chunks = (K + kRowBytes - 1) / kRowBytes;
+  rc = make_sf_map(&msa, sfa, ((M + 255) / 256) * 2 * k_chunks);
+  if (rc) return rc;
+  rc = make_sf_map(&msb, sfb, ((N + 255) / 256) * 2 * k_chunks);
+  if (rc) return rc;
+  const bool out_bf16 = out_dtype == MXQ_BF16;
+  const bool tma_store = (N * (out_bf16 ? 2 : 4)) % 16 == 0;
+  if (tma_store) {
+    rc = make_store_map(&md, d, out_bf16, M, N);
+    if (rc) return rc;
+  } else {
+    md = ma;  // unused by the kernel
+  }
+  Params p;
+  p.sfa = sfa, p.sfb = sfb, p.d = d, p.bias = bias, p.status = status;
+  p.M = (int)M, p.N = (int)N, p.K = (int)K;
+  p.k_chunks = (int)k_chunks;
+  p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(umma_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
+        cudaSuccess)
+      return MXQ_ERR_LAUNCH;
+    attr_set = true;
+  }
+  const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  int grid = sm_count();
+  if (g_max_ctas > 0 && grid > g_max_ctas) grid = g_max_ctas;
+  if (2 * tiles < grid) grid = (int)(2 * tiles);
+  grid &= ~1;
+  if (grid < 2) return MXQ_ERR_UNSUPPORTED;
+  umma_gemm_pair_kernel<<<grid, kThreads, L::kTotal, st>>>(ma, mb, msa, msb, md, p);
+  return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
+}
+
+// 0: single-CTA tiles only; 1: CTA pairs where 256-column tiles fill the GPU; 2: CTA pairs whenever the problem has
+// more than 128 rows and columns (for tests).  Process-wide.
+static int g_pair_mode = 0;
 
 // Tile width: 256 columns when that already gives every SM a tile; narrower tiles for small problems (few rows of
 // activations against a large weight are bound by streaming the weight, which needs many SMs pulling at once).
@@ -595,8 +951,12 @@ static int launch_any(const void *a, const void *b, const uint8_t *sfa, const ui
                       int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, cudaStream_t st) {
   const int64_t tiles_m = (M + BM - 1) / BM;
   const int sms = sm_count();
-  if (tiles_m * ((N + 255) / 256) * 2 > sms || N <= 64)
-    return launch<kKind, 256>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+  const bool wide = tiles_m * ((N + 255) / 256) * 2 > sms || N <= 64;
+  if constexpr (kKind == kMxf8) {
+    if (M > 128 && N > 128 && ((g_pair_mode == 1 && wide) || g_pair_mode == 2))
+      return launch_pair(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+  }
+  if (wide) return launch<kKind, 256>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
   // The block-scaled MMA takes its B scales from TMEM columns whose offset inside a 128-row chunk must be even
   // (0 or 2), so its narrowest tile is 64 columns; the dense kinds go down to 32.
   if (kKind == kMxf8 || tiles_m * ((N + 63) / 64) * 2 > sms || N <= 32)
@@ -616,6 +976,12 @@ extern "C" {
 int mxq_gemm_set_max_ctas(int max_ctas) {
   const int prev = g_max_ctas;
   g_max_ctas = max_ctas > 0 ? max_ctas : 0;
+  return prev;
+}
+
+int mxq_gemm_set_pair_mode(int mode) {
+  const int prev = g_pair_mode;
+  g_pair_mode = mode < 0 || mode > 2 ? 0 : mode;
   return prev;
 }
 

@@ -29,7 +29,15 @@ _STATUS_TEXT = {
     2: "MMA issuer: wait for an operand tile ran out",
     3: "MMA issuer: wait for a free accumulator ran out",
     4: "epilogue: wait for a finished accumulator ran out",
+    5: "CTA pair: the two CTAs got different tensor-memory addresses",
 }
+
+
+def set_pair_mode(mode: int) -> int:
+    """Tile scheme of the block-scaled GEMM (mxq_gemm_set_pair_mode): 0 = one CTA per 128 x 256 tile, 1 = CTA pairs
+    on 256 x 256 tiles when such tiles fill the GPU, 2 = CTA pairs for every problem above 128 rows and columns.
+    Returns the previous mode."""
+    return _lib.lib().mxq_gemm_set_pair_mode(int(mode))
 
 
 def _status(device: torch.device) -> Tensor:

@@ -76,6 +76,31 @@ def test_mxf8_gemm_matches_oracle(shape):
     assert rel_err(y32, ref) <= REL_TOL
 
 
+@pytest.mark.parametrize("shape", [(256, 128, 256), (256, 4096, 256), (512, 1024, 512), (1024, 512, 768), (300, 256, 260),
+                                   (129, 512, 129), (2048, 4096, 4096), (1000, 2048, 1304), (4096, 8192, 512)])
+def test_mxf8_gemm_cta_pairs_match_single_cta_and_oracle(shape):
+    """CTA pairs (cta_group::2, 256 x 256 tiles) give the bits of the single-CTA kernel (same accumulation order),
+    with bias, ragged edges and both output types; both match the oracle."""
+    M, K, N = shape
+    x, w = synthetic.linear_operands(M, K, N, seed=4)
+    g = torch.Generator().manual_seed(4)
+    b = torch.randn(N, generator=g).to(DEV)
+    ref = O.mxfp_fake(x, 32, 4, 3).float() @ O.mxfp_fake(w, 32, 4, 3, 1).float().t() + b.cpu()
+    xp = gemm.pack_mx_operand(x.to(DEV), 4, 3)
+    wp = gemm.pack_mx_operand(w.to(DEV), 4, 3)
+    prev = gemm.set_pair_mode(0)
+    try:
+        single = [gemm.mx_gemm(xp, wp, b, dt) for dt in (torch.float32, torch.bfloat16)]
+        gemm.set_pair_mode(2)
+        pair = [gemm.mx_gemm(xp, wp, b, dt) for dt in (torch.float32, torch.bfloat16)]
+        gemm.check_status()
+    finally:
+        gemm.set_pair_mode(prev)
+    assert torch.equal(single[0], pair[0]) and torch.equal(single[1], pair[1])
+    assert rel_err(pair[0], ref) <= REL_TOL
+    assert rel_err(pair[1], ref) <= 4e-3
+
+
 def test_mxf8_pack_round_trip():
     """Packed codes * scales reproduce the oracle's fake-quant values (up to the documented re-encoding of blocks
     that hold the reference's top E4M3 code)."""
