@@ -84,6 +84,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   return true;
 }
+// the same for a whole warp: every lane waits, and all lanes get the same answer
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
+                                               int code) {
+  return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag, status, code));
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -99,6 +104,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t sr
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(map), "r"(src), "r"(c0), "r"(c1)
                : "memory");
+}
+// true in exactly one lane of a fully active warp (the same lane every time)
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -347,7 +358,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kBarriers + 32 * 8);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kBarriers + 32 * 8 + 8);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;  // warp: provably uniform
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
 
@@ -370,95 +381,100 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // The producer and the MMA issuer are single instruction streams: a lone warp issues a dependent instruction
-  // every few cycles, so what their loops cost per K chunk is their instruction count.  Both keep running
-  // addresses instead of recomputing them, and the producer spreads its copies over lanes.
+  // The producer and the MMA issuer run their loops with all 32 lanes of their warp on identical values and elect
+  // one lane for the TMA / tcgen05 instructions themselves.  Those instructions take their operands from uniform
+  // registers; in a loop that only one lane executes every operand would have to be moved there first, which made
+  // each of them cost about 70 cycles to issue -- more per K chunk than its MMAs take to run.
   if (warp == 0) {
-    // ---------------- TMA producer: one lane per copy of a ring slot ----------------
-    // lane 0: A tile, lane 1: B tile, lane 2: A scale chunk, lanes 3..: B scale chunks (block-scaled kind)
-    constexpr int kCopies = kScaled ? 3 + kSfbChunks : 2;
-    if (lane < kCopies) {
-      const CUtensorMap *map = lane == 0 ? &map_a : lane == 1 ? &map_b : lane == 2 ? &map_sfa : &map_sfb;
-      asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-      if (lane == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
-      const bool is_sf = lane >= 2;
-      // destination inside ring slot 0, and the distance between slots
-      const uint32_t dst0 = is_sf ? s_base + L::kSfBase + (lane - 2) * 512 : s_base + (lane == 1 ? L::kA : 0);
-      const uint32_t dst_step = is_sf ? L::kSf : L::kAB;
-      const int dc0 = is_sf ? 0 : kBlockK, dc1 = is_sf ? 1 : 0;  // coordinate step per K chunk
-      uint32_t dst = dst0, full = full_bar(0), empty = empty_bar(0);
-      int stage = 0;
-      uint32_t phase = 0;
-      int issued = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
-        int c0 = 0;
-        int c1 = lane == 0   ? m_blk * BM
-                 : lane == 1 ? n_blk * BN
-                 : lane == 2 ? m_blk * p.k_chunks
-                             : ((n_blk * BN) / 128 + (lane - 3)) * p.k_chunks;
-        for (int kc = 0; kc < p.k_chunks; ++kc) {
-          if (!mbar_wait(empty, phase ^ 1u, abort_flag, p.status, kErrProducerWait)) {
-            ok = false;
-            break;
-          }
-          if (lane == 0) mbar_expect_tx(full, L::kStage);
-          tma_load_2d(dst, map, full, c0, c1);
-          c0 += dc0, c1 += dc1;
-          dst += dst_step, full += 8, empty += 8, ++issued;
-          if (++stage == kStages) stage = 0, phase ^= 1u, dst = dst0, full = full_bar(0), empty = empty_bar(0);
-        }
+    // ---------------- TMA producer ----------------
+    if (elect_one()) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      if constexpr (kScaled) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfa) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfb) : "memory");
       }
-      if (*abort_flag && lane == 0) {
-        // let the copies that were already issued land before the CTA gives up its shared memory
-        for (int s = 0; s < kStages && s < issued; ++s) {
-          const int last = (issued - 1 - s) / kStages;  // index of the last fill of slot (issued - 1 - s) % kStages
-          const unsigned long long t0 = global_ns();
-          while (!mbar_try_wait(full_bar((issued - 1 - s) % kStages), (uint32_t)last & 1u) &&
-                 global_ns() - t0 < 20000000ull) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
+    }
+    uint32_t sa = s_base, ssf = s_base + L::kSfBase, full = full_bar(0), empty = empty_bar(0);
+    int stage = 0;
+    uint32_t phase = 0;
+    int issued = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
+      const int row_a = m_blk * BM, row_b = n_blk * BN;
+      int chunk_a = m_blk * p.k_chunks, chunk_b = ((n_blk * BN) / 128) * p.k_chunks;  // rows of the scale maps
+      int k0 = 0;
+      for (int kc = 0; kc < p.k_chunks; ++kc) {
+        if (!mbar_wait_warp(empty, phase ^ 1u, abort_flag, p.status, kErrProducerWait)) {
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
+          mbar_expect_tx(full, L::kStage);
+          tma_load_2d(sa, &map_a, full, k0, row_a);
+          tma_load_2d(sa + L::kA, &map_b, full, k0, row_b);
+          if constexpr (kScaled) {
+            tma_load_2d(ssf, &map_sfa, full, 0, chunk_a);
+#pragma unroll
+            for (int j = 0; j < kSfbChunks; ++j)
+              tma_load_2d(ssf + 512 + 512 * j, &map_sfb, full, 0, chunk_b + j * p.k_chunks);
           }
+        }
+        k0 += kBlockK, ++chunk_a, ++chunk_b;
+        sa += L::kAB, ssf += L::kSf, full += 8, empty += 8, ++issued;
+        if (++stage == kStages)
+          stage = 0, phase ^= 1u, sa = s_base, ssf = s_base + L::kSfBase, full = full_bar(0), empty = empty_bar(0);
+      }
+    }
+    if (*abort_flag && lane == 0) {
+      // let the copies that were already issued land before the CTA gives up its shared memory
+      for (int s = 0; s < kStages && s < issued; ++s) {
+        const int last = (issued - 1 - s) / kStages;  // index of the last fill of slot (issued - 1 - s) % kStages
+        const unsigned long long t0 = global_ns();
+        while (!mbar_try_wait(full_bar((issued - 1 - s) % kStages), (uint32_t)last & 1u) &&
+               global_ns() - t0 < 20000000ull) {
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ---------------- MMA issuer ----------------
-      const uint32_t idesc = make_idesc<kKind, BN>();
-      uint32_t idk[4];  // per 32 bytes of K: byte k of each scale word
+    // ---------------- MMA issuer ----------------
+    const uint32_t idesc = make_idesc<kKind, BN>();
+    uint32_t idk[4];  // per 32 bytes of K: byte k of each scale word
 #pragma unroll
-      for (int k = 0; k < 4; ++k) idk[k] = kScaled ? idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4) : idesc;
-      // running operand descriptors (the start-address field counts 16-byte units), barriers and TMEM columns
-      constexpr uint32_t kDescStep = L::kAB >> 4, kSfDescStep = L::kSf >> 4;
-      const uint64_t da0 = desc_sw128(s_base), db0 = desc_sw128(s_base + L::kA);
-      const uint64_t dsf0 = desc_sf(s_base + L::kSfBase);
-      uint64_t da = da0, db = db0, dsf = dsf0;
-      uint32_t sf_t = tmem_base + (uint32_t)kSfCol;
-      uint32_t full = full_bar(0), empty = empty_bar(0);
-      int stage = 0;
-      uint32_t phase = 0;
-      int local = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
-        const int acc = local % kAccStages;
-        const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
-        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
-        if constexpr (kOverlap) {  // the previous tile's epilogue has read the columns both accumulators share
-          if (local > 0 &&
-              !mbar_wait(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc))
-            break;
+    for (int k = 0; k < 4; ++k) idk[k] = kScaled ? idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4) : idesc;
+    // running operand descriptors (the start-address field counts 16-byte units), barriers and TMEM columns
+    constexpr uint32_t kDescStep = L::kAB >> 4, kSfDescStep = L::kSf >> 4;
+    const uint64_t da0 = desc_sw128(s_base), db0 = desc_sw128(s_base + L::kA);
+    const uint64_t dsf0 = desc_sf(s_base + L::kSfBase);
+    uint64_t da = da0, db = db0, dsf = dsf0;
+    uint32_t sf_t = tmem_base + (uint32_t)kSfCol;
+    uint32_t full = full_bar(0), empty = empty_bar(0);
+    int stage = 0;
+    uint32_t phase = 0;
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
+      const int acc = local % kAccStages;
+      const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
+      if (!mbar_wait_warp(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
+      if constexpr (kOverlap) {  // the previous tile's epilogue has read the columns both accumulators share
+        if (local > 0 && !mbar_wait_warp(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc))
+          break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccStride);
+      // a B tile narrower than a 128-row scale chunk starts at one of the chunk's four 32-row TMEM columns
+      const uint32_t sfb_col = (uint32_t)((((tile % tiles_n) * BN) & 127) >> 5);
+      uint32_t accumulate = 0;  // the tile's first MMA overwrites the accumulator
+      for (int kc = 0; kc < p.k_chunks; ++kc) {
+        if (!mbar_wait_warp(full, phase, abort_flag, p.status, kErrMmaWaitFull)) {
+          ok = false;
+          break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccStride);
-        // a B tile narrower than a 128-row scale chunk starts at one of the chunk's four 32-row TMEM columns
-        const uint32_t sfb_col = (uint32_t)((((tile % tiles_n) * BN) & 127) >> 5);
-        uint32_t accumulate = 0;  // the tile's first MMA overwrites the accumulator
-        for (int kc = 0; kc < p.k_chunks; ++kc) {
-          if (!mbar_wait(full, phase, abort_flag, p.status, kErrMmaWaitFull)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
+        if (elect_one()) {
           if constexpr (kScaled) {
             tc_cp_sf(sf_t, dsf);
 #pragma unroll
@@ -468,16 +484,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           umma<kKind>(d_tmem, da, db, idk[0], accumulate, sf_t, sf_t + 4 + sfb_col);
 #pragma unroll
           for (int k = 1; k < 4; ++k) umma<kKind>(d_tmem, da + 2u * k, db + 2u * k, idk[k], 1u, sf_t, sf_t + 4 + sfb_col);
-          accumulate = 1;
           tc_commit(empty);  // arrives when the MMAs that read this slot have completed
-          da += kDescStep, db += kDescStep, dsf += kSfDescStep, sf_t += kSfColsPerStage, full += 8, empty += 8;
-          if (++stage == kStages) {
-            stage = 0, phase ^= 1u;
-            da = da0, db = db0, dsf = dsf0, sf_t = tmem_base + (uint32_t)kSfCol, full = full_bar(0), empty = empty_bar(0);
-          }
         }
-        if (ok) tc_commit(acc_full_bar(acc));
+        accumulate = 1;
+        da += kDescStep, db += kDescStep, dsf += kSfDescStep, sf_t += kSfColsPerStage, full += 8, empty += 8;
+        if (++stage == kStages) {
+          stage = 0, phase ^= 1u;
+          da = da0, db = db0, dsf = dsf0, sf_t = tmem_base + (uint32_t)kSfCol, full = full_bar(0), empty = empty_bar(0);
+        }
       }
+      if (ok && elect_one()) tc_commit(acc_full_bar(acc));
     }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
