@@ -236,7 +236,31 @@ def extras(device, x) -> dict:
         g = quick_gbs(lambda: mb.mxfp_quantizer(xx, 32, 4, 3), xx.numel() * 4, calls=50)
         out[f"mxfp8_bf16_{shape[0]}x{shape[1]}_us"] = xx.numel() * 4 / g / 1e3
     out["linear_mxfp8_4096x4096"] = linear_extras(device)
+    out["decoder_layer_mixed_precision"] = decoder_layer_extras(device)
     return out
+
+
+def decoder_layer_extras(device) -> dict:
+    """Llama-style decoder layer, hidden 4096, 32 heads, FFN 11008, batch 8 x sequence 512 (4096 tokens), bf16:
+    q/k/v/o MXINT8 weights and activations (exact bf16 tensor-core GEMM of the quantized values), gate/up/down MXFP4
+    weights x MXFP8 activations (block-scaled GEMM); norms, RoPE, attention and SiLU unquantized."""
+    import mase_b200 as mb
+    from mase_b200 import gemm, synthetic
+
+    layer = synthetic.quantize_decoder_layer(
+        synthetic.DecoderLayer().to(device),
+        lambda k, n: mb.LinearMXInt(k, n, bias=False, device=device, dtype=torch.bfloat16,
+                                    config=dict(synthetic.MXINT8_LINEAR)),
+        lambda k, n: mb.LinearMXFP(k, n, bias=False, device=device, dtype=torch.bfloat16,
+                                   config=dict(synthetic.MXFP4W_MXFP8A_LINEAR)))
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(8, 512, 4096, generator=g).bfloat16().to(device)
+    with torch.no_grad():
+        t = 1.0 / quick_gbs(lambda: layer(x), 1, calls=10) / 1e9
+    gemm.check_status(device)
+    flops = layer.linear_flops(8 * 512)
+    return {"ms_per_forward": t * 1e3, "linear_TFLOPs": flops / t / 1e12, "tokens": 8 * 512,
+            "linear_flops": flops}
 
 
 def linear_extras(device) -> dict:

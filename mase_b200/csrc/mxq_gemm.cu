@@ -1,22 +1,23 @@
 // D[M,N] = A[M,K] * B[N,K]^T (+ bias[N]) on the 5th-generation tensor cores of sm_100a.
 //
 // One persistent CTA per SM, 192 threads in three roles:
-//   warp 0 (one lane)  TMA producer: 128-byte-swizzled K-major tiles of A (128 rows) and B (BN rows) and, for the
-//                      block-scaled kind, the E8M0 scale chunks, into a 4-stage shared-memory ring (mbarrier
-//                      transaction counts signal arrival);
-//   warp 1 (one lane)  MMA issuer: tcgen05.mma (cta_group::1, M=128, N=BN, 32 bytes of K per instruction) with fp32
-//                      accumulators in tensor memory; tcgen05.commit releases ring slots and publishes finished
-//                      accumulators;
-//   warps 2..5         epilogue: tcgen05.ld the accumulator (each warp owns the 32 TMEM lanes of its quarter), add
-//                      the bias, convert and store to global memory.
+//   warp 0     TMA producer: 128-byte-swizzled K-major tiles of A (128 rows) and B (BN rows) and, for the
+//              block-scaled kind, the E8M0 scale chunks, into a shared-memory ring (mbarrier transaction counts
+//              signal arrival);
+//   warp 1     MMA issuer: tcgen05.mma (M=128, N=BN, 32 bytes of K per instruction) with fp32 accumulators in tensor
+//              memory; tcgen05.commit releases ring slots and publishes finished accumulators;
+//   warps 2..5 epilogue: tcgen05.ld the accumulator (each warp owns the 32 TMEM lanes of its quarter), add the bias,
+//              convert, stage in shared memory and store with TMA.
+// Warps 0 and 1 run their loops with all lanes on identical values and elect one lane per instruction group, so that
+// the operands of the TMA / tcgen05 instructions live in uniform registers.
 // Kinds: bf16 x bf16 (kind::f16), fp32 x fp32 rounded to tf32 (kind::tf32) and MXFP8 E4M3 x E4M3 with one E8M0
-// scale per 32 elements of K (kind::mxf8f6f4.block_scale).  The dense kinds double-buffer the accumulator
-// (2 x 256 TMEM columns) so that the epilogue of a tile overlaps the main loop of the next one; the block-scaled
-// kind needs TMEM columns for the scale factors and uses a single accumulator.
+// scale per 32 elements of K (kind::mxf8f6f4.block_scale).  Accumulators are double-buffered so that the epilogue of
+// a tile overlaps the main loop of the next one (for the block-scaled 256-column tile the two overlap by 64 columns,
+// see the kernel).  A second kernel runs the block-scaled kind on CTA pairs (cta_group::2, 256 x 256 tiles).
 //
-// No thread-block clusters and no multicast loads are used.  Every wait on an mbarrier is bounded: when it runs
-// out the CTA raises an abort flag, records an error code in the caller's status word, waits (bounded) for its own
-// bulk copies in flight, frees its tensor memory and returns.
+// No multicast loads are used.  Every wait on an mbarrier is bounded: when it runs out the CTA raises an abort
+// flag, records an error code in the caller's status word, waits (bounded) for its own bulk copies in flight, frees
+// its tensor memory and returns.
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -637,7 +638,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kBarriers + 32 * 8);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kBarriers + 32 * 8 + 8);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();  // 0 = leader
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
@@ -667,94 +668,114 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   if (ld_cluster_u32(map_to_cta(smem_u32(tmem_slot), rank ^ 1u)) != tmem_base) {
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kErrPairTmem);
   } else if (warp == 0) {
-    if (lane == 0) {
-      // ---------------- TMA producer (both CTAs) ----------------
+    // ---------------- TMA producer (both CTAs; warp-uniform loop, one elected lane issues) ----------------
+    if (elect_one()) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfa) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfb) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
-      int stage = 0;
-      uint32_t phase = 0;
-      uint32_t used = 0, last_phase = 0;
-      bool ok = true;
-      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
-        const int m_blk = (tile / tiles_n) * 2 + (int)rank;      // 128-row block of A and of the A scales
-        const int n_blk = (tile % tiles_n) * 2;                  // first of the tile's two 128-column blocks
-        for (int kc = 0; kc < p.k_chunks; ++kc) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kErrProducerWait)) {
-            ok = false;
-            break;
-          }
-          const uint32_t sa = s_base + stage * L::kAB, sb = sa + L::kA;
-          const uint32_t ssf = s_base + L::kSfBase + stage * L::kSf;
-          const uint32_t bar = map_to_cta(full_bar(stage), 0);
-          if (leader) mbar_expect_tx(full_bar(stage), L::kStageTx);
-          tma_load_2d_pair(sa, &map_a, bar, kc * kRowBytes, m_blk * BM);
-          tma_load_2d_pair(sb, &map_b, bar, kc * kRowBytes, (n_blk + (int)rank) * 128);
-          tma_load_2d_pair(ssf, &map_sfa, bar, 0, m_blk * p.k_chunks + kc);
-          tma_load_2d_pair(ssf + 512, &map_sfb, bar, 0, n_blk * p.k_chunks + kc);
-          tma_load_2d_pair(ssf + 1024, &map_sfb, bar, 0, (n_blk + 1) * p.k_chunks + kc);
-          used |= 1u << stage;
-          last_phase = (last_phase & ~(1u << stage)) | (phase << stage);
-          if (++stage == kStages) stage = 0, phase ^= 1u;
+    }
+    const uint32_t lead_full0 = map_to_cta(full_bar(0), 0);  // the leader's full[0] as a shared::cluster address
+    uint32_t sa = s_base, ssf = s_base + L::kSfBase, full = full_bar(0), lead_full = lead_full0, empty = empty_bar(0);
+    int stage = 0;
+    uint32_t phase = 0;
+    int issued = 0;
+    bool ok = true;
+    for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+      const int m_blk = (tile / tiles_n) * 2 + (int)rank;      // 128-row block of A and of the A scales
+      const int n_blk = (tile % tiles_n) * 2;                  // first of the tile's two 128-column blocks
+      const int row_a = m_blk * BM, row_b = (n_blk + (int)rank) * 128;
+      int chunk_a = m_blk * p.k_chunks, chunk_b = n_blk * p.k_chunks;
+      int k0 = 0;
+      for (int kc = 0; kc < p.k_chunks; ++kc) {
+        if (!mbar_wait_warp(empty, phase ^ 1u, abort_flag, p.status, kErrProducerWait)) {
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
+          if (leader) mbar_expect_tx(full, L::kStageTx);
+          tma_load_2d_pair(sa, &map_a, lead_full, k0, row_a);
+          tma_load_2d_pair(sa + L::kA, &map_b, lead_full, k0, row_b);
+          tma_load_2d_pair(ssf, &map_sfa, lead_full, 0, chunk_a);
+          tma_load_2d_pair(ssf + 512, &map_sfb, lead_full, 0, chunk_b);
+          tma_load_2d_pair(ssf + 1024, &map_sfb, lead_full, 0, chunk_b + p.k_chunks);
+        }
+        k0 += kRowBytes, ++chunk_a, ++chunk_b;
+        sa += L::kAB, ssf += L::kSf, full += 8, lead_full += 8, empty += 8, ++issued;
+        if (++stage == kStages) {
+          stage = 0, phase ^= 1u;
+          sa = s_base, ssf = s_base + L::kSfBase, full = full_bar(0), lead_full = lead_full0, empty = empty_bar(0);
         }
       }
-      if (*abort_flag && leader) {
-        // let the copies that were already issued land before the CTAs give up their shared memory
-        for (int s = 0; s < kStages; ++s) {
-          if (!((used >> s) & 1u)) continue;
-          const unsigned long long t0 = global_ns();
-          while (!mbar_try_wait(full_bar(s), (last_phase >> s) & 1u) && global_ns() - t0 < 20000000ull) {
-          }
+    }
+    if (*abort_flag && leader && lane == 0) {
+      // let the copies that were already issued land before the CTAs give up their shared memory
+      for (int s = 0; s < kStages && s < issued; ++s) {
+        const int last = (issued - 1 - s) / kStages;
+        const unsigned long long t0 = global_ns();
+        while (!mbar_try_wait(full_bar((issued - 1 - s) % kStages), (uint32_t)last & 1u) &&
+               global_ns() - t0 < 20000000ull) {
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && leader) {
-      // ---------------- MMA issuer (leader only) ----------------
+    if (leader) {
+      // ---------------- MMA issuer (leader only; warp-uniform loop, one elected lane issues) ----------------
       // M = 256 (both CTAs), N = 256, E4M3 x E4M3, E8M0 scales
       const uint32_t idesc = ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24) | (1u << 23);
-      const uint32_t peer = rank ^ 1u;
+      uint32_t idk[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) idk[k] = idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4);  // byte k of each scale word
+      constexpr uint32_t kDescStep = L::kAB >> 4, kSfDescStep = L::kSf >> 4;
+      const uint64_t da0 = desc_sw128(s_base), db0 = desc_sw128(s_base + L::kA), dsf0 = desc_sf(s_base + L::kSfBase);
+      const uint32_t my_empty0 = map_to_cta(empty_bar(0), rank), peer_empty0 = map_to_cta(empty_bar(0), rank ^ 1u);
+      uint64_t da = da0, db = db0, dsf = dsf0;
+      uint32_t full = full_bar(0), my_empty = my_empty0, peer_empty = peer_empty0;
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
-      uint32_t chunk = 0;
+      uint32_t slot = 0;  // TMEM scale-factor slot
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
-        if (local > 0 && !mbar_wait(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc))
+        if (!mbar_wait_warp(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
+        if (local > 0 &&
+            !mbar_wait_warp(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc))
           break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccStride);
-        for (int kc = 0; kc < p.k_chunks; ++kc, ++chunk) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, kErrMmaWaitFull)) {
+        uint32_t accumulate = 0;
+        for (int kc = 0; kc < p.k_chunks; ++kc) {
+          if (!mbar_wait_warp(full, phase, abort_flag, p.status, kErrMmaWaitFull)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = s_base + stage * L::kAB, sb = sa + L::kA;
-          const uint64_t da = desc_sw128(sa), db = desc_sw128(sb);
-          const uint32_t ssf = s_base + L::kSfBase + stage * L::kSf;
-          const uint32_t sfa_t = tmem_base + (uint32_t)(kSfCol + (chunk % kSfSlots) * 12), sfb_t = sfa_t + 4;
-          tc_cp_sf_pair(sfa_t, desc_sf(ssf));
-          tc_cp_sf_pair(sfb_t, desc_sf(ssf + 512));
-          tc_cp_sf_pair(sfb_t + 4, desc_sf(ssf + 1024));
+          const uint32_t sf_t = tmem_base + (uint32_t)kSfCol + slot * 12u;
+          if (elect_one()) {
+            tc_cp_sf_pair(sf_t, dsf);
+            tc_cp_sf_pair(sf_t + 4, dsf + 32u);
+            tc_cp_sf_pair(sf_t + 8, dsf + 64u);
+            umma_pair(d_tmem, da, db, idk[0], accumulate, sf_t, sf_t + 4);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t id = idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4);  // byte k of each scale word
-            umma_pair(d_tmem, da + 2u * k, db + 2u * k, id, (kc | k) != 0 ? 1u : 0u, sfa_t, sfb_t);
+            for (int k = 1; k < 4; ++k) umma_pair(d_tmem, da + 2u * k, db + 2u * k, idk[k], 1u, sf_t, sf_t + 4);
+            // both CTAs' slot is free once these MMAs have completed
+            tc_commit_pair(my_empty);
+            tc_commit_pair(peer_empty);
           }
-          // both CTAs' slot s is free once these MMAs have completed
-          tc_commit_pair(map_to_cta(empty_bar(stage), rank));
-          tc_commit_pair(map_to_cta(empty_bar(stage), peer));
-          if (++stage == kStages) stage = 0, phase ^= 1u;
+          accumulate = 1;
+          slot = (slot + 1) % kSfSlots;
+          da += kDescStep, db += kDescStep, dsf += kSfDescStep, full += 8, my_empty += 8, peer_empty += 8;
+          if (++stage == kStages) {
+            stage = 0, phase ^= 1u;
+            da = da0, db = db0, dsf = dsf0, full = full_bar(0), my_empty = my_empty0, peer_empty = peer_empty0;
+          }
         }
-        if (ok) {
+        if (ok && elect_one()) {
           tc_commit_pair(map_to_cta(acc_full_bar(acc), rank));
-          tc_commit_pair(map_to_cta(acc_full_bar(acc), peer));
+          tc_commit_pair(map_to_cta(acc_full_bar(acc), rank ^ 1u));
         }
       }
     }
@@ -958,7 +979,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
 
 // 0: single-CTA tiles only; 1: CTA pairs where 256-column tiles fill the GPU; 2: CTA pairs whenever the problem has
 // more than 128 rows and columns (for tests).  Process-wide.
-static int g_pair_mode = 0;
+static int g_pair_mode = 1;
 
 // Tile width: 256 columns when that already gives every SM a tile; narrower tiles for small problems (few rows of
 // activations against a large weight are bound by streaming the weight, which needs many SMs pulling at once).

@@ -50,3 +50,71 @@ def device_student_t3(rows: int, cols: int, seed: int, device, dtype=torch.bfloa
             chi += torch.randn(r1 - r0, cols, generator=g, device=device) ** 2
         out[r0:r1] = (z / (chi / 3).sqrt() * scale).to(dtype)
     return out
+
+
+# ---- mixed-precision decoder layer (Llama-style, random weights) ---------------------------------------------------
+MXINT8_LINEAR = {"weight_block_size": 32, "weight_width": 8, "data_in_block_size": 32, "data_in_width": 8}
+MXFP4W_MXFP8A_LINEAR = {"weight_block_size": 32, "weight_exponent_width": 2, "weight_frac_width": 1,
+                        "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+
+
+class DecoderLayer(torch.nn.Module):
+    """Pre-norm decoder layer: RMSNorm -> q/k/v -> RoPE -> causal attention -> o -> residual -> RMSNorm -> SwiGLU
+    (gate, up, down) -> residual.  The seven projections are `torch.nn.Linear` children without bias, which a
+    quantize pass (or `quantize_decoder_layer`) swaps for quantized classes; norms (computed in fp32, weights 1),
+    RoPE, softmax and SiLU stay unquantized."""
+
+    ATTENTION = ("q_proj", "k_proj", "v_proj", "o_proj")
+    FFN = ("gate_proj", "up_proj", "down_proj")
+
+    def __init__(self, hidden: int = 4096, heads: int = 32, ffn: int = 11008, eps: float = 1e-6, theta: float = 10000.0,
+                 seed: int = 3, dtype=torch.bfloat16):
+        super().__init__()
+        assert hidden % heads == 0
+        self.hidden, self.heads, self.ffn, self.eps, self.theta = hidden, heads, ffn, eps, theta
+        g = torch.Generator().manual_seed(seed)
+        for name, (k, n) in {"q_proj": (hidden, hidden), "k_proj": (hidden, hidden), "v_proj": (hidden, hidden),
+                             "o_proj": (hidden, hidden), "gate_proj": (hidden, ffn), "up_proj": (hidden, ffn),
+                             "down_proj": (ffn, hidden)}.items():
+            lin = torch.nn.Linear(k, n, bias=False, dtype=dtype)
+            lin.weight.data.copy_((torch.randn(n, k, generator=g) * 0.02).to(dtype))
+            setattr(self, name, lin)
+
+    def _norm(self, x):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype)
+
+    def _rope(self, t):  # t: [B, heads, S, head_dim]
+        s, d = t.shape[-2], t.shape[-1]
+        inv = 1.0 / (self.theta ** (torch.arange(0, d, 2, device=t.device, dtype=torch.float32) / d))
+        ang = torch.arange(s, device=t.device, dtype=torch.float32)[:, None] * inv[None, :]
+        cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+        tf = t.float()
+        rot = torch.cat([-tf[..., d // 2:], tf[..., : d // 2]], -1)
+        return (tf * cos + rot * sin).to(t.dtype)
+
+    def forward(self, x):  # [B, S, hidden]
+        b, s, h = x.shape
+        hd = h // self.heads
+        y = self._norm(x)
+        q, k, v = (proj(y).view(b, s, self.heads, hd).transpose(1, 2) for proj in (self.q_proj, self.k_proj, self.v_proj))
+        q, k = self._rope(q), self._rope(k)
+        att = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+        x = x + self.o_proj(att.transpose(1, 2).reshape(b, s, h))
+        y = self._norm(x)
+        return x + self.down_proj(torch.nn.functional.silu(self.gate_proj(y)) * self.up_proj(y))
+
+    def linear_flops(self, tokens: int) -> int:
+        return 2 * tokens * (4 * self.hidden * self.hidden + 3 * self.hidden * self.ffn)
+
+
+def quantize_decoder_layer(layer: DecoderLayer, make_attention, make_ffn) -> DecoderLayer:
+    """Swap the projections the way MASE's module pass does (construct with `config`, then `load_state_dict` of the
+    original weights): `make_attention(in, out)` / `make_ffn(in, out)` return the replacement modules."""
+    for names, make in ((DecoderLayer.ATTENTION, make_attention), (DecoderLayer.FFN, make_ffn)):
+        for name in names:
+            old = getattr(layer, name)
+            new = make(old.in_features, old.out_features)
+            new.load_state_dict(old.state_dict(), strict=False)
+            setattr(layer, name, new)
+    return layer
