@@ -219,6 +219,7 @@ struct Params {
   int out_bf16;         // output element type: 1 bf16, 0 fp32
   int bias_bf16;        // bias element type
   int tma_store;        // output rows are 16-byte multiples: the epilogue writes through TMA stores
+  int a_box_bytes;      // bytes one A load delivers: fewer than 128 rows when M is small (single-CTA kernel)
 };
 
 // Epilogue of one tile for one warp: drains the warp's 32 TMEM lanes (= 32 tile rows starting at row0) of the
@@ -413,7 +414,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           break;
         }
         if (elect_one()) {
-          mbar_expect_tx(full, L::kStage);
+          mbar_expect_tx(full, L::kStage - L::kA + p.a_box_bytes);
           tma_load_2d(sa, &map_a, full, k0, row_a);
           tma_load_2d(sa + L::kA, &map_b, full, k0, row_b);
           if constexpr (kScaled) {
@@ -895,7 +896,11 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   using L = Layout<BN, kKind == kMxf8>;
   constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
   CUtensorMap ma, mb, md;
-  int rc = make_map(&ma, a, kKind, M, K, BM);
+  // With fewer than 128 rows the A load fetches only the rows that exist (rounded up to the 8-row swizzle atom): the
+  // remaining rows of the tile in shared memory stay as they are, and the accumulator rows they produce are never
+  // stored.  (Letting TMA zero-fill them costs time: M = 16 ran slower than M = 128.)
+  const int a_rows = M < BM ? (int)((M + 7) / 8 * 8) : BM;
+  int rc = make_map(&ma, a, kKind, M, K, a_rows);
   if (rc) return rc;
   rc = make_map(&mb, b, kKind, N, K, BN);
   if (rc) return rc;
@@ -912,6 +917,7 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   p.M = (int)M, p.N = (int)N, p.K = (int)K;
   p.k_chunks = (int)((K * es + kRowBytes - 1) / kRowBytes);
   p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
+  p.a_box_bytes = a_rows * kRowBytes;
   CUtensorMap msa = ma, msb = ma;  // unused by the dense kinds
   if constexpr (kKind == kMxf8) {
     rc = make_sf_map(&msa, sfa, ((M + 255) / 256) * 2 * p.k_chunks);
@@ -960,6 +966,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   p.M = (int)M, p.N = (int)N, p.K = (int)K;
   p.k_chunks = (int)k_chunks;
   p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
+  p.a_box_bytes = BM * kRowBytes;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(umma_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
