@@ -187,12 +187,12 @@ __device__ __forceinline__ uint32_t make_idesc() {
   return d;
 }
 
-// Operand ring of 4 stages and 2 store boxes per epilogue warp.  (A 3-stage ring with a store staging area for a
-// whole tile was measured slower for the block-scaled kind: the main loop is limited by how fast operand tiles
-// arrive from L2, so ring depth matters more than a shorter epilogue.)
+// Operand ring and 2 store boxes per epilogue warp.  256-column tiles: 4 slots of 48 KB (a 3-slot ring with a store
+// staging area for a whole tile was measured slower).  Narrow tiles serve small problems whose time is the latency
+// of streaming the weight through the ring once, so they get 8 slots.
 template <int BN, bool kScaled>
 struct Layout {
-  static constexpr int kStages = 4;
+  static constexpr int kStages = BN <= 64 ? 8 : 4;
   static constexpr int kStoreBufs = 2;  // 2048-byte store boxes per epilogue warp
   static constexpr int kA = BM * kRowBytes;
   static constexpr int kB = BN * kRowBytes;
