@@ -13,8 +13,9 @@ Drop-in counterparts of (paths inside the MASE repository, `src/chop/nn/quantize
 Same names, parameter names, defaults, return types and error behaviour.  Tensors must live on a CUDA
 device: there is no CPU path.  fp32 and bf16 inputs are supported; other dtypes raise
 NotImplementedError rather than silently computing something else.  The calibration-time options
-(`quantile_search=True`, `percentile != 1.0`, `act_tensor`) are not part of the inference path and raise
-NotImplementedError.
+of MXINT (`quantile_search=True`, `percentile != 1.0`, `act_tensor`) are not part of the inference path: they run as
+plain tensor operations on the tensor's device.  The MXFP search raises NotImplementedError (the reference's version
+measures its error on raw code bytes and wraps its uint8 scales, so there is no meaningful behaviour to keep).
 """
 
 from __future__ import annotations
@@ -257,8 +258,19 @@ def mxint_codes(x: Tensor, block_size: int, element_bits: int) -> tuple[Tensor, 
 def extract_mxint_components(x: Tensor, mxint_meta: MXIntMeta, percentile: float = 1.0) -> tuple[Tensor, Tensor]:
     """(scale [n_blocks,1], mantissa [n_blocks,B]), both integer-valued tensors of x.dtype (mxint/fake.py:11-56)."""
     _require_cuda(x, "extract_mxint_components")
-    if percentile != 1.0:
-        raise NotImplementedError("percentile clipping is a calibration-time option and is not provided")
+    if percentile != 1.0:  # calibration-time clipping: tensor operations, see _mxint_candidates
+        B = mxint_meta.block_size
+        assert x.numel() % B == 0, f"Input tensor size {x.numel()} is not divisible by block size {B}."
+        _dtype_code(x.dtype, "mxint")
+        blocks = x.flatten().reshape(-1, B)
+        x_max = blocks.abs().to(torch.float32).quantile(percentile, dim=1, keepdim=True).to(x.dtype)
+        x_max = x_max.clamp(min=torch.finfo(x.dtype).tiny)
+        scale = _ceil_log2_like_host(x_max)
+        scale_bias = 2 ** (mxint_meta.scale_bits - 1) - 1
+        mant = blocks / 2**scale * 2 ** (mxint_meta.element_bits - 1)
+        scale = (scale + scale_bias).clamp(min=0, max=2**mxint_meta.scale_bits - 1)
+        mant = mant.round().clamp(min=-(2 ** (mxint_meta.element_bits - 1)), max=2 ** (mxint_meta.element_bits - 1) - 1)
+        return scale, mant
     if mxint_meta.scale_bits != 8:
         raise NotImplementedError("mxint: only scale_bits=8 is supported")
     scales, mant = mxint_codes(x, mxint_meta.block_size, mxint_meta.element_bits)
@@ -293,8 +305,9 @@ def mxint_quantizer_sim(
 ) -> Tensor:
     """Quantize-dequantize along `block_dim` (mxint/mxint.py:14-171, non-search branch)."""
     _require_cuda(tensor, "mxint_quantizer_sim")
-    if quantile_search or act_tensor is not None:
-        raise NotImplementedError("quantile_search / act_tensor are calibration-time options and are not provided")
+    if quantile_search:
+        out = _mxint_clip_search(tensor, block_dim, mxint_meta, act_tensor, cali_batch_size)
+        return out.to(tensor.dtype)
     ori_shape = tuple(tensor.shape)
     ndim = len(ori_shape)
     assert block_dim < ndim and block_dim >= -ndim
@@ -303,6 +316,67 @@ def mxint_quantizer_sim(
     flat = flatten_for_quantize(tensor, block_dim)
     y = _mxint_fake_flat(flat, mxint_meta, dtype or tensor.dtype)
     return permute_for_dequantize(y, ori_shape, block_dim)
+
+
+# Calibration-time clipping search (mxint/mxint.py:40-136): not on the inference path, so it is the reference's own
+# sequence of tensor operations on the tensor's device.  The one exception is the shared exponent, which uses the
+# same host-derived table as the kernels instead of the device's log2.
+_SEARCH_PERCENTILES = (1.0, 0.995, 0.99, 0.97, 0.95, 0.93, 0.90, 0.80, 0.70, 0.60, 0.50)
+
+
+def _ceil_log2_like_host(x: Tensor) -> Tensor:
+    """ceil(log2(x)) evaluated in x.dtype as torch computes it on this host; x > 0 and normal.  Result in x.dtype."""
+    bits = x.float().contiguous().view(torch.int32)
+    ex = bits >> 23
+    man = ((bits >> 16) & 0x7F) if x.dtype == torch.bfloat16 else (bits & 0x7FFFFF)
+    tab = torch.from_numpy(ceil_table(x.dtype).astype("int32")).to(x.device)
+    return (ex - 127 + (man > tab[ex.long()]).to(torch.int32)).to(x.dtype)
+
+
+def _mxint_candidates(blocks: Tensor, meta: MXIntMeta, percentiles: Tensor) -> Tensor:
+    """Fake-quantized blocks for every clipping percentile: [len(percentiles), n_blocks, B] in blocks.dtype."""
+    dt = blocks.dtype
+    x_max = blocks.abs().to(torch.float32).quantile(percentiles, dim=1, keepdim=True).to(dt)
+    x_max = x_max.clamp(min=torch.finfo(dt).tiny)
+    scale = _ceil_log2_like_host(x_max)
+    scale_bias = 2 ** (meta.scale_bits - 1) - 1
+    x = blocks / 2**scale
+    mant = x * 2 ** (meta.element_bits - 1)
+    scale = (scale + scale_bias).clamp(min=0, max=2**meta.scale_bits - 1)
+    mant = mant.round().clamp(min=-(2 ** (meta.element_bits - 1)), max=2 ** (meta.element_bits - 1) - 1)
+    return mant / 2 ** (meta.element_bits - 1) * 2 ** (scale - scale_bias)
+
+
+def _mxint_clip_search(tensor: Tensor, block_dim: int, meta: MXIntMeta, act_tensor: Tensor | None,
+                       cali_batch_size: int) -> Tensor:
+    _dtype_code(tensor.dtype, "mxint")
+    B = meta.block_size
+    ori_shape = tuple(tensor.shape)
+    ndim = len(ori_shape)
+    assert block_dim < ndim and block_dim >= -ndim
+    target = tensor.flatten().reshape(-1, B)  # the error is taken against the tensor in its original order
+    blocks = flatten_for_quantize(tensor, block_dim).flatten().reshape(-1, B)
+    n_blocks = blocks.shape[0]
+    percentiles = torch.tensor(_SEARCH_PERCENTILES, device=tensor.device, dtype=torch.float32)
+    cand = _mxint_candidates(blocks, meta, percentiles).reshape(len(_SEARCH_PERCENTILES), n_blocks, B)
+    if act_tensor is None:
+        err = torch.norm(cand - target, p=2, dim=-1)
+        best = torch.argmin(err, dim=0).reshape(-1)
+    else:
+        last = act_tensor.shape[-1]
+        if last != B:
+            assert last % B == 0
+            act_tensor = act_tensor.view(*act_tensor.shape[:-1], last // B, B)
+        err = torch.zeros([len(_SEARCH_PERCENTILES), n_blocks], device=tensor.device, dtype=tensor.dtype)
+        with torch.no_grad():
+            for b in range(0, act_tensor.shape[0], cali_batch_size):
+                act_b = act_tensor[b : b + cali_batch_size]
+                out_orig = torch.matmul(act_b, target.T)
+                out_q = torch.einsum("asb,phb->pash", act_b, cand.to(act_tensor.dtype))
+                err += torch.norm(out_q - out_orig, p=2, dim=(1, 2))
+        best = torch.argmin(err, dim=0)
+    chosen = cand[best, torch.arange(n_blocks, device=tensor.device)]
+    return permute_for_dequantize(chosen, ori_shape, block_dim)
 
 
 class MXIntQuantize(torch.autograd.Function):

@@ -223,6 +223,28 @@ def main(root: str) -> None:
             index.append({"kind": "linear", "dtype": dt_name, "tag": tag, "cls": cls.__name__, "config": cfg,
                           "M": M, "K": K, "N": N})
 
+    # MXINT clipping search (calibration-time option): weight-like tensors with outliers, with and without activations
+    from chop.nn.quantizers.mxint.mxint import mxint_quantizer_sim
+
+    g = torch.Generator().manual_seed(123)
+    w32 = torch.randn(48, 128, generator=g) * 0.02
+    w32[torch.rand(48, 128, generator=g) < 0.02] *= 30
+    act32 = torch.randn(5, 7, 32, generator=g)  # the reference only accepts activations whose last dim is the block
+    for dt_name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        w, act = w32.to(dt), act32.to(dt)
+        arrays[f"mxint_search/{dt_name}/x"] = bits(w)
+        arrays[f"mxint_search/{dt_name}/act"] = bits(act)
+        for nbits in (8, 4):
+            meta = MXIntMeta(block_size=32, scale_bits=8, element_bits=nbits)
+            arrays[f"mxint_search/{dt_name}/w{nbits}/fake"] = bits(
+                mxint_quantizer_sim(w, 1, meta, quantile_search=True))
+            arrays[f"mxint_search/{dt_name}/w{nbits}/fake_act"] = bits(
+                mxint_quantizer_sim(w, 1, meta, act_tensor=act, quantile_search=True, cali_batch_size=2))
+            sc, mant = extract_mxint_components(w.flatten(), meta, percentile=0.97)
+            arrays[f"mxint_search/{dt_name}/w{nbits}/p97_scale"] = bits(sc)
+            arrays[f"mxint_search/{dt_name}/w{nbits}/p97_mant"] = bits(mant)
+            index.append({"kind": "mxint_search", "dtype": dt_name, "bits": nbits, "block": 32})
+
     np.savez_compressed(os.path.join(HERE, "reference_vectors.npz"), **arrays)
     with open(os.path.join(HERE, "reference_vectors.json"), "w") as fh:
         json.dump({"torch": torch.__version__, "cases": index}, fh, indent=1)

@@ -123,3 +123,26 @@ def test_meta_classes_validate_like_reference():
     assert m.element_meta.n_bits == 8
     assert set(mb.quantizer_map) == {"mxfp", "mxint", "block_fp"}
     assert set(mb.quantized_module_map) == {"linear_mxfp", "linear_mxint", "linear_block_fp"}
+
+
+def test_mxint_clipping_search_matches_reference_vectors(golden):
+    """The calibration-time search is plain tensor code: on the CPU (through the private, device-agnostic function;
+    the public entry points refuse CPU tensors) it reproduces the reference bit for bit, with and without
+    activations, and so does extraction with a clipping percentile."""
+    from conftest import assert_bits_equal
+    from mase_b200 import quantizers as Q
+
+    for case in (c for c in golden.cases if c["kind"] == "mxint_search"):
+        dt, nbits = case["dtype"], case["bits"]
+        x = golden.tensor(f"mxint_search/{dt}/x", dt)
+        act = golden.tensor(f"mxint_search/{dt}/act", dt)
+        meta = Q.MXIntMeta(block_size=32, scale_bits=8, element_bits=nbits)
+        y = Q._mxint_clip_search(x, 1, meta, None, 32).to(x.dtype)
+        assert_bits_equal(y, golden.tensor(f"mxint_search/{dt}/w{nbits}/fake", dt), f"search {dt} w{nbits}")
+        y = Q._mxint_clip_search(x, 1, meta, act, 2).to(x.dtype)
+        assert_bits_equal(y, golden.tensor(f"mxint_search/{dt}/w{nbits}/fake_act", dt), f"search+act {dt} w{nbits}")
+        # the search picks, block by block, one of the 11 clipped quantizations
+        blocks = x.flatten().reshape(-1, 32)
+        cand = Q._mxint_candidates(blocks, meta, torch.tensor(Q._SEARCH_PERCENTILES, dtype=torch.float32))
+        hit = (cand.view(11, -1, 32) == y.reshape(1, -1, 32)).all(dim=2).any(dim=0)
+        assert bool(hit.all())

@@ -13,7 +13,7 @@ def _cases(golden, kind):
 
 def test_fixture_inventory(golden):
     kinds = {c["kind"] for c in golden.cases}
-    assert kinds == {"mxint", "mxfp", "minifloat", "bfp", "bfp_tiles", "blockdim", "linear"}
+    assert kinds == {"mxint", "mxfp", "minifloat", "bfp", "bfp_tiles", "blockdim", "linear", "mxint_search"}
     assert len(golden.cases) >= 200
 
 

@@ -279,3 +279,32 @@ def test_block_fp_two_dimensional_tiles_vs_oracle(dtype):
         for width, ew, eb in ((8, 8, 127), (7, 8, 127), (12, 8, None)):
             y = mb.block_fp_quantizer(x.to(DEV), width, ew, eb, bs, skip)
             assert_bits_equal(y, O.bfp_fake_tiles(x, width, ew, eb, bh, bw), f"{shape} {bs} w{width}", signed_zero=False)
+
+
+def test_mxint_clipping_search_on_gpu(golden):
+    """Calibration-time options of MXINT on the GPU: tensor code whose quantile / norm reductions may round differently
+    from the host's, so a few blocks may pick a neighbouring percentile; every block is one of the 11 candidates."""
+    for case in (c for c in golden.cases if c["kind"] == "mxint_search"):
+        dt, nbits = case["dtype"], case["bits"]
+        x = golden.tensor(f"mxint_search/{dt}/x", dt)
+        act = golden.tensor(f"mxint_search/{dt}/act", dt)
+        meta = mb.MXIntMeta(block_size=32, scale_bits=8, element_bits=nbits)
+        for key, kwargs in (("fake", {}), ("fake_act", {"act_tensor": act.to(DEV), "cali_batch_size": 2})):
+            y = mb.mxint_quantizer_sim(x.to(DEV), 1, meta, quantile_search=True, **kwargs).cpu()
+            ref = golden.tensor(f"mxint_search/{dt}/w{nbits}/{key}", dt)
+            same = (y.view(-1, 32) == ref.view(-1, 32)).all(dim=1).float().mean().item()
+            assert same >= 0.97, (dt, nbits, key, same)
+        y = mb.mxint_quantizer(x.to(DEV), 32, nbits, 1, 8, True).cpu()
+        from mase_b200 import quantizers as Q
+        cand = Q._mxint_candidates(x.flatten().reshape(-1, 32), meta, torch.tensor(Q._SEARCH_PERCENTILES))
+        assert bool((cand.view(11, -1, 32) == y.reshape(1, -1, 32)).all(dim=2).any(dim=0).all())
+        sc, mant = mb.extract_mxint_components(x.to(DEV).flatten(), meta, percentile=0.97)
+        rs, rm = golden.tensor(f"mxint_search/{dt}/w{nbits}/p97_scale", dt), golden.tensor(f"mxint_search/{dt}/w{nbits}/p97_mant", dt)
+        assert (sc.cpu() == rs).float().mean().item() >= 0.97 and (mant.cpu() == rm).all(dim=1).float().mean().item() >= 0.97
+    # LinearMXInt with clip_search quantizes its weight through the search
+    cfg = {"weight_block_size": 32, "weight_width": 4, "data_in_block_size": 32, "data_in_width": 8, "clip_search": True}
+    layer = mb.LinearMXInt(128, 48, bias=False, device=DEV, dtype=torch.bfloat16, config=cfg)
+    w = golden.tensor("mxint_search/bf16/x", "bf16")
+    layer.load_state_dict({"weight": w.to(DEV)}, strict=False)
+    ref = golden.tensor("mxint_search/bf16/w4/fake", "bf16")
+    assert (layer.weight.data.cpu().view(-1, 32) == ref.view(-1, 32)).all(dim=1).float().mean().item() >= 0.97
