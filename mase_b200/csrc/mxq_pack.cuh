@@ -359,4 +359,105 @@ __device__ __forceinline__ uint4 pack_bf16(const uint4 &raw0, const uint4 &raw1,
                     __byte_perm(bytes[4], bytes[5], 0x7531), __byte_perm(bytes[6], bytes[7], 0x7531));
 }
 
+
+// ---- reference codes (sign | exponent code | fraction) for 16 consecutive bf16 elements ----------------------------
+// Same structure as pack_bf16, for the code-emitting mode of the quantizer (blocks of 32): elements with a normal code
+// (ye >= 1) are read off the rounded pattern with one multiply-add per pair, the others (subnormal codes, underflow,
+// zeros) go through the element codec out of line, and so do blocks with clamped scales, inf / nan or only zeros.
+template <int E, int F>
+__device__ __noinline__ Words8 codes_patch_bf16(Words8 rr, Words8 out, int K, int sh) {
+  const uint32_t(&r)[8] = rr.w;
+  uint32_t(&bytes)[8] = out.w;
+  const uint32_t t1 = (uint32_t)(K + 1) << 23;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t b = h ? (r[k] & 0xFFFF0000u) : (r[k] << 16);
+      if ((b & 0x7FFFFFFFu) < t1) {
+        const uint32_t byte = mxfp_encode(((b & 0x7FFFFFFFu) >> 23) == 0 ? 0u : b, sh, E, F) & 0xFFu;
+        bytes[k] = h ? ((bytes[k] & 0x00FFFFFFu) | (byte << 24)) : ((bytes[k] & 0xFFFF00FFu) | (byte << 8));
+      }
+    }
+  }
+  return out;
+}
+template <int E, int F>
+__device__ __noinline__ Words8 codes_general_bf16(Words8 rr, uint32_t amax, const Log2Tab &tab, int *scale_out) {
+  const uint32_t(&r)[8] = rr.w;
+  Words8 out;
+  const MxfpBlock p = mxfp_block(amax, E, tab);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    uint32_t c[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t b = h ? (r[k] & 0xFFFF0000u) : (r[k] << 16);
+      c[h] = mxfp_encode(((b & 0x7FFFFFFFu) >> 23) == 0 ? 0u : b, p.sh, E, F) & 0xFFu;
+    }
+    out.w[k] = (c[0] << 8) | (c[1] << 24);
+  }
+  *scale_out = p.scale;
+  return out;
+}
+template <int E, int F>
+__device__ __forceinline__ uint4 codes_bf16(const uint4 &raw0, const uint4 &raw1, const Log2Tab &tab, int &scale_out) {
+  constexpr int kTop = (1 << E) - 1;
+  constexpr int kBias = (1 << (E - 1)) - 1;
+  constexpr int kEmax = kTop - kBias;
+  const Words8 rr = {{raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w}};
+  const uint32_t(&r)[8] = rr.w;
+  __nv_bfloat162 v[8], av[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    v[k] = *reinterpret_cast<const __nv_bfloat162 *>(&r[k]);
+    av[k] = __hmax2(v[k], __hneg2(v[k]));
+  }
+  const __nv_bfloat162 m2 = __hmax2(__hmax2(__hmax2(av[0], av[1]), __hmax2(av[2], av[3])),
+                                    __hmax2(__hmax2(av[4], av[5]), __hmax2(av[6], av[7])));
+  const uint32_t mb = *reinterpret_cast<const uint32_t *>(&m2);
+  uint32_t m = max(mb & 0xFFFFu, mb >> 16);
+  m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+  const int exm = (int)(m >> 7);
+  const uint32_t amax = exm ? (m << 16) : 0u;
+  const int K = exm - kTop;
+  Words8 out;
+  uint32_t(&bytes)[8] = out.w;  // two codes per word, in bytes 1 and 3
+  if (K >= 1 && exm <= 240) {
+    const uint32_t t1 = (uint32_t)((K + 1) << 7) * 0x00010001u;  // smallest |x| pattern with a normal code
+    const __nv_bfloat162 t1v = *reinterpret_cast<const __nv_bfloat162 *>(&t1);
+    bool clean = true;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) clean = clean && __hbge2(av[k], t1v);
+    const uint32_t kodd2 = (K & 1) ? 0x00800080u : 0u;
+    constexpr uint32_t kOff = (uint32_t)((127 + 7 - F) << 7) * 0x00010001u;  // 2**(7-F), both halves
+    const __nv_bfloat162 off = *reinterpret_cast<const __nv_bfloat162 *>(&kOff);
+    const __nv_bfloat162 noff = __hneg2(off);
+    // pattern * 2**(F+1) puts (exponent, fraction) of the two elements at bit 8 and bit 24; the addend subtracts K
+    // from both exponents; bit 23 guards the high element against a borrow of the low one
+    const uint32_t addend = (1u << 23) - ((uint32_t)K << (8 + F)) - ((uint32_t)K << (24 + F));
+    constexpr uint32_t kField = ((1u << (E + F)) - 1u) * 0x01000100u;  // exponent code and fraction, bytes 1 and 3
+    constexpr uint32_t kSign = (1u << (E + F)) * 0x01000100u;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t pw = r[k] & 0xFF80FF80u;
+      const __nv_bfloat162 p = *reinterpret_cast<const __nv_bfloat162 *>(&pw);
+      const __nv_bfloat162 y = __hfma2(p, noff, __hfma2(p, off, v[k]));  // |x| rounded to F fraction bits
+      uint32_t yq = *reinterpret_cast<const uint32_t *>(&y);
+      yq -= (yq ^ r[k]) & (r[k] ^ kodd2) & 0x00800080u;  // carry lost when the exponent code is odd
+      const uint32_t e = yq * (1u << (F + 1)) + addend;
+      if constexpr (E + F == 7)
+        bytes[k] = (e & kField) | (r[k] & ~kField);                      // the sign is already at bit 7 of the byte
+      else
+        bytes[k] = (e & kField) | ((r[k] >> (7 - E - F)) & kSign);
+    }
+    if (!clean) out = codes_patch_bf16<E, F>(rr, out, K, exm - 127 - kEmax);
+    scale_out = exm - kEmax;
+  } else {
+    out = codes_general_bf16<E, F>(rr, amax, tab, &scale_out);
+  }
+  return make_uint4(__byte_perm(bytes[0], bytes[1], 0x7531), __byte_perm(bytes[2], bytes[3], 0x7531),
+                    __byte_perm(bytes[4], bytes[5], 0x7531), __byte_perm(bytes[6], bytes[7], 0x7531));
+}
+
 }  // namespace mxq

@@ -483,7 +483,8 @@ def mxfp_quantizer_sim(
     """Quantize-dequantize along `block_dim` (mxfp/mxfp.py:14-115, non-search branch)."""
     _require_cuda(tensor, "mxfp_quantizer_sim")
     if quantile_search or act_tensor is not None:
-        raise NotImplementedError("quantile_search / act_tensor are calibration-time options and are not provided")
+        raise NotImplementedError("mxfp: the clipping search is not provided (the reference measures its error on raw code "
+                                  "bytes and wraps its uint8 scales)")
     ori_shape = tuple(tensor.shape)
     ndim = len(ori_shape)
     assert block_dim < ndim and block_dim >= -ndim

@@ -117,6 +117,10 @@ def test_wide_dynamic_range_vs_oracle(dtype):
     xd = x.to(DEV)
     for E, F in ((4, 3), (2, 1), (5, 2), (3, 2), (2, 3), (1, 2)):
         assert_bits_equal(mb.mxfp_quantizer(xd, 32, E, F), O.mxfp_fake(x, 32, E, F), f"mxfp e{E}m{F}")
+        sc, co = mb.extract_mxfp_components(xd.flatten(), mb.MXFPMeta(32, 8, E, F, True, "rn"))
+        osc, oco = O.mxfp_extract(x.flatten(), 32, E, F)
+        assert_bits_equal(sc, osc, f"scales e{E}m{F}")
+        assert_bits_equal(co, oco, f"codes e{E}m{F}")
     for bits in (8, 4, 2):
         assert_bits_equal(mb.mxint_quantizer(xd, 32, bits), O.mxint_fake(x, 32, bits), f"mxint{bits}")
     assert_bits_equal(mb.block_fp_quantizer(xd, 8, 8, 127, [1, 32], True), O.bfp_fake_rows(x, 8, 8, 127, 32), "bfp")
@@ -148,6 +152,10 @@ def test_mxfp_small_codes_exhaustive_vs_oracle(dtype):
         td = t.to(DEV)
         for E, F in ((4, 3), (2, 1), (5, 2), (3, 2), (2, 3), (1, 2)):
             assert_bits_equal(mb.mxfp_quantizer(td, 32, E, F), O.mxfp_fake(t, 32, E, F), f"mxfp e{E}m{F}")
+            sc, co = mb.extract_mxfp_components(td.flatten(), mb.MXFPMeta(32, 8, E, F, True, "rn"))
+            osc, oco = O.mxfp_extract(t.flatten(), 32, E, F)
+            assert_bits_equal(sc, osc, f"scales e{E}m{F}")
+            assert_bits_equal(co, oco, f"codes e{E}m{F}")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -214,7 +222,7 @@ def test_errors_and_unsupported():
     with pytest.raises(NotImplementedError):
         mb.mxint_quantizer(torch.randn(4, 32, device=DEV).half(), 32, 8)
     with pytest.raises(NotImplementedError):
-        mb.mxint_quantizer(torch.randn(4, 32, device=DEV), 32, 8, quantile_search=True)
+        mb.mxfp_quantizer(torch.randn(4, 32, device=DEV), 32, 4, 3, quantile_search=True)
     with pytest.raises(AssertionError):
         mb.mxfp_quantizer(torch.randn(4, 32, device=DEV), 32, 3, 3)
     with pytest.raises(NotImplementedError):
