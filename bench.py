@@ -220,6 +220,11 @@ def extras(device, x) -> dict:
     meta = mb.MXFPMeta(32, 8, 4, 3, True, "rn")
     out["mxfp8_pack_codes_bf16_65536x8192_GBps"] = quick_gbs(
         lambda: mb.extract_mxfp_components(x.view(-1), meta), int(n * (2 + 1 + 1 / 32)))
+    from mase_b200 import gemm
+    out["mxfp8_tensor_core_operands_bf16_65536x8192_GBps"] = quick_gbs(
+        lambda: gemm.pack_mx_operand(x, 4, 3), int(n * (2 + 1 + 1 / 32)))
+    out["mxint8_codes_bf16_65536x8192_GBps"] = quick_gbs(
+        lambda: mb.mxint_codes(x.view(-1), 32, 8), int(n * (2 + 1 + 1 / 32)))
     # MXINT8 of fp32 [4096,4096] (N(0,1) with outliers): rotate 8 tensors (512 MB) so that HBM, not L2, is measured
     xs = [synthetic.normal_with_outliers(4096, 4096, seed=0).to(device) for _ in range(1)]
     xs = xs + [xs[0].clone() for _ in range(7)]
