@@ -768,8 +768,10 @@ int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t k_chunks = (k + 127) / 128;
   const int64_t sf_bytes = ((rows + 255) / 256) * 2 * k_chunks * 512;
-  // padding (rows up to a multiple of 256, K up to a multiple of 128) reads as 2**-127; without padding every byte is written
-  if ((rows % 256 || k % 128) && cudaMemsetAsync(scales_mma, 0, sf_bytes, st) != cudaSuccess) return MXQ_ERR_LAUNCH;
+  // Scales of K blocks past the end of a row (K not a multiple of 128) must be finite: the codes there read as zero,
+  // and zero times an unset scale byte (0xFF is NaN) would poison valid outputs.  Scales of rows past the end only
+  // reach accumulator rows that are never stored, so they may stay unset.
+  if (k % 128 && cudaMemsetAsync(scales_mma, 0, sf_bytes, st) != cudaSuccess) return MXQ_ERR_LAUNCH;
   if (in_dtype == MXQ_F32) {
     const int64_t n_vec = rows * k / 4;
 #define MXQ_PACK(e, f)                                                                                  \
