@@ -72,6 +72,7 @@ class DecoderLayer(torch.nn.Module):
         super().__init__()
         assert hidden % heads == 0
         self.hidden, self.heads, self.ffn, self.eps, self.theta = hidden, heads, ffn, eps, theta
+        self._rope_cache = {}
         g = torch.Generator().manual_seed(seed)
         for name, (k, n) in {"q_proj": (hidden, hidden), "k_proj": (hidden, hidden), "v_proj": (hidden, hidden),
                              "o_proj": (hidden, hidden), "gate_proj": (hidden, ffn), "up_proj": (hidden, ffn),
@@ -81,17 +82,22 @@ class DecoderLayer(torch.nn.Module):
             setattr(self, name, lin)
 
     def _norm(self, x):
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype)
+        return torch.nn.functional.rms_norm(x, (self.hidden,), None, self.eps)  # fp32 inside, weights 1
+
+    def _rope_tables(self, s, d, device):
+        key = (s, d, str(device))
+        if self._rope_cache.get("key") != key:
+            inv = 1.0 / (self.theta ** (torch.arange(0, d, 2, device=device, dtype=torch.float32) / d))
+            ang = torch.arange(s, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+            ang = torch.cat([ang, ang], -1)
+            self._rope_cache = {"key": key, "cos": ang.cos(), "sin": ang.sin()}
+        return self._rope_cache["cos"], self._rope_cache["sin"]
 
     def _rope(self, t):  # t: [B, heads, S, head_dim]
         s, d = t.shape[-2], t.shape[-1]
-        inv = 1.0 / (self.theta ** (torch.arange(0, d, 2, device=t.device, dtype=torch.float32) / d))
-        ang = torch.arange(s, device=t.device, dtype=torch.float32)[:, None] * inv[None, :]
-        cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
-        tf = t.float()
-        rot = torch.cat([-tf[..., d // 2:], tf[..., : d // 2]], -1)
-        return (tf * cos + rot * sin).to(t.dtype)
+        cos, sin = self._rope_tables(s, d, t.device)
+        rot = torch.cat([-t[..., d // 2:], t[..., : d // 2]], -1)
+        return torch.addcmul(t * cos, rot, sin).to(t.dtype)  # the tables are fp32: products and sum in fp32
 
     def forward(self, x):  # [B, S, hidden]
         b, s, h = x.shape
