@@ -128,8 +128,8 @@ int mxq_gemm_set_max_ctas(int max_ctas);
 
 /* Tile scheme of mxq_gemm_mxf8 / mxq_mx_linear for problems of more than 128 rows and columns.
  *   0  one CTA per 128 x 256 tile (tcgen05 cta_group::1);
- *   1  CTA pairs on 256 x 256 tiles (thread-block clusters of two, tcgen05 cta_group::2) when such tiles fill the
- *      GPU: each SM reads half of the B tile from its shared memory, which is what limits the single-CTA kernel;
+ *   1  (default) CTA pairs on 256 x 256 tiles (thread-block clusters of two, tcgen05 cta_group::2) when such tiles
+ *      fill the GPU: one MMA instruction drives both SMs and each SM keeps a smaller share of the tile in its ring;
  *   2  CTA pairs for every such problem, however small (for tests).
  * Process-wide; returns the previous value.  No reference counterpart. */
 int mxq_gemm_set_pair_mode(int mode);
@@ -141,7 +141,8 @@ int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k);
  * extract_mxfp_components (chop/nn/quantizers/mxfp/fake.py:12-72) -- and store them as tensor-core operands:
  * hardware E4M3 bytes [rows, k] plus E8M0 scales in 512-byte chunks per 128 rows x 128 columns.  E <= 4, F <= 3.
  * A block that holds the reference's top E4M3 code (480, NaN in hardware) is stored one binade lower with its
- * scale raised by one. */
+ * scale raised by one.  The scale array is padded to whole 256-row tiles; scale bytes of rows past `rows` are left
+ * unset (they only reach accumulator rows that the GEMM never stores), scale bytes of K blocks past `k` are zero. */
 int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k, int E,
                       int F, const uint8_t *floor_tab_host, void *stream);
 

@@ -997,8 +997,11 @@ static int launch_any(const void *a, const void *b, const uint8_t *sfa, const ui
   const int sms = sm_count();
   const bool wide = tiles_m * ((N + 255) / 256) * 2 > sms || N <= 64;
   if constexpr (kKind == kMxf8) {
-    if (M > 128 && N > 128 && ((g_pair_mode == 1 && wide) || g_pair_mode == 2))
-      return launch_pair(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+    if (M > 128 && N > 128 && ((g_pair_mode == 1 && wide) || g_pair_mode == 2)) {
+      // a context that cannot place clusters of two such CTAs falls back to one CTA per tile
+      const int rc = launch_pair(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+      if (rc != MXQ_ERR_LAUNCH && rc != MXQ_ERR_UNSUPPORTED) return rc;
+    }
   }
   if (wide) return launch<kKind, 256>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
   // The block-scaled MMA takes its B scales from TMEM columns whose offset inside a 128-row chunk must be even
