@@ -398,18 +398,19 @@ def run_ours(args) -> None:
     hx = torch.empty((ROWS, COLS), dtype=torch.bfloat16).pin_memory()
     hy = torch.empty((ROWS, COLS), dtype=torch.bfloat16).pin_memory()
     hx.copy_(x)
-    streams = [torch.cuda.Stream(device=device) for _ in range(2)]
-    dbuf = [torch.empty((rows_c, COLS), dtype=torch.bfloat16, device=device) for _ in range(2)]
+    n_streams = 2  # one chunk uploading while the other downloads (four streams measured slower: 87 vs 93 GB/s)
+    streams = [torch.cuda.Stream(device=device) for _ in range(n_streams)]
+    dbuf = [torch.empty((rows_c, COLS), dtype=torch.bfloat16, device=device) for _ in range(n_streams)]
 
     def e2e_step():
         cur = torch.cuda.current_stream()
         for s in streams:
             s.wait_stream(cur)
         for c in range(chunks):
-            s = streams[c % 2]
+            s = streams[c % n_streams]
             with torch.cuda.stream(s):
-                dbuf[c % 2].copy_(hx[c * rows_c:(c + 1) * rows_c], non_blocking=True)
-                yq = mb.mxfp_quantizer(dbuf[c % 2], BLOCK, EXP_BITS, FRAC_BITS)
+                dbuf[c % n_streams].copy_(hx[c * rows_c:(c + 1) * rows_c], non_blocking=True)
+                yq = mb.mxfp_quantizer(dbuf[c % n_streams], BLOCK, EXP_BITS, FRAC_BITS)
                 hy[c * rows_c:(c + 1) * rows_c].copy_(yq, non_blocking=True)
                 yq.record_stream(s)
         for s in streams:

@@ -33,6 +33,7 @@ from .modules import (  # noqa: F401
     quantized_func_map,
     quantized_module_map,
 )
+from .functional import bmm_mxfp, bmm_mxint, matmul_mxfp, matmul_mxint  # noqa: F401
 from .patch import patch  # noqa: F401
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -14,7 +14,7 @@ from __future__ import annotations
 import importlib
 import sys
 
-from . import modules, quantizers
+from . import functional, modules, quantizers
 
 _QUANTIZER_NAMES = {
     "mxfp_quantizer": quantizers.mxfp_quantizer,
@@ -59,6 +59,11 @@ def patch(chop=None) -> list[str]:
     if fm is not None and hasattr(fm, "quantized_func_map"):
         fm.quantized_func_map["linear_block_fp"] = modules.linearBlockFP
         done.append("chop.nn.quantized.functional.quantized_func_map['linear_block_fp']")
+        for key, fn in functional.quantized_func_map.items():
+            fm.quantized_func_map[key] = fn
+            if hasattr(fm, key):
+                setattr(fm, key, fn)
+            done.append(f"chop.nn.quantized.functional.quantized_func_map[{key!r}]")
     fl = _maybe("chop.nn.quantized.functional.linear")
     if fl is not None:
         fl.linearBlockFP = modules.linearBlockFP

@@ -159,3 +159,30 @@ def test_small_m_with_bias_vs_oracle(shape):
     assert rel_err(y1, ref) <= 4e-3
     layer.output_dtype = torch.float32
     assert rel_err(layer(x.to(DEV)), ref) <= 1e-3
+
+
+@pytest.mark.parametrize("kind", ["mxfp", "mxint"])
+def test_functional_matmul_and_bmm_vs_oracle(kind):
+    """matmul_* / bmm_*: both operands fake-quantized along their last dimension, as the reference does."""
+    g = torch.Generator().manual_seed(17)
+    x = torch.randn(3, 40, 256, generator=g).bfloat16()
+    y2 = (torch.randn(256, 96, generator=g) * 0.05).bfloat16()
+    y3 = (torch.randn(3, 256, 96, generator=g) * 0.05).bfloat16()
+    if kind == "mxfp":
+        cfg = {"data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3,
+               "weight_block_size": 32, "weight_exponent_width": 2, "weight_frac_width": 1}
+        q = lambda t, w: O.mxfp_fake(t, 32, *((4, 3) if w == "x" else (2, 1)))
+        mm, bmm = mb.matmul_mxfp, mb.bmm_mxfp
+    else:
+        cfg = {"data_in_block_size": 32, "data_in_width": 8, "weight_block_size": 32, "weight_width": 4}
+        q = lambda t, w: O.mxint_fake(t, 32, 8 if w == "x" else 4)
+        mm, bmm = mb.matmul_mxint, mb.bmm_mxint
+    ref2 = q(x, "x").float() @ q(y2, "y").float()
+    ref3 = torch.bmm(q(x, "x").float(), q(y3, "y").float())
+    out2 = mm(x.to(DEV), y2.to(DEV), cfg)
+    out3 = bmm(x.to(DEV), y3.to(DEV), cfg)
+    outb = mm(x.to(DEV), y3.to(DEV), cfg)
+    gemm.check_status()
+    assert out2.dtype == torch.bfloat16 and out2.shape == (3, 40, 96)
+    assert rel_err(out2, ref2) <= 4e-3 and rel_err(out3, ref3) <= 1e-2 and rel_err(outb, ref3) <= 1e-2
+    assert torch.equal(mm(x.to(DEV), y2.to(DEV), {"bypass": True}), torch.matmul(x.to(DEV), y2.to(DEV)))
