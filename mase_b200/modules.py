@@ -46,6 +46,16 @@ class LinearMXFP(_LinearBase):
 
     def load_state_dict(self, state_dict, strict=True, assign=False):
         """Load pretrained weights, then quantize them in place (blocks run along in_features)."""
+        if "weight_codes" in state_dict:  # written by a layer after drop_dense_weight()
+            dev = self.weight.device
+            self._weight_dtype = self.weight.dtype
+            self.register_buffer("weight_codes", state_dict["weight_codes"].to(dev), persistent=True)
+            self.register_buffer("weight_scales", state_dict["weight_scales"].to(dev), persistent=True)
+            self.weight = torch.nn.Parameter(torch.empty(0, dtype=self._weight_dtype, device=dev), requires_grad=False)
+            self._dense_dropped = True
+            if self.bias is not None and "bias" in state_dict:
+                self.bias.data.copy_(state_dict["bias"])
+            return torch.nn.modules.module._IncompatibleKeys([], [])
         result = super().load_state_dict(state_dict, strict=strict, assign=assign)
         if self.bypass or self.gptq:
             return result
@@ -92,6 +102,9 @@ class LinearMXFP(_LinearBase):
         self._mx_weight_version = self.weight._version
 
     def _packed_weight(self) -> MXOperand | None:
+        if getattr(self, "_dense_dropped", False):
+            codes = self._buffers["weight_codes"]
+            return MXOperand(codes, self._buffers["weight_scales"], codes.shape[0], codes.shape[1])
         codes = self._buffers.get("_mx_w_codes")
         if codes is None or getattr(self, "_mx_weight_version", None) != self.weight._version:
             return None
@@ -99,12 +112,33 @@ class LinearMXFP(_LinearBase):
             return None
         return MXOperand(codes, self._buffers["_mx_w_scales"], codes.shape[0], codes.shape[1])
 
+    def drop_dense_weight(self) -> None:
+        """Weight-only memory saving (not in the reference, whose state_dict keeps the fake-quantized tensor in the
+        original dtype): keep only the tensor-core operands -- one byte per element plus one scale byte per 32 --
+        and release the bf16 / fp32 `weight`.  The state_dict then carries `weight_codes` and `weight_scales`
+        (which `load_state_dict` accepts) and an empty `weight`; forward needs CUDA inputs of the original dtype."""
+        packed = self._packed_weight()
+        if packed is None:
+            raise RuntimeError("drop_dense_weight: this layer has no tensor-core operands (load a weight on a CUDA "
+                               "device with weight and data_in formats that fit the block-scaled MMA first)")
+        self._weight_dtype = self.weight.dtype
+        for name in ("_mx_w_codes", "_mx_w_scales"):
+            self._buffers.pop(name, None)
+        self.register_buffer("weight_codes", packed.codes, persistent=True)
+        self.register_buffer("weight_scales", packed.scales, persistent=True)
+        self.weight = torch.nn.Parameter(torch.empty(0, dtype=self._weight_dtype, device=packed.codes.device),
+                                         requires_grad=False)
+        self._dense_dropped = True
+
     @torch.no_grad()
     def forward(self, x: Tensor) -> Tensor:
         if self.bypass:
             return linear_forward(x, self.weight, self.bias, self.output_dtype)
         cfg = self.config
         x_block, x_exp, x_frac = cfg.get("data_in_block_size"), cfg.get("data_in_exponent_width"), cfg.get("data_in_frac_width")
+        if getattr(self, "_dense_dropped", False) and not (x.is_cuda and x.dtype == self.weight.dtype):
+            raise RuntimeError("this layer keeps only packed weights: inputs must be CUDA tensors of dtype "
+                               f"{self.weight.dtype}")
         if x_block is not None and x_exp is not None:
             packed = self._packed_weight()
             if packed is not None and x.is_cuda and x.dtype == self.weight.dtype:

@@ -186,3 +186,28 @@ def test_functional_matmul_and_bmm_vs_oracle(kind):
     assert out2.dtype == torch.bfloat16 and out2.shape == (3, 40, 96)
     assert rel_err(out2, ref2) <= 4e-3 and rel_err(out3, ref3) <= 1e-2 and rel_err(outb, ref3) <= 1e-2
     assert torch.equal(mm(x.to(DEV), y2.to(DEV), {"bypass": True}), torch.matmul(x.to(DEV), y2.to(DEV)))
+
+
+def test_weight_only_storage_round_trip():
+    """drop_dense_weight keeps only codes + scales (about half the bytes of the bf16 weight), gives the same outputs,
+    and its state_dict loads into a fresh layer."""
+    x, w = synthetic.linear_operands(64, 1024, 768, seed=9)
+    cfg = {"weight_block_size": 32, "weight_exponent_width": 2, "weight_frac_width": 1,
+           "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    layer = mb.LinearMXFP(1024, 768, bias=False, device=DEV, dtype=torch.bfloat16, config=dict(cfg))
+    layer.load_state_dict({"weight": w.to(DEV)}, strict=False)
+    y0 = layer(x.to(DEV))
+    dense_bytes = layer.weight.numel() * 2
+    layer.drop_dense_weight()
+    assert layer.weight.numel() == 0
+    packed_bytes = layer.weight_codes.numel() + layer.weight_scales.numel()
+    assert packed_bytes <= 0.55 * dense_bytes
+    assert torch.equal(layer(x.to(DEV)), y0)
+    state = layer.state_dict()
+    assert "weight_codes" in state and "weight_scales" in state
+    fresh = mb.LinearMXFP(1024, 768, bias=False, device=DEV, dtype=torch.bfloat16, config=dict(cfg))
+    fresh.load_state_dict(state)
+    assert torch.equal(fresh(x.to(DEV)), y0)
+    gemm.check_status()
+    with pytest.raises(RuntimeError):
+        fresh(x.to(DEV).float())
