@@ -33,7 +33,10 @@ from .modules import (  # noqa: F401
     quantized_func_map,
     quantized_module_map,
 )
-from .functional import bmm_mxfp, bmm_mxint, matmul_mxfp, matmul_mxint  # noqa: F401
+from .functional import (  # noqa: F401
+    bmm_mxfp, bmm_mxint, kv_cache_mxfp, kv_cache_mxint, matmul_mxfp, matmul_mxint, rope_mxfp, rope_mxint, silu_mxfp,
+    silu_mxint, softmax_mxfp, softmax_mxint,
+)
 from .patch import patch  # noqa: F401
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -211,3 +211,35 @@ def test_weight_only_storage_round_trip():
     gemm.check_status()
     with pytest.raises(RuntimeError):
         fresh(x.to(DEV).float())
+
+
+def test_functional_elementwise_mx_ops_vs_oracle():
+    """kv_cache_* / softmax_* / silu_* / rope_*: the quantization is bit-exact, the surrounding torch op is the same."""
+    g = torch.Generator().manual_seed(19)
+    k = torch.randn(2, 4, 48, 64, generator=g).bfloat16()
+    v = torch.randn(2, 4, 48, 64, generator=g).bfloat16()
+    cfp = {"data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    cint = {"data_in_block_size": 32, "data_in_width": 8}
+    kq, vq = mb.kv_cache_mxfp(k.to(DEV), v.to(DEV), cfp)
+    assert_bits_equal(kq, O.mxfp_fake(k, 32, 4, 3), "k")
+    assert_bits_equal(vq, O.mxfp_fake(v, 32, 4, 3), "v")
+    kq, vq = mb.kv_cache_mxint(k.to(DEV), v.to(DEV), cint)
+    assert_bits_equal(kq, O.mxint_fake(k, 32, 8), "k int")
+    s = torch.randn(2, 4, 48, 64, generator=g).bfloat16() * 3
+    for fn, oq in ((mb.softmax_mxfp, O.mxfp_fake(s, 32, 4, 3)), (mb.softmax_mxint, O.mxint_fake(s, 32, 8))):
+        ref = torch.softmax(oq.float(), -1)
+        out = fn(s.to(DEV), cfp if fn is mb.softmax_mxfp else cint)
+        assert out.dtype == torch.bfloat16 and (out.float().cpu() - ref).abs().max() <= 4e-3
+    out = mb.silu_mxfp(s.to(DEV), cfp)
+    assert (out.float().cpu() - torch.nn.functional.silu(O.mxfp_fake(s, 32, 4, 3).float())).abs().max() <= 3e-2
+    out = mb.silu_mxint(s.to(DEV), cint)
+    assert (out.float().cpu() - torch.nn.functional.silu(O.mxint_fake(s, 32, 8).float())).abs().max() <= 3e-2
+    ang = torch.rand(2, 48, 64, generator=g) * 6.28
+    cos, sin = ang.cos().bfloat16(), ang.sin().bfloat16()
+    qe, ke = mb.rope_mxfp(k.to(DEV), v.to(DEV), cos.to(DEV), sin.to(DEV), cfp)
+    cq, sq = O.mxfp_fake(cos, 32, 4, 3).float().unsqueeze(1), O.mxfp_fake(sin, 32, 4, 3).float().unsqueeze(1)
+    rot = lambda t: torch.cat((-t[..., 32:], t[..., :32]), -1)
+    assert (qe.float().cpu() - (k.float() * cq + rot(k.float()) * sq)).abs().max() <= 5e-2
+    assert (ke.float().cpu() - (v.float() * cq + rot(v.float()) * sq)).abs().max() <= 5e-2
+    qe, ke = mb.rope_mxint(k.to(DEV), v.to(DEV), cos.to(DEV), sin.to(DEV), cint)
+    assert qe.shape == k.shape and ke.shape == v.shape
