@@ -126,7 +126,7 @@ int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int 
  * the previous value.  No counterpart in the reference. */
 int mxq_gemm_set_max_ctas(int max_ctas);
 
-/* Tile scheme of mxq_gemm_mxf8 / mxq_mx_linear for problems of more than 128 rows and columns.
+/* Tile scheme of mxq_gemm_dense / mxq_gemm_mxf8 / mxq_mx_linear for problems of more than 128 rows and columns.
  *   0  one CTA per 128 x 256 tile (tcgen05 cta_group::1);
  *   1  (default) CTA pairs on 256 x 256 tiles (thread-block clusters of two, tcgen05 cta_group::2) when such tiles
  *      fill the GPU: one MMA instruction drives both SMs and each SM keeps a smaller share of the tile in its ring;

@@ -533,7 +533,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }
 
 // =====================================================================================================================
-// Block-scaled GEMM on CTA pairs (tcgen05 cta_group::2).
+// GEMM on CTA pairs (tcgen05 cta_group::2), all three kinds.
 //
 // Two CTAs of a cluster share a 256 x 256 output tile.  CTA r of the pair holds 128 rows of A (rows m0 + 128 r ...)
 // and 128 rows of B (columns n0 + 128 r ... of the output) in its shared memory and accumulates its 128 x 256 half
@@ -547,7 +547,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 //   empty[s]     one per CTA; the leader commits the MMAs of slot s to its own and to the peer's barrier.
 //   acc_full[a]  one per CTA, committed the same way when a tile's MMAs are done.
 //   acc_empty[a], overlap: leader's barriers; the epilogue warps of both CTAs arrive (the peer's remotely).
-// Scale factors: each CTA loads the chunk of its own A rows and both chunks of the tile's B columns;
+// Scale factors (block-scaled kind): each CTA loads the chunk of its own A rows and both chunks of the tile's B columns;
 // tcgen05.cp.cta_group::2 moves them from each CTA's shared memory into that CTA's tensor memory.
 // Both CTAs allocate all 512 TMEM columns, so their accumulator and scale addresses agree (checked at start-up).
 // A cluster barrier before the CTAs free their tensor memory keeps each alive while the other may still touch its
@@ -555,13 +555,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // =====================================================================================================================
 constexpr int kErrPairTmem = 5;
 
+template <bool kScaled>
 struct PairLayout {
   static constexpr int kStages = 6;
   static constexpr int kStoreBufs = 2;
   static constexpr int kA = BM * kRowBytes;            // this CTA's 128 rows of A
   static constexpr int kB = 128 * kRowBytes;           // this CTA's 128 rows of B
   static constexpr int kAB = kA + kB;
-  static constexpr int kSf = 512 + 2 * 512;            // own A chunk, both B chunks
+  static constexpr int kSf = kScaled ? 512 + 2 * 512 : 0;  // own A chunk, both B chunks
   static constexpr int kStageTx = 2 * (kAB + kSf);     // bytes of both CTAs that complete on the leader's barrier
   static constexpr int kSfBase = kStages * kAB;
   static constexpr int kStaging = (kStages * (kAB + kSf) + 1023) & ~1023;
@@ -606,24 +607,45 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
 __device__ __forceinline__ void tc_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
+template <int kKind>
 __device__ __forceinline__ void umma_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc, uint32_t sfa,
                                           uint32_t sfb) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(acc)
-      : "memory");
+  if constexpr (kKind == kBf16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc)
+        : "memory");
+  } else if constexpr (kKind == kTf32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(acc)
+        : "memory");
+  }
 }
 
+template <int kKind>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                       const __grid_constant__ CUtensorMap map_d, const Params p) {
-  using L = PairLayout;
+  constexpr bool kScaled = kKind == kMxf8;
+  using L = PairLayout<kScaled>;
   constexpr int BN = 256;
   constexpr int kStages = L::kStages;
   constexpr int kStoreBufs = L::kStoreBufs;
-  constexpr int kAccStride = 192;  // accumulators [0, 256) and [192, 448), scale factors from column 448
+  constexpr int kElem = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
+  constexpr int kBlockK = kRowBytes / kElem;  // elements of K per ring slot
+  // block-scaled: accumulators [0, 256) and [192, 448) overlap, scale factors from column 448; dense: [0, 256), [256, 512)
+  constexpr bool kOverlap = kScaled;
+  constexpr int kAccStride = kScaled ? 192 : 256;
   constexpr int kSfCol = 448;
   constexpr int kSfSlots = 4;      // TMEM scale-factor slots of 12 columns, used round-robin per K chunk
 
@@ -673,8 +695,10 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (elect_one()) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfa) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfb) : "memory");
+      if constexpr (kScaled) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfa) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfb) : "memory");
+      }
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
     }
     const uint32_t lead_full0 = map_to_cta(full_bar(0), 0);  // the leader's full[0] as a shared::cluster address
@@ -698,11 +722,13 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           if (leader) mbar_expect_tx(full, L::kStageTx);
           tma_load_2d_pair(sa, &map_a, lead_full, k0, row_a);
           tma_load_2d_pair(sa + L::kA, &map_b, lead_full, k0, row_b);
-          tma_load_2d_pair(ssf, &map_sfa, lead_full, 0, chunk_a);
-          tma_load_2d_pair(ssf + 512, &map_sfb, lead_full, 0, chunk_b);
-          tma_load_2d_pair(ssf + 1024, &map_sfb, lead_full, 0, chunk_b + p.k_chunks);
+          if constexpr (kScaled) {
+            tma_load_2d_pair(ssf, &map_sfa, lead_full, 0, chunk_a);
+            tma_load_2d_pair(ssf + 512, &map_sfb, lead_full, 0, chunk_b);
+            tma_load_2d_pair(ssf + 1024, &map_sfb, lead_full, 0, chunk_b + p.k_chunks);
+          }
         }
-        k0 += kRowBytes, ++chunk_a, ++chunk_b;
+        k0 += kBlockK, ++chunk_a, ++chunk_b;
         sa += L::kAB, ssf += L::kSf, full += 8, lead_full += 8, empty += 8, ++issued;
         if (++stage == kStages) {
           stage = 0, phase ^= 1u;
@@ -723,11 +749,12 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   } else if (warp == 1) {
     if (leader) {
       // ---------------- MMA issuer (leader only; warp-uniform loop, one elected lane issues) ----------------
-      // M = 256 (both CTAs), N = 256, E4M3 x E4M3, E8M0 scales
-      const uint32_t idesc = ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24) | (1u << 23);
+      // the single-CTA descriptor with M = 256 (both CTAs) instead of 128
+      const uint32_t idesc = (make_idesc<kKind, BN>() & ~(0x1Fu << 24)) | ((uint32_t)(256 >> 4) << 24);
       uint32_t idk[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) idk[k] = idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4);  // byte k of each scale word
+      for (int k = 0; k < 4; ++k)  // block-scaled: byte k of each scale word
+        idk[k] = kScaled ? idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4) : idesc;
       constexpr uint32_t kDescStep = L::kAB >> 4, kSfDescStep = L::kSf >> 4;
       const uint64_t da0 = desc_sw128(s_base), db0 = desc_sw128(s_base + L::kA), dsf0 = desc_sf(s_base + L::kSfBase);
       const uint32_t my_empty0 = map_to_cta(empty_bar(0), rank), peer_empty0 = map_to_cta(empty_bar(0), rank ^ 1u);
@@ -742,9 +769,11 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int acc = local & 1;
         const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
         if (!mbar_wait_warp(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
-        if (local > 0 &&
-            !mbar_wait_warp(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc))
-          break;
+        if constexpr (kOverlap) {
+          if (local > 0 &&
+              !mbar_wait_warp(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc))
+            break;
+        }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccStride);
         uint32_t accumulate = 0;
@@ -756,12 +785,14 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           tc_fence_after();
           const uint32_t sf_t = tmem_base + (uint32_t)kSfCol + slot * 12u;
           if (elect_one()) {
-            tc_cp_sf_pair(sf_t, dsf);
-            tc_cp_sf_pair(sf_t + 4, dsf + 32u);
-            tc_cp_sf_pair(sf_t + 8, dsf + 64u);
-            umma_pair(d_tmem, da, db, idk[0], accumulate, sf_t, sf_t + 4);
+            if constexpr (kScaled) {
+              tc_cp_sf_pair(sf_t, dsf);
+              tc_cp_sf_pair(sf_t + 4, dsf + 32u);
+              tc_cp_sf_pair(sf_t + 8, dsf + 64u);
+            }
+            umma_pair<kKind>(d_tmem, da, db, idk[0], accumulate, sf_t, sf_t + 4);
 #pragma unroll
-            for (int k = 1; k < 4; ++k) umma_pair(d_tmem, da + 2u * k, db + 2u * k, idk[k], 1u, sf_t, sf_t + 4);
+            for (int k = 1; k < 4; ++k) umma_pair<kKind>(d_tmem, da + 2u * k, db + 2u * k, idk[k], 1u, sf_t, sf_t + 4);
             // both CTAs' slot is free once these MMAs have completed
             tc_commit_pair(my_empty);
             tc_commit_pair(peer_empty);
@@ -793,8 +824,9 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait)) break;
       tc_fence_after();
-      drain_accumulator<BN, true, kStoreBufs>(
-          p, &map_d, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride), acc == 0 ? BN / 32 - 2 : 0,
+      drain_accumulator<BN, kOverlap, kStoreBufs>(
+          p, &map_d, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride),
+          kOverlap && acc == 0 ? BN / 32 - 2 : 0,
           m_blk * BM + quarter * 32, n_blk * BN, lane, stage_buf, buf, [&] { mbar_arrive_cluster(lead_overlap); });
       tc_fence_before();
       __syncwarp();
@@ -940,19 +972,24 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
 }
 
 // Block-scaled GEMM on CTA pairs; the scale buffers are padded to whole 256-row tiles (mxq_mma_scale_bytes).
+template <int kKind>
 static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
                        int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, cudaStream_t st) {
-  using L = PairLayout;
+  using L = PairLayout<kKind == kMxf8>;
+  constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
   CUtensorMap ma, mb, msa, msb, md;
-  int rc = make_map(&ma, a, kMxf8, M, K, BM);
+  int rc = make_map(&ma, a, kKind, M, K, BM);
   if (rc) return rc;
-  rc = make_map(&mb, b, kMxf8, N, K, 128);
+  rc = make_map(&mb, b, kKind, N, K, 128);
   if (rc) return rc;
-  const int64_t k_chunks = (K + kRowBytes - 1) / kRowBytes;
-  rc = make_sf_map(&msa, sfa, ((M + 255) / 256) * 2 * k_chunks);
-  if (rc) return rc;
-  rc = make_sf_map(&msb, sfb, ((N + 255) / 256) * 2 * k_chunks);
-  if (rc) return rc;
+  const int64_t k_chunks = (K * es + kRowBytes - 1) / kRowBytes;
+  msa = ma, msb = ma;  // unused by the dense kinds
+  if constexpr (kKind == kMxf8) {
+    rc = make_sf_map(&msa, sfa, ((M + 255) / 256) * 2 * k_chunks);
+    if (rc) return rc;
+    rc = make_sf_map(&msb, sfb, ((N + 255) / 256) * 2 * k_chunks);
+    if (rc) return rc;
+  }
   const bool out_bf16 = out_dtype == MXQ_BF16;
   const bool tma_store = (N * (out_bf16 ? 2 : 4)) % 16 == 0;
   if (tma_store) {
@@ -969,7 +1006,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   p.a_box_bytes = BM * kRowBytes;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(umma_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
+    if (cudaFuncSetAttribute(umma_gemm_pair_kernel<kKind>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
         cudaSuccess)
       return MXQ_ERR_LAUNCH;
     attr_set = true;
@@ -980,7 +1017,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   if (2 * tiles < grid) grid = (int)(2 * tiles);
   grid &= ~1;
   if (grid < 2) return MXQ_ERR_UNSUPPORTED;
-  umma_gemm_pair_kernel<<<grid, kThreads, L::kTotal, st>>>(ma, mb, msa, msb, md, p);
+  umma_gemm_pair_kernel<kKind><<<grid, kThreads, L::kTotal, st>>>(ma, mb, msa, msb, md, p);
   return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
@@ -996,12 +1033,10 @@ static int launch_any(const void *a, const void *b, const uint8_t *sfa, const ui
   const int64_t tiles_m = (M + BM - 1) / BM;
   const int sms = sm_count();
   const bool wide = tiles_m * ((N + 255) / 256) * 2 > sms || N <= 64;
-  if constexpr (kKind == kMxf8) {
-    if (M > 128 && N > 128 && ((g_pair_mode == 1 && wide) || g_pair_mode == 2)) {
-      // a context that cannot place clusters of two such CTAs falls back to one CTA per tile
-      const int rc = launch_pair(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
-      if (rc != MXQ_ERR_LAUNCH && rc != MXQ_ERR_UNSUPPORTED) return rc;
-    }
+  if (M > 128 && N > 128 && ((g_pair_mode == 1 && wide) || g_pair_mode == 2)) {
+    // a context that cannot place clusters of two such CTAs falls back to one CTA per tile
+    const int rc = launch_pair<kKind>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+    if (rc != MXQ_ERR_LAUNCH && rc != MXQ_ERR_UNSUPPORTED) return rc;
   }
   if (wide) return launch<kKind, 256>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
   // The block-scaled MMA takes its B scales from TMEM columns whose offset inside a 128-row chunk must be even

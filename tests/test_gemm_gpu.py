@@ -101,6 +101,27 @@ def test_mxf8_gemm_cta_pairs_match_single_cta_and_oracle(shape):
     assert rel_err(pair[1], ref) <= 4e-3
 
 
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1024, 512, 768), (300, 264, 260), (2048, 4096, 4096)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_dense_gemm_cta_pairs_match_single_cta(shape, dtype):
+    """The dense kinds on CTA pairs give the bits of the single-CTA kernel, with bias and ragged edges."""
+    M, K, N = shape
+    x, w = quantized_operands(M, K, N, 6, dtype)
+    g = torch.Generator().manual_seed(6)
+    b = torch.randn(N, generator=g).to(dtype).to(DEV)
+    prev = gemm.set_pair_mode(0)
+    try:
+        single = gemm.linear_forward(x.to(DEV), w.to(DEV), b)
+        gemm.set_pair_mode(2)
+        pair = gemm.linear_forward(x.to(DEV), w.to(DEV), b)
+        gemm.check_status()
+    finally:
+        gemm.set_pair_mode(prev)
+    assert torch.equal(single, pair)
+    ref = x.float() @ w.float().t() + b.float().cpu()
+    assert rel_err(pair, ref) <= (4e-3 if dtype == torch.bfloat16 else REL_TOL)
+
+
 def test_mxf8_pack_round_trip():
     """Packed codes * scales reproduce the oracle's fake-quant values (up to the documented re-encoding of blocks
     that hold the reference's top E4M3 code)."""
