@@ -911,6 +911,12 @@ static int make_sf_map(CUtensorMap *map, const void *ptr, int64_t chunks) {
 // mxq_gemm_set_max_ctas by callers that want to keep SMs free for a concurrent collective.
 static int g_max_ctas = 0;
 
+static int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dev;
+}
+
 static int sm_count() {
   static int n = 0;
   if (!n) {
@@ -957,7 +963,8 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
     rc = make_sf_map(&msb, sfb, ((N + 255) / 256) * 2 * p.k_chunks);
     if (rc) return rc;
   }
-  static bool attr_set = false;
+  static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
+  bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
         cudaSuccess)
@@ -1004,7 +1011,8 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   p.k_chunks = (int)k_chunks;
   p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
   p.a_box_bytes = BM * kRowBytes;
-  static bool attr_set = false;
+  static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
+  bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {
     if (cudaFuncSetAttribute(umma_gemm_pair_kernel<kKind>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
         cudaSuccess)
