@@ -460,4 +460,50 @@ __device__ __forceinline__ uint4 codes_bf16(const uint4 &raw0, const uint4 &raw1
                     __byte_perm(bytes[4], bytes[5], 0x7531), __byte_perm(bytes[6], bytes[7], 0x7531));
 }
 
+
+// ---- MXINT mantissas (int8) and shared exponents for 16 consecutive bf16 elements (half a block of 32) ----------------
+// mant = clamp(rint(x / 2**s * 2**(bits-1))) with s = ceil(log2(amax)) as the host evaluates it in bf16.  The scalings
+// are exact in fp32; rint is the add of 1.5 * 2**23 inside an fma (round half to even in the last integer bit), after
+// which the integer sits in the low bits of the pattern and is clamped with integer min / max.
+__device__ __forceinline__ uint4 mxint_codes_bf16(const uint4 &raw0, const uint4 &raw1, const Log2Tab &tab, int bits,
+                                                  int &scale_out) {
+  const uint32_t r[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
+  __nv_bfloat162 av[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162 *>(&r[k]);
+    av[k] = __hmax2(v, __hneg2(v));
+  }
+  const __nv_bfloat162 m2 = __hmax2(__hmax2(__hmax2(av[0], av[1]), __hmax2(av[2], av[3])),
+                                    __hmax2(__hmax2(av[4], av[5]), __hmax2(av[6], av[7])));
+  const uint32_t mb = *reinterpret_cast<const uint32_t *>(&m2);
+  uint32_t m = max(mb & 0xFFFFu, mb >> 16);
+  m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+  m = max(m, 0x0080u);  // finfo.tiny: the same pattern for bf16 and fp32 exponents
+  const int ex = (int)(m >> 7);
+  const int s = ex - 127 + ((m & 0x7Fu) > tab.t[ex] ? 1 : 0);
+  scale_out = min(max(s + 127, 0), 255);
+  uint32_t out[4];
+  if (s >= 128) {  // the reference divides by 2**128 = inf: every mantissa is a (signed) zero
+    out[0] = out[1] = out[2] = out[3] = 0u;
+  } else {
+    const float c1a = pow2f(-s), c1b = (float)(1 << (bits - 1));
+    const int hi = 0x4B400000 + (1 << (bits - 1)) - 1, lo = 0x4B400000 - (1 << (bits - 1));
+    uint32_t q[16];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float x = __uint_as_float(h ? (r[k] & 0xFFFF0000u) : (r[k] << 16));
+        const float t = __fmaf_rn(x * c1a, c1b, 12582912.f);  // 1.5 * 2**23
+        q[2 * k + h] = (uint32_t)min(max(__float_as_int(t), lo), hi);
+      }
+    }
+#pragma unroll
+    for (int w = 0; w < 4; ++w)  // low bytes of four integers
+      out[w] = __byte_perm(__byte_perm(q[4 * w], q[4 * w + 1], 0x0040), __byte_perm(q[4 * w + 2], q[4 * w + 3], 0x0040), 0x5410);
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
 }  // namespace mxq

@@ -359,6 +359,36 @@ mxfp_pack_mma_bf16_kernel(const __nv_bfloat16 *__restrict__ x, uint8_t *__restri
   }
 }
 
+// MXINT mantissas and shared exponents of bf16 tensors in blocks of 32: the same half-block-per-lane scheme.
+template <bool kWide>
+__global__ void __launch_bounds__(kThreads, 4)
+mxint_codes_bf16_kernel(const __nv_bfloat16 *__restrict__ x, int8_t *__restrict__ mant, uint8_t *__restrict__ scales,
+                        int64_t n_unit, int bits, const __grid_constant__ Log2Tab tab) {
+  constexpr int kU = 2;
+  const int64_t step = (int64_t)gridDim.x * kThreads * kU;
+  for (int64_t base = (int64_t)blockIdx.x * kThreads * kU; base < n_unit; base += step) {
+    uint4 raws[kU][2];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int64_t j = base + u * kThreads + threadIdx.x;
+      if (j < n_unit)
+        load_unit<kWide>(x, j, raws[u][0], raws[u][1]);
+      else
+        raws[u][0] = raws[u][1] = make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int64_t j = base + u * kThreads + threadIdx.x;
+      int scale;
+      const uint4 c16 = mxint_codes_bf16(raws[u][0], raws[u][1], tab, bits, scale);  // all lanes take part
+      if (j < n_unit) {
+        __stcs(reinterpret_cast<uint4 *>(mant) + j, c16);
+        if ((threadIdx.x & 1) == 0) scales[j >> 1] = (uint8_t)scale;
+      }
+    }
+  }
+}
+
 // Reference codes and E8M0 scales of bf16 tensors in blocks of 32: 32 bytes (half a block) per lane and step, codes
 // stored 16 bytes per lane, one scale byte per pair of lanes.
 template <int E, int F, bool kWide>
@@ -602,6 +632,17 @@ template <typename Tin, typename Tout, Mode kMode>
 static int launch_mxint(const void *x, void *y, int8_t *mant, uint8_t *scales, int64_t n_blocks, int block, int bits,
                         const Log2Tab &tab, cudaStream_t st) {
   const int group = fast_group<Tin>(block);
+  if constexpr (kMode == Mode::kCodes && Elem<Tin>::kBf16) {
+    if (block == 32 && aligned16(x) && aligned16(mant)) {
+      const int64_t n_unit = n_blocks * 2;
+      const int grid = grid_for(n_unit, kThreads * 2);
+      if ((reinterpret_cast<uintptr_t>(x) & 31) == 0)
+        mxint_codes_bf16_kernel<true><<<grid, kThreads, 0, st>>>((const __nv_bfloat16 *)x, mant, scales, n_unit, bits, tab);
+      else
+        mxint_codes_bf16_kernel<false><<<grid, kThreads, 0, st>>>((const __nv_bfloat16 *)x, mant, scales, n_unit, bits, tab);
+      return check_launch();
+    }
+  }
   if (group && aligned16(x) && (kMode == Mode::kCodes ? aligned16(mant) : aligned16(y))) {
     const int64_t n_vec = n_blocks * group;
     mxint_kernel<Tin, Tout, kMode><<<grid_for(n_vec, kThreads * kUnroll), kThreads, 0, st>>>(

@@ -123,6 +123,10 @@ def test_wide_dynamic_range_vs_oracle(dtype):
         assert_bits_equal(co, oco, f"codes e{E}m{F}")
     for bits in (8, 4, 2):
         assert_bits_equal(mb.mxint_quantizer(xd, 32, bits), O.mxint_fake(x, 32, bits), f"mxint{bits}")
+        sc, m = mb.mxint_codes(xd.flatten(), 32, bits)
+        osc, om = O.mxint_extract(x.flatten(), 32, bits)
+        assert_bits_equal(sc.view(-1, 1).float(), osc.float(), f"mxint{bits} scales")
+        assert_bits_equal(m.float(), om.float(), f"mxint{bits} mantissas", signed_zero=False)  # int8 has no -0
     assert_bits_equal(mb.block_fp_quantizer(xd, 8, 8, 127, [1, 32], True), O.bfp_fake_rows(x, 8, 8, 127, 32), "bfp")
     assert_bits_equal(mb.block_fp_quantizer(xd, 12, 8, None, [16], True), O.bfp_fake_rows(x, 12, 8, None, 16), "bfp12")
 
@@ -173,6 +177,10 @@ def test_power_of_two_neighbourhoods_vs_oracle(dtype):
     x = x.to(dtype)
     xd = x.to(DEV)
     assert_bits_equal(mb.mxint_quantizer(xd, 32, 8), O.mxint_fake(x, 32, 8), "mxint8")
+    sc, m = mb.mxint_codes(xd.flatten(), 32, 8)
+    osc, om = O.mxint_extract(x.flatten(), 32, 8)
+    assert_bits_equal(sc.view(-1, 1).float(), osc.float(), "mxint8 scales")
+    assert_bits_equal(m.float(), om.float(), "mxint8 mantissas", signed_zero=False)
     assert_bits_equal(mb.mxfp_quantizer(xd, 32, 4, 3), O.mxfp_fake(x, 32, 4, 3), "mxfp8")
     assert_bits_equal(mb.block_fp_quantizer(xd, 8, 8, 127, [1, 32], True), O.bfp_fake_rows(x, 8, 8, 127, 32), "bfp")
 
