@@ -140,7 +140,8 @@ def test_large_m_with_bias_vs_oracle():
     assert torch.equal(y1, y3)
 
 
-@pytest.mark.parametrize("shape", [(1, 4096, 4096), (16, 4096, 4096), (128, 2048, 1024), (100, 1024, 1000), (7, 8192, 512)])
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (16, 4096, 4096), (128, 2048, 1024), (100, 1024, 1000), (7, 8192, 512),
+                                   (5, 96, 72), (13, 160, 8), (16, 4128, 1000), (17, 4096, 256)])
 def test_small_m_with_bias_vs_oracle(shape):
     """At most 128 rows (narrow tiles), bias, ragged N, bf16 and fp32 outputs; results are repeatable."""
     M, K, N = shape
