@@ -112,6 +112,7 @@ __device__ __forceinline__ bool elect_one() {
   asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
   return pred != 0;
 }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -382,6 +383,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Launched with programmatic stream serialization: everything above (barriers, tensor memory) may run while the
+  // previous kernel of the stream -- normally the activation pack -- is still finishing; its results are visible
+  // from here on.  Without that launch attribute this is a no-op.
+  grid_dependency_wait();
 
   // The producer and the MMA issuer run their loops with all 32 lanes of their warp on identical values and elect
   // one lane for the TMA / tcgen05 instructions themselves.  Those instructions take their operands from uniform
@@ -687,6 +692,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   cluster_sync();  // both CTAs' barriers are initialised and both tensor-memory addresses are published
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();  // see the single-CTA kernel
   // the MMAs address both CTAs' tensor memory with one address: the two allocations must coincide
   if (ld_cluster_u32(map_to_cta(smem_u32(tmem_slot), rank ^ 1u)) != tmem_base) {
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kErrPairTmem);
@@ -928,6 +934,20 @@ static int sm_count() {
   return n;
 }
 
+// Launch with programmatic stream serialization: the kernel may start while the previous kernel of the stream is
+// still running (once that kernel has let its dependents go, or finished) and waits for it on the device.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st,
+                                    Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid), cfg.blockDim = dim3((unsigned)block), cfg.dynamicSmemBytes = smem, cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <int kKind, int BN>
 static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
                   int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, cudaStream_t st) {
@@ -974,8 +994,8 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (g_max_ctas > 0 && grid > g_max_ctas) grid = g_max_ctas;
-  umma_gemm_kernel<kKind, BN><<<grid, kThreads, L::kTotal, st>>>(ma, mb, msa, msb, md, p);
-  return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
+  const cudaError_t err = launch_dependent(umma_gemm_kernel<kKind, BN>, grid, kThreads, L::kTotal, st, ma, mb, msa, msb, md, p);
+  return err == cudaSuccess && cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
 // Block-scaled GEMM on CTA pairs; the scale buffers are padded to whole 256-row tiles (mxq_mma_scale_bytes).
@@ -1025,7 +1045,11 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   if (2 * tiles < grid) grid = (int)(2 * tiles);
   grid &= ~1;
   if (grid < 2) return MXQ_ERR_UNSUPPORTED;
-  umma_gemm_pair_kernel<kKind><<<grid, kThreads, L::kTotal, st>>>(ma, mb, msa, msb, md, p);
+  const cudaError_t err = launch_dependent(umma_gemm_pair_kernel<kKind>, grid, kThreads, L::kTotal, st, ma, mb, msa, msb, md, p);
+  if (err != cudaSuccess) {
+    cudaGetLastError();  // clear it: the caller falls back to single-CTA tiles
+    return MXQ_ERR_LAUNCH;
+  }
   return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 

@@ -315,6 +315,9 @@ mxfp_pack_mma_bf16_kernel(const __nv_bfloat16 *__restrict__ x, uint8_t *__restri
                           uint8_t *__restrict__ scales, int64_t n_unit64, uint32_t unit_per_row, int64_t k_chunks,
                           UnitStep jump, UnitStep stride, const __grid_constant__ Log2Tab tab) {
   constexpr int kU = 2;
+  // the GEMM that follows in the stream may be launched from now on: it sets up its barriers and tensor memory while
+  // this kernel finishes and waits for the operands on the device (griddepcontrol.wait)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const I n_unit = (I)n_unit64;
   const I step = (I)gridDim.x * kThreads * kU;
   I base = (I)blockIdx.x * kThreads * kU;
