@@ -13,7 +13,7 @@
 // Kinds: bf16 x bf16 (kind::f16), fp32 x fp32 rounded to tf32 (kind::tf32) and MXFP8 E4M3 x E4M3 with one E8M0
 // scale per 32 elements of K (kind::mxf8f6f4.block_scale).  Accumulators are double-buffered so that the epilogue of
 // a tile overlaps the main loop of the next one (for the block-scaled 256-column tile the two overlap by 64 columns,
-// see the kernel).  A second kernel runs the block-scaled kind on CTA pairs (cta_group::2, 256 x 256 tiles).
+// see the kernel).  A second kernel runs all kinds on CTA pairs (cta_group::2, 256 x 256 tiles).
 //
 // No multicast loads are used.  Every wait on an mbarrier is bounded: when it runs out the CTA raises an abort
 // flag, records an error code in the caller's status word, waits (bounded) for its own bulk copies in flight, frees
