@@ -134,6 +134,12 @@ int mxq_gemm_set_max_ctas(int max_ctas);
  * Process-wide; returns the previous value.  No reference counterpart. */
 int mxq_gemm_set_pair_mode(int mode);
 
+/* Small problems (at most 128 rows, tiles that leave half of the SMs idle, K of at least 32 x 128 bytes): two CTAs of a
+ * thread-block cluster share one 128 x 64 tile, each taking half of K; the second hands its fp32 accumulator to the
+ * first through distributed shared memory (fixed summation order).  1 = on (default), 0 = off.  Process-wide; returns
+ * the previous value.  No reference counterpart. */
+int mxq_gemm_set_split_k(int on);
+
 /* Size in bytes of the scale array that mxq_mxfp_pack_mma writes for a [rows, k] operand. */
 int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k);
 

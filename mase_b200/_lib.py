@@ -27,6 +27,7 @@ _PROTOTYPES = {
     "mxq_mma_scale_bytes": [c_int64, c_int64],
     "mxq_gemm_set_max_ctas": [c_int],
     "mxq_gemm_set_pair_mode": [c_int],
+    "mxq_gemm_set_split_k": [c_int],
     "mxq_mxfp_pack_mma": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p],
     "mxq_gemm_mxf8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
                       c_int64, c_void_p, c_void_p],

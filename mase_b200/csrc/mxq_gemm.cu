@@ -106,6 +106,34 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t sr
                ::"l"(map), "r"(src), "r"(c0), "r"(c1)
                : "memory");
 }
+// ---- thread-block clusters ----
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_cluster_u32(uint32_t cluster_addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
 // true in exactly one lane of a fully active warp (the same lane every time)
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
@@ -191,9 +219,11 @@ __device__ __forceinline__ uint32_t make_idesc() {
 // Operand ring and 2 store boxes per epilogue warp.  256-column tiles: 4 slots of 48 KB (a 3-slot ring with a store
 // staging area for a whole tile was measured slower).  Narrow tiles serve small problems whose time is the latency
 // of streaming the weight through the ring once, so they get 8 slots.
-template <int BN, bool kScaled>
+template <int BN, bool kScaled, bool kSplit = false>
 struct Layout {
-  static constexpr int kStages = BN <= 64 ? 8 : 4;
+  // kSplit: two CTAs of a cluster share one narrow tile, each taking half of K; the second one hands its fp32
+  // accumulator over through a column-major exchange buffer in its shared memory (128 rows x BN columns)
+  static constexpr int kStages = kSplit ? 6 : (BN <= 64 ? 8 : 4);
   static constexpr int kStoreBufs = 2;  // 2048-byte store boxes per epilogue warp
   static constexpr int kA = BM * kRowBytes;
   static constexpr int kB = BN * kRowBytes;
@@ -205,7 +235,8 @@ struct Layout {
   static constexpr int kStage = kAB + kSf;              // bytes that arrive per stage (the transaction count)
   static constexpr int kSfBase = kStages * kAB;         // scale chunks live after all operand tiles
   static constexpr int kStaging = (kStages * kStage + 1023) & ~1023;  // epilogue: 4 warps x kStoreBufs x 2048 bytes
-  static constexpr int kBarriers = kStaging + 4 * kStoreBufs * 2048;  // full[], empty[], acc_full[2], acc_empty[2]
+  static constexpr int kXbuf = kStaging + 4 * kStoreBufs * 2048;
+  static constexpr int kBarriers = kXbuf + (kSplit ? BM * BN * 4 : 0);  // full[], empty[], acc_full[2], acc_empty[2]
   static constexpr int kTotal = kBarriers + 32 * 8 + 16 + 1024;  // + tmem slot, abort flag, alignment slack
 };
 
@@ -229,10 +260,13 @@ struct Params {
 // TMA store, which writes whole lines and clips at the matrix edges; output matrices whose rows are not 16-byte
 // multiples take direct predicated stores.  With overlapping accumulators `shared_columns_read` is called (lane 0)
 // once the first two chunks -- the columns both accumulators share -- are in registers.
-template <int BN, bool kOverlap, int kStoreBufs, typename F>
+struct NoCombine {
+  __device__ __forceinline__ void operator()(uint32_t (&)[32], int) const {}
+};
+template <int BN, bool kOverlap, int kStoreBufs, typename F, typename C = NoCombine>
 __device__ __forceinline__ void drain_accumulator(const Params &p, const CUtensorMap *map_d, uint32_t t_acc, int first,
                                                   int row0, int n0, int lane, uint8_t *stage_buf, int &buf,
-                                                  F shared_columns_read) {
+                                                  F shared_columns_read, C combine = C()) {
   // two chunks in flight: the TMEM load of chunk c+1 is issued before chunk c is converted and stored
   // chunk order: with overlapping accumulators the 64 shared columns go first (the last two chunks of
   // accumulator 0, the first two of accumulator 1)
@@ -245,6 +279,7 @@ __device__ __forceinline__ void drain_accumulator(const Params &p, const CUtenso
     const bool active = n0 + c < p.N;  // uniform across the warp; chunks past the edge are read but not stored
     uint32_t(&v)[32] = vv[ci & 1];
     if (ci + 1 < BN / 32) tmem_ld32(t_acc + (uint32_t)(((ci + 1 + first) % (BN / 32)) * 32), vv[(ci + 1) & 1]);
+    combine(v, c);  // split-K: add the other CTA's partial sums of these 32 columns
     if (p.bias != nullptr) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
@@ -323,7 +358,7 @@ __device__ __forceinline__ void drain_accumulator(const Params &p, const CUtenso
   }
 }
 
-template <int kKind, int BN>
+template <int kKind, int BN, bool kSplit = false>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
@@ -343,7 +378,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       kOverlap || 2 * kAccCols + (kScaled ? kMaxStages * kSfColsPerStage : 0) <= kTmemCols ? 2 : 1;
   constexpr int kAccStride = kOverlap ? 192 : kAccCols;  // first column of accumulator stage 1
   constexpr int kSfCol = kOverlap ? 448 : kAccStages * kAccCols;  // first TMEM column of the scale factors
-  using L = Layout<BN, kScaled>;
+  using L = Layout<BN, kScaled, kSplit>;
   constexpr int kStages = L::kStages;
   constexpr int kStoreBufs = L::kStoreBufs;
   constexpr int kElem = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
@@ -364,6 +399,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;  // warp: provably uniform
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
+  // Split K (small problems, launched as clusters of two with one tile per cluster): CTA `rank` of the cluster takes
+  // the K chunks [kc_begin, kc_end) of tile blockIdx.x / 2; rank 1 hands its accumulator to rank 0, which stores.
+  const int rank = kSplit ? (int)cluster_rank() : 0;
+  const int first_tile = kSplit ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int tile_step = kSplit ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int kc_half = (p.k_chunks + 1) / 2;
+  const int kc_begin = kSplit && rank == 1 ? kc_half : 0;
+  const int kc_end = kSplit && rank == 0 ? kc_half : p.k_chunks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), 1), mbar_init(empty_bar(s), 1);
@@ -408,12 +451,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint32_t phase = 0;
     int issued = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step) {
       const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
       const int row_a = m_blk * BM, row_b = n_blk * BN;
-      int chunk_a = m_blk * p.k_chunks, chunk_b = ((n_blk * BN) / 128) * p.k_chunks;  // rows of the scale maps
-      int k0 = 0;
-      for (int kc = 0; kc < p.k_chunks; ++kc) {
+      // rows of the scale maps
+      int chunk_a = m_blk * p.k_chunks + kc_begin, chunk_b = ((n_blk * BN) / 128) * p.k_chunks + kc_begin;
+      int k0 = kc_begin * kBlockK;
+      for (int kc = kc_begin; kc < kc_end; ++kc) {
         if (!mbar_wait_warp(empty, phase ^ 1u, abort_flag, p.status, kErrProducerWait)) {
           ok = false;
           break;
@@ -462,7 +506,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint32_t phase = 0;
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step, ++local) {
       const int acc = local % kAccStages;
       const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
       if (!mbar_wait_warp(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
@@ -475,7 +519,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // a B tile narrower than a 128-row scale chunk starts at one of the chunk's four 32-row TMEM columns
       const uint32_t sfb_col = (uint32_t)((((tile % tiles_n) * BN) & 127) >> 5);
       uint32_t accumulate = 0;  // the tile's first MMA overwrites the accumulator
-      for (int kc = 0; kc < p.k_chunks; ++kc) {
+      for (int kc = kc_begin; kc < kc_end; ++kc) {
         if (!mbar_wait_warp(full, phase, abort_flag, p.status, kErrMmaWaitFull)) {
           ok = false;
           break;
@@ -512,21 +556,68 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint8_t *stage_buf = smem + L::kStaging + (warp - 2) * (kStoreBufs * 2048);
     int buf = 0;
     int local = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
-      const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
-      const int acc = local % kAccStages;
-      const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
-      if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait)) break;
-      tc_fence_after();
-      drain_accumulator<BN, kOverlap, kStoreBufs>(
-          p, &map_d, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride),
-          kOverlap && acc == 0 ? BN / 32 - 2 : 0, m_blk * BM + quarter * 32, n_blk * BN, lane, stage_buf, buf,
-          [&] { mbar_arrive(overlap_bar); });
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+    if constexpr (!kSplit) {
+      for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++local) {
+        const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
+        const int acc = local % kAccStages;
+        const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
+        if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait)) break;
+        tc_fence_after();
+        drain_accumulator<BN, kOverlap, kStoreBufs>(
+            p, &map_d, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride),
+            kOverlap && acc == 0 ? BN / 32 - 2 : 0, m_blk * BM + quarter * 32, n_blk * BN, lane, stage_buf, buf,
+            [&] { mbar_arrive(overlap_bar); });
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+      }
+    } else if (rank == 1 && first_tile < n_tiles) {
+      // split K, second CTA: park the fp32 accumulator in the exchange buffer, column-major (element (row, col) at
+      // col * 128 + row) so that the 32 lanes of a warp, one row each, hit 32 different banks
+      float *xbuf = reinterpret_cast<float *>(smem + L::kXbuf);
+      if (mbar_wait(acc_full_bar(0), 0u, abort_flag, p.status, kErrEpilogueWait)) {
+        tc_fence_after();
+        const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(t_acc + (uint32_t)c, v);
+          tmem_ld_wait(v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) xbuf[(c + j) * BM + quarter * 32 + lane] = __uint_as_float(v[j]);
+        }
+        tc_fence_before();
+      }
     }
-    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores done before the CTA exits
+    if constexpr (!kSplit) {
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores done before the CTA exits
+    }
+  }
+
+  if constexpr (kSplit) {
+    // every thread of both CTAs: the second CTA's partial sums are in its exchange buffer
+    cluster_sync();
+    if (warp >= 2 && rank == 0 && first_tile < n_tiles) {
+      const int quarter = warp & 3;
+      uint8_t *stage_buf = smem + L::kStaging + (warp - 2) * (kStoreBufs * 2048);
+      int buf = 0;
+      const int tile = first_tile, m_blk = tile / tiles_n, n_blk = tile % tiles_n;
+      if (mbar_wait(acc_full_bar(0), 0u, abort_flag, p.status, kErrEpilogueWait)) {
+        tc_fence_after();
+        const uint32_t peer = map_to_cta(s_base + L::kXbuf, 1u) + (uint32_t)(quarter * 32 + lane) * 4u;
+        drain_accumulator<BN, false, kStoreBufs>(
+            p, &map_d, tmem_base + ((uint32_t)(quarter * 32) << 16), 0, m_blk * BM + quarter * 32, n_blk * BN, lane,
+            stage_buf, buf, [] {},
+            [&](uint32_t(&v)[32], int c) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                v[j] = __float_as_uint(__uint_as_float(v[j]) + ld_cluster_f32(peer + (uint32_t)((c + j) * BM) * 4u));
+            });
+        tc_fence_before();
+      }
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+    cluster_sync();  // the second CTA keeps its shared memory until the first one has read it
   }
 
   tc_fence_before();
@@ -575,28 +666,6 @@ struct PairLayout {
   static constexpr int kTotal = kBarriers + 32 * 8 + 16 + 1024;
 };
 
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_cluster_u32(uint32_t cluster_addr) {
-  uint32_t v;
-  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
-  return v;
-}
 // TMA load of a CTA pair: the data lands in this CTA's shared memory, the bytes complete on `bar`, which may be a
 // barrier of the peer CTA (shared::cluster address)
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
@@ -938,20 +1007,25 @@ static int sm_count() {
 // still running (once that kernel has let its dependents go, or finished) and waits for it on the device.
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st,
-                                    Args... args) {
+                                    int cluster, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid), cfg.blockDim = dim3((unsigned)block), cfg.dynamicSmemBytes = smem, cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = 1;
+  if (cluster > 1) {  // kernels without a compile-time cluster size: clusters of `cluster` CTAs along x
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)cluster, attr[1].val.clusterDim.y = 1, attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-template <int kKind, int BN>
+template <int kKind, int BN, bool kSplit = false>
 static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
                   int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, cudaStream_t st) {
-  using L = Layout<BN, kKind == kMxf8>;
+  using L = Layout<BN, kKind == kMxf8, kSplit>;
   constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
   CUtensorMap ma, mb, md;
   // With fewer than 128 rows the A load fetches only the rows that exist (rounded up to the 8-row swizzle atom): the
@@ -986,7 +1060,7 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
   bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {
-    if (cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
+    if (cudaFuncSetAttribute(umma_gemm_kernel<kKind, BN, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
         cudaSuccess)
       return MXQ_ERR_LAUNCH;
     attr_set = true;
@@ -994,8 +1068,17 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (g_max_ctas > 0 && grid > g_max_ctas) grid = g_max_ctas;
-  const cudaError_t err = launch_dependent(umma_gemm_kernel<kKind, BN>, grid, kThreads, L::kTotal, st, ma, mb, msa, msb, md, p);
-  return err == cudaSuccess && cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
+  if (kSplit) {  // one tile per cluster of two; the caller checked that 2 * tiles CTAs fit
+    grid = 2 * tiles;
+    if (g_max_ctas > 0 && grid > g_max_ctas) return MXQ_ERR_UNSUPPORTED;
+  }
+  const cudaError_t err = launch_dependent(umma_gemm_kernel<kKind, BN, kSplit>, grid, kThreads, L::kTotal, st,
+                                           kSplit ? 2 : 0, ma, mb, msa, msb, md, p);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return MXQ_ERR_LAUNCH;
+  }
+  return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
 // Block-scaled GEMM on CTA pairs; the scale buffers are padded to whole 256-row tiles (mxq_mma_scale_bytes).
@@ -1045,7 +1128,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   if (2 * tiles < grid) grid = (int)(2 * tiles);
   grid &= ~1;
   if (grid < 2) return MXQ_ERR_UNSUPPORTED;
-  const cudaError_t err = launch_dependent(umma_gemm_pair_kernel<kKind>, grid, kThreads, L::kTotal, st, ma, mb, msa, msb, md, p);
+  const cudaError_t err = launch_dependent(umma_gemm_pair_kernel<kKind>, grid, kThreads, L::kTotal, st, 0, ma, mb, msa, msb, md, p);
   if (err != cudaSuccess) {
     cudaGetLastError();  // clear it: the caller falls back to single-CTA tiles
     return MXQ_ERR_LAUNCH;
@@ -1056,6 +1139,8 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
 // 0: single-CTA tiles only; 1: CTA pairs where 256-column tiles fill the GPU; 2: CTA pairs whenever the problem has
 // more than 128 rows and columns (for tests).  Process-wide.
 static int g_pair_mode = 1;
+// split K over the two CTAs of a cluster for small problems (mxq_gemm_set_split_k)
+static int g_split_k = 1;
 
 // Tile width: 256 columns when that already gives every SM a tile; narrower tiles for small problems (few rows of
 // activations against a large weight are bound by streaming the weight, which needs many SMs pulling at once).
@@ -1073,8 +1158,17 @@ static int launch_any(const void *a, const void *b, const uint8_t *sfa, const ui
   if (wide) return launch<kKind, 256>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
   // The block-scaled MMA takes its B scales from TMEM columns whose offset inside a 128-row chunk must be even
   // (0 or 2), so its narrowest tile is 64 columns; the dense kinds go down to 32.
-  if (kKind == kMxf8 || tiles_m * ((N + 63) / 64) * 2 > sms || N <= 32)
+  if (kKind == kMxf8 || tiles_m * ((N + 63) / 64) * 2 > sms || N <= 32) {
+    // one row of tiles that leaves at least half of the SMs idle and a long K: two CTAs per tile, half of K each
+    constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
+    const int64_t tiles = tiles_m * ((N + 63) / 64), k_chunks = (K * es + kRowBytes - 1) / kRowBytes;
+    // (the hand-over costs ~2 us: measured slower below 32 chunks of K, 7 % faster at 32, 26 % at 64)
+    if (g_split_k && tiles_m == 1 && 2 * tiles <= sms && k_chunks >= 32) {
+      const int rc = launch<kKind, 64, true>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+      if (rc != MXQ_ERR_LAUNCH && rc != MXQ_ERR_UNSUPPORTED) return rc;
+    }
     return launch<kKind, 64>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+  }
   if constexpr (kKind != kMxf8)
     return launch<kKind, 32>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
   return MXQ_ERR_UNSUPPORTED;
@@ -1096,6 +1190,12 @@ int mxq_gemm_set_max_ctas(int max_ctas) {
 int mxq_gemm_set_pair_mode(int mode) {
   const int prev = g_pair_mode;
   g_pair_mode = mode < 0 || mode > 2 ? 0 : mode;
+  return prev;
+}
+
+int mxq_gemm_set_split_k(int on) {
+  const int prev = g_split_k;
+  g_split_k = on ? 1 : 0;
   return prev;
 }
 

@@ -104,6 +104,11 @@ def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None, out_dtype: to
     return out.reshape(*lead, N)
 
 
+def set_split_k(on: bool) -> bool:
+    """Split K over the two CTAs of a cluster for small problems (mxq_gemm_set_split_k).  Returns the previous state."""
+    return bool(_lib.lib().mxq_gemm_set_split_k(1 if on else 0))
+
+
 @dataclass
 class MXOperand:
     """A [rows, K] matrix as tensor-core operands: hardware E4M3 bytes and E8M0 scales in the MMA chunk layout."""

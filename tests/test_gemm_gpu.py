@@ -151,3 +151,34 @@ def test_mxfp4_weight_mxfp8_activation():
     y = gemm.mx_gemm(gemm.pack_mx_operand(x.to(DEV), 4, 3), wp, None, torch.float32)
     gemm.check_status()
     assert rel_err(y, ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (16, 4096, 4096), (128, 8192, 2048), (100, 4128, 1000), (7, 8192, 512)])
+def test_split_k_over_a_cluster_matches_unsplit(shape):
+    """Small problems split K over the two CTAs of a cluster; the sum of the two halves may differ from the unsplit
+    accumulation by fp32 rounding only, repeats exactly, and matches the oracle."""
+    M, K, N = shape
+    x, w = synthetic.linear_operands(M, K, N, seed=8)
+    g = torch.Generator().manual_seed(8)
+    b = torch.randn(N, generator=g).bfloat16().to(DEV)
+    xp, wp = gemm.pack_mx_operand(x.to(DEV), 4, 3), gemm.pack_mx_operand(w.to(DEV), 4, 3)
+    ref = O.mxfp_fake(x, 32, 4, 3).float() @ O.mxfp_fake(w, 32, 4, 3, 1).float().t() + b.float().cpu()
+    prev = gemm.set_split_k(False)
+    try:
+        plain = gemm.mx_gemm(xp, wp, b, torch.float32)
+        gemm.set_split_k(True)
+        split1 = gemm.mx_gemm(xp, wp, b, torch.float32)
+        split2 = gemm.mx_gemm(xp, wp, b, torch.float32)
+        split_bf16 = gemm.mx_gemm(xp, wp, b, torch.bfloat16)
+        xq, wq = O.mxfp_fake(x, 32, 4, 3).to(DEV), O.mxfp_fake(w, 32, 4, 3, 1).to(DEV)
+        dense_split = gemm.linear_forward(xq, wq, b)
+        gemm.set_split_k(False)
+        dense_plain = gemm.linear_forward(xq, wq, b)
+        gemm.check_status()
+    finally:
+        gemm.set_split_k(prev)
+    assert torch.equal(split1, split2)
+    assert rel_err(split1, ref) <= REL_TOL and rel_err(plain, ref) <= REL_TOL
+    assert float((split1 - plain).abs().max() / plain.abs().max()) <= 1e-5
+    assert rel_err(split_bf16, ref) <= 4e-3
+    assert rel_err(dense_split, ref) <= 4e-3 and rel_err(dense_plain, ref) <= 4e-3
