@@ -15,7 +15,7 @@
 // a tile overlaps the main loop of the next one (for the block-scaled 256-column tile the two overlap by 64 columns,
 // see the kernel).  A second kernel runs all kinds on CTA pairs (cta_group::2, 256 x 256 tiles).
 //
-// No multicast loads are used.  Every wait on an mbarrier is bounded: when it runs out the CTA raises an abort
+// Every load targets one CTA only (no cluster-wide broadcast loads).  Every wait on an mbarrier is bounded: when it runs out the CTA raises an abort
 // flag, records an error code in the caller's status word, waits (bounded) for its own bulk copies in flight, frees
 // its tensor memory and returns.
 
@@ -639,7 +639,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 //
 // Synchronisation (every wait bounded as in the single-CTA kernel):
 //   full[s]      leader's barrier.  The leader's producer arrives with the byte count of BOTH CTAs' slot s; all loads
-//                of both CTAs (cta_group::2 form of the TMA load, no multicast) complete on it.
+//                of both CTAs (cta_group::2 form of the TMA load, one destination CTA each) complete on it.
 //   empty[s]     one per CTA; the leader commits the MMAs of slot s to its own and to the peer's barrier.
 //   acc_full[a]  one per CTA, committed the same way when a tile's MMAs are done.
 //   acc_empty[a], overlap: leader's barriers; the epilogue warps of both CTAs arrive (the peer's remotely).
