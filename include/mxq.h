@@ -4,7 +4,10 @@
  *
  * Conventions
  *   - every pointer named x/y/codes/scales/... is DEVICE memory owned by the caller; the library never
- *     allocates, frees or keeps device memory, and never synchronises the host with the device;
+ *     allocates or frees device memory, keeps no caller pointer past the call, and never synchronises the host with
+ *     the device.  The one piece of device memory it owns is the fixed scratch array of mxq_mx_linear_static
+ *     (MXQ_STATIC_SCRATCH_BYTES per GPU, part of the library's device image, used by that entry point only);
+ *   - the library has no mutable process-wide settings: per-call behaviour travels in mxq_gemm_options;
  *   - every kernel is enqueued on `stream` (a cudaStream_t passed as void*; NULL = legacy default stream);
  *   - log2 tables are HOST pointers to 256 bytes, copied by value into the launch;
  *   - functions return MXQ_OK (0) or a negative MXQ_ERR_* code; nothing throws or exits.
@@ -114,31 +117,53 @@ int mxq_bfp_fake_tiles(const void *x, void *y, int dtype, int64_t batch, int64_t
  * there instead of hanging; the caller reads it when it next synchronises.
  */
 
+/*
+ * Per-call options of the GEMM entry points (mxq_gemm_dense, mxq_gemm_mxf8, mxq_mx_linear, mxq_mx_linear_static).
+ * No counterpart in the reference.  The library keeps no mutable process-wide state: everything that steers a launch
+ * travels with the call, so calls from different threads or streams never influence one another.  Pass NULL for the
+ * defaults; a zero-filled struct means the same.  The struct is read during the call and not kept.
+ */
+typedef struct mxq_gemm_options {
+  /* Upper bound on the CTAs (= SMs) the launch occupies; 0 = every SM.  The GEMM kernels are persistent, one CTA per
+   * SM, each holding nearly all of the SM's shared memory, so a kernel of another stream (an NCCL collective, say)
+   * cannot start on an SM until a GEMM CTA leaves it; a caller that overlaps such a kernel leaves it some SMs. */
+  int32_t max_ctas;
+  /* Tile scheme for problems of more than 128 rows and columns.
+   *   MXQ_TILES_AUTO    CTA pairs on 256 x 256 tiles (thread-block clusters of two, tcgen05 cta_group::2) when such
+   *                     tiles fill the GPU, one CTA per 128 x 256 tile otherwise;
+   *   MXQ_TILES_SINGLE  one CTA per tile only;
+   *   MXQ_TILES_PAIRS   CTA pairs for every such problem, however small (for tests).
+   * The schemes accumulate in the same order: results are bit-identical. */
+  int32_t tiles;
+  /* Small problems (at most 128 rows): K is split over the CTAs of a thread-block cluster, which hand their fp32
+   * partial sums over through distributed shared memory in a fixed order.  0 = let the library decide, 1 = never. */
+  int32_t no_split_k;
+  /* mxq_mx_linear only.  0: for large problems the block-scaled GEMM starts while the activation pack is still
+   * running and waits, 128-row panel by panel, for the rows it is about to load; 1: pack first, then multiply. */
+  int32_t no_overlap;
+  /* Limit of every device-side wait in nanoseconds; 0 = one second.  When a wait runs out the kernel stores a
+   * non-zero code in the status word, lets its copies in flight land, frees its tensor memory and returns. */
+  int64_t wait_limit_ns;
+  /* Test hook: MXQ_TEST_DROP_LAST_LOAD makes the loader skip the last operand tile of the launch, so that the wait of
+   * the MMA issuer runs out and the error path above is taken (no fault is involved; the output is left incomplete
+   * and the status word reads 2).  Leave 0 otherwise. */
+  int32_t test_hook;
+  int32_t reserved;
+} mxq_gemm_options;
+
+#define MXQ_TILES_AUTO 0
+#define MXQ_TILES_SINGLE 1
+#define MXQ_TILES_PAIRS 2
+#define MXQ_TEST_DROP_LAST_LOAD 1
+
+/* sizeof(mxq_gemm_options) as the library was built, for bindings that mirror the struct by hand. */
+int mxq_gemm_options_size(void);
+
 /* Operands that already hold quantized values in bf16 (exact for every MX / block-fp format with <= 8 significant
  * bits) or fp32 (multiplied as tf32: exact for up to 11 significant bits).  A: [M,K], B: [N,K], row-major,
  * 16-byte aligned rows (K % 8 == 0 for bf16, K % 4 == 0 for fp32).  D: [M,N] of out_dtype. */
 int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int in_dtype, int out_dtype, int bias_dtype,
-                   int64_t M, int64_t N, int64_t K, int *status, void *stream);
-
-/* The GEMM kernels are persistent: one CTA per SM, each holding nearly all of the SM's shared memory, so a kernel
- * of another stream (an NCCL collective, say) cannot start on an SM until a GEMM CTA leaves it.  This process-wide
- * knob caps the CTAs of later GEMM launches (0 = use every SM) so that such a kernel finds free SMs; it returns
- * the previous value.  No counterpart in the reference. */
-int mxq_gemm_set_max_ctas(int max_ctas);
-
-/* Tile scheme of mxq_gemm_dense / mxq_gemm_mxf8 / mxq_mx_linear for problems of more than 128 rows and columns.
- *   0  one CTA per 128 x 256 tile (tcgen05 cta_group::1);
- *   1  (default) CTA pairs on 256 x 256 tiles (thread-block clusters of two, tcgen05 cta_group::2) when such tiles
- *      fill the GPU: one MMA instruction drives both SMs and each SM keeps a smaller share of the tile in its ring;
- *   2  CTA pairs for every such problem, however small (for tests).
- * Process-wide; returns the previous value.  No reference counterpart. */
-int mxq_gemm_set_pair_mode(int mode);
-
-/* Small problems (at most 128 rows, tiles that leave half of the SMs idle, K of at least 32 x 128 bytes): two CTAs of a
- * thread-block cluster share one 128 x 64 tile, each taking half of K; the second hands its fp32 accumulator to the
- * first through distributed shared memory (fixed summation order).  1 = on (default), 0 = off.  Process-wide; returns
- * the previous value.  No reference counterpart. */
-int mxq_gemm_set_split_k(int on);
+                   int64_t M, int64_t N, int64_t K, int *status, const mxq_gemm_options *options, void *stream);
 
 /* Size in bytes of the scale array that mxq_mxfp_pack_mma writes for a [rows, k] operand. */
 int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k);
@@ -156,16 +181,20 @@ int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in
  * K).  Replaces quantize-activations + F.linear of LinearMXFP.forward (chop/nn/quantized/modules/linear.py:877-895). */
 int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_codes, const uint8_t *b_scales,
                   void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status,
-                  void *stream);
+                  const mxq_gemm_options *options, void *stream);
 
 /* LinearMXFP.forward in one call (chop/nn/quantized/modules/linear.py:877-895): quantize x[M,K] to MXFP(E,F),
  * block 32 along K, into `workspace` (scratch owned by the caller, 256-byte aligned, at least
- * mxq_mx_linear_workspace_bytes(M, K) bytes), then D = x_q * W_q^T (+ bias) with the block-scaled GEMM.
+ * mxq_mx_linear_workspace_bytes(M, K) bytes: codes, scale chunks and one counter per 128-row panel), then
+ * D = x_q * W_q^T (+ bias) with the block-scaled GEMM.  For large problems the GEMM is launched while the pack is
+ * still running and takes each 128-row panel of activations as soon as its counter says it is complete
+ * (options->no_overlap = 1 runs the two steps one after the other).
  * w_codes / w_scales come from mxq_mxfp_pack_mma on the [N,K] weight. */
 int64_t mxq_mx_linear_workspace_bytes(int64_t M, int64_t K);
 int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d, const void *bias,
                   int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
-                  const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status, void *stream);
+                  const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status,
+                  const mxq_gemm_options *options, void *stream);
 
 /* Allocation-free variant of mxq_mx_linear.  It has no counterpart in the reference.
  *
@@ -181,15 +210,19 @@ int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uin
  *   - calls no cudaMalloc / cudaFree and no allocating library routine; inputs and the output are the caller's;
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  *     current) and caches it: make that first call with the right device current and before any stream capture;
- *   - every call on a device shares the one array.  A call only reads scratch bytes it has written itself (it
- *     zeroes the scale region and overwrites the code region it uses), so leftovers of earlier calls are harmless,
- *     but two calls that overlap in time on the same GPU (different streams or threads) race on it and corrupt
- *     each other's result: serialise them.
+ *   - every call on a device shares the one array, which keeps whatever the last call left in it.  A call overwrites
+ *     the M x K code bytes, the scale bytes of its M rows and the panel counters it uses before it reads them.  The
+ *     scale bytes of the padding rows (M rounded up to 256) are NOT rewritten and may hold an earlier call's bytes:
+ *     the tensor cores do read them, but they only scale accumulator rows >= M, which are never stored.  Scale bytes
+ *     of K blocks past the end of a row (K not a multiple of 128) are cleared by every call, because there a stale
+ *     0xFF (NaN) would meet the zero-filled codes of rows that are stored.  So leftovers are harmless, but two calls
+ *     that overlap in time on the same GPU (different streams or threads) race on the array and corrupt each
+ *     other's result: serialise them.
  * Arguments and results are otherwise those of mxq_mx_linear. */
 #define MXQ_STATIC_SCRATCH_BYTES (40u << 20)
 int mxq_mx_linear_static(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d,
                          const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
-                         const uint8_t *floor_tab_host, int *status, void *stream);
+                         const uint8_t *floor_tab_host, int *status, const mxq_gemm_options *options, void *stream);
 
 #ifdef __cplusplus
 }

@@ -23,23 +23,33 @@ _PROTOTYPES = {
     "mxq_mxfp_compose": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p],
     "mxq_minifloat_fake": [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_void_p],
     "mxq_gemm_dense": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_void_p,
-                       c_void_p],
+                       c_void_p, c_void_p],
     "mxq_mma_scale_bytes": [c_int64, c_int64],
-    "mxq_gemm_set_max_ctas": [c_int],
-    "mxq_gemm_set_pair_mode": [c_int],
-    "mxq_gemm_set_split_k": [c_int],
+    "mxq_gemm_options_size": [],
     "mxq_mxfp_pack_mma": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p],
     "mxq_gemm_mxf8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
-                      c_int64, c_void_p, c_void_p],
+                      c_int64, c_void_p, c_void_p, c_void_p],
     "mxq_mx_linear_workspace_bytes": [c_int64, c_int64],
     "mxq_mx_linear": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64,
-                      c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
+                      c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p],
     "mxq_mx_linear_static": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
-                             c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p],
+                             c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "mxq_bfp_fake_tiles": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
                            c_void_p, c_void_p],
     "mxq_bfp_fake": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
 }
+
+
+class GemmOptions(ctypes.Structure):
+    """`mxq_gemm_options` of include/mxq.h: per-call settings of the GEMM entry points (all zero = defaults)."""
+
+    _fields_ = [("max_ctas", ctypes.c_int32), ("tiles", ctypes.c_int32), ("no_split_k", ctypes.c_int32),
+                ("no_overlap", ctypes.c_int32), ("wait_limit_ns", ctypes.c_int64), ("test_hook", ctypes.c_int32),
+                ("reserved", ctypes.c_int32)]
+
+
+TILES_AUTO, TILES_SINGLE, TILES_PAIRS = 0, 1, 2
+TEST_DROP_LAST_LOAD = 1
 
 
 class MxqError(RuntimeError):
@@ -70,6 +80,8 @@ def lib():
             fn.restype = c_int64 if name.endswith("_bytes") else c_int
         handle.mxq_error_string.argtypes = [c_int]
         handle.mxq_error_string.restype = c_char_p
+        if handle.mxq_gemm_options_size() != ctypes.sizeof(GemmOptions):
+            raise MxqError("mxq_gemm_options of libmxq.so and its ctypes mirror differ in size: rebuild the library")
         _lib = handle
     return _lib
 

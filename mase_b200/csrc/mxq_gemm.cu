@@ -25,6 +25,7 @@
 #include <stdint.h>
 
 #include "mxq.h"
+#include "mxq_internal.h"
 
 namespace mxq {
 namespace gemm {
@@ -34,12 +35,11 @@ constexpr int kMaxStages = 8;
 constexpr int kThreads = 192;
 constexpr int kRowBytes = 128;            // bytes of K per row per stage = one 128B swizzle atom
 constexpr int kTmemCols = 512;
-constexpr unsigned long long kTimeoutNs = 1000000000ull;  // 1 s per wait
 
 enum Kind { kBf16 = 0, kTf32 = 1, kMxf8 = 2 };
 
 // error codes written to the status word
-constexpr int kErrProducerWait = 1, kErrMmaWaitFull = 2, kErrMmaWaitAcc = 3, kErrEpilogueWait = 4;
+constexpr int kErrProducerWait = 1, kErrMmaWaitFull = 2, kErrMmaWaitAcc = 3, kErrEpilogueWait = 4, kErrPanelWait = 6;
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -69,14 +69,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out of time).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                          unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xFFu) == 0) {
       if (*abort_flag) return false;
-      if (global_ns() - t0 > kTimeoutNs) {
+      if (global_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
@@ -87,8 +88,37 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 // the same for a whole warp: every lane waits, and all lanes get the same answer
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
-                                               int code) {
-  return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag, status, code));
+                                               int code, unsigned long long limit_ns) {
+  return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag, status, code, limit_ns));
+}
+// Bounded wait until the activation pack that runs next to this kernel has finished a 128-row panel: `counter`
+// (global memory, written by the pack with release semantics) reaches `target`.  The bulk-copy engine reads the
+// panel afterwards, hence the proxy fence behind the acquire.  Every lane of the warp polls and gets the same answer.
+__device__ __forceinline__ bool panel_wait_warp(const uint32_t *counter, uint32_t target, volatile int *abort_flag,
+                                                int *status, int code, unsigned long long limit_ns) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+  bool ok = true;
+  if (v < target) {
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+      __nanosleep(100);
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+      if (v >= target) break;
+      if (*abort_flag) {
+        ok = false;
+        break;
+      }
+      if (global_ns() - t0 > limit_ns) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        ok = false;
+        break;
+      }
+    }
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return __all_sync(0xFFFFFFFFu, ok);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
   asm volatile(
@@ -252,7 +282,19 @@ struct Params {
   int bias_bf16;        // bias element type
   int tma_store;        // output rows are 16-byte multiples: the epilogue writes through TMA stores
   int a_box_bytes;      // bytes one A load delivers: fewer than 128 rows when M is small (single-CTA kernel)
+  unsigned long long wait_ns;  // limit of every wait
+  int drop_last_load;   // test hook: CTA 0 never loads the last K chunk of its first tile
+  // Set when the activation pack runs concurrently with this kernel (mxq_mx_linear): one counter per 128-row panel
+  // of A that the pack raises by the 32-byte units it has stored; a panel is complete at rows_in_panel * units_per_row.
+  const uint32_t *panel_ready;
+  uint32_t units_per_row;
 };
+
+// counter value at which the 128-row panel `m_blk` of A is completely packed (0 for panels past the last row)
+__device__ __forceinline__ uint32_t panel_target(const Params &p, int m_blk) {
+  const int rows = p.M - m_blk * BM;
+  return rows <= 0 ? 0u : (uint32_t)(rows < BM ? rows : BM) * p.units_per_row;
+}
 
 // Epilogue of one tile for one warp: drains the warp's 32 TMEM lanes (= 32 tile rows starting at row0) of the
 // accumulator at t_acc in chunks of 32 columns, starting with chunk `first`.  A chunk is converted, written to a
@@ -428,8 +470,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
   // Launched with programmatic stream serialization: everything above (barriers, tensor memory) may run while the
   // previous kernel of the stream -- normally the activation pack -- is still finishing; its results are visible
-  // from here on.  Without that launch attribute this is a no-op.
-  grid_dependency_wait();
+  // from here on.  Without that launch attribute this is a no-op.  When the pack runs concurrently (panel counters)
+  // there is nothing to wait for here: the producer waits for each panel of A instead, and B was packed long ago.
+  if (p.panel_ready == nullptr) grid_dependency_wait();
 
   // The producer and the MMA issuer run their loops with all 32 lanes of their warp on identical values and elect
   // one lane for the TMA / tcgen05 instructions themselves.  Those instructions take their operands from uniform
@@ -457,11 +500,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // rows of the scale maps
       int chunk_a = m_blk * p.k_chunks + kc_begin, chunk_b = ((n_blk * BN) / 128) * p.k_chunks + kc_begin;
       int k0 = kc_begin * kBlockK;
+      if (p.panel_ready != nullptr &&
+          !panel_wait_warp(p.panel_ready + m_blk, panel_target(p, m_blk), abort_flag, p.status, kErrPanelWait, p.wait_ns)) {
+        ok = false;
+        break;
+      }
       for (int kc = kc_begin; kc < kc_end; ++kc) {
-        if (!mbar_wait_warp(empty, phase ^ 1u, abort_flag, p.status, kErrProducerWait)) {
+        if (!mbar_wait_warp(empty, phase ^ 1u, abort_flag, p.status, kErrProducerWait, p.wait_ns)) {
           ok = false;
           break;
         }
+        // test hook: this slot is never filled, so the MMA issuer's wait for it runs out
+        if (p.drop_last_load && blockIdx.x == 0 && tile == first_tile && kc == kc_end - 1) break;
         if (elect_one()) {
           mbar_expect_tx(full, L::kStage - L::kA + p.a_box_bytes);
           tma_load_2d(sa, &map_a, full, k0, row_a);
@@ -509,9 +559,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step, ++local) {
       const int acc = local % kAccStages;
       const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
-      if (!mbar_wait_warp(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
+      if (!mbar_wait_warp(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc, p.wait_ns)) break;
       if constexpr (kOverlap) {  // the previous tile's epilogue has read the columns both accumulators share
-        if (local > 0 && !mbar_wait_warp(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc))
+        if (local > 0 && !mbar_wait_warp(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc, p.wait_ns))
           break;
       }
       tc_fence_after();
@@ -520,7 +570,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const uint32_t sfb_col = (uint32_t)((((tile % tiles_n) * BN) & 127) >> 5);
       uint32_t accumulate = 0;  // the tile's first MMA overwrites the accumulator
       for (int kc = kc_begin; kc < kc_end; ++kc) {
-        if (!mbar_wait_warp(full, phase, abort_flag, p.status, kErrMmaWaitFull)) {
+        if (!mbar_wait_warp(full, phase, abort_flag, p.status, kErrMmaWaitFull, p.wait_ns)) {
           ok = false;
           break;
         }
@@ -561,7 +611,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
         const int acc = local % kAccStages;
         const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
-        if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait)) break;
+        if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait, p.wait_ns)) break;
         tc_fence_after();
         drain_accumulator<BN, kOverlap, kStoreBufs>(
             p, &map_d, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride),
@@ -575,7 +625,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // split K, second CTA: park the fp32 accumulator in the exchange buffer, column-major (element (row, col) at
       // col * 128 + row) so that the 32 lanes of a warp, one row each, hit 32 different banks
       float *xbuf = reinterpret_cast<float *>(smem + L::kXbuf);
-      if (mbar_wait(acc_full_bar(0), 0u, abort_flag, p.status, kErrEpilogueWait)) {
+      if (mbar_wait(acc_full_bar(0), 0u, abort_flag, p.status, kErrEpilogueWait, p.wait_ns)) {
         tc_fence_after();
         const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll
@@ -602,7 +652,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint8_t *stage_buf = smem + L::kStaging + (warp - 2) * (kStoreBufs * 2048);
       int buf = 0;
       const int tile = first_tile, m_blk = tile / tiles_n, n_blk = tile % tiles_n;
-      if (mbar_wait(acc_full_bar(0), 0u, abort_flag, p.status, kErrEpilogueWait)) {
+      if (mbar_wait(acc_full_bar(0), 0u, abort_flag, p.status, kErrEpilogueWait, p.wait_ns)) {
         tc_fence_after();
         const uint32_t peer = map_to_cta(s_base + L::kXbuf, 1u) + (uint32_t)(quarter * 32 + lane) * 4u;
         drain_accumulator<BN, false, kStoreBufs>(
@@ -645,7 +695,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 //   acc_empty[a], overlap: leader's barriers; the epilogue warps of both CTAs arrive (the peer's remotely).
 // Scale factors (block-scaled kind): each CTA loads the chunk of its own A rows and both chunks of the tile's B columns;
 // tcgen05.cp.cta_group::2 moves them from each CTA's shared memory into that CTA's tensor memory.
-// Both CTAs allocate all 512 TMEM columns, so their accumulator and scale addresses agree (checked at start-up).
+// Both CTAs take part in one cta_group::2 allocation of all 512 TMEM columns, so their accumulator and scale
+// addresses agree (still checked at start-up: a mismatch is reported in the status word, nothing is computed).
 // A cluster barrier before the CTAs free their tensor memory keeps each alive while the other may still touch its
 // barriers or read its half of B.
 // =====================================================================================================================
@@ -751,17 +802,19 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+    // every tcgen05 instruction of this kernel is the cta_group::2 form: one warp of each CTA of the pair takes
+    // part in the allocation, which hands both CTAs the same columns
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"(kTmemCols)
                  : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   cluster_sync();  // both CTAs' barriers are initialised and both tensor-memory addresses are published
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  grid_dependency_wait();  // see the single-CTA kernel
+  if (p.panel_ready == nullptr) grid_dependency_wait();  // see the single-CTA kernel
   // the MMAs address both CTAs' tensor memory with one address: the two allocations must coincide
   if (ld_cluster_u32(map_to_cta(smem_u32(tmem_slot), rank ^ 1u)) != tmem_base) {
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kErrPairTmem);
@@ -788,8 +841,13 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const int row_a = m_blk * BM, row_b = (n_blk + (int)rank) * 128;
       int chunk_a = m_blk * p.k_chunks, chunk_b = n_blk * p.k_chunks;
       int k0 = 0;
+      if (p.panel_ready != nullptr &&
+          !panel_wait_warp(p.panel_ready + m_blk, panel_target(p, m_blk), abort_flag, p.status, kErrPanelWait, p.wait_ns)) {
+        ok = false;
+        break;
+      }
       for (int kc = 0; kc < p.k_chunks; ++kc) {
-        if (!mbar_wait_warp(empty, phase ^ 1u, abort_flag, p.status, kErrProducerWait)) {
+        if (!mbar_wait_warp(empty, phase ^ 1u, abort_flag, p.status, kErrProducerWait, p.wait_ns)) {
           ok = false;
           break;
         }
@@ -843,17 +901,17 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-        if (!mbar_wait_warp(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc)) break;
+        if (!mbar_wait_warp(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kErrMmaWaitAcc, p.wait_ns)) break;
         if constexpr (kOverlap) {
           if (local > 0 &&
-              !mbar_wait_warp(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc))
+              !mbar_wait_warp(overlap_bar, (uint32_t)(local - 1) & 1u, abort_flag, p.status, kErrMmaWaitAcc, p.wait_ns))
             break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccStride);
         uint32_t accumulate = 0;
         for (int kc = 0; kc < p.k_chunks; ++kc) {
-          if (!mbar_wait_warp(full, phase, abort_flag, p.status, kErrMmaWaitFull)) {
+          if (!mbar_wait_warp(full, phase, abort_flag, p.status, kErrMmaWaitFull, p.wait_ns)) {
             ok = false;
             break;
           }
@@ -897,7 +955,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const int m_blk = (tile / tiles_n) * 2 + (int)rank, n_blk = tile % tiles_n;
       const int acc = local & 1;
       const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-      if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait)) break;
+      if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait, p.wait_ns)) break;
       tc_fence_after();
       drain_accumulator<BN, kOverlap, kStoreBufs>(
           p, &map_d, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride),
@@ -915,7 +973,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   cluster_sync();  // neither CTA frees tensor memory or exits while the other may still use it
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -982,9 +1040,18 @@ static int make_sf_map(CUtensorMap *map, const void *ptr, int64_t chunks) {
   return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
-// Upper bound on the CTAs (= SMs) a GEMM launch occupies; 0 = all of them.  Process-wide, set through
-// mxq_gemm_set_max_ctas by callers that want to keep SMs free for a concurrent collective.
-static int g_max_ctas = 0;
+Opts make_opts(const mxq_gemm_options *o) {
+  Opts r;
+  if (o) {
+    r.max_ctas = o->max_ctas > 0 ? o->max_ctas : 0;
+    r.tiles = o->tiles == MXQ_TILES_SINGLE || o->tiles == MXQ_TILES_PAIRS ? o->tiles : MXQ_TILES_AUTO;
+    r.split_k = o->no_split_k == 0;
+    r.overlap = o->no_overlap == 0;
+    if (o->wait_limit_ns > 0) r.wait_ns = (unsigned long long)o->wait_limit_ns;
+    r.test_hook = o->test_hook;
+  }
+  return r;
+}
 
 static int current_device() {
   int dev = 0;
@@ -992,13 +1059,16 @@ static int current_device() {
   return dev;
 }
 
-static int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
+// SM count of the current device (cached per device ordinal; the value never changes, so a racing first call writes
+// the same number)
+int sm_count() {
+  static int cached[64] = {};
+  const int dev = current_device();
+  int &n = cached[dev & 63];
+  if (n <= 0) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    n = v > 0 ? v : 148;
   }
   return n;
 }
@@ -1024,7 +1094,8 @@ static cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int bloc
 
 template <int kKind, int BN, bool kSplit = false>
 static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
-                  int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, cudaStream_t st) {
+                  int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, const Opts &o,
+                  cudaStream_t st) {
   using L = Layout<BN, kKind == kMxf8, kSplit>;
   constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
   CUtensorMap ma, mb, md;
@@ -1050,6 +1121,8 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   p.k_chunks = (int)((K * es + kRowBytes - 1) / kRowBytes);
   p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
   p.a_box_bytes = a_rows * kRowBytes;
+  p.wait_ns = o.wait_ns, p.drop_last_load = !kSplit && o.test_hook == MXQ_TEST_DROP_LAST_LOAD;
+  p.panel_ready = o.panel_ready, p.units_per_row = o.units_per_row;
   CUtensorMap msa = ma, msb = ma;  // unused by the dense kinds
   if constexpr (kKind == kMxf8) {
     rc = make_sf_map(&msa, sfa, ((M + 255) / 256) * 2 * p.k_chunks);
@@ -1067,10 +1140,10 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   }
   const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
   int grid = tiles < sm_count() ? tiles : sm_count();
-  if (g_max_ctas > 0 && grid > g_max_ctas) grid = g_max_ctas;
+  if (o.max_ctas > 0 && grid > o.max_ctas) grid = o.max_ctas;
   if (kSplit) {  // one tile per cluster of two; the caller checked that 2 * tiles CTAs fit
     grid = 2 * tiles;
-    if (g_max_ctas > 0 && grid > g_max_ctas) return MXQ_ERR_UNSUPPORTED;
+    if (o.max_ctas > 0 && grid > o.max_ctas) return MXQ_ERR_UNSUPPORTED;
   }
   const cudaError_t err = launch_dependent(umma_gemm_kernel<kKind, BN, kSplit>, grid, kThreads, L::kTotal, st,
                                            kSplit ? 2 : 0, ma, mb, msa, msb, md, p);
@@ -1084,7 +1157,8 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
 // Block-scaled GEMM on CTA pairs; the scale buffers are padded to whole 256-row tiles (mxq_mma_scale_bytes).
 template <int kKind>
 static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
-                       int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, cudaStream_t st) {
+                       int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, const Opts &o,
+                       cudaStream_t st) {
   using L = PairLayout<kKind == kMxf8>;
   constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
   CUtensorMap ma, mb, msa, msb, md;
@@ -1114,6 +1188,8 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   p.k_chunks = (int)k_chunks;
   p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
   p.a_box_bytes = BM * kRowBytes;
+  p.wait_ns = o.wait_ns, p.drop_last_load = 0;
+  p.panel_ready = o.panel_ready, p.units_per_row = o.units_per_row;
   static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
   bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {
@@ -1124,7 +1200,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   }
   const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
   int grid = sm_count();
-  if (g_max_ctas > 0 && grid > g_max_ctas) grid = g_max_ctas;
+  if (o.max_ctas > 0 && grid > o.max_ctas) grid = o.max_ctas;
   if (2 * tiles < grid) grid = (int)(2 * tiles);
   grid &= ~1;
   if (grid < 2) return MXQ_ERR_UNSUPPORTED;
@@ -1136,26 +1212,21 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
-// 0: single-CTA tiles only; 1: CTA pairs where 256-column tiles fill the GPU; 2: CTA pairs whenever the problem has
-// more than 128 rows and columns (for tests).  Process-wide.
-static int g_pair_mode = 1;
-// split K over the two CTAs of a cluster for small problems (mxq_gemm_set_split_k)
-static int g_split_k = 1;
-
 // Tile width: 256 columns when that already gives every SM a tile; narrower tiles for small problems (few rows of
 // activations against a large weight are bound by streaming the weight, which needs many SMs pulling at once).
 template <int kKind>
 static int launch_any(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
-                      int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, cudaStream_t st) {
+                      int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, const Opts &o,
+                      cudaStream_t st) {
   const int64_t tiles_m = (M + BM - 1) / BM;
   const int sms = sm_count();
   const bool wide = tiles_m * ((N + 255) / 256) * 2 > sms || N <= 64;
-  if (M > 128 && N > 128 && ((g_pair_mode == 1 && wide) || g_pair_mode == 2)) {
+  if (M > 128 && N > 128 && ((o.tiles == MXQ_TILES_AUTO && wide) || o.tiles == MXQ_TILES_PAIRS)) {
     // a context that cannot place clusters of two such CTAs falls back to one CTA per tile
-    const int rc = launch_pair<kKind>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+    const int rc = launch_pair<kKind>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st);
     if (rc != MXQ_ERR_LAUNCH && rc != MXQ_ERR_UNSUPPORTED) return rc;
   }
-  if (wide) return launch<kKind, 256>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+  if (wide) return launch<kKind, 256>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st);
   // The block-scaled MMA takes its B scales from TMEM columns whose offset inside a 128-row chunk must be even
   // (0 or 2), so its narrowest tile is 64 columns; the dense kinds go down to 32.
   if (kKind == kMxf8 || tiles_m * ((N + 63) / 64) * 2 > sms || N <= 32) {
@@ -1163,14 +1234,14 @@ static int launch_any(const void *a, const void *b, const uint8_t *sfa, const ui
     constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
     const int64_t tiles = tiles_m * ((N + 63) / 64), k_chunks = (K * es + kRowBytes - 1) / kRowBytes;
     // (the hand-over costs ~2 us: measured slower below 32 chunks of K, 7 % faster at 32, 26 % at 64)
-    if (g_split_k && tiles_m == 1 && 2 * tiles <= sms && k_chunks >= 32) {
-      const int rc = launch<kKind, 64, true>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+    if (o.split_k && tiles_m == 1 && 2 * tiles <= sms && k_chunks >= 32) {
+      const int rc = launch<kKind, 64, true>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st);
       if (rc != MXQ_ERR_LAUNCH && rc != MXQ_ERR_UNSUPPORTED) return rc;
     }
-    return launch<kKind, 64>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+    return launch<kKind, 64>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st);
   }
   if constexpr (kKind != kMxf8)
-    return launch<kKind, 32>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+    return launch<kKind, 32>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st);
   return MXQ_ERR_UNSUPPORTED;
 }
 
@@ -1181,23 +1252,7 @@ using namespace mxq::gemm;
 
 extern "C" {
 
-int mxq_gemm_set_max_ctas(int max_ctas) {
-  const int prev = g_max_ctas;
-  g_max_ctas = max_ctas > 0 ? max_ctas : 0;
-  return prev;
-}
-
-int mxq_gemm_set_pair_mode(int mode) {
-  const int prev = g_pair_mode;
-  g_pair_mode = mode < 0 || mode > 2 ? 0 : mode;
-  return prev;
-}
-
-int mxq_gemm_set_split_k(int on) {
-  const int prev = g_split_k;
-  g_split_k = on ? 1 : 0;
-  return prev;
-}
+int mxq_gemm_options_size(void) { return (int)sizeof(mxq_gemm_options); }
 
 int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k) {
   if (rows < 0 || k < 0) return MXQ_ERR_SHAPE;
@@ -1207,9 +1262,10 @@ int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k) {
 }
 
 int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int in_dtype, int out_dtype, int bias_dtype,
-                   int64_t M, int64_t N, int64_t K, int *status, void *stream) {
+                   int64_t M, int64_t N, int64_t K, int *status, const mxq_gemm_options *options, void *stream) {
   if (M == 0 || N == 0) return MXQ_OK;
   if (!a || !b || !d) return MXQ_ERR_NULL;
+  const Opts o = make_opts(options);
   if (M < 0 || N < 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return MXQ_ERR_SHAPE;
   if (out_dtype != MXQ_F32 && out_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
   if (bias && bias_dtype != MXQ_F32 && bias_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
@@ -1218,18 +1274,31 @@ int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int 
   cudaStream_t st = (cudaStream_t)stream;
   if (in_dtype == MXQ_BF16) {
     if (K % 8) return MXQ_ERR_SHAPE;  // rows must be 16-byte multiples for the tensor map
-    return launch_any<kBf16>(a, b, nullptr, nullptr, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+    return launch_any<kBf16>(a, b, nullptr, nullptr, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st);
   }
   if (in_dtype == MXQ_F32) {
     if (K % 4) return MXQ_ERR_SHAPE;
-    return launch_any<kTf32>(a, b, nullptr, nullptr, d, bias, out_dtype, bias_dtype, M, N, K, status, st);
+    return launch_any<kTf32>(a, b, nullptr, nullptr, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st);
   }
   return MXQ_ERR_DTYPE;
 }
 
 int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_codes, const uint8_t *b_scales,
                   void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status,
-                  void *stream) {
+                  const mxq_gemm_options *options, void *stream) {
+  return mxq::gemm::gemm_mxf8(a_codes, a_scales, b_codes, b_scales, d, bias, out_dtype, bias_dtype, M, N, K, status,
+                              make_opts(options), (cudaStream_t)stream);
+}
+
+}  // extern "C"
+
+namespace mxq {
+namespace gemm {
+
+// mxq_gemm_mxf8 with the options resolved; mxq_mx_linear calls it with the panel counters of its concurrent pack
+int gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_codes, const uint8_t *b_scales, void *d,
+              const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status,
+              const Opts &o, cudaStream_t st) {
   if (M == 0 || N == 0) return MXQ_OK;
   if (!a_codes || !a_scales || !b_codes || !b_scales || !d) return MXQ_ERR_NULL;
   if (M < 0 || N < 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || K % 32) return MXQ_ERR_SHAPE;
@@ -1238,8 +1307,8 @@ int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t
   if ((reinterpret_cast<uintptr_t>(a_codes) | reinterpret_cast<uintptr_t>(b_codes) | reinterpret_cast<uintptr_t>(d) |
        reinterpret_cast<uintptr_t>(a_scales) | reinterpret_cast<uintptr_t>(b_scales)) & 15u)
     return MXQ_ERR_ALIGN;
-  return launch_any<kMxf8>(a_codes, b_codes, a_scales, b_scales, d, bias, out_dtype, bias_dtype, M, N, K, status,
-                            (cudaStream_t)stream);
+  return launch_any<kMxf8>(a_codes, b_codes, a_scales, b_scales, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st);
 }
 
-}  // extern "C"
+}  // namespace gemm
+}  // namespace mxq

@@ -1,5 +1,5 @@
-// Packing of MXFP operands for the block-scaled tensor-core GEMM (shared by the stand-alone pack kernel and by the
-// quantizer warps of the fused Linear kernel).
+// Packing of MXFP operands for the block-scaled tensor-core GEMM: per-lane routines of the pack kernels in
+// mxq_quant.cu (hardware E4M3 bytes plus E8M0 scale bytes in the tensor-core chunk layout).
 #pragma once
 
 #include <cuda_fp8.h>

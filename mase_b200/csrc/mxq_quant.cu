@@ -11,6 +11,7 @@
 // span, or a ragged row tail for block-fp) is handled by one thread per block with scalar accesses.
 
 #include "mxq_common.cuh"
+#include "mxq_internal.h"
 #include "mxq_pack.cuh"
 
 namespace mxq {
@@ -309,11 +310,15 @@ __device__ __forceinline__ void load_unit(const __nv_bfloat16 *x, int64_t unit, 
   }
 }
 // I = uint32_t when unit indices and scale offsets fit in 32 bits (the usual case), else int64_t.
-template <int E, int F, bool kWide, typename I>
+// kSignal: the GEMM that consumes the operands runs next to this kernel.  After every step the CTA adds the units it
+// has stored to the counter of their 128-row panel (release at GPU scope behind a CTA barrier), and the GEMM's loader
+// takes a panel when its counter reaches rows * units per row.  Launched with a grid that is resident as a whole.
+template <int E, int F, bool kWide, typename I, bool kSignal = false>
 __global__ void __launch_bounds__(kThreads, 4)
 mxfp_pack_mma_bf16_kernel(const __nv_bfloat16 *__restrict__ x, uint8_t *__restrict__ codes,
                           uint8_t *__restrict__ scales, int64_t n_unit64, uint32_t unit_per_row, int64_t k_chunks,
-                          UnitStep jump, UnitStep stride, const __grid_constant__ Log2Tab tab) {
+                          UnitStep jump, UnitStep stride, const __grid_constant__ Log2Tab tab,
+                          uint32_t *__restrict__ panel_ready = nullptr) {
   constexpr int kU = 2;
   // the GEMM that follows in the stream may be launched from now on: it sets up its barriers and tensor memory while
   // this kernel finishes and waits for the operands on the device (griddepcontrol.wait)
@@ -359,6 +364,25 @@ mxfp_pack_mma_bf16_kernel(const __nv_bfloat16 *__restrict__ x, uint8_t *__restri
     }
     col += stride.units, row += stride.rows;
     if (col >= unit_per_row) col -= unit_per_row, ++row;
+    if constexpr (kSignal) {
+      __syncthreads();  // every store of this step is ordered before thread 0's release below
+      if (threadIdx.x == 0) {
+        const uint64_t first = (uint64_t)base;
+        uint64_t end = first + (uint64_t)kThreads * kU;
+        if (end > (uint64_t)n_unit) end = (uint64_t)n_unit;
+        const uint64_t per_panel = 128ull * unit_per_row;  // units of one 128-row panel
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");  // the consumer reads through the bulk-copy engine
+        for (uint64_t u = first; u < end;) {
+          const uint64_t panel = u / per_panel;
+          uint64_t stop = (panel + 1) * per_panel;
+          if (stop > end) stop = end;
+          asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(panel_ready + panel), "r"((uint32_t)(stop - u))
+                       : "memory");
+          u = stop;
+        }
+      }
+    }
   }
 }
 
@@ -606,7 +630,7 @@ bfp_tile_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t batch, int r
 // ---------------------------------------------------------------------------------------------------
 static int grid_for(int64_t work_items, int per_cta) {
   int64_t g = (work_items + per_cta - 1) / per_cta;
-  const int64_t cap = 148 * 16;  // a few waves of resident CTAs on 148 SMs; the kernels loop beyond that
+  const int64_t cap = (int64_t)mxq::gemm::sm_count() * 16;  // a few waves of resident CTAs; the kernels loop beyond that
   if (g > cap) g = cap;
   if (g < 1) g = 1;
   return (int)g;
@@ -857,6 +881,42 @@ int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in
 #undef MXQ_PACK_ARGS
   return MXQ_ERR_FORMAT;
 }
+
+}  // extern "C"
+
+// See mxq_internal.h.  Two CTAs of 256 threads per SM: next to a GEMM CTA (192 threads, ~130 registers each, nearly all
+// of the shared memory, none of which this kernel needs) that is what the register file holds, and a grid that is
+// resident as a whole lets the GEMM launch as soon as this kernel has started.
+int mxq::pack_mma_signal(const void *x, uint8_t *codes, uint8_t *scales_mma, int64_t rows, int64_t k, int E, int F,
+                         const uint8_t *floor_tab_host, uint32_t *panel_ready, cudaStream_t st) {
+  if (!x || !codes || !scales_mma || !floor_tab_host || !panel_ready) return MXQ_ERR_NULL;
+  if (rows <= 0 || k <= 0 || k % 128) return MXQ_ERR_UNSUPPORTED;  // (K % 128 != 0 needs the scale memset first)
+  if (!legal_ef(E, F) || E > 4 || F > 3) return MXQ_ERR_FORMAT;
+  if ((reinterpret_cast<uintptr_t>(x) & 31) || !aligned16(codes)) return MXQ_ERR_UNSUPPORTED;
+  const Log2Tab tab = load_tab(floor_tab_host);
+  const int64_t k_chunks = k / 128;
+  const int64_t sf_bytes = ((rows + 255) / 256) * 2 * k_chunks * 512;
+  const int64_t n_unit = rows * k / 16;
+  const uint32_t upr = (uint32_t)(k / 16);
+  int64_t grid64 = (n_unit + kThreads * 2 - 1) / (kThreads * 2);
+  const int64_t cap = 2 * (int64_t)mxq::gemm::sm_count();
+  const int grid = (int)(grid64 < cap ? grid64 : cap);
+  const int64_t step = (int64_t)grid * kThreads * 2;
+  if (!(n_unit + step < (1ll << 31) && sf_bytes < (1ll << 31)) || 128ll * upr >= (1ll << 31)) return MXQ_ERR_UNSUPPORTED;
+  const UnitStep jump = {(uint32_t)(kThreads / upr), (uint32_t)(kThreads % upr)};
+  const UnitStep stride = {(uint32_t)(step / upr), (uint32_t)(step % upr)};
+#define MXQ_PACK(e, f)                                                                                        \
+  if (E == e && F == f) {                                                                                     \
+    mxfp_pack_mma_bf16_kernel<e, f, true, uint32_t, true><<<grid, kThreads, 0, st>>>(                         \
+        (const __nv_bfloat16 *)x, codes, scales_mma, n_unit, upr, k_chunks, jump, stride, tab, panel_ready);  \
+    return check_launch();                                                                                    \
+  }
+  MXQ_PACK(4, 3) MXQ_PACK(2, 3) MXQ_PACK(3, 2) MXQ_PACK(2, 1) MXQ_PACK(1, 2)
+#undef MXQ_PACK
+  return MXQ_ERR_FORMAT;
+}
+
+extern "C" {
 
 int mxq_mxfp_compose(const uint8_t *codes, const uint8_t *scales, void *y, int out_dtype, int64_t n_blocks, int block,
                      int E, int F, void *stream) {

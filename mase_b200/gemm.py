@@ -12,7 +12,10 @@ elements of K and are multiplied by `tcgen05.mma.kind::mxf8f6f4.block_scale`.
 
 from __future__ import annotations
 
+import contextlib
+import ctypes
 import os
+import threading
 from dataclasses import dataclass
 
 import torch
@@ -30,14 +33,33 @@ _STATUS_TEXT = {
     3: "MMA issuer: wait for a free accumulator ran out",
     4: "epilogue: wait for a finished accumulator ran out",
     5: "CTA pair: the two CTAs got different tensor-memory addresses",
+    6: "TMA producer: wait for a panel of activations from the concurrent pack ran out",
 }
 
 
-def set_pair_mode(mode: int) -> int:
-    """Tile scheme of the block-scaled GEMM (mxq_gemm_set_pair_mode): 0 = one CTA per 128 x 256 tile, 1 = CTA pairs
-    on 256 x 256 tiles when such tiles fill the GPU, 2 = CTA pairs for every problem above 128 rows and columns.
-    Returns the previous mode."""
-    return _lib.lib().mxq_gemm_set_pair_mode(int(mode))
+_TLS = threading.local()
+
+
+@contextlib.contextmanager
+def options(**fields):
+    """Per-call GEMM options (`mxq_gemm_options` of include/mxq.h) for every GEMM this thread issues inside the
+    `with` block: `max_ctas` (leave SMs to a concurrent kernel), `tiles` (_lib.TILES_AUTO / TILES_SINGLE /
+    TILES_PAIRS), `no_split_k`, `no_overlap`, `wait_limit_ns`, `test_hook`.  The options travel with each call into
+    the library, which keeps no settings of its own; other threads are not affected.  Blocks nest: inner fields
+    override outer ones."""
+    prev = getattr(_TLS, "opts", None)
+    merged = dict(prev[1]) if prev else {}
+    merged.update(fields)
+    _TLS.opts = (_lib.GemmOptions(**merged), merged)
+    try:
+        yield
+    finally:
+        _TLS.opts = prev
+
+
+def _options_ptr():
+    cur = getattr(_TLS, "opts", None)
+    return None if cur is None else ctypes.addressof(cur[0])
 
 
 def _status(device: torch.device) -> Tensor:
@@ -97,16 +119,12 @@ def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None, out_dtype: to
     st = _status(x.device)
     with _on_device(x):
         rc = _lib.lib().mxq_gemm_dense(a.data_ptr(), w.data_ptr(), out.data_ptr(), 0 if b is None else b.data_ptr(),
-                                       _DT[x.dtype], _DT[out.dtype], bdt, M, N, K, st.data_ptr(), _stream(x))
+                                       _DT[x.dtype], _DT[out.dtype], bdt, M, N, K, st.data_ptr(), _options_ptr(),
+                                       _stream(x))
     _lib.check(rc, "mxq_gemm_dense")
     if _CHECK_EVERY_CALL:
         check_status(x.device)
     return out.reshape(*lead, N)
-
-
-def set_split_k(on: bool) -> bool:
-    """Split K over the two CTAs of a cluster for small problems (mxq_gemm_set_split_k).  Returns the previous state."""
-    return bool(_lib.lib().mxq_gemm_set_split_k(1 if on else 0))
 
 
 @dataclass
@@ -155,7 +173,7 @@ def mx_gemm(a: MXOperand, b: MXOperand, bias: Tensor | None, out_dtype: torch.dt
     with _on_device(a.codes):
         rc = _lib.lib().mxq_gemm_mxf8(a.codes.data_ptr(), a.scales.data_ptr(), b.codes.data_ptr(), b.scales.data_ptr(),
                                       out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[out_dtype], bdt, a.rows,
-                                      b.rows, a.k, st.data_ptr(), _stream(a.codes))
+                                      b.rows, a.k, st.data_ptr(), _options_ptr(), _stream(a.codes))
     _lib.check(rc, "mxq_gemm_mxf8")
     if _CHECK_EVERY_CALL:
         check_status(a.codes.device)
@@ -185,7 +203,8 @@ def mx_linear(x: Tensor, weight: MXOperand, bias: Tensor | None, exp_bits: int, 
     with _on_device(x):
         rc = lib.mxq_mx_linear(a.data_ptr(), _DT[x.dtype], weight.codes.data_ptr(), weight.scales.data_ptr(),
                                out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[out.dtype], bdt, M, N, K, exp_bits,
-                               frac_bits, _floor_tab_ptr(), ws.data_ptr(), ws_bytes, st.data_ptr(), _stream(x))
+                               frac_bits, _floor_tab_ptr(), ws.data_ptr(), ws_bytes, st.data_ptr(), _options_ptr(),
+                               _stream(x))
     _lib.check(rc, "mxq_mx_linear")
     if _CHECK_EVERY_CALL:
         check_status(x.device)

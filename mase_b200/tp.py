@@ -16,6 +16,7 @@ injected local layer (tests) and under NCCL with the CUDA layers of this package
 
 from __future__ import annotations
 
+import contextlib
 import math
 from dataclasses import dataclass
 
@@ -214,13 +215,13 @@ def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, c
         for layer in layers:
             x = layer(x)
         return x
-    prev = None
+    ctx = contextlib.nullcontext()
     if x.is_cuda and comm_sms > 0:
-        from . import _lib
+        from . import gemm
 
         sms = torch.cuda.get_device_properties(x.device).multi_processor_count
-        prev = _lib.lib().mxq_gemm_set_max_ctas(max(1, sms - comm_sms))
-    try:
+        ctx = gemm.options(max_ctas=max(1, sms - comm_sms))
+    with ctx:
         parts = list(x.chunk(micro_batches, dim=0))
         handles = [None] * len(parts)
         prev_layer = None
@@ -232,8 +233,3 @@ def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, c
                 handles[i] = layer.down.start(layer.hidden(inp))
             prev_layer = layer
         return torch.cat([prev_layer.down.finish(h) for h in handles], dim=0)
-    finally:
-        if prev is not None:
-            from . import _lib
-
-            _lib.lib().mxq_gemm_set_max_ctas(prev)

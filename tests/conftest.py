@@ -13,6 +13,15 @@ if ROOT not in sys.path:
 GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
 
 
+def mase_chop_dir() -> str | None:
+    """`src/chop` of a MASE checkout for the tests that run the reference itself: $MASE_CHOP_DIR, else a checkout
+    named `reference` next to this repository.  None when there is none (those tests are skipped)."""
+    for cand in (os.environ.get("MASE_CHOP_DIR"), os.path.join(os.path.dirname(ROOT), "reference", "src", "chop")):
+        if cand and os.path.isdir(cand):
+            return cand
+    return None
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
 

@@ -252,4 +252,6 @@ def main(root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src/chop")
+    if len(sys.argv) < 2 and not os.environ.get("MASE_CHOP_DIR"):
+        raise SystemExit("usage: python make_golden.py <path to src/chop of a MASE checkout>  (or set MASE_CHOP_DIR)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["MASE_CHOP_DIR"])

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import mase_b200 as mb
-from mase_b200 import gemm, synthetic
+from mase_b200 import _lib, gemm, synthetic
 from oracle import mx_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -88,14 +88,11 @@ def test_mxf8_gemm_cta_pairs_match_single_cta_and_oracle(shape):
     ref = O.mxfp_fake(x, 32, 4, 3).float() @ O.mxfp_fake(w, 32, 4, 3, 1).float().t() + b.cpu()
     xp = gemm.pack_mx_operand(x.to(DEV), 4, 3)
     wp = gemm.pack_mx_operand(w.to(DEV), 4, 3)
-    prev = gemm.set_pair_mode(0)
-    try:
+    with gemm.options(tiles=_lib.TILES_SINGLE):
         single = [gemm.mx_gemm(xp, wp, b, dt) for dt in (torch.float32, torch.bfloat16)]
-        gemm.set_pair_mode(2)
+    with gemm.options(tiles=_lib.TILES_PAIRS):
         pair = [gemm.mx_gemm(xp, wp, b, dt) for dt in (torch.float32, torch.bfloat16)]
-        gemm.check_status()
-    finally:
-        gemm.set_pair_mode(prev)
+    gemm.check_status()
     assert torch.equal(single[0], pair[0]) and torch.equal(single[1], pair[1])
     assert rel_err(pair[0], ref) <= REL_TOL
     assert rel_err(pair[1], ref) <= 4e-3
@@ -109,14 +106,11 @@ def test_dense_gemm_cta_pairs_match_single_cta(shape, dtype):
     x, w = quantized_operands(M, K, N, 6, dtype)
     g = torch.Generator().manual_seed(6)
     b = torch.randn(N, generator=g).to(dtype).to(DEV)
-    prev = gemm.set_pair_mode(0)
-    try:
+    with gemm.options(tiles=_lib.TILES_SINGLE):
         single = gemm.linear_forward(x.to(DEV), w.to(DEV), b)
-        gemm.set_pair_mode(2)
+    with gemm.options(tiles=_lib.TILES_PAIRS):
         pair = gemm.linear_forward(x.to(DEV), w.to(DEV), b)
-        gemm.check_status()
-    finally:
-        gemm.set_pair_mode(prev)
+    gemm.check_status()
     assert torch.equal(single, pair)
     ref = x.float() @ w.float().t() + b.float().cpu()
     assert rel_err(pair, ref) <= (4e-3 if dtype == torch.bfloat16 else REL_TOL)
@@ -163,20 +157,15 @@ def test_split_k_over_a_cluster_matches_unsplit(shape):
     b = torch.randn(N, generator=g).bfloat16().to(DEV)
     xp, wp = gemm.pack_mx_operand(x.to(DEV), 4, 3), gemm.pack_mx_operand(w.to(DEV), 4, 3)
     ref = O.mxfp_fake(x, 32, 4, 3).float() @ O.mxfp_fake(w, 32, 4, 3, 1).float().t() + b.float().cpu()
-    prev = gemm.set_split_k(False)
-    try:
+    xq, wq = O.mxfp_fake(x, 32, 4, 3).to(DEV), O.mxfp_fake(w, 32, 4, 3, 1).to(DEV)
+    with gemm.options(no_split_k=1):
         plain = gemm.mx_gemm(xp, wp, b, torch.float32)
-        gemm.set_split_k(True)
-        split1 = gemm.mx_gemm(xp, wp, b, torch.float32)
-        split2 = gemm.mx_gemm(xp, wp, b, torch.float32)
-        split_bf16 = gemm.mx_gemm(xp, wp, b, torch.bfloat16)
-        xq, wq = O.mxfp_fake(x, 32, 4, 3).to(DEV), O.mxfp_fake(w, 32, 4, 3, 1).to(DEV)
-        dense_split = gemm.linear_forward(xq, wq, b)
-        gemm.set_split_k(False)
         dense_plain = gemm.linear_forward(xq, wq, b)
-        gemm.check_status()
-    finally:
-        gemm.set_split_k(prev)
+    split1 = gemm.mx_gemm(xp, wp, b, torch.float32)
+    split2 = gemm.mx_gemm(xp, wp, b, torch.float32)
+    split_bf16 = gemm.mx_gemm(xp, wp, b, torch.bfloat16)
+    dense_split = gemm.linear_forward(xq, wq, b)
+    gemm.check_status()
     assert torch.equal(split1, split2)
     assert rel_err(split1, ref) <= REL_TOL and rel_err(plain, ref) <= REL_TOL
     assert float((split1 - plain).abs().max() / plain.abs().max()) <= 1e-5

@@ -44,6 +44,46 @@ def test_argument_validation_without_gpu(library):
     assert library.mxq_bfp_fake(16, 16, 0, 4, 64, 32, 40, 8, 127, tab, None) == -3
 
 
+def test_gemm_options_travel_with_the_call(library):
+    """The library has no process-wide settings: options are a struct passed per call, mirrored by ctypes, and the
+    Python-side `gemm.options` context is per thread."""
+    import threading
+
+    from mase_b200 import gemm
+
+    assert library.mxq_gemm_options_size() == ctypes.sizeof(_lib.GemmOptions) == 32
+    for gone in ("mxq_gemm_set_max_ctas", "mxq_gemm_set_pair_mode", "mxq_gemm_set_split_k"):
+        assert not hasattr(library, gone)
+    assert gemm._options_ptr() is None
+    seen = {}
+    barrier = threading.Barrier(2)
+
+    def worker(name, **fields):
+        with gemm.options(**fields):
+            barrier.wait()  # both threads are inside their blocks at the same time
+            o = _lib.GemmOptions.from_address(gemm._options_ptr())
+            seen[name] = (o.max_ctas, o.tiles, o.no_split_k)
+            with gemm.options(no_split_k=1):  # nested: inherits the outer fields
+                o = _lib.GemmOptions.from_address(gemm._options_ptr())
+                seen[name + "/inner"] = (o.max_ctas, o.tiles, o.no_split_k)
+            barrier.wait()
+        seen[name + "/after"] = gemm._options_ptr()
+
+    threads = [threading.Thread(target=worker, args=("a",), kwargs={"max_ctas": 100, "tiles": _lib.TILES_SINGLE}),
+               threading.Thread(target=worker, args=("b",), kwargs={"tiles": _lib.TILES_PAIRS})]
+    [t.start() for t in threads]
+    [t.join() for t in threads]
+    assert seen["a"] == (100, 1, 0) and seen["b"] == (0, 2, 0)
+    assert seen["a/inner"] == (100, 1, 1) and seen["b/inner"] == (0, 2, 1)
+    assert seen["a/after"] is None and seen["b/after"] is None
+    assert gemm._options_ptr() is None
+    # argument validation happens before any launch, with and without options
+    opts = _lib.GemmOptions(max_ctas=8)
+    assert library.mxq_gemm_mxf8(None, None, None, None, None, None, 1, 0, 4, 4, 32, None, ctypes.addressof(opts), None) == -5
+    assert library.mxq_gemm_dense(16, 16, 16, None, 5, 1, 0, 4, 4, 32, None, None, None) == -1
+    assert library.mxq_mx_linear_workspace_bytes(8192, 4096) == 8192 * 4096 + 64 * 32 * 512 + 256
+
+
 def test_missing_library_is_loud(monkeypatch):
     monkeypatch.setattr(_lib, "_lib", None)
     monkeypatch.setattr(_lib, "_PATH", "/nonexistent/libmxq.so")

@@ -3,7 +3,7 @@
 import pytest
 import torch
 
-from conftest import assert_bits_equal
+from conftest import assert_bits_equal, mase_chop_dir
 from oracle import mx_oracle as O
 
 
@@ -121,14 +121,14 @@ def test_linear_oracle_matches_reference(golden):
         assert float(err) <= tol, f"{tag}: {float(err)}"
 
 
-@pytest.mark.skipif(not __import__("os").path.isdir("/root/reference/src/chop"), reason="no MASE checkout")
+@pytest.mark.skipif(mase_chop_dir() is None, reason="no MASE checkout")
 def test_oracle_vs_live_reference_random():
     """Where a MASE checkout is present, compare on fresh random data as well (larger than the fixtures)."""
     import sys, os
     sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
     import make_golden
 
-    make_golden.import_reference("/root/reference/src/chop")
+    make_golden.import_reference(mase_chop_dir())
     import chop.nn.quantizers as q
 
     g = torch.Generator().manual_seed(2024)

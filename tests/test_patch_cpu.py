@@ -8,9 +8,10 @@ import pytest
 import torch
 
 import mase_b200 as mb
+from conftest import mase_chop_dir
 
-CHOP = "/root/reference/src/chop"
-pytestmark = pytest.mark.skipif(not os.path.isdir(CHOP), reason="no MASE checkout")
+CHOP = mase_chop_dir()
+pytestmark = pytest.mark.skipif(CHOP is None, reason="no MASE checkout")
 
 
 @pytest.fixture(scope="module")
