@@ -13,10 +13,13 @@ is no collective) and the reported value is the aggregate ("weak" scaling).
   e2e     the same metric through the public API with pinned HOST buffers: host->device copy, quantize,
           device->host copy of the result inside the timed region (chunked over two streams)
   roofline  the fake-quant kernel against the measured HBM copy bandwidth
-  cpu_baseline  the CPU port of MASE's algorithm (oracle/) on a bounded sample of the same tensor, rank 0 only
-  extra   other formats / shapes of the sweep and the MX Linear forward, measured outside the timed region
+  cpu_baseline  MASE's own CPU quantizer (staged by oracle/stage_reference.py into oracle/_ref, kind "reference") or,
+          where that is absent, the CPU port in oracle/ (kind "port"), on a bounded sample of the same tensor, rank 0
+  extra   other formats / shapes of the sweep, the MX Linear forward, the mixed-precision decoder layer and the
+          tensor-parallel Linear stack, measured outside the timed region.  The MX-Linear half of the metric is also
+          nested in the contract's objects: roofline["mx_linear"], cpu_baseline["mx_linear"], roofline["peaks"].
 
-`--impl reference` times the CPU port on the host cores instead (bounded sample per step).
+`--impl reference` times the CPU implementation on the host cores instead (bounded sample per step).
 """
 
 from __future__ import annotations
@@ -52,6 +55,67 @@ def measured_peaks() -> tuple[float, str]:
             return float(json.load(fh)["hbm_gbs"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, "fallback"
+
+
+def measured_bf16_tflops() -> tuple[float, float, str]:
+    """(burst, sustained, source) of the dense bf16 library GEMM from MEASURED_PEAKS.json, else the fallback."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            d = json.load(fh)
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    except Exception:
+        return 1590.0, 1400.0, "fallback"
+
+
+def measure_fp8_peak(device) -> dict:
+    """FP8-rate tensor-core peak measured the way MEASURED_PEAKS.json measures bf16: the library FP8 GEMM
+    (`torch._scaled_mm`, E4M3 x E4M3, per-tensor scales, bf16 output) at 8192^3, best of 10 launches (burst) and
+    back to back for ~2 s (sustained).  Measurement only: nothing on the product path calls it."""
+    n = 8192
+    try:
+        a = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=device).to(torch.float8_e4m3fn).t()  # column-major second operand
+        one = torch.ones((), device=device, dtype=torch.float32)
+        run = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)  # noqa: E731
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        flops = 2.0 * n * n * n
+        best = float("inf")
+        for _ in range(10):
+            s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s_.record()
+            run()
+            e_.record()
+            torch.cuda.synchronize()
+            best = min(best, s_.elapsed_time(e_) / 1e3)
+        reps = max(10, int(2.0 / best))
+        s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_.record()
+        for _ in range(reps):
+            run()
+        e_.record()
+        torch.cuda.synchronize()
+        sustained = flops * reps / (s_.elapsed_time(e_) / 1e3) / 1e12
+        del a, b
+        return {"fp8_tflops": flops / best / 1e12, "fp8_tflops_sustained": sustained,
+                "how": f"torch._scaled_mm E4M3 x E4M3 (per-tensor scale, bf16 out) {n}^3: best of 10 (burst); {reps} "
+                       "back to back (sustained); CUDA events"}
+    except Exception as exc:  # library without an FP8 GEMM: the 2 x bf16 stand-in is used and labelled
+        return {"fp8_tflops": None, "fp8_tflops_sustained": None, "how": f"unavailable: {type(exc).__name__}: {exc}"[:200]}
+
+
+def tensor_peaks(device) -> dict:
+    """Denominators of the tensor-bound rooflines: measured FP8-rate peak (this run), 2 x measured bf16, nominal."""
+    bf16, bf16_sus, src = measured_bf16_tflops()
+    pk = measure_fp8_peak(device)
+    pk.update({"bf16_tflops": bf16, "bf16_tflops_sustained": bf16_sus, "bf16_source": src + " cuBLAS bf16 8192^3",
+               "fp8_nominal_tflops": 4500.0, "bf16_nominal_tflops": 2250.0})
+    if pk["fp8_tflops"]:
+        pk["fp8_used"], pk["fp8_used_source"] = pk["fp8_tflops"], "measured library FP8 GEMM, burst (this run)"
+    else:
+        pk["fp8_used"], pk["fp8_used_source"] = 2.0 * bf16, f"2 x {src} bf16 burst (no FP8 library GEMM measured)"
+    return pk
 
 
 class ClockSampler:
@@ -119,21 +183,52 @@ def dist_env():
     return rank, world, local
 
 
-def cpu_port_time(rows: int, repeats: int = 1) -> tuple[float, int]:
-    """Seconds for the CPU port to fake-quantize `rows` rows of the workload; uses every host thread."""
-    from mase_b200 import synthetic
-    from oracle import mx_oracle as O
+def cpu_quantizers():
+    """The CPU implementation that is timed beside the GPU numbers: MASE's own `chop.nn.quantizers` when it has been
+    staged into oracle/_ref (kind "reference"), else the restatement in oracle/mx_oracle.py (kind "port").
+    Returns ({"mxfp": f(x, block, E, F), "mxint": f(x, block, bits)}, kind); both quantize along the last dim."""
+    try:
+        from oracle import stage_reference
 
+        q = stage_reference.import_staged_quantizers()
+        return {"mxfp": lambda x, block, e, f: q.mxfp_quantizer(x, block, e, f),
+                "mxint": lambda x, block, bits: q.mxint_quantizer(x, block, bits)}, "reference"
+    except Exception:
+        from oracle import mx_oracle as O
+
+        return {"mxfp": lambda x, block, e, f: O.mxfp_fake(x, block, e, f),
+                "mxint": lambda x, block, bits: O.mxint_fake(x, block, bits)}, "port"
+
+
+def cpu_quantizer_time(rows: int, repeats: int = 1) -> tuple[float, int, str]:
+    """Seconds for the CPU implementation to fake-quantize `rows` rows of the workload; uses every host thread."""
+    from mase_b200 import synthetic
+
+    qs, kind = cpu_quantizers()
+    fake = qs["mxfp"]
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     x = synthetic.student_t3(rows, COLS, seed=1)
-    O.mxfp_fake(x[:64], BLOCK, EXP_BITS, FRAC_BITS)  # warm-up
+    fake(x[:64], BLOCK, EXP_BITS, FRAC_BITS)  # warm-up
     best = float("inf")
     for _ in range(repeats):
         t0 = time.perf_counter()
-        O.mxfp_fake(x, BLOCK, EXP_BITS, FRAC_BITS)
+        fake(x, BLOCK, EXP_BITS, FRAC_BITS)
         best = min(best, time.perf_counter() - t0)
-    return best, torch.get_num_threads()
+    return best, torch.get_num_threads(), kind
+
+
+def cpu_linear_time(x: torch.Tensor, wq: torch.Tensor, e: int = 4, f: int = 3) -> tuple[float, str]:
+    """Seconds for the CPU forward of an MX Linear on the rows of `x` the way MASE runs it
+    (chop/nn/quantized/modules/linear.py:877-895): MXFP-quantize x along K, then `F.linear` in x.dtype against the
+    weight that was quantized at load time."""
+    qs, kind = cpu_quantizers()
+    fake = qs["mxfp"]
+    torch.set_num_threads(os.cpu_count() or 1)
+    torch.nn.functional.linear(fake(x[:8], 32, e, f), wq)  # warm-up
+    t0 = time.perf_counter()
+    torch.nn.functional.linear(fake(x, 32, e, f), wq)
+    return time.perf_counter() - t0, kind
 
 
 def run_reference(args) -> None:
@@ -142,25 +237,26 @@ def run_reference(args) -> None:
     if rank != 0:
         return
     from mase_b200 import synthetic
-    from oracle import mx_oracle as O
 
+    qs, kind = cpu_quantizers()
+    fake = qs["mxfp"]
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     x = synthetic.student_t3(CPU_SAMPLE_ROWS, COLS, seed=1)
     for _ in range(args.warmup):
-        O.mxfp_fake(x[:256], BLOCK, EXP_BITS, FRAC_BITS)
+        fake(x[:256], BLOCK, EXP_BITS, FRAC_BITS)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        O.mxfp_fake(x, BLOCK, EXP_BITS, FRAC_BITS)
+        fake(x, BLOCK, EXP_BITS, FRAC_BITS)
     dt = (time.perf_counter() - t0) / args.steps
     gbs = CPU_SAMPLE_ROWS * COLS * BYTES_PER_ELEM / dt / 1e9
-    sample = f"{CPU_SAMPLE_ROWS} of {ROWS} rows per step"
+    sample = f"{CPU_SAMPLE_ROWS} of {ROWS} rows per step (one GPU's tensor; not multiplied by the number of GPUs)"
     print(json.dumps({
         "impl": "reference", "metric": "mx_quant_dequant_GBps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": kind, "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -206,7 +302,7 @@ def quick_gbs(fn, bytes_per_call: int, calls: int = 10) -> float:
     return bytes_per_call * calls / (s.elapsed_time(e) / 1e3) / 1e9
 
 
-def extras(device, x) -> dict:
+def extras(device, x, peaks: dict) -> dict:
     """Other rows of the sweep, measured after the timed region (not part of `value`)."""
     import mase_b200 as mb
     from mase_b200 import synthetic
@@ -240,12 +336,12 @@ def extras(device, x) -> dict:
         xx = synthetic.student_t3(*shape, seed=1).to(device)
         g = quick_gbs(lambda: mb.mxfp_quantizer(xx, 32, 4, 3), xx.numel() * 4, calls=50)
         out[f"mxfp8_bf16_{shape[0]}x{shape[1]}_us"] = xx.numel() * 4 / g / 1e3
-    out["linear_mxfp8_4096x4096"] = linear_extras(device)
-    out["decoder_layer_mixed_precision"] = decoder_layer_extras(device)
+    out["linear_mxfp8_4096x4096"] = linear_extras(device, peaks)
+    out["decoder_layer_mixed_precision"] = decoder_layer_extras(device, peaks)
     return out
 
 
-def decoder_layer_extras(device) -> dict:
+def decoder_layer_extras(device, peaks: dict) -> dict:
     """Llama-style decoder layer, hidden 4096, 32 heads, FFN 11008, batch 8 x sequence 512 (4096 tokens), bf16:
     q/k/v/o MXINT8 weights and activations (exact bf16 tensor-core GEMM of the quantized values), gate/up/down MXFP4
     weights x MXFP8 activations (block-scaled GEMM); norms, RoPE, attention and SiLU unquantized."""
@@ -259,31 +355,61 @@ def decoder_layer_extras(device) -> dict:
         lambda k, n: mb.LinearMXFP(k, n, bias=False, device=device, dtype=torch.bfloat16,
                                    config=dict(synthetic.MXFP4W_MXFP8A_LINEAR)))
     g = torch.Generator().manual_seed(3)
-    x = torch.randn(8, 512, 4096, generator=g).bfloat16().to(device)
+    tokens = 8 * 512
+    x = torch.randn(8, 512, 4096, generator=g).bfloat16()
+    xd = x.to(device)
     with torch.no_grad():
-        t = 1.0 / quick_gbs(lambda: layer(x), 1, calls=10) / 1e9
+        t = 1.0 / quick_gbs(lambda: layer(xd), 1, calls=10) / 1e9
     gemm.check_status(device)
-    flops = layer.linear_flops(8 * 512)
-    return {"ms_per_forward": t * 1e3, "linear_TFLOPs": flops / t / 1e12, "tokens": 8 * 512,
-            "linear_flops": flops}
+    flops = layer.linear_flops(tokens)
+    flops_int = 2.0 * tokens * 4 * layer.hidden * layer.hidden   # q/k/v/o on the bf16 kind
+    flops_ffn = flops - flops_int                                 # gate/up/down at the FP8 rate
+    t_ideal = flops_int / (peaks["bf16_tflops"] * 1e12) + flops_ffn / (peaks["fp8_used"] * 1e12)
+    # CPU: the seven projections of the layer the way MASE runs them (quantize the input, F.linear in bf16) on a
+    # sample of the tokens; norms, RoPE and attention are left out on both sides of this ratio
+    qs, kind = cpu_quantizers()
+    sample = 64
+    xs = x.view(-1, 4096)[:sample]
+    hs = torch.randn(sample, layer.ffn, generator=g).bfloat16()
+    weights = {n: getattr(layer, n).weight.data.cpu() for n in synthetic.DecoderLayer.ATTENTION + synthetic.DecoderLayer.FFN}
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    for n in synthetic.DecoderLayer.ATTENTION:
+        torch.nn.functional.linear(qs["mxint"](xs, 32, 8), weights[n])
+    for n in ("gate_proj", "up_proj"):
+        torch.nn.functional.linear(qs["mxfp"](xs, 32, 4, 3), weights[n])
+    torch.nn.functional.linear(qs["mxfp"](hs, 32, 4, 3), weights["down_proj"])
+    t_cpu = time.perf_counter() - t0
+    return {"ms_per_forward": t * 1e3, "linear_TFLOPs": flops / t / 1e12, "tokens": tokens, "linear_flops": flops,
+            "roofline": {"bound": "tensor", "achieved": flops / t / 1e12, "peak": flops / t_ideal / 1e12,
+                         "unit": "TFLOP/s", "frac": t_ideal / t,
+                         "peak_source": "Linear FLOPs at their rates: q/k/v/o at the measured bf16 peak, gate/up/down at "
+                                        + peaks["fp8_used_source"] + "; attention, norms and RoPE count as overhead"},
+            "cpu_baseline": {"value": layer.linear_flops(sample) / t_cpu / 1e12, "unit": "TFLOP/s",
+                             "cores": torch.get_num_threads(), "kind": kind,
+                             "sample": f"the 7 projections (quantize input + bf16 F.linear) on {sample} of {tokens} tokens"}}
 
 
-def linear_extras(device) -> dict:
-    """MXFP8 Linear forward 4096 -> 4096 (bf16, no bias): activation quantization + block-scaled tcgen05 GEMM."""
+def linear_extras(device, peaks: dict) -> dict:
+    """MXFP8 Linear forward 4096 -> 4096 (bf16, no bias): activation quantization + block-scaled tcgen05 GEMM.
+    Each M carries its roofline (HBM-bound up to M = 128, tensor-bound above) and the CPU forward timed beside it."""
     import mase_b200 as mb
     from mase_b200 import gemm, synthetic
 
     K = N = 4096
     cfg = {"weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3,
            "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    hbm, hbm_kind = measured_peaks()
     out = {}
     layer = None
     for M in (1, 16, 128, 2048, 8192):
         x, w = synthetic.linear_operands(M, K, N, seed=2)
+        xh = x
         x = x.to(device)
         if layer is None:
             layer = mb.LinearMXFP(K, N, bias=False, device=device, dtype=torch.bfloat16, config=cfg)
             layer.load_state_dict({"weight": w.to(device)}, strict=False)
+            wq_cpu = layer.weight.data.cpu()
         flops = 2.0 * M * N * K
         calls = 20 if M >= 2048 else 50
         t_fwd = 1.0 / quick_gbs(lambda: layer(x), 1, calls=calls) / 1e9   # seconds per call
@@ -298,20 +424,47 @@ def linear_extras(device) -> dict:
             layer(x)
         t_graph = 1.0 / quick_gbs(graph.replay, 1, calls=calls) / 1e9
         del graph
+        if M <= 128:
+            algo = N * K * (1 + 1 / 32) + M * K * 2 + M * N * 2
+            roof = {"bound": "hbm", "achieved": algo / t_graph / 1e9, "peak": hbm, "unit": "GB/s",
+                    "frac": algo / t_graph / 1e9 / hbm, "gemm_only_frac": algo / t_gemm / 1e9 / hbm,
+                    "peak_source": f"{hbm_kind} copy bandwidth", "algorithmic_bytes": algo,
+                    "timed": "whole forward (activation pack + GEMM) replayed from a CUDA graph"}
+        else:
+            ach = flops / t_graph / 1e12
+            roof = {"bound": "tensor", "achieved": ach, "peak": peaks["fp8_used"], "unit": "TFLOP/s",
+                    "frac": ach / peaks["fp8_used"], "gemm_only_frac": flops / t_gemm / 1e12 / peaks["fp8_used"],
+                    "peak_source": peaks["fp8_used_source"],
+                    "frac_of_2x_measured_bf16": ach / (2 * peaks["bf16_tflops"]),
+                    "frac_of_nominal_4500": ach / peaks["fp8_nominal_tflops"],
+                    "timed": "whole forward (activation pack + GEMM) replayed from a CUDA graph"}
+        sample = min(M, 256)
+        t_cpu, kind = cpu_linear_time(xh[:sample], wq_cpu)
         out[f"M{M}"] = {"forward_us": t_fwd * 1e6, "forward_TFLOPs": flops / t_fwd / 1e12,
                         "forward_cuda_graph_us": t_graph * 1e6, "forward_cuda_graph_TFLOPs": flops / t_graph / 1e12,
                         "gemm_only_us": t_gemm * 1e6, "gemm_only_TFLOPs": flops / t_gemm / 1e12,
-                        "bf16_gemm_of_fake_quant_us": t_dense * 1e6, "bf16_gemm_TFLOPs": flops / t_dense / 1e12}
+                        "bf16_gemm_of_fake_quant_us": t_dense * 1e6, "bf16_gemm_TFLOPs": flops / t_dense / 1e12,
+                        "roofline": roof,
+                        "cpu_baseline": {"value": 2.0 * sample * N * K / t_cpu / 1e12, "unit": "TFLOP/s",
+                                         "cores": torch.get_num_threads(), "kind": kind,
+                                         "sample": f"{sample} of {M} rows: MXFP8-quantize x, F.linear in bf16"}}
     gemm.check_status()
     return out
 
 
-def tp_stack_extras(device, rank: int, world: int) -> dict:
+def oracle_quantize_weight(w: torch.Tensor, e: int, f: int, rows_per_chunk: int = 2048) -> torch.Tensor:
+    """MXFP fake-quantization of a [N, K] weight along K with the CPU oracle, in row chunks (bounded host memory)."""
+    from oracle import mx_oracle as O
+
+    return torch.cat([O.mxfp_fake(w[r:r + rows_per_chunk], 32, e, f, 1) for r in range(0, w.shape[0], rows_per_chunk)])
+
+
+def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
     """Tensor-parallel Linear stack at the 70B shape: hidden 8192, FFN 28672, 4 gated-MLP layers, M = 8192 tokens,
     MXFP4 (E2M1) weights / MXFP8 (E4M3) activations, gate/up column parallel, down row parallel with an fp32
-    all-reduce.  Strong scaling (total work fixed); every rank runs it."""
-    import torch.distributed as dist
-
+    reduction.  Strong scaling (total work fixed); every rank runs it.  Outside the timed region rank 0 recomputes a
+    few output rows of the first layer on the CPU with the oracle (weights regenerated from the seed and quantized by
+    the oracle) and reports the largest deviation, so the multi-GPU result is checked in the run that times it."""
     import mase_b200 as mb
     from mase_b200 import gemm, tp as tpmod
 
@@ -322,18 +475,16 @@ def tp_stack_extras(device, rank: int, world: int) -> dict:
     gen = torch.Generator(device=device).manual_seed(4)
     stack = []
     for _ in range(layers):
-        mods = []
-        for (n, k, mode) in ((ffn, hidden, "column"), (ffn, hidden, "column"), (hidden, ffn, "row")):
-            # every rank draws the same full weight (same seed) and keeps its shard
-            w = (torch.randn(n, k, generator=gen, device=device) * 0.02).to(torch.bfloat16)
-            kw = {"reduce": "scatter_gather"} if mode == "row" else {}
-            mods.append(tpmod.build_tp_linear(mb.LinearMXFP, w, None, cfg, mode, tp, device=device, **kw))
-            del w
-        stack.append(tpmod.TPGatedMLP(*mods))
+        # every rank draws the same full weights (same seed) and keeps its shards
+        ws = [(torch.randn(n, k, generator=gen, device=device) * 0.02).to(torch.bfloat16)
+              for (n, k) in ((ffn, hidden), (ffn, hidden), (hidden, ffn))]
+        stack.append(tpmod.build_tp_gated_mlp(mb.LinearMXFP, ws[0], ws[1], ws[2], cfg, tp, device=device,
+                                              reduce="scatter_gather"))
+        del ws
     x0 = torch.randn(M, hidden, generator=gen, device=device).to(torch.bfloat16)
 
     results = {}
-    for micro in ((1,) if world == 1 else (1, 2)):
+    for micro in ((1,) if world == 1 else (1, 2, 4)):
         def step():
             return tpmod.run_mlp_stack(stack, x0, micro_batches=micro)
 
@@ -344,13 +495,57 @@ def tp_stack_extras(device, rank: int, world: int) -> dict:
     gemm.check_status()
     micro, sec_step = min(results.items(), key=lambda kv: kv[1])
     flops = layers * 3 * 2.0 * M * hidden * ffn
-    del stack
+
+    # ---- parity of layer 1 against the oracle (all ranks run the layer; rank 0 checks) ----
+    y1 = stack[0](x0)
+    gemm.check_status()
+    parity = cpu = None
+    if rank == 0:
+        from oracle import mx_oracle as O
+
+        rows = torch.tensor([0, 1171, 4097, M - 1])
+        g1 = torch.Generator(device=device).manual_seed(4)
+        wq = []
+        for (n, k) in ((ffn, hidden), (ffn, hidden), (hidden, ffn)):
+            w = (torch.randn(n, k, generator=g1, device=device) * 0.02).to(torch.bfloat16).cpu()
+            wq.append(oracle_quantize_weight(w, 2, 1))
+            del w
+        xs = x0[rows.to(device)].cpu()
+        xq = O.mxfp_fake(xs, 32, 4, 3).float()
+        gate = (xq @ wq[0].float().t()).bfloat16()
+        up = (xq @ wq[1].float().t()).bfloat16()
+        h = torch.nn.functional.silu(gate) * up
+        ref = O.mxfp_fake(h, 32, 4, 3).float() @ wq[2].float().t()
+        got = y1[rows.to(device)].float().cpu()
+        parity = float((got - ref).abs().max() / ref.abs().max())
+        # CPU baseline: one layer the way MASE's modules run it (quantize, F.linear in bf16) on a sample of the rows
+        qs, kind = cpu_quantizers()
+        sample = 64
+        xc = x0[:sample].cpu()
+        torch.set_num_threads(os.cpu_count() or 1)
+        t0 = time.perf_counter()
+        xq16 = qs["mxfp"](xc, 32, 4, 3)
+        hc = torch.nn.functional.silu(torch.nn.functional.linear(xq16, wq[0])) * torch.nn.functional.linear(xq16, wq[1])
+        torch.nn.functional.linear(qs["mxfp"](hc, 32, 4, 3), wq[2])
+        t_cpu = time.perf_counter() - t0
+        cpu = {"value": 3 * 2.0 * sample * hidden * ffn / t_cpu / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+               "kind": kind, "sample": f"one layer (gate, up, SiLU*mul, down) on {sample} of {M} rows, unsharded"}
+        del wq
+    del stack, y1
     torch.cuda.empty_cache()
-    return {"config": "4 x (gate, up: 8192->28672 column; down: 28672->8192 row + all-reduce), M=8192, W E2M1 / A E4M3",
-            "ms_per_step": sec_step * 1e3, "TFLOPs_aggregate": flops / sec_step / 1e12, "n_gpus": world,
+    ach = flops / sec_step / 1e12
+    return {"config": "4 x (gate+up: 8192->2x28672 column; down: 28672->8192 row + fp32 reduction), M=8192, W E2M1 / A E4M3",
+            "ms_per_step": sec_step * 1e3, "TFLOPs_aggregate": ach, "n_gpus": world,
             "scaling": "strong", "micro_batches": micro,
             "ms_per_step_by_micro_batches": {str(k): v * 1e3 for k, v in results.items()},
-            "reduction": "fp32 reduce-scatter + bf16 all-gather on a side stream"}
+            "reduction": "fp32 reduce-scatter + bf16 all-gather on a side stream",
+            "parity_max_rel_err": parity,
+            "parity_check": "layer 1, rows 0/1171/4097/8191, against the CPU oracle (bf16 roundings of gate, up and "
+                            "SiLU*mul as torch does them)",
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": world * peaks["fp8_used"], "unit": "TFLOP/s",
+                         "frac": ach / (world * peaks["fp8_used"]),
+                         "peak_source": f"{world} x " + peaks["fp8_used_source"]},
+            "cpu_baseline": cpu}
 
 
 def run_ours(args) -> None:
@@ -421,6 +616,10 @@ def run_ours(args) -> None:
     e2e_sec = time_region(e2e_step, e2e_steps, world, device)
     e2e_value = world * step_bytes * e2e_steps / e2e_sec / 1e9
     ok = torch.equal(hy[:rows_c].view(torch.int16), state["y"][:rows_c].cpu().view(torch.int16))
+    from oracle import mx_oracle as O  # checker only, outside every timed region
+
+    probe = torch.arange(0, ROWS, max(1, ROWS // 16))[:16]
+    ok_oracle = torch.equal(hy[probe].view(torch.int16), O.mxfp_fake(hx[probe], BLOCK, EXP_BITS, FRAC_BITS).view(torch.int16))
     clocks = sampler.stop()
     del hx, hy, dbuf
     tp_extra = None
@@ -428,7 +627,8 @@ def run_ours(args) -> None:
         state.clear()
         del x
         torch.cuda.empty_cache()
-        tp_extra = tp_stack_extras(device, rank, world)
+        peaks = tensor_peaks(device)
+        tp_extra = tp_stack_extras(device, rank, world, peaks)
         x = synthetic.device_student_t3(ROWS, COLS, seed=1 + rank, device=device)
 
     if rank == 0:
@@ -437,19 +637,31 @@ def run_ours(args) -> None:
                 "peak_source": f"{peak_kind} copy bandwidth", "kernel": "mxq::mxfp_kernel<bf16,bf16,fake,E4M3>",
                 "algorithmic_bytes_per_launch": step_bytes,
                 "traffic": None if NCU_DRAM_BYTES_PER_ELEM is None else NCU_DRAM_BYTES_PER_ELEM * n}
-        cpu_sec, cores = cpu_port_time(CPU_SAMPLE_ROWS)
+        cpu_sec, cores, cpu_kind = cpu_quantizer_time(CPU_SAMPLE_ROWS)
         cpu = {"value": CPU_SAMPLE_ROWS * COLS * BYTES_PER_ELEM / cpu_sec / 1e9, "unit": "GB/s", "cores": cores,
-               "kind": "port", "sample": f"{CPU_SAMPLE_ROWS} of {ROWS} rows, one pass"}
-        extra = extras(device, x) if not args.no_extra else {}
+               "kind": cpu_kind, "sample": f"{CPU_SAMPLE_ROWS} of {ROWS} rows, one pass"}
+        extra = extras(device, x, peaks) if not args.no_extra else {}
         if tp_extra is not None:
             extra["tp_linear_stack_70b_shape"] = tp_extra
+        if extra:
+            # the MX-Linear half of the metric, inside the objects of the bench contract
+            lin = extra["linear_mxfp8_4096x4096"]
+            roof["peaks"] = peaks
+            roof["mx_linear"] = {m: v["roofline"] for m, v in lin.items()}
+            roof["decoder_layer"] = extra["decoder_layer_mixed_precision"]["roofline"]
+            roof["tp_linear_stack"] = dict(tp_extra["roofline"], ms_per_step=tp_extra["ms_per_step"],
+                                           parity_max_rel_err=tp_extra["parity_max_rel_err"])
+            cpu["mx_linear"] = {m: v["cpu_baseline"] for m, v in lin.items()}
+            cpu["decoder_layer"] = extra["decoder_layer_mixed_precision"]["cpu_baseline"]
+            cpu["tp_linear_stack"] = tp_extra["cpu_baseline"]
         print(json.dumps({
             "metric": "mx_quant_dequant_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world),
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": n * 2, "d2h_bytes_per_step": n * 2,
-                    "steps": e2e_steps, "result_matches_device_path": bool(ok)},
+                    "steps": e2e_steps, "result_matches_device_path": bool(ok),
+                    "result_rows_match_cpu_oracle": bool(ok_oracle)},
             "gpu_launches": args.steps, "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "extra": extra,
         }))
     if world > 1:

@@ -79,8 +79,11 @@ class ColumnParallelLinear(nn.Module):
     """Output features split over the ranks.  `inner` is a quantized Linear of shape [N/G, K] (any module mapping
     [..., K] -> [..., N/G]); the input is replicated, the output stays sharded unless `gather_output`."""
 
-    def __init__(self, inner: nn.Module, tp: TPGroup, gather_output: bool = False):
+    def __init__(self, inner: nn.Module, tp: TPGroup, gather_output: bool = False, out_features: int | None = None):
         super().__init__()
+        if gather_output and out_features is not None and out_features % tp.world:
+            raise ValueError(f"gather_output needs out_features ({out_features}) divisible by the {tp.world} ranks: "
+                             "all-gather takes equal shards")
         self.inner, self.tp, self.gather_output = inner, tp, gather_output
 
     def forward(self, x: Tensor) -> Tensor:
@@ -184,7 +187,7 @@ def build_tp_linear(cls, weight: Tensor, bias: Tensor | None, config: dict, mode
         if b is not None:
             state["bias"] = b.to(device=device, dtype=dtype)
         inner.load_state_dict(state, strict=False)
-        return ColumnParallelLinear(inner, tp, **kwargs)
+        return ColumnParallelLinear(inner, tp, out_features=weight.shape[0], **kwargs)
     inner = cls(k_local, n_local, bias=False, device=device, dtype=dtype, config=dict(config))
     inner.load_state_dict({"weight": w.to(device=device, dtype=dtype)}, strict=False)
     return RowParallelLinear(inner, tp, None if bias is None else bias.to(device=device, dtype=dtype), **kwargs)
@@ -193,17 +196,39 @@ def build_tp_linear(cls, weight: Tensor, bias: Tensor | None, config: dict, mode
 
 
 class TPGatedMLP(nn.Module):
-    """y = down(silu(gate(x)) * up(x)) with gate/up column parallel and down row parallel: one reduction per layer."""
+    """y = down(silu(gate(x)) * up(x)) with gate/up column parallel and down row parallel: one reduction per layer.
 
-    def __init__(self, gate: nn.Module, up: nn.Module, down: nn.Module):
+    With `gate_up` the two column-parallel projections are one layer whose local weight stacks this rank's gate rows
+    on top of its up rows (`[2 * ffn / G, K]`): x is quantized once and one GEMM produces both halves."""
+
+    def __init__(self, gate: nn.Module | None, up: nn.Module | None, down: nn.Module, gate_up: nn.Module | None = None):
         super().__init__()
-        self.gate, self.up, self.down = gate, up, down
+        assert (gate_up is None) != (gate is None and up is None), "pass gate and up, or gate_up"
+        self.gate, self.up, self.down, self.gate_up = gate, up, down, gate_up
 
     def hidden(self, x: Tensor) -> Tensor:
-        return torch.nn.functional.silu(self.gate(x)) * self.up(x)
+        if self.gate_up is None:
+            return torch.nn.functional.silu(self.gate(x)) * self.up(x)
+        gu = self.gate_up(x)
+        half = gu.shape[-1] // 2
+        return torch.nn.functional.silu(gu[..., :half]) * gu[..., half:]
 
     def forward(self, x: Tensor) -> Tensor:
         return self.down(self.hidden(x))
+
+
+def build_tp_gated_mlp(cls, w_gate: Tensor, w_up: Tensor, w_down: Tensor, config: dict, tp: TPGroup, device=None,
+                       dtype=None, reduce: str = "all_reduce") -> TPGatedMLP:
+    """Shard the three weights of a gated MLP for this rank: gate and up rows are cut the same way and stacked into
+    one column-parallel layer, down is row parallel.  MX blocks run along K, so stacking rows changes no block."""
+    if w_gate.shape != w_up.shape:
+        raise ValueError("gate and up must have the same shape")
+    local = torch.cat([shard_linear_weight(w_gate, "column", tp), shard_linear_weight(w_up, "column", tp)], dim=0)
+    fused_tp = TPGroup(0, 1, None)  # the stacked weight is already this rank's shard
+    gate_up = build_tp_linear(cls, local, None, config, "column", fused_tp, device=device, dtype=dtype)
+    del local
+    down = build_tp_linear(cls, w_down, None, config, "row", tp, device=device, dtype=dtype, reduce=reduce)
+    return TPGatedMLP(None, None, down, gate_up=gate_up)
 
 
 def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, comm_sms: int = 32) -> Tensor:
