@@ -136,7 +136,8 @@ typedef struct mxq_gemm_options {
    * The schemes accumulate in the same order: results are bit-identical. */
   int32_t tiles;
   /* Small problems (at most 128 rows): K is split over the CTAs of a thread-block cluster, which hand their fp32
-   * partial sums over through distributed shared memory in a fixed order.  0 = let the library decide, 1 = never. */
+   * partial sums over through distributed shared memory in a fixed order (repeatable results).  0 = let the library
+   * decide, 1 = never. */
   int32_t no_split_k;
   /* mxq_mx_linear only.  0: for large problems the block-scaled GEMM starts while the activation pack is still
    * running and waits, 128-row panel by panel, for the rows it is about to load; 1: pack first, then multiply. */
@@ -148,7 +149,10 @@ typedef struct mxq_gemm_options {
    * the MMA issuer runs out and the error path above is taken (no fault is involved; the output is left incomplete
    * and the status word reads 2).  Leave 0 otherwise. */
   int32_t test_hook;
-  int32_t reserved;
+  /* Problems of at most 128 rows run a transposed kernel: the weight is the 128-row operand of the MMA, the few
+   * activation rows are its narrow one, and K is split over a cluster of up to 8 CTAs.  1 = use the regular tiles
+   * instead (for comparisons). */
+  int32_t no_transposed;
 } mxq_gemm_options;
 
 #define MXQ_TILES_AUTO 0

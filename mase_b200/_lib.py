@@ -45,7 +45,7 @@ class GemmOptions(ctypes.Structure):
 
     _fields_ = [("max_ctas", ctypes.c_int32), ("tiles", ctypes.c_int32), ("no_split_k", ctypes.c_int32),
                 ("no_overlap", ctypes.c_int32), ("wait_limit_ns", ctypes.c_int64), ("test_hook", ctypes.c_int32),
-                ("reserved", ctypes.c_int32)]
+                ("no_transposed", ctypes.c_int32)]
 
 
 TILES_AUTO, TILES_SINGLE, TILES_PAIRS = 0, 1, 2

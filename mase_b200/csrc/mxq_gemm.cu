@@ -977,6 +977,271 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   }
 }
 
+// =====================================================================================================================
+// Few rows of activations against a large weight (M <= 128): the transposed product D^T[N, M] = W[N, K] X[M, K]^T.
+//
+// Such a problem is the latency of streaming the weight once.  Here the weight is the 128-row operand of the MMA and
+// the activations are its narrow one (16, 32, 64 or 128 columns of the accumulator), so one instruction covers 128
+// weight rows with a short pass through the tensor pipe, and a CTA's 128-row stripe of the weight is fetched by a
+// producer that never waits for the activations: its weight and weight-scale loads are issued before the dependency
+// wait on the previous kernel of the stream (the activation pack), the activation loads behind it, into a ring deep
+// enough to hold a CTA's whole share of K for the common shapes.  K is split over the 1, 2, 4 or 8 CTAs of a
+// thread-block cluster so that about every SM pulls on the weight; the CTAs park their fp32 partial sums in their own
+// shared memory and the first CTA adds them in rank order through distributed shared memory (repeatable), adds the
+// bias and stores D transposed back: lane = weight row, so a warp writes 32 consecutive elements of one output row.
+// =====================================================================================================================
+constexpr int kSwapMaxStages = 12;
+
+template <int BNX, bool kScaled>
+struct SwapLayout {
+  static constexpr int kW = BM * kRowBytes;   // 128 weight rows
+  static constexpr int kX = BNX * kRowBytes;  // activation rows (the ones past M are never stored)
+  static constexpr int kWX = kW + kX;
+  static constexpr int kSf = kScaled ? 1024 : 0;  // weight chunk, activation chunk
+  static constexpr int kBudget = 200 * 1024;
+  static constexpr int kFit = kBudget / (kWX + kSf);
+  static constexpr int kStages = kFit < 10 ? kFit : 10;
+  static constexpr int kSfBase = kStages * kWX;
+  static constexpr int kRing = (kStages * (kWX + kSf) + 1023) & ~1023;
+  static constexpr int kXbuf = 0;  // partial sums reuse the ring once the MMAs are done (BNX x 128 fp32 <= 64 KB)
+  static constexpr int kBarriers = kRing;  // full[], empty[], acc_full
+  static constexpr int kTotal = kBarriers + (2 * kSwapMaxStages + 2) * 8 + 16 + 1024;
+  static_assert(BNX * BM * 4 <= kRing, "exchange buffer must fit in the ring");
+};
+
+struct SwapParams {
+  void *d;
+  const void *bias;
+  int *status;
+  int M, N;
+  int k_chunks;
+  int split;         // CTAs per cluster = shares of K
+  int x_box_bytes;   // bytes one activation load delivers
+  int out_bf16, bias_bf16;
+  unsigned long long wait_ns;
+};
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                    "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :: "memory");
+}
+
+template <int kKind, int BNX>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                      const __grid_constant__ CUtensorMap map_sfw, const __grid_constant__ CUtensorMap map_sfx,
+                      const SwapParams p) {
+  constexpr bool kScaled = kKind == kMxf8;
+  using L = SwapLayout<BNX, kScaled>;
+  constexpr int kStages = L::kStages;
+  constexpr int kElem = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
+  constexpr int kBlockK = kRowBytes / kElem;
+  constexpr int kSfCol = 128;          // scale factors behind the (at most 128) accumulator columns
+  constexpr int kSwapTmemCols = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t bar_base = s_base + L::kBarriers;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kSwapMaxStages + s); };
+  const uint32_t acc_full = bar_base + 8u * (2 * kSwapMaxStages);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kBarriers + (2 * kSwapMaxStages + 2) * 8);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::kBarriers + (2 * kSwapMaxStages + 2) * 8 + 8);
+
+  const int warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
+  const int rank = p.split > 1 ? (int)cluster_rank() : 0;
+  const int n_blk = (int)blockIdx.x / p.split;        // 128-row stripe of the weight
+  // this CTA's share of the K chunks: the first `rem` ranks take one more
+  const int base = p.k_chunks / p.split, rem = p.k_chunks % p.split;
+  const int kc_begin = rank * base + (rank < rem ? rank : rem);
+  const int kc_count = base + (rank < rem ? 1 : 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), 1), mbar_init(empty_bar(s), 1);
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kSwapTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (elect_one()) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      if constexpr (kScaled) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfw) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfx) : "memory");
+      }
+    }
+    const int row_w = n_blk * BM;
+    const uint32_t stage_tx = (uint32_t)(L::kW + L::kSf) + (uint32_t)p.x_box_bytes;
+    // the weight does not depend on the previous kernel of the stream: fill the ring's first pass with it now
+    const int first_pass = kc_count < kStages ? kc_count : kStages;
+    for (int i = 0; i < first_pass; ++i) {
+      if (elect_one()) {
+        const int kc = kc_begin + i;
+        mbar_expect_tx(full_bar(i), stage_tx);
+        tma_load_2d(s_base + i * L::kWX, &map_w, full_bar(i), kc * kBlockK, row_w);
+        if constexpr (kScaled) tma_load_2d(s_base + L::kSfBase + i * L::kSf, &map_sfw, full_bar(i), 0, n_blk * p.k_chunks + kc);
+      }
+    }
+    grid_dependency_wait();  // the activations (and their scales) come from the previous kernel
+    for (int i = 0; i < first_pass; ++i) {
+      if (elect_one()) {
+        const int kc = kc_begin + i;
+        tma_load_2d(s_base + i * L::kWX + L::kW, &map_x, full_bar(i), kc * kBlockK, 0);
+        if constexpr (kScaled) tma_load_2d(s_base + L::kSfBase + i * L::kSf + 512, &map_sfx, full_bar(i), 0, kc);
+      }
+    }
+    int issued = first_pass;
+    for (int i = first_pass; i < kc_count; ++i) {
+      const int s = i % kStages;
+      if (!mbar_wait_warp(empty_bar(s), (uint32_t)(i / kStages - 1) & 1u, abort_flag, p.status, kErrProducerWait, p.wait_ns))
+        break;
+      if (elect_one()) {
+        const int kc = kc_begin + i;
+        mbar_expect_tx(full_bar(s), stage_tx);
+        tma_load_2d(s_base + s * L::kWX, &map_w, full_bar(s), kc * kBlockK, row_w);
+        tma_load_2d(s_base + s * L::kWX + L::kW, &map_x, full_bar(s), kc * kBlockK, 0);
+        if constexpr (kScaled) {
+          tma_load_2d(s_base + L::kSfBase + s * L::kSf, &map_sfw, full_bar(s), 0, n_blk * p.k_chunks + kc);
+          tma_load_2d(s_base + L::kSfBase + s * L::kSf + 512, &map_sfx, full_bar(s), 0, kc);
+        }
+      }
+      ++issued;
+    }
+    if (*abort_flag && lane == 0) {
+      // let the copies that were already issued land before the CTA gives up its shared memory
+      for (int s = 0; s < kStages && s < issued; ++s) {
+        const int last = (issued - 1 - s) / kStages;
+        const unsigned long long t0 = global_ns();
+        while (!mbar_try_wait(full_bar((issued - 1 - s) % kStages), (uint32_t)last & 1u) &&
+               global_ns() - t0 < 20000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    const uint32_t idesc = make_idesc<kKind, BNX>();
+    uint32_t idk[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) idk[k] = kScaled ? idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4) : idesc;
+    bool ok = true;
+    for (int i = 0; i < kc_count; ++i) {
+      const int s = i % kStages;
+      if (!mbar_wait_warp(full_bar(s), (uint32_t)(i / kStages) & 1u, abort_flag, p.status, kErrMmaWaitFull, p.wait_ns)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      if (elect_one()) {
+        const uint64_t dw = desc_sw128(s_base + s * L::kWX), dx = desc_sw128(s_base + s * L::kWX + L::kW);
+        const uint32_t sf_t = tmem_base + (uint32_t)(kSfCol + 8 * s);
+        if constexpr (kScaled) {
+          const uint64_t dsf = desc_sf(s_base + L::kSfBase + s * L::kSf);
+          tc_cp_sf(sf_t, dsf);
+          tc_cp_sf(sf_t + 4, dsf + 32u);  // 512 bytes on: the activations' chunk
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma<kKind>(tmem_base, dw + 2u * k, dx + 2u * k, idk[k], (i | k) ? 1u : 0u, sf_t, sf_t + 4);
+        tc_commit(empty_bar(s));
+      }
+    }
+    if (ok && elect_one()) tc_commit(acc_full);
+  }
+
+  // ---------------- epilogue (warps 2..5): TMEM lane = weight row ----------------
+  const int quarter = warp & 3;
+  const int row_in_tile = quarter * 32 + lane;
+  const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16);
+  float *xbuf = reinterpret_cast<float *>(smem + L::kXbuf);
+  bool have_acc = false;
+  if (warp >= 2) {
+    have_acc = mbar_wait_warp(acc_full, 0u, abort_flag, p.status, kErrEpilogueWait, p.wait_ns);
+    tc_fence_after();
+    if (have_acc && rank != 0) {
+      // park this CTA's partial sums, column-major (element (row, col) at col * 128 + row: the 32 lanes of a warp, one
+      // row each, hit 32 different banks); the ring is free: acc_full says every MMA that read it has completed
+#pragma unroll
+      for (int c = 0; c < BNX; c += 16) {
+        uint32_t v[16];
+        tmem_ld16(t_acc + (uint32_t)c, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) xbuf[(c + j) * BM + row_in_tile] = __uint_as_float(v[j]);
+      }
+      tc_fence_before();
+    }
+  }
+  if (p.split > 1) cluster_sync();  // every thread of every CTA of the cluster
+  if (warp >= 2 && rank == 0 && have_acc) {
+    grid_dependency_wait();  // nothing of the previous kernel may still be reading D
+    const int n = n_blk * BM + row_in_tile;
+    float bias = 0.f;
+    if (p.bias != nullptr && n < p.N)
+      bias = p.bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.bias)[n])
+                         : reinterpret_cast<const float *>(p.bias)[n];
+    const uint32_t xoff = s_base + L::kXbuf + (uint32_t)row_in_tile * 4u;
+#pragma unroll
+    for (int c = 0; c < BNX; c += 16) {
+      if (c >= p.M) break;
+      uint32_t v[16];
+      tmem_ld16(t_acc + (uint32_t)c, v);
+      float f[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(v[j]);
+      for (int r = 1; r < p.split; ++r) {  // fixed order: repeatable sums
+        const uint32_t peer = map_to_cta(xoff, (uint32_t)r);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) f[j] += ld_cluster_f32(peer + (uint32_t)((c + j) * BM) * 4u);
+      }
+      if (n < p.N) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = c + j;
+          if (m < p.M) {
+            const size_t off = (size_t)m * p.N + n;
+            if (p.out_bf16)
+              reinterpret_cast<__nv_bfloat16 *>(p.d)[off] = __float2bfloat16_rn(f[j] + bias);
+            else
+              reinterpret_cast<float *>(p.d)[off] = f[j] + bias;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  if (p.split > 1) cluster_sync();  // the other CTAs keep their shared memory until the first one has read it
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kSwapTmemCols) : "memory");
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -1047,6 +1312,7 @@ Opts make_opts(const mxq_gemm_options *o) {
     r.tiles = o->tiles == MXQ_TILES_SINGLE || o->tiles == MXQ_TILES_PAIRS ? o->tiles : MXQ_TILES_AUTO;
     r.split_k = o->no_split_k == 0;
     r.overlap = o->no_overlap == 0;
+    r.transposed = o->no_transposed == 0;
     if (o->wait_limit_ns > 0) r.wait_ns = (unsigned long long)o->wait_limit_ns;
     r.test_hook = o->test_hook;
   }
@@ -1212,6 +1478,66 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
+// Transposed kernel for M <= 128 (see umma_gemm_swap_kernel): a = activations [M, K], b = weight [N, K].
+template <int kKind, int BNX>
+static int launch_swap(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
+                       int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, const Opts &o,
+                       cudaStream_t st) {
+  using L = SwapLayout<BNX, kKind == kMxf8>;
+  constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
+  const int64_t k_chunks = (K * es + kRowBytes - 1) / kRowBytes;
+  const int x_rows = (int)((M + 7) / 8 * 8) < BNX ? (int)((M + 7) / 8 * 8) : BNX;
+  CUtensorMap mw, mx, msw, msx;
+  int rc = make_map(&mw, b, kKind, N, K, BM);
+  if (rc) return rc;
+  rc = make_map(&mx, a, kKind, M, K, x_rows);
+  if (rc) return rc;
+  msw = mw, msx = mw;  // unused by the dense kinds
+  if constexpr (kKind == kMxf8) {
+    rc = make_sf_map(&msw, sfb, ((N + 255) / 256) * 2 * k_chunks);
+    if (rc) return rc;
+    rc = make_sf_map(&msx, sfa, ((M + 255) / 256) * 2 * k_chunks);
+    if (rc) return rc;
+  }
+  const int64_t tiles = (N + BM - 1) / BM;
+  const int sms = o.max_ctas > 0 && o.max_ctas < sm_count() ? o.max_ctas : sm_count();
+  // shares of K: as many CTAs as there are SMs, at least 4 chunks each, clusters of at most 8
+  int split = 1;
+  while (o.split_k && split < 8 && tiles * split * 2 <= sms && k_chunks / (split * 2) >= 4) split *= 2;
+  SwapParams p;
+  p.d = d, p.bias = bias, p.status = status, p.M = (int)M, p.N = (int)N, p.k_chunks = (int)k_chunks, p.split = split;
+  p.x_box_bytes = x_rows * kRowBytes;
+  p.out_bf16 = out_dtype == MXQ_BF16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.wait_ns = o.wait_ns;
+  static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
+  bool &attr_set = attr_done[current_device() & 63];
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(umma_gemm_swap_kernel<kKind, BNX>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
+        cudaSuccess)
+      return MXQ_ERR_LAUNCH;
+    attr_set = true;
+  }
+  const cudaError_t err = launch_dependent(umma_gemm_swap_kernel<kKind, BNX>, (int)(tiles * split), kThreads, L::kTotal, st,
+                                           split, mw, mx, msw, msx, p);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return MXQ_ERR_LAUNCH;
+  }
+  return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
+}
+
+template <int kKind>
+static int launch_swap_any(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
+                           int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, const Opts &o,
+                           cudaStream_t st) {
+#define MXQ_SWAP(bnx) \
+  return launch_swap<kKind, bnx>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st)
+  if (M <= 16) MXQ_SWAP(16);
+  if (M <= 32) MXQ_SWAP(32);
+  if (M <= 64) MXQ_SWAP(64);
+  MXQ_SWAP(128);
+#undef MXQ_SWAP
+}
+
 // Tile width: 256 columns when that already gives every SM a tile; narrower tiles for small problems (few rows of
 // activations against a large weight are bound by streaming the weight, which needs many SMs pulling at once).
 template <int kKind>
@@ -1220,6 +1546,12 @@ static int launch_any(const void *a, const void *b, const uint8_t *sfa, const ui
                       cudaStream_t st) {
   const int64_t tiles_m = (M + BM - 1) / BM;
   const int sms = sm_count();
+  if (M <= BM && o.transposed && o.test_hook == 0) {
+    // few rows: the weight streams through as the 128-row operand (a context that cannot place the clusters falls
+    // back to the tiles below)
+    const int rc = launch_swap_any<kKind>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st);
+    if (rc != MXQ_ERR_LAUNCH && rc != MXQ_ERR_UNSUPPORTED) return rc;
+  }
   const bool wide = tiles_m * ((N + 255) / 256) * 2 > sms || N <= 64;
   if (M > 128 && N > 128 && ((o.tiles == MXQ_TILES_AUTO && wide) || o.tiles == MXQ_TILES_PAIRS)) {
     // a context that cannot place clusters of two such CTAs falls back to one CTA per tile

@@ -18,6 +18,7 @@ struct Opts {
   int tiles = MXQ_TILES_AUTO;
   bool split_k = true;
   bool overlap = true;
+  bool transposed = true;  // problems of at most 128 rows go to the transposed (weight-major) kernel
   unsigned long long wait_ns = kDefaultWaitNs;
   int test_hook = 0;
   const uint32_t *panel_ready = nullptr;  // counters of the concurrent pack, one per 128-row panel of A

@@ -171,3 +171,33 @@ def test_split_k_over_a_cluster_matches_unsplit(shape):
     assert float((split1 - plain).abs().max() / plain.abs().max()) <= 1e-5
     assert rel_err(split_bf16, ref) <= 4e-3
     assert rel_err(dense_split, ref) <= 4e-3 and rel_err(dense_plain, ref) <= 4e-3
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (7, 1024, 1000), (16, 4096, 4096), (17, 160, 96), (32, 8192, 512),
+                                   (33, 4128, 1304), (64, 2048, 11008), (100, 512, 768), (128, 4096, 4096)])
+def test_transposed_small_m_kernel_vs_oracle_and_regular_tiles(shape):
+    """Problems of at most 128 rows run the transposed kernel (weight as the 128-row MMA operand, K split over a
+    cluster): against the oracle, against the regular tiles, repeatable, with bias, ragged N and K, both outputs, and
+    for the dense kinds on the fake-quantized tensors."""
+    M, K, N = shape
+    x, w = synthetic.linear_operands(M, K, N, seed=9)
+    g = torch.Generator().manual_seed(9)
+    b = torch.randn(N, generator=g).bfloat16().to(DEV)
+    xq, wq = O.mxfp_fake(x, 32, 4, 3), O.mxfp_fake(w, 32, 4, 3, 1)
+    ref = xq.float() @ wq.float().t() + b.float().cpu()
+    xp, wp = gemm.pack_mx_operand(x.to(DEV), 4, 3), gemm.pack_mx_operand(w.to(DEV), 4, 3)
+    y1 = gemm.mx_gemm(xp, wp, b, torch.float32)
+    y2 = gemm.mx_gemm(xp, wp, b, torch.float32)
+    y16 = gemm.mx_gemm(xp, wp, b, torch.bfloat16)
+    with gemm.options(no_split_k=1):
+        y_unsplit = gemm.mx_gemm(xp, wp, b, torch.float32)
+    with gemm.options(no_transposed=1):
+        y_tiles = gemm.mx_gemm(xp, wp, b, torch.float32)
+    d16 = gemm.linear_forward(xq.to(DEV), wq.to(DEV), b)
+    d32 = gemm.linear_forward(xq.float().to(DEV), wq.float().to(DEV), b.float())
+    gemm.check_status()
+    assert torch.equal(y1, y2)
+    assert rel_err(y1, ref) <= REL_TOL and rel_err(y_unsplit, ref) <= REL_TOL and rel_err(y_tiles, ref) <= REL_TOL
+    assert float((y1 - y_tiles).abs().max() / y_tiles.abs().max()) <= 1e-5
+    assert rel_err(y16, ref) <= 4e-3
+    assert rel_err(d16, ref) <= 4e-3 and rel_err(d32, ref) <= REL_TOL
