@@ -139,9 +139,7 @@ typedef struct mxq_gemm_options {
    * partial sums over through distributed shared memory in a fixed order (repeatable results).  0 = let the library
    * decide, 1 = never. */
   int32_t no_split_k;
-  /* mxq_mx_linear only.  0: for large problems the block-scaled GEMM starts while the activation pack is still
-   * running and waits, 128-row panel by panel, for the rows it is about to load; 1: pack first, then multiply. */
-  int32_t no_overlap;
+  int32_t reserved;  /* leave 0 */
   /* Limit of every device-side wait in nanoseconds; 0 = one second.  When a wait runs out the kernel stores a
    * non-zero code in the status word, lets its copies in flight land, frees its tensor memory and returns. */
   int64_t wait_limit_ns;
@@ -189,16 +187,31 @@ int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t
 
 /* LinearMXFP.forward in one call (chop/nn/quantized/modules/linear.py:877-895): quantize x[M,K] to MXFP(E,F),
  * block 32 along K, into `workspace` (scratch owned by the caller, 256-byte aligned, at least
- * mxq_mx_linear_workspace_bytes(M, K) bytes: codes, scale chunks and one counter per 128-row panel), then
- * D = x_q * W_q^T (+ bias) with the block-scaled GEMM.  For large problems the GEMM is launched while the pack is
- * still running and takes each 128-row panel of activations as soon as its counter says it is complete
- * (options->no_overlap = 1 runs the two steps one after the other).
+ * mxq_mx_linear_workspace_bytes(M, K) bytes), then D = x_q * W_q^T (+ bias) with the block-scaled GEMM.
  * w_codes / w_scales come from mxq_mxfp_pack_mma on the [N,K] weight. */
 int64_t mxq_mx_linear_workspace_bytes(int64_t M, int64_t K);
 int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d, const void *bias,
                   int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
                   const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status,
                   const mxq_gemm_options *options, void *stream);
+
+/* Hidden state of a gated MLP as tensor-core operands in one pass: h = silu(gate) * up, then the MXFP(E, F) pack of
+ * mxq_mxfp_pack_mma on h.  Replaces the elementwise `act_fn(gate) * up` between the projections
+ * (chop/nn/quantized/modules/llama/mlp.py:56-61, the unquantized-SiLU form) followed by the activation quantization
+ * of the down projection (chop/nn/quantized/modules/linear.py:877-890).  gate and up are bf16 [rows, k] views with
+ * a common row stride of `ld` elements (ld >= k, ld % 8 == 0, both 16-byte aligned): the two halves of one
+ * [rows, 2k] GEMM output, for instance.  h is rounded as the framework's elementwise kernels round it: silu in fp32
+ * as g / (1 + exp(-g)) -> bf16, product in fp32 -> bf16. */
+int mxq_silu_mul_pack_mma(const void *gate, const void *up, int64_t ld, uint8_t *codes, uint8_t *scales_mma,
+                          int64_t rows, int64_t k, int E, int F, const uint8_t *floor_tab_host, void *stream);
+
+/* Second half of a gated MLP in one call: D[M,N] = MXFP(silu(gate) * up)[M,K] * W_q[N,K]^T (+ bias), i.e.
+ * mxq_silu_mul_pack_mma into `workspace` followed by the block-scaled GEMM.  Workspace size and the other arguments
+ * as for mxq_mx_linear (K = columns of gate / up). */
+int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint8_t *w_codes, const uint8_t *w_scales,
+                        void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E,
+                        int F, const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status,
+                        const mxq_gemm_options *options, void *stream);
 
 /* Allocation-free variant of mxq_mx_linear.  It has no counterpart in the reference.
  *
@@ -215,7 +228,7 @@ int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uin
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  *     current) and caches it: make that first call with the right device current and before any stream capture;
  *   - every call on a device shares the one array, which keeps whatever the last call left in it.  A call overwrites
- *     the M x K code bytes, the scale bytes of its M rows and the panel counters it uses before it reads them.  The
+ *     the M x K code bytes and the scale bytes of its M rows before it reads them.  The
  *     scale bytes of the padding rows (M rounded up to 256) are NOT rewritten and may hold an earlier call's bytes:
  *     the tensor cores do read them, but they only scale accumulator rows >= M, which are never stored.  Scale bytes
  *     of K blocks past the end of a row (K not a multiple of 128) are cleared by every call, because there a stale

@@ -32,6 +32,10 @@ _PROTOTYPES = {
     "mxq_mx_linear_workspace_bytes": [c_int64, c_int64],
     "mxq_mx_linear": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64,
                       c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p],
+    "mxq_silu_mul_pack_mma": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p,
+                              c_void_p],
+    "mxq_mx_gated_linear": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
+                            c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p],
     "mxq_mx_linear_static": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
                              c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "mxq_bfp_fake_tiles": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
@@ -44,7 +48,7 @@ class GemmOptions(ctypes.Structure):
     """`mxq_gemm_options` of include/mxq.h: per-call settings of the GEMM entry points (all zero = defaults)."""
 
     _fields_ = [("max_ctas", ctypes.c_int32), ("tiles", ctypes.c_int32), ("no_split_k", ctypes.c_int32),
-                ("no_overlap", ctypes.c_int32), ("wait_limit_ns", ctypes.c_int64), ("test_hook", ctypes.c_int32),
+                ("reserved", ctypes.c_int32), ("wait_limit_ns", ctypes.c_int64), ("test_hook", ctypes.c_int32),
                 ("no_transposed", ctypes.c_int32)]
 
 

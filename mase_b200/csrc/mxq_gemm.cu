@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "mxq.h"
 #include "mxq_internal.h"
@@ -39,7 +40,7 @@ constexpr int kTmemCols = 512;
 enum Kind { kBf16 = 0, kTf32 = 1, kMxf8 = 2 };
 
 // error codes written to the status word
-constexpr int kErrProducerWait = 1, kErrMmaWaitFull = 2, kErrMmaWaitAcc = 3, kErrEpilogueWait = 4, kErrPanelWait = 6;
+constexpr int kErrProducerWait = 1, kErrMmaWaitFull = 2, kErrMmaWaitAcc = 3, kErrEpilogueWait = 4;
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -90,35 +91,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
                                                int code, unsigned long long limit_ns) {
   return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag, status, code, limit_ns));
-}
-// Bounded wait until the activation pack that runs next to this kernel has finished a 128-row panel: `counter`
-// (global memory, written by the pack with release semantics) reaches `target`.  The bulk-copy engine reads the
-// panel afterwards, hence the proxy fence behind the acquire.  Every lane of the warp polls and gets the same answer.
-__device__ __forceinline__ bool panel_wait_warp(const uint32_t *counter, uint32_t target, volatile int *abort_flag,
-                                                int *status, int code, unsigned long long limit_ns) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-  bool ok = true;
-  if (v < target) {
-    const unsigned long long t0 = global_ns();
-    for (;;) {
-      __nanosleep(100);
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-      if (v >= target) break;
-      if (*abort_flag) {
-        ok = false;
-        break;
-      }
-      if (global_ns() - t0 > limit_ns) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
-        ok = false;
-        break;
-      }
-    }
-  }
-  asm volatile("fence.proxy.async;" ::: "memory");
-  return __all_sync(0xFFFFFFFFu, ok);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
   asm volatile(
@@ -284,17 +256,7 @@ struct Params {
   int a_box_bytes;      // bytes one A load delivers: fewer than 128 rows when M is small (single-CTA kernel)
   unsigned long long wait_ns;  // limit of every wait
   int drop_last_load;   // test hook: CTA 0 never loads the last K chunk of its first tile
-  // Set when the activation pack runs concurrently with this kernel (mxq_mx_linear): one counter per 128-row panel
-  // of A that the pack raises by the 32-byte units it has stored; a panel is complete at rows_in_panel * units_per_row.
-  const uint32_t *panel_ready;
-  uint32_t units_per_row;
 };
-
-// counter value at which the 128-row panel `m_blk` of A is completely packed (0 for panels past the last row)
-__device__ __forceinline__ uint32_t panel_target(const Params &p, int m_blk) {
-  const int rows = p.M - m_blk * BM;
-  return rows <= 0 ? 0u : (uint32_t)(rows < BM ? rows : BM) * p.units_per_row;
-}
 
 // Epilogue of one tile for one warp: drains the warp's 32 TMEM lanes (= 32 tile rows starting at row0) of the
 // accumulator at t_acc in chunks of 32 columns, starting with chunk `first`.  A chunk is converted, written to a
@@ -470,9 +432,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
   // Launched with programmatic stream serialization: everything above (barriers, tensor memory) may run while the
   // previous kernel of the stream -- normally the activation pack -- is still finishing; its results are visible
-  // from here on.  Without that launch attribute this is a no-op.  When the pack runs concurrently (panel counters)
-  // there is nothing to wait for here: the producer waits for each panel of A instead, and B was packed long ago.
-  if (p.panel_ready == nullptr) grid_dependency_wait();
+  // from here on.  Without that launch attribute this is a no-op.
+  grid_dependency_wait();
 
   // The producer and the MMA issuer run their loops with all 32 lanes of their warp on identical values and elect
   // one lane for the TMA / tcgen05 instructions themselves.  Those instructions take their operands from uniform
@@ -500,11 +461,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // rows of the scale maps
       int chunk_a = m_blk * p.k_chunks + kc_begin, chunk_b = ((n_blk * BN) / 128) * p.k_chunks + kc_begin;
       int k0 = kc_begin * kBlockK;
-      if (p.panel_ready != nullptr &&
-          !panel_wait_warp(p.panel_ready + m_blk, panel_target(p, m_blk), abort_flag, p.status, kErrPanelWait, p.wait_ns)) {
-        ok = false;
-        break;
-      }
       for (int kc = kc_begin; kc < kc_end; ++kc) {
         if (!mbar_wait_warp(empty, phase ^ 1u, abort_flag, p.status, kErrProducerWait, p.wait_ns)) {
           ok = false;
@@ -814,7 +770,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   cluster_sync();  // both CTAs' barriers are initialised and both tensor-memory addresses are published
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (p.panel_ready == nullptr) grid_dependency_wait();  // see the single-CTA kernel
+  grid_dependency_wait();  // see the single-CTA kernel
   // the MMAs address both CTAs' tensor memory with one address: the two allocations must coincide
   if (ld_cluster_u32(map_to_cta(smem_u32(tmem_slot), rank ^ 1u)) != tmem_base) {
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kErrPairTmem);
@@ -841,11 +797,6 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const int row_a = m_blk * BM, row_b = (n_blk + (int)rank) * 128;
       int chunk_a = m_blk * p.k_chunks, chunk_b = n_blk * p.k_chunks;
       int k0 = 0;
-      if (p.panel_ready != nullptr &&
-          !panel_wait_warp(p.panel_ready + m_blk, panel_target(p, m_blk), abort_flag, p.status, kErrPanelWait, p.wait_ns)) {
-        ok = false;
-        break;
-      }
       for (int kc = 0; kc < p.k_chunks; ++kc) {
         if (!mbar_wait_warp(empty, phase ^ 1u, abort_flag, p.status, kErrProducerWait, p.wait_ns)) {
           ok = false;
@@ -1311,7 +1262,6 @@ Opts make_opts(const mxq_gemm_options *o) {
     r.max_ctas = o->max_ctas > 0 ? o->max_ctas : 0;
     r.tiles = o->tiles == MXQ_TILES_SINGLE || o->tiles == MXQ_TILES_PAIRS ? o->tiles : MXQ_TILES_AUTO;
     r.split_k = o->no_split_k == 0;
-    r.overlap = o->no_overlap == 0;
     r.transposed = o->no_transposed == 0;
     if (o->wait_limit_ns > 0) r.wait_ns = (unsigned long long)o->wait_limit_ns;
     r.test_hook = o->test_hook;
@@ -1388,7 +1338,6 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
   p.a_box_bytes = a_rows * kRowBytes;
   p.wait_ns = o.wait_ns, p.drop_last_load = !kSplit && o.test_hook == MXQ_TEST_DROP_LAST_LOAD;
-  p.panel_ready = o.panel_ready, p.units_per_row = o.units_per_row;
   CUtensorMap msa = ma, msb = ma;  // unused by the dense kinds
   if constexpr (kKind == kMxf8) {
     rc = make_sf_map(&msa, sfa, ((M + 255) / 256) * 2 * p.k_chunks);
@@ -1455,7 +1404,6 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
   p.a_box_bytes = BM * kRowBytes;
   p.wait_ns = o.wait_ns, p.drop_last_load = 0;
-  p.panel_ready = o.panel_ready, p.units_per_row = o.units_per_row;
   static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
   bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {
@@ -1504,6 +1452,7 @@ static int launch_swap(const void *a, const void *b, const uint8_t *sfa, const u
   // shares of K: as many CTAs as there are SMs, at least 4 chunks each, clusters of at most 8
   int split = 1;
   while (o.split_k && split < 8 && tiles * split * 2 <= sms && k_chunks / (split * 2) >= 4) split *= 2;
+  if (const char *e = getenv("MXQ_EXP_SPLIT")) split = atoi(e);  // EXPERIMENT
   SwapParams p;
   p.d = d, p.bias = bias, p.status = status, p.M = (int)M, p.N = (int)N, p.k_chunks = (int)k_chunks, p.split = split;
   p.x_box_bytes = x_rows * kRowBytes;
@@ -1627,7 +1576,7 @@ int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t
 namespace mxq {
 namespace gemm {
 
-// mxq_gemm_mxf8 with the options resolved; mxq_mx_linear calls it with the panel counters of its concurrent pack
+// mxq_gemm_mxf8 with the options resolved
 int gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_codes, const uint8_t *b_scales, void *d,
               const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status,
               const Opts &o, cudaStream_t st) {

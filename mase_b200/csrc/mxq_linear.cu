@@ -1,17 +1,12 @@
 // Forward of an MX Linear layer in one call: quantize the activations to MXFP along K into a caller-provided
 // workspace (E4M3 bytes + E8M0 scale chunks), then run the block-scaled tensor-core GEMM against a weight that was
-// packed once with mxq_mxfp_pack_mma.  Both steps are enqueued on the caller's stream.
-//
-// Large problems overlap the two steps: the pack kernel is launched with a grid that is resident as a whole and lets
-// its dependents go at once, the GEMM kernel starts next to it, and the GEMM's loader waits (bounded) for the counter
-// of each 128-row panel of activations before it fetches the panel.  The pack never waits for the GEMM, and two of its
-// CTAs fit on an SM next to a GEMM CTA, so it always makes progress.
+// packed once with mxq_mxfp_pack_mma.  Both steps are enqueued on the caller's stream; the GEMM is launched with
+// programmatic stream serialization, so its set-up (and, for few rows, its weight loads) runs under the pack's tail.
 
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "mxq.h"
-#include "mxq_internal.h"
 
 #include <mutex>
 
@@ -39,19 +34,13 @@ static int static_scratch_address(uint8_t **out) {
   return MXQ_OK;
 }
 
-// The pack and the GEMM overlap when the GEMM has several waves of tiles to get through while the pack is still
-// running; below that the sequential form (with the GEMM's set-up hidden under the pack's tail) is as fast.
-static bool overlap_applies(const void *x, int in_dtype, int64_t M, int64_t K) {
-  return in_dtype == MXQ_BF16 && M >= 512 && K % 128 == 0 && (reinterpret_cast<uintptr_t>(x) & 31) == 0;
-}
-
 extern "C" {
 
 int64_t mxq_mx_linear_workspace_bytes(int64_t M, int64_t K) {
   if (M < 0 || K < 0) return MXQ_ERR_SHAPE;
   const int64_t sf = mxq_mma_scale_bytes(M, K);
   if (sf < 0) return sf;
-  return align256(M * K) + align256(sf) + align256(((M + 127) / 128) * 4);  // codes, scale chunks, panel counters
+  return align256(M * K) + align256(sf);  // codes, scale chunks
 }
 
 int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d, const void *bias,
@@ -64,24 +53,28 @@ int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uin
   const int64_t need = mxq_mx_linear_workspace_bytes(M, K);
   if (need < 0) return (int)need;
   if (workspace_bytes < need) return MXQ_ERR_SHAPE;
-  cudaStream_t st = (cudaStream_t)stream;
   uint8_t *a_codes = static_cast<uint8_t *>(workspace);
   uint8_t *a_scales = a_codes + align256(M * K);
-  uint32_t *panels = reinterpret_cast<uint32_t *>(a_scales + align256(mxq_mma_scale_bytes(M, K)));
-  mxq::gemm::Opts o = mxq::gemm::make_opts(options);
-  if (o.overlap && overlap_applies(x, in_dtype, M, K)) {
-    if (cudaMemsetAsync(panels, 0, (size_t)((M + 127) / 128) * 4, st) != cudaSuccess) return MXQ_ERR_LAUNCH;
-    const int rc = mxq::pack_mma_signal(x, a_codes, a_scales, M, K, E, F, floor_tab_host, panels, st);
-    if (rc == MXQ_OK) {
-      o.panel_ready = panels, o.units_per_row = (uint32_t)(K / 16);
-      return mxq::gemm::gemm_mxf8(a_codes, a_scales, w_codes, w_scales, d, bias, out_dtype, bias_dtype, M, N, K, status, o,
-                                  st);
-    }
-    if (rc != MXQ_ERR_UNSUPPORTED) return rc;
-  }
   const int rc = mxq_mxfp_pack_mma(x, a_codes, a_scales, in_dtype, M, K, E, F, floor_tab_host, stream);
   if (rc != MXQ_OK) return rc;
-  return mxq::gemm::gemm_mxf8(a_codes, a_scales, w_codes, w_scales, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st);
+  return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, d, bias, out_dtype, bias_dtype, M, N, K, status, options, stream);
+}
+
+int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint8_t *w_codes, const uint8_t *w_scales,
+                        void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E,
+                        int F, const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status,
+                        const mxq_gemm_options *options, void *stream) {
+  if (M == 0 || N == 0) return MXQ_OK;
+  if (!workspace) return MXQ_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return MXQ_ERR_ALIGN;
+  const int64_t need = mxq_mx_linear_workspace_bytes(M, K);
+  if (need < 0) return (int)need;
+  if (workspace_bytes < need) return MXQ_ERR_SHAPE;
+  uint8_t *a_codes = static_cast<uint8_t *>(workspace);
+  uint8_t *a_scales = a_codes + align256(M * K);
+  const int rc = mxq_silu_mul_pack_mma(gate, up, ld, a_codes, a_scales, M, K, E, F, floor_tab_host, stream);
+  if (rc != MXQ_OK) return rc;
+  return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, d, bias, out_dtype, bias_dtype, M, N, K, status, options, stream);
 }
 
 int mxq_mx_linear_static(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d,
@@ -94,10 +87,10 @@ int mxq_mx_linear_static(const void *x, int in_dtype, const uint8_t *w_codes, co
   uint8_t *scratch = nullptr;
   const int rc = static_scratch_address(&scratch);  // first call on a device resolves the symbol's address
   if (rc != MXQ_OK) return rc;
-  // The array keeps the previous call's bytes.  This call rewrites the M * K code bytes, the scale bytes of its M rows
-  // and its panel counters before reading them; scale bytes of the padding rows (up to the next multiple of 256) may be
-  // an earlier call's and are read by the tensor cores, but only scale accumulator rows >= M, which are never stored;
-  // scale bytes of K blocks past the end of a row are cleared by the pack step whenever K % 128 != 0.
+  // The array keeps the previous call's bytes.  This call rewrites the M * K code bytes and the scale bytes of its M
+  // rows before reading them; scale bytes of the padding rows (up to the next multiple of 256) may be an earlier call's
+  // and are read by the tensor cores, but only scale accumulator rows >= M, which are never stored; scale bytes of K
+  // blocks past the end of a row are cleared by the pack step whenever K % 128 != 0.
   return mxq_mx_linear(x, in_dtype, w_codes, w_scales, d, bias, out_dtype, bias_dtype, M, N, K, E, F, floor_tab_host,
                        scratch, MXQ_STATIC_SCRATCH_BYTES, status, options, stream);
 }

@@ -310,15 +310,11 @@ __device__ __forceinline__ void load_unit(const __nv_bfloat16 *x, int64_t unit, 
   }
 }
 // I = uint32_t when unit indices and scale offsets fit in 32 bits (the usual case), else int64_t.
-// kSignal: the GEMM that consumes the operands runs next to this kernel.  After every step the CTA adds the units it
-// has stored to the counter of their 128-row panel (release at GPU scope behind a CTA barrier), and the GEMM's loader
-// takes a panel when its counter reaches rows * units per row.  Launched with a grid that is resident as a whole.
-template <int E, int F, bool kWide, typename I, bool kSignal = false>
+template <int E, int F, bool kWide, typename I>
 __global__ void __launch_bounds__(kThreads, 4)
 mxfp_pack_mma_bf16_kernel(const __nv_bfloat16 *__restrict__ x, uint8_t *__restrict__ codes,
                           uint8_t *__restrict__ scales, int64_t n_unit64, uint32_t unit_per_row, int64_t k_chunks,
-                          UnitStep jump, UnitStep stride, const __grid_constant__ Log2Tab tab,
-                          uint32_t *__restrict__ panel_ready = nullptr) {
+                          UnitStep jump, UnitStep stride, const __grid_constant__ Log2Tab tab) {
   constexpr int kU = 2;
   // the GEMM that follows in the stream may be launched from now on: it sets up its barriers and tensor memory while
   // this kernel finishes and waits for the operands on the device (griddepcontrol.wait)
@@ -364,24 +360,50 @@ mxfp_pack_mma_bf16_kernel(const __nv_bfloat16 *__restrict__ x, uint8_t *__restri
     }
     col += stride.units, row += stride.rows;
     if (col >= unit_per_row) col -= unit_per_row, ++row;
-    if constexpr (kSignal) {
-      __syncthreads();  // every store of this step is ordered before thread 0's release below
-      if (threadIdx.x == 0) {
-        const uint64_t first = (uint64_t)base;
-        uint64_t end = first + (uint64_t)kThreads * kU;
-        if (end > (uint64_t)n_unit) end = (uint64_t)n_unit;
-        const uint64_t per_panel = 128ull * unit_per_row;  // units of one 128-row panel
-        __threadfence();
-        asm volatile("fence.proxy.async;" ::: "memory");  // the consumer reads through the bulk-copy engine
-        for (uint64_t u = first; u < end;) {
-          const uint64_t panel = u / per_panel;
-          uint64_t stop = (panel + 1) * per_panel;
-          if (stop > end) stop = end;
-          asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(panel_ready + panel), "r"((uint32_t)(stop - u))
-                       : "memory");
-          u = stop;
-        }
-      }
+  }
+}
+
+// Gated-MLP hidden state straight into tensor-core operands: h = silu(gate) * up in bf16 exactly as the framework's
+// elementwise kernels compute it (silu evaluated in fp32 as g / (1 + exp(-g)) and rounded to bf16, the product
+// evaluated in fp32 and rounded to bf16), then the MXFP pack of the kernel above on h.  gate and up are [rows, k]
+// views with a common row stride (the two halves of one [rows, 2k] GEMM output, for instance).  One unit = 16
+// elements per lane and step.
+__device__ __forceinline__ uint32_t silu_mul_pair(uint32_t g2, uint32_t u2) {
+  float g0 = __uint_as_float(g2 << 16), g1 = __uint_as_float(g2 & 0xFFFF0000u);
+  float u0 = __uint_as_float(u2 << 16), u1 = __uint_as_float(u2 & 0xFFFF0000u);
+  const float s0 = __bfloat162float(__float2bfloat16_rn(g0 / (1.0f + expf(-g0))));
+  const float s1 = __bfloat162float(__float2bfloat16_rn(g1 / (1.0f + expf(-g1))));
+  const __nv_bfloat162 h = __floats2bfloat162_rn(s0 * u0, s1 * u1);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+__device__ __forceinline__ uint4 silu_mul_vec(const uint4 &g, const uint4 &u) {
+  return make_uint4(silu_mul_pair(g.x, u.x), silu_mul_pair(g.y, u.y), silu_mul_pair(g.z, u.z), silu_mul_pair(g.w, u.w));
+}
+template <int E, int F>
+__global__ void __launch_bounds__(kThreads, 2)
+silu_mul_pack_mma_kernel(const __nv_bfloat16 *__restrict__ gate, const __nv_bfloat16 *__restrict__ up, int64_t ld,
+                         uint8_t *__restrict__ codes, uint8_t *__restrict__ scales, int64_t n_unit,
+                         uint32_t unit_per_row, int64_t k_chunks, const __grid_constant__ Log2Tab tab) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int64_t step = (int64_t)gridDim.x * kThreads;
+  for (int64_t base = (int64_t)blockIdx.x * kThreads; base < n_unit; base += step) {
+    const int64_t j = base + threadIdx.x;
+    const bool live = j < n_unit;
+    int64_t row = 0;
+    uint32_t col = 0;
+    uint4 h_lo = make_uint4(0, 0, 0, 0), h_hi = h_lo;
+    if (live) {
+      row = j / unit_per_row, col = (uint32_t)(j - row * unit_per_row);
+      const uint4 *pg = reinterpret_cast<const uint4 *>(gate + row * ld + (int64_t)col * 16);
+      const uint4 *pu = reinterpret_cast<const uint4 *>(up + row * ld + (int64_t)col * 16);
+      const uint4 g_lo = ld_stream(pg), g_hi = ld_stream(pg + 1), u_lo = ld_stream(pu), u_hi = ld_stream(pu + 1);
+      h_lo = silu_mul_vec(g_lo, u_lo), h_hi = silu_mul_vec(g_hi, u_hi);
+    }
+    int scale;
+    const uint4 c16 = pack_bf16<E, F>(h_lo, h_hi, tab, scale);  // all lanes take part (shuffle inside)
+    if (live) {
+      __stcs(reinterpret_cast<uint4 *>(codes) + j, c16);
+      if ((threadIdx.x & 1) == 0) scales[mma_scale_offset<int64_t>(row, (int64_t)(col >> 1), k_chunks)] = (uint8_t)scale;
     }
   }
 }
@@ -882,41 +904,33 @@ int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in
   return MXQ_ERR_FORMAT;
 }
 
-}  // extern "C"
-
-// See mxq_internal.h.  Two CTAs of 256 threads per SM: next to a GEMM CTA (192 threads, ~130 registers each, nearly all
-// of the shared memory, none of which this kernel needs) that is what the register file holds, and a grid that is
-// resident as a whole lets the GEMM launch as soon as this kernel has started.
-int mxq::pack_mma_signal(const void *x, uint8_t *codes, uint8_t *scales_mma, int64_t rows, int64_t k, int E, int F,
-                         const uint8_t *floor_tab_host, uint32_t *panel_ready, cudaStream_t st) {
-  if (!x || !codes || !scales_mma || !floor_tab_host || !panel_ready) return MXQ_ERR_NULL;
-  if (rows <= 0 || k <= 0 || k % 128) return MXQ_ERR_UNSUPPORTED;  // (K % 128 != 0 needs the scale memset first)
+int mxq_silu_mul_pack_mma(const void *gate, const void *up, int64_t ld, uint8_t *codes, uint8_t *scales_mma,
+                          int64_t rows, int64_t k, int E, int F, const uint8_t *floor_tab_host, void *stream) {
+  if (rows == 0 || k == 0) return MXQ_OK;
+  if (!gate || !up || !codes || !scales_mma || !floor_tab_host) return MXQ_ERR_NULL;
+  if (rows < 0 || k < 0 || k % 32 || ld < k || ld % 8) return MXQ_ERR_SHAPE;
   if (!legal_ef(E, F) || E > 4 || F > 3) return MXQ_ERR_FORMAT;
-  if ((reinterpret_cast<uintptr_t>(x) & 31) || !aligned16(codes)) return MXQ_ERR_UNSUPPORTED;
+  if (!aligned16(gate) || !aligned16(up) || !aligned16(codes)) return MXQ_ERR_ALIGN;
   const Log2Tab tab = load_tab(floor_tab_host);
-  const int64_t k_chunks = k / 128;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t k_chunks = (k + 127) / 128;
   const int64_t sf_bytes = ((rows + 255) / 256) * 2 * k_chunks * 512;
+  // scale bytes of K blocks past the end of a row must be finite (see mxq_mxfp_pack_mma)
+  if (k % 128 && cudaMemsetAsync(scales_mma, 0, sf_bytes, st) != cudaSuccess) return MXQ_ERR_LAUNCH;
   const int64_t n_unit = rows * k / 16;
   const uint32_t upr = (uint32_t)(k / 16);
-  int64_t grid64 = (n_unit + kThreads * 2 - 1) / (kThreads * 2);
-  const int64_t cap = 2 * (int64_t)mxq::gemm::sm_count();
-  const int grid = (int)(grid64 < cap ? grid64 : cap);
-  const int64_t step = (int64_t)grid * kThreads * 2;
-  if (!(n_unit + step < (1ll << 31) && sf_bytes < (1ll << 31)) || 128ll * upr >= (1ll << 31)) return MXQ_ERR_UNSUPPORTED;
-  const UnitStep jump = {(uint32_t)(kThreads / upr), (uint32_t)(kThreads % upr)};
-  const UnitStep stride = {(uint32_t)(step / upr), (uint32_t)(step % upr)};
-#define MXQ_PACK(e, f)                                                                                        \
-  if (E == e && F == f) {                                                                                     \
-    mxfp_pack_mma_bf16_kernel<e, f, true, uint32_t, true><<<grid, kThreads, 0, st>>>(                         \
-        (const __nv_bfloat16 *)x, codes, scales_mma, n_unit, upr, k_chunks, jump, stride, tab, panel_ready);  \
-    return check_launch();                                                                                    \
+  const int grid = grid_for(n_unit, kThreads);
+#define MXQ_PACK(e, f)                                                                                         \
+  if (E == e && F == f) {                                                                                      \
+    silu_mul_pack_mma_kernel<e, f><<<grid, kThreads, 0, st>>>((const __nv_bfloat16 *)gate,                     \
+                                                              (const __nv_bfloat16 *)up, ld, codes, scales_mma, \
+                                                              n_unit, upr, k_chunks, tab);                     \
+    return check_launch();                                                                                     \
   }
   MXQ_PACK(4, 3) MXQ_PACK(2, 3) MXQ_PACK(3, 2) MXQ_PACK(2, 1) MXQ_PACK(1, 2)
 #undef MXQ_PACK
   return MXQ_ERR_FORMAT;
 }
-
-extern "C" {
 
 int mxq_mxfp_compose(const uint8_t *codes, const uint8_t *scales, void *y, int out_dtype, int64_t n_blocks, int block,
                      int E, int F, void *stream) {

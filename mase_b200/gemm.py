@@ -33,7 +33,6 @@ _STATUS_TEXT = {
     3: "MMA issuer: wait for a free accumulator ran out",
     4: "epilogue: wait for a finished accumulator ran out",
     5: "CTA pair: the two CTAs got different tensor-memory addresses",
-    6: "TMA producer: wait for a panel of activations from the concurrent pack ran out",
 }
 
 
@@ -44,7 +43,7 @@ _TLS = threading.local()
 def options(**fields):
     """Per-call GEMM options (`mxq_gemm_options` of include/mxq.h) for every GEMM this thread issues inside the
     `with` block: `max_ctas` (leave SMs to a concurrent kernel), `tiles` (_lib.TILES_AUTO / TILES_SINGLE /
-    TILES_PAIRS), `no_split_k`, `no_overlap`, `wait_limit_ns`, `test_hook`.  The options travel with each call into
+    TILES_PAIRS), `no_split_k`, `no_transposed`, `wait_limit_ns`, `test_hook`.  The options travel with each call into
     the library, which keeps no settings of its own; other threads are not affected.  Blocks nest: inner fields
     override outer ones."""
     prev = getattr(_TLS, "opts", None)
@@ -162,6 +161,63 @@ def pack_mx_operand(x: Tensor, exp_bits: int, frac_bits: int) -> MXOperand:
                                    frac_bits, _floor_tab_ptr(), _stream(x))
     _lib.check(rc, "mxq_mxfp_pack_mma")
     return MXOperand(codes, scales, rows, k)
+
+
+def pack_gated_operand(gate: Tensor, up: Tensor, exp_bits: int, frac_bits: int) -> MXOperand:
+    """MXFP(exp_bits, frac_bits) tensor-core operand of silu(gate) * up in one pass over gate and up (bf16 [rows, k]
+    views with the same row stride, e.g. the two halves of a [rows, 2k] GEMM output).  The product is rounded exactly
+    as `torch.nn.functional.silu(gate) * up` rounds it in bf16, so codes and scales equal those of packing that
+    tensor."""
+    _require_cuda(gate, "pack_gated_operand")
+    if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16:
+        raise NotImplementedError("pack_gated_operand: gate and up must be bfloat16")
+    assert gate.dim() == 2 and gate.shape == up.shape
+    rows, k = gate.shape
+    if not mma_supported(exp_bits, frac_bits, 32, k):
+        raise NotImplementedError("block-scaled operands need E <= 4, F <= 3 and K divisible by 32")
+    ok = lambda t: t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0  # noqa: E731
+    if not (ok(gate) and ok(up) and gate.stride(0) == up.stride(0)):
+        gate, up = gate.contiguous(), up.contiguous()
+    lib = _lib.lib()
+    codes = torch.empty((rows, k), dtype=torch.uint8, device=gate.device)
+    scales = torch.empty((int(lib.mxq_mma_scale_bytes(rows, k)),), dtype=torch.uint8, device=gate.device)
+    with _on_device(gate):
+        rc = lib.mxq_silu_mul_pack_mma(gate.data_ptr(), up.data_ptr(), gate.stride(0), codes.data_ptr(), scales.data_ptr(),
+                                       rows, k, exp_bits, frac_bits, _floor_tab_ptr(), _stream(gate))
+    _lib.check(rc, "mxq_silu_mul_pack_mma")
+    return MXOperand(codes, scales, rows, k)
+
+
+def mx_gated_linear(gate: Tensor, up: Tensor, weight: MXOperand, bias: Tensor | None, exp_bits: int, frac_bits: int,
+                    out_dtype: torch.dtype | None = None) -> Tensor:
+    """(silu(gate) * up) quantized to MXFP(exp_bits, frac_bits) along K and multiplied with a packed weight, in one
+    C call: the second half of a gated MLP without materialising the hidden state."""
+    _require_cuda(gate, "mx_gated_linear")
+    if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16:
+        raise NotImplementedError("mx_gated_linear: gate and up must be bfloat16")
+    K = gate.shape[-1]
+    assert K == weight.k and gate.shape == up.shape
+    lead = gate.shape[:-1]
+    g2, u2 = gate.reshape(-1, K), up.reshape(-1, K)
+    ok = lambda t: t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0  # noqa: E731
+    if not (ok(g2) and ok(u2) and g2.stride(0) == u2.stride(0)):
+        g2, u2 = g2.contiguous(), u2.contiguous()
+    M, N = g2.shape[0], weight.rows
+    lib = _lib.lib()
+    ws_bytes = int(lib.mxq_mx_linear_workspace_bytes(M, K))
+    ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=gate.device)
+    out = torch.empty((M, N), dtype=out_dtype or gate.dtype, device=gate.device)
+    bb, bdt = _bias_args(bias)
+    st = _status(gate.device)
+    with _on_device(gate):
+        rc = lib.mxq_mx_gated_linear(g2.data_ptr(), u2.data_ptr(), g2.stride(0), weight.codes.data_ptr(),
+                                     weight.scales.data_ptr(), out.data_ptr(), 0 if bb is None else bb.data_ptr(),
+                                     _DT[out.dtype], bdt, M, N, K, exp_bits, frac_bits, _floor_tab_ptr(), ws.data_ptr(),
+                                     ws_bytes, st.data_ptr(), _options_ptr(), _stream(gate))
+    _lib.check(rc, "mxq_mx_gated_linear")
+    if _CHECK_EVERY_CALL:
+        check_status(gate.device)
+    return out.reshape(*lead, N)
 
 
 def mx_gemm(a: MXOperand, b: MXOperand, bias: Tensor | None, out_dtype: torch.dtype) -> Tensor:

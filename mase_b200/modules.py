@@ -15,7 +15,7 @@ from functools import partial
 import torch
 from torch import Tensor
 
-from .gemm import MXOperand, linear_forward, mma_supported, mx_linear, pack_mx_operand
+from .gemm import (MXOperand, linear_forward, mma_supported, mx_gated_linear, mx_gemm, mx_linear, pack_mx_operand)
 from .quantizers import block_fp_quantizer, mxfp_quantizer, mxint_quantizer
 
 
@@ -149,6 +149,48 @@ class LinearMXFP(_LinearBase):
         return linear_forward(x, self.weight, self.bias, self.output_dtype)
 
 
+    # ---- sharing one activation quantization between sibling projections (q/k/v, gate/up) ----------------------
+    def _input_format(self):
+        cfg = self.config
+        return ("mxfp", cfg.get("data_in_block_size"), cfg.get("data_in_exponent_width"), cfg.get("data_in_frac_width"))
+
+    def _uses_packed_path(self, x: Tensor) -> bool:
+        _, x_block, x_exp, _ = self._input_format()
+        return (not self.bypass and x_block is not None and x_exp is not None and self._packed_weight() is not None
+                and x.is_cuda and x.dtype == self.weight.dtype)
+
+    @torch.no_grad()
+    def quantize_input(self, x: Tensor):
+        """The quantized form of x that `forward_quantized` takes: tensor-core operands when this layer multiplies
+        block-scaled codes, else the fake-quantized tensor (or x itself for a layer without input quantization)."""
+        _, x_block, x_exp, x_frac = self._input_format()
+        if self._uses_packed_path(x):
+            x2 = x.reshape(-1, x.shape[-1])
+            return pack_mx_operand(x2, x_exp, x_frac), x.shape[:-1]
+        if self.bypass or x_block is None or x_exp is None:
+            return x, None
+        return mxfp_quantizer(x, block_size=x_block, element_exp_bits=x_exp, element_frac_bits=x_frac, block_dim=-1), None
+
+    @torch.no_grad()
+    def forward_quantized(self, quantized) -> Tensor:
+        """forward(x) for an x that went through `quantize_input` of a layer with the same input format."""
+        xq, lead = quantized
+        if isinstance(xq, MXOperand):
+            out_dtype = self.output_dtype or self.weight.dtype
+            return mx_gemm(xq, self._packed_weight(), self.bias, out_dtype).reshape(*lead, self.out_features)
+        return linear_forward(xq, self.weight, self.bias, self.output_dtype)
+
+    @torch.no_grad()
+    def forward_gated(self, gate: Tensor, up: Tensor) -> Tensor:
+        """forward(silu(gate) * up) -- the down projection of a gated MLP -- without materialising the product: one
+        kernel reads gate and up and writes the quantized tensor-core operand.  Falls back to the plain forward where
+        the block-scaled path does not apply."""
+        _, x_block, x_exp, x_frac = self._input_format()
+        if gate.dtype == torch.bfloat16 and self._uses_packed_path(gate):
+            return mx_gated_linear(gate, up, self._packed_weight(), self.bias, x_exp, x_frac, self.output_dtype)
+        return self.forward(torch.nn.functional.silu(gate) * up)
+
+
 class LinearMXInt(_LinearBase):
     """Linear with MXINT weight (quantized at load time) and MXINT activations.  Inference only."""
 
@@ -186,6 +228,38 @@ class LinearMXInt(_LinearBase):
         if x_block is not None and x_bits is not None:
             x = mxint_quantizer(x, block_size=x_block, element_bits=x_bits, block_dim=-1)
         return linear_forward(x, self.weight, self.bias, self.output_dtype)
+
+
+    def _input_format(self):
+        cfg = self.config
+        return ("mxint", cfg.get("data_in_block_size"), cfg.get("data_in_width"))
+
+    @torch.no_grad()
+    def quantize_input(self, x: Tensor):
+        _, x_block, x_bits = self._input_format()
+        if self.bypass or x_block is None or x_bits is None:
+            return x, None
+        return mxint_quantizer(x, block_size=x_block, element_bits=x_bits, block_dim=-1), None
+
+    @torch.no_grad()
+    def forward_quantized(self, quantized) -> Tensor:
+        return linear_forward(quantized[0], self.weight, self.bias, self.output_dtype)
+
+
+def forward_siblings(layers, x: Tensor) -> list[Tensor]:
+    """[layer(x) for layer in layers] for projections that read the same input (q/k/v; gate/up), quantizing x once
+    when the layers are of one class, share the input format and take the same kind of quantized operand.  The
+    reference quantizes x inside every forward (chop/nn/quantized/modules/linear.py:877-890, :956-969); the values
+    are the same, only the repeated work is dropped."""
+    first = layers[0]
+    shareable = all(hasattr(m, "quantize_input") and type(m) is type(first) and not m.bypass
+                    and m._input_format() == first._input_format() for m in layers)
+    if shareable and isinstance(first, LinearMXFP):
+        shareable = len({m._uses_packed_path(x) for m in layers}) == 1
+    if not shareable:
+        return [m(x) for m in layers]
+    q = first.quantize_input(x)
+    return [m.forward_quantized(q) for m in layers]
 
 
 def linearBlockFP(x: Tensor, weight: Tensor, bias: Tensor = None, config: dict = None, out_dtype=None) -> Tensor:

@@ -102,13 +102,19 @@ class DecoderLayer(torch.nn.Module):
     def forward(self, x):  # [B, S, hidden]
         b, s, h = x.shape
         hd = h // self.heads
+        from .modules import forward_siblings  # plain nn.Linear children simply get called one by one
+
         y = self._norm(x)
-        q, k, v = (proj(y).view(b, s, self.heads, hd).transpose(1, 2) for proj in (self.q_proj, self.k_proj, self.v_proj))
+        q, k, v = (t.view(b, s, self.heads, hd).transpose(1, 2)
+                   for t in forward_siblings([self.q_proj, self.k_proj, self.v_proj], y))
         q, k = self._rope(q), self._rope(k)
         att = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
         x = x + self.o_proj(att.transpose(1, 2).reshape(b, s, h))
         y = self._norm(x)
-        return x + self.down_proj(torch.nn.functional.silu(self.gate_proj(y)) * self.up_proj(y))
+        gate, up = forward_siblings([self.gate_proj, self.up_proj], y)
+        if hasattr(self.down_proj, "forward_gated"):
+            return x + self.down_proj.forward_gated(gate, up)
+        return x + self.down_proj(torch.nn.functional.silu(gate) * up)
 
     def linear_flops(self, tokens: int) -> int:
         return 2 * tokens * (4 * self.hidden * self.hidden + 3 * self.hidden * self.ffn)

@@ -121,11 +121,21 @@ class RowParallelLinear(nn.Module):
             self._comm_stream = torch.cuda.Stream(device=device)
         return self._comm_stream
 
-    def start(self, x_shard: Tensor):
+    def start_gated(self, gate: Tensor, up: Tensor):
+        """`start(silu(gate) * up)` for a gated MLP; the product goes straight into the inner layer's quantized
+        operand when that layer can take it (`forward_gated`)."""
+        if hasattr(self.inner, "forward_gated"):
+            k = gate.shape[-1]
+            return self.start(None, partial=self.inner.forward_gated(gate.reshape(-1, k), up.reshape(-1, k)),
+                              like=gate)
+        return self.start(torch.nn.functional.silu(gate) * up)
+
+    def start(self, x_shard: Tensor | None, partial: Tensor | None = None, like: Tensor | None = None):
         """Local GEMM on the current stream, collective on a side stream; returns a handle for `finish`."""
-        out_dtype = x_shard.dtype
-        lead = x_shard.shape[:-1]
-        p = self.inner(x_shard.reshape(-1, x_shard.shape[-1]))
+        like = x_shard if like is None else like
+        out_dtype = like.dtype
+        lead = like.shape[:-1]
+        p = partial if partial is not None else self.inner(x_shard.reshape(-1, x_shard.shape[-1]))
         if p.dtype != torch.float32:
             p = p.float()
         if self.tp.world == 1:
@@ -206,15 +216,26 @@ class TPGatedMLP(nn.Module):
         assert (gate_up is None) != (gate is None and up is None), "pass gate and up, or gate_up"
         self.gate, self.up, self.down, self.gate_up = gate, up, down, gate_up
 
-    def hidden(self, x: Tensor) -> Tensor:
+    def gate_and_up(self, x: Tensor) -> tuple[Tensor, Tensor]:
         if self.gate_up is None:
-            return torch.nn.functional.silu(self.gate(x)) * self.up(x)
+            return self.gate(x), self.up(x)
         gu = self.gate_up(x)
         half = gu.shape[-1] // 2
-        return torch.nn.functional.silu(gu[..., :half]) * gu[..., half:]
+        return gu[..., :half], gu[..., half:]
+
+    def start(self, x: Tensor):
+        """Both column-parallel GEMMs, SiLU * mul and the row-parallel GEMM on the current stream, the reduction on
+        the down layer's side stream; `self.down.finish(handle)` gives the layer's output."""
+        gate, up = self.gate_and_up(x)
+        if hasattr(self.down, "start_gated"):
+            return self.down.start_gated(gate, up)
+        return self.down.start(torch.nn.functional.silu(gate) * up)
 
     def forward(self, x: Tensor) -> Tensor:
-        return self.down(self.hidden(x))
+        gate, up = self.gate_and_up(x)
+        if hasattr(self.down, "start_gated"):
+            return self.down.finish(self.down.start_gated(gate, up))
+        return self.down(torch.nn.functional.silu(gate) * up)
 
 
 def build_tp_gated_mlp(cls, w_gate: Tensor, w_up: Tensor, w_down: Tensor, config: dict, tp: TPGroup, device=None,
@@ -255,6 +276,6 @@ def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, c
                 # a part waits only for its own reduction of the previous layer; the other parts' reductions stay
                 # in flight underneath this part's GEMMs
                 inp = parts[i] if prev_layer is None else prev_layer.down.finish(handles[i])
-                handles[i] = layer.down.start(layer.hidden(inp))
+                handles[i] = layer.start(inp)
             prev_layer = layer
         return torch.cat([prev_layer.down.finish(h) for h in handles], dim=0)

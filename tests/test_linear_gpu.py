@@ -244,3 +244,55 @@ def test_functional_elementwise_mx_ops_vs_oracle():
     assert (ke.float().cpu() - (v.float() * cq + rot(v.float()) * sq)).abs().max() <= 5e-2
     qe, ke = mb.rope_mxint(k.to(DEV), v.to(DEV), cos.to(DEV), sin.to(DEV), cint)
     assert qe.shape == k.shape and ke.shape == v.shape
+
+
+@pytest.mark.parametrize("shape", [(96, 1376, 512), (300, 3584, 256), (2048, 1024, 768)])
+def test_gated_pack_and_gated_linear(shape):
+    """silu(gate) * up -> MXFP8 operand in one kernel: the codes of packing torch's own bf16 product, the GEMM result
+    of the two-step route bit for bit, and the oracle's codes of the CPU product up to the rare element where the
+    host's and the device's exp differ in the last fp32 bit before the bf16 rounding."""
+    M, F, N = shape
+    g = torch.Generator().manual_seed(11)
+    gu = (torch.randn(M, 2 * F, generator=g) * 2).bfloat16()
+    w = (torch.randn(N, F, generator=g) * 0.02).bfloat16()
+    gud = gu.to(DEV)
+    gate, up = gud[:, :F], gud[:, F:]          # strided views: the two halves of one GEMM output
+    h = torch.nn.functional.silu(gate) * up
+    fused = gemm.pack_gated_operand(gate, up, 4, 3)
+    plain = gemm.pack_mx_operand(h, 4, 3)
+    assert torch.equal(fused.codes, plain.codes)
+    wp = gemm.pack_mx_operand(w.to(DEV), 4, 3)
+    y_fused = gemm.mx_gated_linear(gate, up, wp, None, 4, 3, torch.float32)
+    y_plain = gemm.mx_linear(h, wp, None, 4, 3, torch.float32)
+    gemm.check_status()
+    assert torch.equal(y_fused, y_plain)
+    h_cpu = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    assert float((h_cpu != h.cpu()).float().mean()) < 1e-3
+    ref = O.mxfp_fake(h_cpu, 32, 4, 3).float() @ O.mxfp_fake(w, 32, 4, 3, 1).float().t()
+    assert rel_err(y_fused, ref) <= 2e-3
+    # module level: the down projection of a gated MLP
+    cfg = dict(synthetic.MXFP4W_MXFP8A_LINEAR)
+    down = mb.LinearMXFP(F, N, bias=False, device=DEV, dtype=torch.bfloat16, config=cfg)
+    down.load_state_dict({"weight": w.to(DEV)}, strict=False)
+    assert torch.equal(down.forward_gated(gate, up), down(h))
+
+
+def test_sibling_projections_share_one_activation_quantization():
+    from mase_b200.modules import forward_siblings
+
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(3, 50, 512, generator=g).bfloat16().to(DEV)
+    for cls, cfg in ((mb.LinearMXInt, synthetic.MXINT8_LINEAR), (mb.LinearMXFP, synthetic.MXFP4W_MXFP8A_LINEAR)):
+        layers = []
+        for n in (512, 256, 768):
+            m = cls(512, n, bias=True, device=DEV, dtype=torch.bfloat16, config=dict(cfg))
+            m.load_state_dict({"weight": (torch.randn(n, 512, generator=g) * 0.02).bfloat16().to(DEV),
+                               "bias": torch.randn(n, generator=g).bfloat16().to(DEV)}, strict=False)
+            layers.append(m)
+        shared = forward_siblings(layers, x)
+        for m, y in zip(layers, shared):
+            assert torch.equal(y, m(x)) and y.shape == (3, 50, m.out_features)
+    gemm.check_status()
+    # layers that cannot share (different classes) are simply called one by one
+    mixed = forward_siblings([layers[0], torch.nn.Linear(512, 64, dtype=torch.bfloat16, device=DEV)], x)
+    assert mixed[1].shape == (3, 50, 64)

@@ -38,8 +38,13 @@ def _worker(rank, world, port, results):
         )
         y = mlp(x.to(dev))
         y2 = tpmod.run_mlp_stack([mlp], x.to(dev), micro_batches=2)
+        # the same layer with gate and up stacked into one column-parallel GEMM (one activation pack, one launch)
+        fused = tpmod.build_tp_gated_mlp(mb.LinearMXFP, wg, wu, wd, CFG, tp, device=dev, reduce="scatter_gather")
+        y3 = fused(x.to(dev))
+        y4 = tpmod.run_mlp_stack([fused], x.to(dev), micro_batches=4)
         torch.cuda.synchronize()
-        assert torch.equal(y, y2)
+        assert torch.equal(y, y2) and torch.equal(y3, y4)
+        assert float((y3.float() - y.float()).abs().max() / y.float().abs().max()) <= 8e-3  # bf16 output rounding
         gemm.check_status()
         if rank == 0:
             q = lambda w: O.mxfp_fake(w, 32, 2, 1, 1)

@@ -35,8 +35,8 @@ def _run(entry, x, wp, out, workspace=None):
 
 def test_static_scratch_entry_matches_workspace_entry_on_calls_in_a_row():
     """Calls in a row with different shapes: each one finds the previous one's leftovers in the shared array.  The
-    shapes cover the overlapped pack + GEMM form (M >= 512), the sequential form, and K % 128 != 0 (whose scale region
-    holds an earlier call's bytes until the pack clears it).  Results must be the bits of the workspace entry, within
+    shapes cover CTA pairs, single-CTA tiles, the transposed small-M kernel and K % 128 != 0 (whose scale region holds
+    an earlier call's bytes until the pack clears it).  Results must be the bits of the workspace entry, within
     the bf16 bar of the oracle, and neither torch's allocator nor the device's free memory may move."""
     lib = _lib.lib()
     torch.cuda.set_device(0)
