@@ -23,7 +23,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdlib.h>
 
 #include "mxq.h"
 #include "mxq_internal.h"
@@ -934,30 +933,33 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 // Such a problem is the latency of streaming the weight once.  Here the weight is the 128-row operand of the MMA and
 // the activations are its narrow one (16, 32, 64 or 128 columns of the accumulator), so one instruction covers 128
 // weight rows with a short pass through the tensor pipe, and a CTA's 128-row stripe of the weight is fetched by a
-// producer that never waits for the activations: its weight and weight-scale loads are issued before the dependency
-// wait on the previous kernel of the stream (the activation pack), the activation loads behind it, into a ring deep
-// enough to hold a CTA's whole share of K for the common shapes.  K is split over the 1, 2, 4 or 8 CTAs of a
-// thread-block cluster so that about every SM pulls on the weight; the CTAs park their fp32 partial sums in their own
-// shared memory and the first CTA adds them in rank order through distributed shared memory (repeatable), adds the
-// bias and stores D transposed back: lane = weight row, so a warp writes 32 consecutive elements of one output row.
+// producer that never waits for the activations: it initialises the barriers itself and issues its weight and
+// weight-scale loads at once -- before the rest of the CTA has set up tensor memory and before the dependency wait on
+// the previous kernel of the stream (the activation pack) -- and the activation loads behind that wait, into a ring
+// deep enough to hold a CTA's whole share of K for the common shapes.  K is split over the 1, 2 or 4 CTAs of a
+// thread-block cluster so that about every SM pulls on the weight; the other CTAs push their fp32 partial sums into
+// the first CTA's shared memory (distributed shared memory stores, one cluster barrier), which adds them in rank
+// order (repeatable), adds the bias and stores D transposed back: lane = weight row, so a warp writes 32 consecutive
+// elements of one output row.
 // =====================================================================================================================
 constexpr int kSwapMaxStages = 12;
 
 template <int BNX, bool kScaled>
 struct SwapLayout {
+  static constexpr int kMaxSplit = BNX <= 32 ? 4 : 2;  // shares of K (CTAs per cluster)
   static constexpr int kW = BM * kRowBytes;   // 128 weight rows
   static constexpr int kX = BNX * kRowBytes;  // activation rows (the ones past M are never stored)
   static constexpr int kWX = kW + kX;
   static constexpr int kSf = kScaled ? 1024 : 0;  // weight chunk, activation chunk
-  static constexpr int kBudget = 200 * 1024;
+  // partial sums of the other CTAs of the cluster land here in the first CTA: [rank - 1][column][row] fp32
+  static constexpr int kXbufBytes = (kMaxSplit - 1) * BNX * BM * 4;
+  static constexpr int kBudget = 200 * 1024 - kXbufBytes;
   static constexpr int kFit = kBudget / (kWX + kSf);
   static constexpr int kStages = kFit < 10 ? kFit : 10;
   static constexpr int kSfBase = kStages * kWX;
-  static constexpr int kRing = (kStages * (kWX + kSf) + 1023) & ~1023;
-  static constexpr int kXbuf = 0;  // partial sums reuse the ring once the MMAs are done (BNX x 128 fp32 <= 64 KB)
-  static constexpr int kBarriers = kRing;  // full[], empty[], acc_full
+  static constexpr int kXbuf = (kStages * (kWX + kSf) + 1023) & ~1023;
+  static constexpr int kBarriers = kXbuf + kXbufBytes;  // full[], empty[], acc_full
   static constexpr int kTotal = kBarriers + (2 * kSwapMaxStages + 2) * 8 + 16 + 1024;
-  static_assert(BNX * BM * 4 <= kRing, "exchange buffer must fit in the ring");
 };
 
 struct SwapParams {
@@ -984,6 +986,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
                     "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
                :: "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
 
 template <int kKind, int BNX>
@@ -1016,39 +1021,23 @@ umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   const int base = p.k_chunks / p.split, rem = p.k_chunks % p.split;
   const int kc_begin = rank * base + (rank < rem ? rank : rem);
   const int kc_count = base + (rank < rem ? 1 : 0);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), 1), mbar_init(empty_bar(s), 1);
-    mbar_init(acc_full, 1);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(kSwapTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const int first_pass = kc_count < kStages ? kc_count : kStages;
+  const int row_w = n_blk * BM;
+  const uint32_t stage_tx = (uint32_t)(L::kW + L::kSf) + (uint32_t)p.x_box_bytes;
+  // Every CTA of a cluster must be running before another one touches its shared memory: arrive now, wait (long
+  // since satisfied) right before the partial sums are pushed.
+  if (p.split > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (elect_one()) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-      if constexpr (kScaled) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfw) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfx) : "memory");
-      }
+    // The producer does not wait for the rest of the CTA: it initialises the barriers and starts the weight stream.
+    if (lane == 0) {
+      for (int s = 0; s < kStages; ++s) mbar_init(full_bar(s), 1), mbar_init(empty_bar(s), 1);
+      mbar_init(acc_full, 1);
+      *abort_flag = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    const int row_w = n_blk * BM;
-    const uint32_t stage_tx = (uint32_t)(L::kW + L::kSf) + (uint32_t)p.x_box_bytes;
-    // the weight does not depend on the previous kernel of the stream: fill the ring's first pass with it now
-    const int first_pass = kc_count < kStages ? kc_count : kStages;
+    __syncwarp();
     for (int i = 0; i < first_pass; ++i) {
       if (elect_one()) {
         const int kc = kc_begin + i;
@@ -1057,6 +1046,19 @@ umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         if constexpr (kScaled) tma_load_2d(s_base + L::kSfBase + i * L::kSf, &map_sfw, full_bar(i), 0, n_blk * p.k_chunks + kc);
       }
     }
+  } else if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kSwapTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();  // barriers initialised, tensor memory allocated
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer, continued ----------------
     grid_dependency_wait();  // the activations (and their scales) come from the previous kernel
     for (int i = 0; i < first_pass; ++i) {
       if (elect_one()) {
@@ -1123,29 +1125,31 @@ umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     if (ok && elect_one()) tc_commit(acc_full);
   }
 
+  if (p.split > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // all CTAs of the cluster have started
   // ---------------- epilogue (warps 2..5): TMEM lane = weight row ----------------
   const int quarter = warp & 3;
   const int row_in_tile = quarter * 32 + lane;
   const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16);
-  float *xbuf = reinterpret_cast<float *>(smem + L::kXbuf);
   bool have_acc = false;
   if (warp >= 2) {
     have_acc = mbar_wait_warp(acc_full, 0u, abort_flag, p.status, kErrEpilogueWait, p.wait_ns);
     tc_fence_after();
     if (have_acc && rank != 0) {
-      // park this CTA's partial sums, column-major (element (row, col) at col * 128 + row: the 32 lanes of a warp, one
-      // row each, hit 32 different banks); the ring is free: acc_full says every MMA that read it has completed
+      // push this CTA's partial sums into the first CTA's exchange buffer, column-major (element (row, col) at
+      // col * 128 + row: the 32 lanes of a warp write 128 consecutive bytes)
+      const uint32_t dst = map_to_cta(s_base + L::kXbuf, 0u) + (uint32_t)((rank - 1) * BNX * BM + row_in_tile) * 4u;
 #pragma unroll
       for (int c = 0; c < BNX; c += 16) {
+        if (c >= p.M) break;
         uint32_t v[16];
         tmem_ld16(t_acc + (uint32_t)c, v);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) xbuf[(c + j) * BM + row_in_tile] = __uint_as_float(v[j]);
+        for (int j = 0; j < 16; ++j) st_cluster_f32(dst + (uint32_t)((c + j) * BM) * 4u, __uint_as_float(v[j]));
       }
       tc_fence_before();
     }
   }
-  if (p.split > 1) cluster_sync();  // every thread of every CTA of the cluster
+  if (p.split > 1) cluster_sync();  // every thread of every CTA: the pushed sums are visible in the first CTA
   if (warp >= 2 && rank == 0 && have_acc) {
     grid_dependency_wait();  // nothing of the previous kernel may still be reading D
     const int n = n_blk * BM + row_in_tile;
@@ -1153,7 +1157,7 @@ umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     if (p.bias != nullptr && n < p.N)
       bias = p.bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.bias)[n])
                          : reinterpret_cast<const float *>(p.bias)[n];
-    const uint32_t xoff = s_base + L::kXbuf + (uint32_t)row_in_tile * 4u;
+    const float *xbuf = reinterpret_cast<const float *>(smem + L::kXbuf) + row_in_tile;
 #pragma unroll
     for (int c = 0; c < BNX; c += 16) {
       if (c >= p.M) break;
@@ -1163,9 +1167,8 @@ umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 #pragma unroll
       for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(v[j]);
       for (int r = 1; r < p.split; ++r) {  // fixed order: repeatable sums
-        const uint32_t peer = map_to_cta(xoff, (uint32_t)r);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) f[j] += ld_cluster_f32(peer + (uint32_t)((c + j) * BM) * 4u);
+        for (int j = 0; j < 16; ++j) f[j] += xbuf[((r - 1) * BNX + c + j) * BM];
       }
       if (n < p.N) {
 #pragma unroll
@@ -1183,7 +1186,6 @@ umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
     tc_fence_before();
   }
-  if (p.split > 1) cluster_sync();  // the other CTAs keep their shared memory until the first one has read it
 
   tc_fence_before();
   __syncthreads();
@@ -1449,10 +1451,9 @@ static int launch_swap(const void *a, const void *b, const uint8_t *sfa, const u
   }
   const int64_t tiles = (N + BM - 1) / BM;
   const int sms = o.max_ctas > 0 && o.max_ctas < sm_count() ? o.max_ctas : sm_count();
-  // shares of K: as many CTAs as there are SMs, at least 4 chunks each, clusters of at most 8
+  // shares of K: as many CTAs as there are SMs, at least 4 chunks each
   int split = 1;
-  while (o.split_k && split < 8 && tiles * split * 2 <= sms && k_chunks / (split * 2) >= 4) split *= 2;
-  if (const char *e = getenv("MXQ_EXP_SPLIT")) split = atoi(e);  // EXPERIMENT
+  while (o.split_k && split < L::kMaxSplit && tiles * split * 2 <= sms && k_chunks / (split * 2) >= 4) split *= 2;
   SwapParams p;
   p.d = d, p.bias = bias, p.status = status, p.M = (int)M, p.N = (int)N, p.k_chunks = (int)k_chunks, p.split = split;
   p.x_box_bytes = x_rows * kRowBytes;
