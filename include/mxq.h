@@ -179,19 +179,33 @@ int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k);
 int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k, int E,
                       int F, const uint8_t *floor_tab_host, void *stream);
 
-/* Block-scaled GEMM on operands produced by mxq_mxfp_pack_mma (kind::mxf8f6f4, one E8M0 scale per 32 elements of
- * K).  Replaces quantize-activations + F.linear of LinearMXFP.forward (chop/nn/quantized/modules/linear.py:877-895). */
+/* The same for MXFP4 (E2M1) only, with the codes nibble-packed: codes4 is [rows, k/2] bytes, element 2i of a row in
+ * the low nibble of byte i and element 2i+1 in the high nibble, each nibble the reference's code sign|exponent|fraction
+ * (chop/nn/quantizers/_minifloat_mx/fake.py:90-91), which is the hardware's FP4 encoding as it stands.  Scales as
+ * above.  Weight storage of 0.53 bytes per element: the copy engine expands the nibbles on their way into shared
+ * memory, so the GEMM also moves half the weight bytes.  k % 64 == 0; codes4 32-byte aligned. */
+int mxq_mxfp4_pack_mma(const void *x, uint8_t *codes4, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k,
+                       const uint8_t *floor_tab_host, void *stream);
+
+/* layout of the codes of a GEMM operand */
+#define MXQ_CODES_E4M3 0    /* one hardware E4M3 byte per element (mxq_mxfp_pack_mma) */
+#define MXQ_CODES_E2M1X2 1  /* two E2M1 nibbles per byte (mxq_mxfp4_pack_mma); B operand only */
+
+/* Block-scaled GEMM on operands produced by mxq_mxfp_pack_mma / mxq_mxfp4_pack_mma (kind::mxf8f6f4, one E8M0 scale
+ * per 32 elements of K).  A is always E4M3 bytes; b_format says how B (the weight) is stored.  Replaces
+ * quantize-activations + F.linear of LinearMXFP.forward (chop/nn/quantized/modules/linear.py:877-895). */
 int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_codes, const uint8_t *b_scales,
-                  void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status,
-                  const mxq_gemm_options *options, void *stream);
+                  int b_format, void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K,
+                  int *status, const mxq_gemm_options *options, void *stream);
 
 /* LinearMXFP.forward in one call (chop/nn/quantized/modules/linear.py:877-895): quantize x[M,K] to MXFP(E,F),
  * block 32 along K, into `workspace` (scratch owned by the caller, 256-byte aligned, at least
  * mxq_mx_linear_workspace_bytes(M, K) bytes), then D = x_q * W_q^T (+ bias) with the block-scaled GEMM.
- * w_codes / w_scales come from mxq_mxfp_pack_mma on the [N,K] weight. */
+ * w_codes / w_scales come from mxq_mxfp_pack_mma (w_format MXQ_CODES_E4M3) or mxq_mxfp4_pack_mma (MXQ_CODES_E2M1X2) on
+ * the [N,K] weight. */
 int64_t mxq_mx_linear_workspace_bytes(int64_t M, int64_t K);
-int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d, const void *bias,
-                  int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
+int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, int w_format, void *d,
+                  const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
                   const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status,
                   const mxq_gemm_options *options, void *stream);
 
@@ -209,7 +223,7 @@ int mxq_silu_mul_pack_mma(const void *gate, const void *up, int64_t ld, uint8_t 
  * mxq_silu_mul_pack_mma into `workspace` followed by the block-scaled GEMM.  Workspace size and the other arguments
  * as for mxq_mx_linear (K = columns of gate / up). */
 int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint8_t *w_codes, const uint8_t *w_scales,
-                        void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E,
+                        int w_format, void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E,
                         int F, const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status,
                         const mxq_gemm_options *options, void *stream);
 
@@ -237,7 +251,7 @@ int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint
  *     other's result: serialise them.
  * Arguments and results are otherwise those of mxq_mx_linear. */
 #define MXQ_STATIC_SCRATCH_BYTES (40u << 20)
-int mxq_mx_linear_static(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d,
+int mxq_mx_linear_static(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, int w_format, void *d,
                          const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
                          const uint8_t *floor_tab_host, int *status, const mxq_gemm_options *options, void *stream);
 

@@ -27,16 +27,17 @@ _PROTOTYPES = {
     "mxq_mma_scale_bytes": [c_int64, c_int64],
     "mxq_gemm_options_size": [],
     "mxq_mxfp_pack_mma": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p],
-    "mxq_gemm_mxf8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
+    "mxq_mxfp4_pack_mma": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p],
+    "mxq_gemm_mxf8": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
                       c_int64, c_void_p, c_void_p, c_void_p],
     "mxq_mx_linear_workspace_bytes": [c_int64, c_int64],
-    "mxq_mx_linear": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64,
+    "mxq_mx_linear": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64,
                       c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p],
     "mxq_silu_mul_pack_mma": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p,
                               c_void_p],
-    "mxq_mx_gated_linear": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
+    "mxq_mx_gated_linear": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64,
                             c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p],
-    "mxq_mx_linear_static": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
+    "mxq_mx_linear_static": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
                              c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "mxq_bfp_fake_tiles": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
                            c_void_p, c_void_p],
@@ -53,6 +54,7 @@ class GemmOptions(ctypes.Structure):
 
 
 TILES_AUTO, TILES_SINGLE, TILES_PAIRS = 0, 1, 2
+CODES_E4M3, CODES_E2M1X2 = 0, 1
 TEST_DROP_LAST_LOAD = 1
 
 

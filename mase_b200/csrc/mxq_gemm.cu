@@ -207,6 +207,9 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
                :: "memory");
 }
 
+// element format codes of the block-scaled kind's instruction descriptor (A: bits 7-9, B: bits 10-12); E4M3 is 0
+constexpr uint32_t kFormatE2M1 = 5;
+
 // instruction descriptor: fp32 accumulate, K-major A and B, M = 128, N = BN
 template <int kKind, int BN>
 __device__ __forceinline__ uint32_t make_idesc() {
@@ -255,6 +258,7 @@ struct Params {
   int a_box_bytes;      // bytes one A load delivers: fewer than 128 rows when M is small (single-CTA kernel)
   unsigned long long wait_ns;  // limit of every wait
   int drop_last_load;   // test hook: CTA 0 never loads the last K chunk of its first tile
+  uint32_t b_fp4;       // block-scaled kind: B holds E2M1 elements (two per byte in global memory) instead of E4M3 bytes
 };
 
 // Epilogue of one tile for one warp: drains the warp's 32 TMEM lanes (= 32 tile rows starting at row0) of the
@@ -496,7 +500,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    const uint32_t idesc = make_idesc<kKind, BN>();
+    const uint32_t idesc = make_idesc<kKind, BN>() | (p.b_fp4 ? kFormatE2M1 << 10 : 0u);
     uint32_t idk[4];  // per 32 bytes of K: byte k of each scale word
 #pragma unroll
     for (int k = 0; k < 4; ++k) idk[k] = kScaled ? idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4) : idesc;
@@ -833,7 +837,8 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (leader) {
       // ---------------- MMA issuer (leader only; warp-uniform loop, one elected lane issues) ----------------
       // the single-CTA descriptor with M = 256 (both CTAs) instead of 128
-      const uint32_t idesc = (make_idesc<kKind, BN>() & ~(0x1Fu << 24)) | ((uint32_t)(256 >> 4) << 24);
+      const uint32_t idesc = (make_idesc<kKind, BN>() & ~(0x1Fu << 24)) | ((uint32_t)(256 >> 4) << 24) |
+                             (p.b_fp4 ? kFormatE2M1 << 10 : 0u);
       uint32_t idk[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k)  // block-scaled: byte k of each scale word
@@ -971,6 +976,7 @@ struct SwapParams {
   int split;         // CTAs per cluster = shares of K
   int x_box_bytes;   // bytes one activation load delivers
   int out_bf16, bias_bf16;
+  uint32_t w_fp4;    // block-scaled kind: the weight holds E2M1 elements, two per byte in global memory
   unsigned long long wait_ns;
 };
 
@@ -1096,7 +1102,7 @@ umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    const uint32_t idesc = make_idesc<kKind, BNX>();
+    const uint32_t idesc = make_idesc<kKind, BNX>() | (p.w_fp4 ? kFormatE2M1 << 7 : 0u);  // the weight is operand A here
     uint32_t idk[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) idk[k] = kScaled ? idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4) : idesc;
@@ -1229,6 +1235,23 @@ static int make_map(CUtensorMap *map, const void *ptr, int kind, int64_t rows, i
   return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
+// Tensor map of a K-major matrix [rows, k] of 4-bit elements stored two per byte: the copy engine expands each group
+// of 16 elements (8 bytes in global memory) to 16 bytes of shared memory, the padded form in which the block-scaled
+// MMA reads 4-bit operands.  A box is box_rows x 128 elements and lands as box_rows x 128 bytes, 128-byte swizzle --
+// the footprint of an E4M3 box -- while only half the bytes travel.  Needs k % 64 == 0 and a 32-byte aligned base.
+static int make_map_fp4(CUtensorMap *map, const void *ptr, int64_t rows, int64_t k, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return MXQ_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k / 2};
+  cuuint32_t box[2] = {128, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_UNSUPPORTED;
+}
+
 // tensor map of the output [rows, n] for stores of 32-row x 64-byte boxes, 64-byte swizzle
 static int make_store_map(CUtensorMap *map, void *ptr, bool bf16, int64_t rows, int64_t n) {
   EncodeTiledFn fn = encode_fn();
@@ -1323,7 +1346,7 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   const int a_rows = M < BM ? (int)((M + 7) / 8 * 8) : BM;
   int rc = make_map(&ma, a, kKind, M, K, a_rows);
   if (rc) return rc;
-  rc = make_map(&mb, b, kKind, N, K, BN);
+  rc = o.b_fp4 ? make_map_fp4(&mb, b, N, K, BN) : make_map(&mb, b, kKind, N, K, BN);
   if (rc) return rc;
   const bool out_bf16 = out_dtype == MXQ_BF16;
   const bool tma_store = (N * (out_bf16 ? 2 : 4)) % 16 == 0;
@@ -1340,6 +1363,7 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
   p.a_box_bytes = a_rows * kRowBytes;
   p.wait_ns = o.wait_ns, p.drop_last_load = !kSplit && o.test_hook == MXQ_TEST_DROP_LAST_LOAD;
+  p.b_fp4 = o.b_fp4 ? 1u : 0u;
   CUtensorMap msa = ma, msb = ma;  // unused by the dense kinds
   if constexpr (kKind == kMxf8) {
     rc = make_sf_map(&msa, sfa, ((M + 255) / 256) * 2 * p.k_chunks);
@@ -1381,7 +1405,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   CUtensorMap ma, mb, msa, msb, md;
   int rc = make_map(&ma, a, kKind, M, K, BM);
   if (rc) return rc;
-  rc = make_map(&mb, b, kKind, N, K, 128);
+  rc = o.b_fp4 ? make_map_fp4(&mb, b, N, K, 128) : make_map(&mb, b, kKind, N, K, 128);
   if (rc) return rc;
   const int64_t k_chunks = (K * es + kRowBytes - 1) / kRowBytes;
   msa = ma, msb = ma;  // unused by the dense kinds
@@ -1406,6 +1430,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   p.out_bf16 = out_bf16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.tma_store = tma_store;
   p.a_box_bytes = BM * kRowBytes;
   p.wait_ns = o.wait_ns, p.drop_last_load = 0;
+  p.b_fp4 = o.b_fp4 ? 1u : 0u;
   static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
   bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {
@@ -1438,7 +1463,7 @@ static int launch_swap(const void *a, const void *b, const uint8_t *sfa, const u
   const int64_t k_chunks = (K * es + kRowBytes - 1) / kRowBytes;
   const int x_rows = (int)((M + 7) / 8 * 8) < BNX ? (int)((M + 7) / 8 * 8) : BNX;
   CUtensorMap mw, mx, msw, msx;
-  int rc = make_map(&mw, b, kKind, N, K, BM);
+  int rc = o.b_fp4 ? make_map_fp4(&mw, b, N, K, BM) : make_map(&mw, b, kKind, N, K, BM);
   if (rc) return rc;
   rc = make_map(&mx, a, kKind, M, K, x_rows);
   if (rc) return rc;
@@ -1458,6 +1483,7 @@ static int launch_swap(const void *a, const void *b, const uint8_t *sfa, const u
   p.d = d, p.bias = bias, p.status = status, p.M = (int)M, p.N = (int)N, p.k_chunks = (int)k_chunks, p.split = split;
   p.x_box_bytes = x_rows * kRowBytes;
   p.out_bf16 = out_dtype == MXQ_BF16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.wait_ns = o.wait_ns;
+  p.w_fp4 = o.b_fp4 ? 1u : 0u;
   static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
   bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {
@@ -1566,10 +1592,13 @@ int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int 
 }
 
 int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_codes, const uint8_t *b_scales,
-                  void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status,
-                  const mxq_gemm_options *options, void *stream) {
-  return mxq::gemm::gemm_mxf8(a_codes, a_scales, b_codes, b_scales, d, bias, out_dtype, bias_dtype, M, N, K, status,
-                              make_opts(options), (cudaStream_t)stream);
+                  int b_format, void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K,
+                  int *status, const mxq_gemm_options *options, void *stream) {
+  Opts o = make_opts(options);
+  if (b_format != MXQ_CODES_E4M3 && b_format != MXQ_CODES_E2M1X2) return MXQ_ERR_FORMAT;
+  o.b_fp4 = b_format == MXQ_CODES_E2M1X2;
+  return mxq::gemm::gemm_mxf8(a_codes, a_scales, b_codes, b_scales, d, bias, out_dtype, bias_dtype, M, N, K, status, o,
+                              (cudaStream_t)stream);
 }
 
 }  // extern "C"
@@ -1584,6 +1613,7 @@ int gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_
   if (M == 0 || N == 0) return MXQ_OK;
   if (!a_codes || !a_scales || !b_codes || !b_scales || !d) return MXQ_ERR_NULL;
   if (M < 0 || N < 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || K % 32) return MXQ_ERR_SHAPE;
+  if (o.b_fp4 && (K % 64 || (reinterpret_cast<uintptr_t>(b_codes) & 31u))) return MXQ_ERR_SHAPE;
   if (out_dtype != MXQ_F32 && out_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
   if (bias && bias_dtype != MXQ_F32 && bias_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
   if ((reinterpret_cast<uintptr_t>(a_codes) | reinterpret_cast<uintptr_t>(b_codes) | reinterpret_cast<uintptr_t>(d) |

@@ -19,6 +19,7 @@ struct Opts {
   bool transposed = true;  // problems of at most 128 rows go to the transposed (weight-major) kernel
   unsigned long long wait_ns = kDefaultWaitNs;
   int test_hook = 0;
+  bool b_fp4 = false;  // block-scaled kind: B (the weight) holds E2M1 elements, two per byte
 };
 
 Opts make_opts(const mxq_gemm_options *o);

@@ -43,8 +43,8 @@ int64_t mxq_mx_linear_workspace_bytes(int64_t M, int64_t K) {
   return align256(M * K) + align256(sf);  // codes, scale chunks
 }
 
-int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d, const void *bias,
-                  int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
+int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, int w_format, void *d,
+                  const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
                   const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status,
                   const mxq_gemm_options *options, void *stream) {
   if (M == 0 || N == 0) return MXQ_OK;
@@ -57,11 +57,12 @@ int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uin
   uint8_t *a_scales = a_codes + align256(M * K);
   const int rc = mxq_mxfp_pack_mma(x, a_codes, a_scales, in_dtype, M, K, E, F, floor_tab_host, stream);
   if (rc != MXQ_OK) return rc;
-  return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, d, bias, out_dtype, bias_dtype, M, N, K, status, options, stream);
+  return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, w_format, d, bias, out_dtype, bias_dtype, M, N, K, status,
+                       options, stream);
 }
 
 int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint8_t *w_codes, const uint8_t *w_scales,
-                        void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E,
+                        int w_format, void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E,
                         int F, const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status,
                         const mxq_gemm_options *options, void *stream) {
   if (M == 0 || N == 0) return MXQ_OK;
@@ -74,10 +75,11 @@ int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint
   uint8_t *a_scales = a_codes + align256(M * K);
   const int rc = mxq_silu_mul_pack_mma(gate, up, ld, a_codes, a_scales, M, K, E, F, floor_tab_host, stream);
   if (rc != MXQ_OK) return rc;
-  return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, d, bias, out_dtype, bias_dtype, M, N, K, status, options, stream);
+  return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, w_format, d, bias, out_dtype, bias_dtype, M, N, K, status,
+                       options, stream);
 }
 
-int mxq_mx_linear_static(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, void *d,
+int mxq_mx_linear_static(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, int w_format, void *d,
                          const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int E, int F,
                          const uint8_t *floor_tab_host, int *status, const mxq_gemm_options *options, void *stream) {
   if (M == 0 || N == 0) return MXQ_OK;
@@ -91,7 +93,7 @@ int mxq_mx_linear_static(const void *x, int in_dtype, const uint8_t *w_codes, co
   // rows before reading them; scale bytes of the padding rows (up to the next multiple of 256) may be an earlier call's
   // and are read by the tensor cores, but only scale accumulator rows >= M, which are never stored; scale bytes of K
   // blocks past the end of a row are cleared by the pack step whenever K % 128 != 0.
-  return mxq_mx_linear(x, in_dtype, w_codes, w_scales, d, bias, out_dtype, bias_dtype, M, N, K, E, F, floor_tab_host,
+  return mxq_mx_linear(x, in_dtype, w_codes, w_scales, w_format, d, bias, out_dtype, bias_dtype, M, N, K, E, F, floor_tab_host,
                        scratch, MXQ_STATIC_SCRATCH_BYTES, status, options, stream);
 }
 

@@ -408,6 +408,40 @@ silu_mul_pack_mma_kernel(const __nv_bfloat16 *__restrict__ gate, const __nv_bflo
   }
 }
 
+// MXFP4 (E2M1) weights as nibble-packed tensor-core operands: one thread per block of 32 elements, the element codec
+// of the generic path, two codes per byte (element 2i in the low nibble), the scale in the tensor-core chunk layout.
+// Runs once per weight at load time.
+template <typename Tin>
+__global__ void __launch_bounds__(kThreads)
+mxfp4_pack_mma_kernel(const Tin *__restrict__ x, uint8_t *__restrict__ codes4, uint8_t *__restrict__ scales,
+                      int64_t n_blocks, int64_t blocks_per_row, int64_t k_chunks, const __grid_constant__ Log2Tab tab) {
+  for (int64_t blk = (int64_t)blockIdx.x * kThreads + threadIdx.x; blk < n_blocks;
+       blk += (int64_t)gridDim.x * kThreads) {
+    const Tin *xb = x + blk * 32;
+    uint32_t bits[32];
+    uint32_t amax = 0;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      uint32_t b = __float_as_uint(load_scalar(xb + k));
+      if (((b & 0x7FFFFFFFu) >> 23) == 0) b = 0;  // zero and fp32-subnormal inputs are flushed
+      bits[k] = b;
+      amax = max(amax, b & 0x7FFFFFFFu);
+    }
+    const MxfpBlock p = mxfp_block(amax, 2, tab);
+    uint32_t w[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) word |= (mxfp_encode(bits[8 * q + k], p.sh, 2, 1) & 0xFu) << (4 * k);
+      w[q] = word;
+    }
+    *reinterpret_cast<uint4 *>(codes4 + blk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    const int64_t row = blk / blocks_per_row, kb = blk - row * blocks_per_row;
+    scales[mma_scale_offset<int64_t>(row, kb, k_chunks)] = (uint8_t)p.scale;
+  }
+}
+
 // MXINT mantissas and shared exponents of bf16 tensors in blocks of 32: the same half-block-per-lane scheme.
 template <bool kWide>
 __global__ void __launch_bounds__(kThreads, 4)
@@ -902,6 +936,30 @@ int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in
 #undef MXQ_PACK
 #undef MXQ_PACK_ARGS
   return MXQ_ERR_FORMAT;
+}
+
+int mxq_mxfp4_pack_mma(const void *x, uint8_t *codes4, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k,
+                       const uint8_t *floor_tab_host, void *stream) {
+  if (rows == 0 || k == 0) return MXQ_OK;
+  if (!x || !codes4 || !scales_mma || !floor_tab_host) return MXQ_ERR_NULL;
+  if (rows < 0 || k < 0 || k % 64) return MXQ_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(codes4) & 31u) return MXQ_ERR_ALIGN;
+  const Log2Tab tab = load_tab(floor_tab_host);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t k_chunks = (k + 127) / 128;
+  const int64_t sf_bytes = ((rows + 255) / 256) * 2 * k_chunks * 512;
+  // scale bytes of K blocks past the end of a row must be finite (see mxq_mxfp_pack_mma)
+  if (k % 128 && cudaMemsetAsync(scales_mma, 0, sf_bytes, st) != cudaSuccess) return MXQ_ERR_LAUNCH;
+  const int64_t n_blocks = rows * (k / 32);
+  if (in_dtype == MXQ_F32)
+    mxfp4_pack_mma_kernel<float><<<grid_for(n_blocks, kThreads), kThreads, 0, st>>>((const float *)x, codes4, scales_mma,
+                                                                                   n_blocks, k / 32, k_chunks, tab);
+  else if (in_dtype == MXQ_BF16)
+    mxfp4_pack_mma_kernel<__nv_bfloat16><<<grid_for(n_blocks, kThreads), kThreads, 0, st>>>(
+        (const __nv_bfloat16 *)x, codes4, scales_mma, n_blocks, k / 32, k_chunks, tab);
+  else
+    return MXQ_ERR_DTYPE;
+  return check_launch();
 }
 
 int mxq_silu_mul_pack_mma(const void *gate, const void *up, int64_t ld, uint8_t *codes, uint8_t *scales_mma,

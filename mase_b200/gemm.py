@@ -130,10 +130,15 @@ def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None, out_dtype: to
 class MXOperand:
     """A [rows, K] matrix as tensor-core operands: hardware E4M3 bytes and E8M0 scales in the MMA chunk layout."""
 
-    codes: Tensor   # uint8 [rows, K]
+    codes: Tensor   # uint8 [rows, K] (E4M3 bytes) or [rows, K / 2] (two E2M1 nibbles per byte, `fp4`)
     scales: Tensor  # uint8 [mxq_mma_scale_bytes(rows, K)]
     rows: int
     k: int
+    fp4: bool = False  # weights only: MXFP4 codes nibble-packed; the copy engine expands them on the way to the MMA
+
+    @property
+    def format(self) -> int:
+        return _lib.CODES_E2M1X2 if self.fp4 else _lib.CODES_E4M3
 
 
 def mma_supported(exp_bits: int, frac_bits: int, block_size: int, k: int) -> bool:
@@ -141,8 +146,14 @@ def mma_supported(exp_bits: int, frac_bits: int, block_size: int, k: int) -> boo
     return block_size == 32 and exp_bits <= 4 and frac_bits <= 3 and k % 32 == 0
 
 
-def pack_mx_operand(x: Tensor, exp_bits: int, frac_bits: int) -> MXOperand:
-    """MXFP(exp_bits, frac_bits), block 32 along the last dim, of a 2-D tensor, stored for the tensor cores."""
+def fp4_supported(exp_bits: int, frac_bits: int, k: int) -> bool:
+    """Weights that can be kept as nibble-packed MXFP4: E2M1 elements and rows of whole 32-byte groups."""
+    return exp_bits == 2 and frac_bits == 1 and k % 64 == 0
+
+
+def pack_mx_operand(x: Tensor, exp_bits: int, frac_bits: int, fp4: bool = False) -> MXOperand:
+    """MXFP(exp_bits, frac_bits), block 32 along the last dim, of a 2-D tensor, stored for the tensor cores.
+    `fp4=True` (E2M1 weights): two codes per byte instead of one E4M3 byte per element."""
     _require_cuda(x, "pack_mx_operand")
     if x.dtype not in _DT:
         raise NotImplementedError(f"pack_mx_operand: dtype {x.dtype} is not supported")
@@ -154,8 +165,17 @@ def pack_mx_operand(x: Tensor, exp_bits: int, frac_bits: int) -> MXOperand:
     if xc.data_ptr() % 16:
         xc = xc.clone()
     lib = _lib.lib()
-    codes = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
     scales = torch.empty((int(lib.mxq_mma_scale_bytes(rows, k)),), dtype=torch.uint8, device=x.device)
+    if fp4:
+        if not fp4_supported(exp_bits, frac_bits, k):
+            raise NotImplementedError("nibble-packed operands need E2M1 elements and K divisible by 64")
+        codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+        with _on_device(x):
+            rc = lib.mxq_mxfp4_pack_mma(xc.data_ptr(), codes.data_ptr(), scales.data_ptr(), _DT[x.dtype], rows, k,
+                                        _floor_tab_ptr(), _stream(x))
+        _lib.check(rc, "mxq_mxfp4_pack_mma")
+        return MXOperand(codes, scales, rows, k, True)
+    codes = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
     with _on_device(x):
         rc = lib.mxq_mxfp_pack_mma(xc.data_ptr(), codes.data_ptr(), scales.data_ptr(), _DT[x.dtype], rows, k, exp_bits,
                                    frac_bits, _floor_tab_ptr(), _stream(x))
@@ -211,7 +231,8 @@ def mx_gated_linear(gate: Tensor, up: Tensor, weight: MXOperand, bias: Tensor | 
     st = _status(gate.device)
     with _on_device(gate):
         rc = lib.mxq_mx_gated_linear(g2.data_ptr(), u2.data_ptr(), g2.stride(0), weight.codes.data_ptr(),
-                                     weight.scales.data_ptr(), out.data_ptr(), 0 if bb is None else bb.data_ptr(),
+                                     weight.scales.data_ptr(), weight.format, out.data_ptr(),
+                                     0 if bb is None else bb.data_ptr(),
                                      _DT[out.dtype], bdt, M, N, K, exp_bits, frac_bits, _floor_tab_ptr(), ws.data_ptr(),
                                      ws_bytes, st.data_ptr(), _options_ptr(), _stream(gate))
     _lib.check(rc, "mxq_mx_gated_linear")
@@ -222,13 +243,13 @@ def mx_gated_linear(gate: Tensor, up: Tensor, weight: MXOperand, bias: Tensor | 
 
 def mx_gemm(a: MXOperand, b: MXOperand, bias: Tensor | None, out_dtype: torch.dtype) -> Tensor:
     """[a.rows, b.rows] = a @ b^T (+ bias) with block-scaled MXFP8 tensor-core MMAs, fp32 accumulation."""
-    assert a.k == b.k
+    assert a.k == b.k and not a.fp4, "the first operand is always E4M3 bytes"
     out = torch.empty((a.rows, b.rows), dtype=out_dtype, device=a.codes.device)
     bb, bdt = _bias_args(bias)
     st = _status(a.codes.device)
     with _on_device(a.codes):
         rc = _lib.lib().mxq_gemm_mxf8(a.codes.data_ptr(), a.scales.data_ptr(), b.codes.data_ptr(), b.scales.data_ptr(),
-                                      out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[out_dtype], bdt, a.rows,
+                                      b.format, out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[out_dtype], bdt, a.rows,
                                       b.rows, a.k, st.data_ptr(), _options_ptr(), _stream(a.codes))
     _lib.check(rc, "mxq_gemm_mxf8")
     if _CHECK_EVERY_CALL:
@@ -258,7 +279,7 @@ def mx_linear(x: Tensor, weight: MXOperand, bias: Tensor | None, exp_bits: int, 
     st = _status(x.device)
     with _on_device(x):
         rc = lib.mxq_mx_linear(a.data_ptr(), _DT[x.dtype], weight.codes.data_ptr(), weight.scales.data_ptr(),
-                               out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[out.dtype], bdt, M, N, K, exp_bits,
+                               weight.format, out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[out.dtype], bdt, M, N, K, exp_bits,
                                frac_bits, _floor_tab_ptr(), ws.data_ptr(), ws_bytes, st.data_ptr(), _options_ptr(),
                                _stream(x))
     _lib.check(rc, "mxq_mx_linear")

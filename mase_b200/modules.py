@@ -15,7 +15,8 @@ from functools import partial
 import torch
 from torch import Tensor
 
-from .gemm import (MXOperand, linear_forward, mma_supported, mx_gated_linear, mx_gemm, mx_linear, pack_mx_operand)
+from .gemm import (MXOperand, fp4_supported, linear_forward, mma_supported, mx_gated_linear, mx_gemm, mx_linear,
+                   pack_mx_operand)
 from .quantizers import block_fp_quantizer, mxfp_quantizer, mxint_quantizer
 
 
@@ -47,7 +48,21 @@ class LinearMXFP(_LinearBase):
     def load_state_dict(self, state_dict, strict=True, assign=False):
         """Load pretrained weights, then quantize them in place (blocks run along in_features)."""
         if "weight_codes" in state_dict:  # written by a layer after drop_dense_weight()
+            from . import _lib
+
             dev = self.weight.device
+            codes, scales = state_dict["weight_codes"], state_dict["weight_scales"]
+            want = [(self.out_features, self.in_features), (self.out_features, self.in_features // 2)]
+            if tuple(codes.shape) not in want or codes.dtype != torch.uint8:
+                raise RuntimeError(f"weight_codes of shape {tuple(codes.shape)} do not fit a layer "
+                                   f"{self.in_features} -> {self.out_features}")
+            if scales.numel() != int(_lib.lib().mxq_mma_scale_bytes(self.out_features, self.in_features)):
+                raise RuntimeError(f"weight_scales hold {scales.numel()} bytes, not the scale array of a "
+                                   f"[{self.out_features}, {self.in_features}] operand")
+            if strict:
+                unexpected = [k for k in state_dict if k not in ("weight", "bias", "weight_codes", "weight_scales")]
+                if unexpected:
+                    raise RuntimeError(f"unexpected keys in state_dict: {unexpected}")
             self._weight_dtype = self.weight.dtype
             self.register_buffer("weight_codes", state_dict["weight_codes"].to(dev), persistent=True)
             self.register_buffer("weight_scales", state_dict["weight_scales"].to(dev), persistent=True)
@@ -96,26 +111,48 @@ class LinearMXFP(_LinearBase):
         if not (mma_supported(cfg["weight_exponent_width"], cfg["weight_frac_width"], cfg["weight_block_size"], w.shape[1])
                 and mma_supported(x_exp, x_frac, x_block, w.shape[1])):
             return
-        op = pack_mx_operand(w, cfg["weight_exponent_width"], cfg["weight_frac_width"])
+        # MXFP4 weights stay nibble-packed (0.53 bytes per element with the scales); other formats are E4M3 bytes
+        op = pack_mx_operand(w, cfg["weight_exponent_width"], cfg["weight_frac_width"],
+                             fp4=fp4_supported(cfg["weight_exponent_width"], cfg["weight_frac_width"], w.shape[1]))
         self.register_buffer("_mx_w_codes", op.codes, persistent=False)
         self.register_buffer("_mx_w_scales", op.scales, persistent=False)
         self._mx_weight_version = self.weight._version
+        self._mx_weight_key = (self.weight.data_ptr(), tuple(self.weight.shape), self.weight.dtype)
+
+    def _apply(self, fn, recurse=True):
+        """Module.to / .cuda move `weight` and the packed copy together: the copy stays valid when only the device
+        (and with it the storage pointer) changed, not when the move also changed the dtype."""
+        valid = self._buffers.get("_mx_w_codes") is not None and self._packed_weight() is not None
+        dtype = self.weight.dtype
+        out = super()._apply(fn, recurse)
+        if valid and self.weight.dtype == dtype and self._buffers["_mx_w_codes"].device == self.weight.device:
+            self._mx_weight_version = self.weight._version
+            self._mx_weight_key = (self.weight.data_ptr(), tuple(self.weight.shape), self.weight.dtype)
+        return out
+
+    def _operand(self, codes: Tensor, scales: Tensor) -> MXOperand:
+        fp4 = codes.shape[1] * 2 == self.in_features and codes.shape[1] != self.in_features
+        return MXOperand(codes, scales, codes.shape[0], self.in_features, fp4)
 
     def _packed_weight(self) -> MXOperand | None:
+        """The tensor-core copy of the weight, or None when there is none or `weight` has changed since it was made.
+        The copy is tied to the parameter's version counter, storage pointer and shape; an update that bypasses all
+        three (writing through `weight.data` in place) needs a call of `_pack_weight_for_tensor_cores()`."""
         if getattr(self, "_dense_dropped", False):
-            codes = self._buffers["weight_codes"]
-            return MXOperand(codes, self._buffers["weight_scales"], codes.shape[0], codes.shape[1])
+            return self._operand(self._buffers["weight_codes"], self._buffers["weight_scales"])
         codes = self._buffers.get("_mx_w_codes")
         if codes is None or getattr(self, "_mx_weight_version", None) != self.weight._version:
             return None
+        if getattr(self, "_mx_weight_key", None) != (self.weight.data_ptr(), tuple(self.weight.shape), self.weight.dtype):
+            return None
         if codes.device != self.weight.device:
             return None
-        return MXOperand(codes, self._buffers["_mx_w_scales"], codes.shape[0], codes.shape[1])
+        return self._operand(codes, self._buffers["_mx_w_scales"])
 
     def drop_dense_weight(self) -> None:
         """Weight-only memory saving (not in the reference, whose state_dict keeps the fake-quantized tensor in the
-        original dtype): keep only the tensor-core operands -- one byte per element plus one scale byte per 32 --
-        and release the bf16 / fp32 `weight`.  The state_dict then carries `weight_codes` and `weight_scales`
+        original dtype): keep only the tensor-core operands -- one byte per element (half a byte for MXFP4 weights,
+        which are stored nibble-packed) plus one scale byte per 32 -- and release the bf16 / fp32 `weight`.  The state_dict then carries `weight_codes` and `weight_scales`
         (which `load_state_dict` accepts) and an empty `weight`; forward needs CUDA inputs of the original dtype."""
         packed = self._packed_weight()
         if packed is None:

@@ -201,3 +201,34 @@ def test_transposed_small_m_kernel_vs_oracle_and_regular_tiles(shape):
     assert float((y1 - y_tiles).abs().max() / y_tiles.abs().max()) <= 1e-5
     assert rel_err(y16, ref) <= 4e-3
     assert rel_err(d16, ref) <= 4e-3 and rel_err(d32, ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (16, 1024, 1000), (100, 4032, 768), (128, 512, 512), (300, 1024, 260),
+                                   (512, 2048, 1024), (2048, 4096, 4096), (1000, 11008, 1304)])
+def test_nibble_packed_mxfp4_weight_matches_e4m3_bytes(shape):
+    """MXFP4 weights stored two codes per byte (the copy engine expands them on the way into shared memory) give the
+    bits of the same weights stored as E4M3 bytes, on every tile scheme, and match the oracle."""
+    M, K, N = shape
+    x, w = synthetic.linear_operands(M, K, N, seed=10)
+    g = torch.Generator().manual_seed(10)
+    b = torch.randn(N, generator=g).bfloat16().to(DEV)
+    ref = O.mxfp_fake(x, 32, 4, 3).float() @ O.mxfp_fake(w, 32, 2, 1, 1).float().t() + b.float().cpu()
+    xp = gemm.pack_mx_operand(x.to(DEV), 4, 3)
+    w8 = gemm.pack_mx_operand(w.to(DEV), 2, 1)
+    w4 = gemm.pack_mx_operand(w.to(DEV), 2, 1, fp4=True)
+    assert w4.codes.shape == (N, K // 2) and w4.fp4
+    # the nibbles are the reference's own codes
+    sc, co = O.mxfp_extract(w, 32, 2, 1)
+    co = co.view(N, K)
+    assert torch.equal(w4.codes.cpu(), co[:, 0::2] | (co[:, 1::2] << 4))
+    schemes = [{}] if M <= 128 else [{"tiles": _lib.TILES_SINGLE}, {"tiles": _lib.TILES_PAIRS}]
+    if M <= 128:
+        schemes.append({"no_transposed": 1})
+    for fields in schemes:
+        with gemm.options(**fields):
+            y8 = gemm.mx_gemm(xp, w8, b, torch.float32)
+            y4 = gemm.mx_gemm(xp, w4, b, torch.float32)
+            y4_16 = gemm.mx_linear(x.to(DEV), w4, b, 4, 3)
+        gemm.check_status()
+        assert torch.equal(y8, y4), fields
+        assert rel_err(y4, ref) <= REL_TOL and rel_err(y4_16, ref) <= 4e-3, fields

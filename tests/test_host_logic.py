@@ -79,7 +79,8 @@ def test_gemm_options_travel_with_the_call(library):
     assert gemm._options_ptr() is None
     # argument validation happens before any launch, with and without options
     opts = _lib.GemmOptions(max_ctas=8)
-    assert library.mxq_gemm_mxf8(None, None, None, None, None, None, 1, 0, 4, 4, 32, None, ctypes.addressof(opts), None) == -5
+    assert library.mxq_gemm_mxf8(None, None, None, None, 0, None, None, 1, 0, 4, 4, 32, None, ctypes.addressof(opts), None) == -5
+    assert library.mxq_gemm_mxf8(32, 32, 32, 32, 7, 32, None, 1, 0, 4, 4, 32, None, None, None) == -3  # unknown codes layout
     assert library.mxq_gemm_dense(16, 16, 16, None, 5, 1, 0, 4, 4, 32, None, None, None) == -1
     assert library.mxq_mx_linear_workspace_bytes(8192, 4096) == 8192 * 4096 + 64 * 32 * 512
 

@@ -24,8 +24,8 @@ def _run(entry, x, wp, out, workspace=None):
     M, K = x.shape
     st = gemm._status(x.device)
     stream = torch.cuda.current_stream().cuda_stream
-    common = (x.data_ptr(), 1, wp.codes.data_ptr(), wp.scales.data_ptr(), out.data_ptr(), None, 1, 0, M, wp.rows, K, 4, 3,
-              _floor_tab_ptr())
+    common = (x.data_ptr(), 1, wp.codes.data_ptr(), wp.scales.data_ptr(), wp.format, out.data_ptr(), None, 1, 0, M, wp.rows,
+              K, 4, 3, _floor_tab_ptr())
     if entry == "static":
         rc = lib.mxq_mx_linear_static(*common, st.data_ptr(), None, stream)
     else:
@@ -78,7 +78,7 @@ def test_static_scratch_entry_rejects_oversized_problems():
     assert int(lib.mxq_mx_linear_workspace_bytes(M, K)) > STATIC_BYTES
     x = torch.zeros(8, 32, dtype=torch.bfloat16, device=DEV)  # never touched: the size check comes first
     st = gemm._status(x.device)
-    rc = lib.mxq_mx_linear_static(x.data_ptr(), 1, x.data_ptr(), x.data_ptr(), x.data_ptr(), None, 1, 0, M, 256, K, 4, 3,
+    rc = lib.mxq_mx_linear_static(x.data_ptr(), 1, x.data_ptr(), x.data_ptr(), 0, x.data_ptr(), None, 1, 0, M, 256, K, 4, 3,
                                   _floor_tab_ptr(), st.data_ptr(), None, None)
     assert rc == -9
     assert b"MXQ_STATIC_SCRATCH_BYTES" in lib.mxq_error_string(rc)
