@@ -183,7 +183,7 @@ int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in
  * the low nibble of byte i and element 2i+1 in the high nibble, each nibble the reference's code sign|exponent|fraction
  * (chop/nn/quantizers/_minifloat_mx/fake.py:90-91), which is the hardware's FP4 encoding as it stands.  Scales as
  * above.  Weight storage of 0.53 bytes per element: the copy engine expands the nibbles on their way into shared
- * memory, so the GEMM also moves half the weight bytes.  k % 64 == 0; codes4 32-byte aligned. */
+ * memory, so the GEMM also moves half the weight bytes.  k % 128 == 0; codes4 32-byte aligned. */
 int mxq_mxfp4_pack_mma(const void *x, uint8_t *codes4, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k,
                        const uint8_t *floor_tab_host, void *stream);
 

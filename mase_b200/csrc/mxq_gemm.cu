@@ -259,6 +259,7 @@ struct Params {
   unsigned long long wait_ns;  // limit of every wait
   int drop_last_load;   // test hook: CTA 0 never loads the last K chunk of its first tile
   uint32_t b_fp4;       // block-scaled kind: B holds E2M1 elements (two per byte in global memory) instead of E4M3 bytes
+  uint32_t tx_less;     // a 4-bit box counts its packed bytes on the barrier, half of what lands in shared memory
 };
 
 // Epilogue of one tile for one warp: drains the warp's 32 TMEM lanes (= 32 tile rows starting at row0) of the
@@ -472,7 +473,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // test hook: this slot is never filled, so the MMA issuer's wait for it runs out
         if (p.drop_last_load && blockIdx.x == 0 && tile == first_tile && kc == kc_end - 1) break;
         if (elect_one()) {
-          mbar_expect_tx(full, L::kStage - L::kA + p.a_box_bytes);
+          mbar_expect_tx(full, L::kStage - L::kA + p.a_box_bytes - p.tx_less);
           tma_load_2d(sa, &map_a, full, k0, row_a);
           tma_load_2d(sa + L::kA, &map_b, full, k0, row_b);
           if constexpr (kScaled) {
@@ -806,7 +807,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           break;
         }
         if (elect_one()) {
-          if (leader) mbar_expect_tx(full, L::kStageTx);
+          if (leader) mbar_expect_tx(full, L::kStageTx - p.tx_less);
           tma_load_2d_pair(sa, &map_a, lead_full, k0, row_a);
           tma_load_2d_pair(sa + L::kA, &map_b, lead_full, k0, row_b);
           if constexpr (kScaled) {
@@ -977,6 +978,7 @@ struct SwapParams {
   int x_box_bytes;   // bytes one activation load delivers
   int out_bf16, bias_bf16;
   uint32_t w_fp4;    // block-scaled kind: the weight holds E2M1 elements, two per byte in global memory
+  uint32_t tx_less;  // a 4-bit box counts its packed bytes on the barrier, half of what lands in shared memory
   unsigned long long wait_ns;
 };
 
@@ -1029,7 +1031,7 @@ umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   const int kc_count = base + (rank < rem ? 1 : 0);
   const int first_pass = kc_count < kStages ? kc_count : kStages;
   const int row_w = n_blk * BM;
-  const uint32_t stage_tx = (uint32_t)(L::kW + L::kSf) + (uint32_t)p.x_box_bytes;
+  const uint32_t stage_tx = (uint32_t)(L::kW + L::kSf) + (uint32_t)p.x_box_bytes - p.tx_less;
   // Every CTA of a cluster must be running before another one touches its shared memory: arrive now, wait (long
   // since satisfied) right before the partial sums are pushed.
   if (p.split > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
@@ -1238,7 +1240,8 @@ static int make_map(CUtensorMap *map, const void *ptr, int kind, int64_t rows, i
 // Tensor map of a K-major matrix [rows, k] of 4-bit elements stored two per byte: the copy engine expands each group
 // of 16 elements (8 bytes in global memory) to 16 bytes of shared memory, the padded form in which the block-scaled
 // MMA reads 4-bit operands.  A box is box_rows x 128 elements and lands as box_rows x 128 bytes, 128-byte swizzle --
-// the footprint of an E4M3 box -- while only half the bytes travel.  Needs k % 64 == 0 and a 32-byte aligned base.
+// the footprint of an E4M3 box -- while only half the bytes travel (and half are counted on the mbarrier).  Needs
+// k % 128 == 0 and a 32-byte aligned base.
 static int make_map_fp4(CUtensorMap *map, const void *ptr, int64_t rows, int64_t k, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return MXQ_ERR_UNSUPPORTED;
@@ -1364,6 +1367,7 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   p.a_box_bytes = a_rows * kRowBytes;
   p.wait_ns = o.wait_ns, p.drop_last_load = !kSplit && o.test_hook == MXQ_TEST_DROP_LAST_LOAD;
   p.b_fp4 = o.b_fp4 ? 1u : 0u;
+  p.tx_less = o.b_fp4 ? BN * (kRowBytes / 2) : 0;
   CUtensorMap msa = ma, msb = ma;  // unused by the dense kinds
   if constexpr (kKind == kMxf8) {
     rc = make_sf_map(&msa, sfa, ((M + 255) / 256) * 2 * p.k_chunks);
@@ -1431,6 +1435,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   p.a_box_bytes = BM * kRowBytes;
   p.wait_ns = o.wait_ns, p.drop_last_load = 0;
   p.b_fp4 = o.b_fp4 ? 1u : 0u;
+  p.tx_less = o.b_fp4 ? 2 * 128 * (kRowBytes / 2) : 0;  // the B boxes of both CTAs
   static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
   bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {
@@ -1484,6 +1489,7 @@ static int launch_swap(const void *a, const void *b, const uint8_t *sfa, const u
   p.x_box_bytes = x_rows * kRowBytes;
   p.out_bf16 = out_dtype == MXQ_BF16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.wait_ns = o.wait_ns;
   p.w_fp4 = o.b_fp4 ? 1u : 0u;
+  p.tx_less = o.b_fp4 ? BM * (kRowBytes / 2) : 0;
   static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
   bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {
@@ -1613,7 +1619,7 @@ int gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_
   if (M == 0 || N == 0) return MXQ_OK;
   if (!a_codes || !a_scales || !b_codes || !b_scales || !d) return MXQ_ERR_NULL;
   if (M < 0 || N < 0 || K <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || K % 32) return MXQ_ERR_SHAPE;
-  if (o.b_fp4 && (K % 64 || (reinterpret_cast<uintptr_t>(b_codes) & 31u))) return MXQ_ERR_SHAPE;
+  if (o.b_fp4 && (K % 128 || (reinterpret_cast<uintptr_t>(b_codes) & 31u))) return MXQ_ERR_SHAPE;
   if (out_dtype != MXQ_F32 && out_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
   if (bias && bias_dtype != MXQ_F32 && bias_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
   if ((reinterpret_cast<uintptr_t>(a_codes) | reinterpret_cast<uintptr_t>(b_codes) | reinterpret_cast<uintptr_t>(d) |

@@ -942,14 +942,11 @@ int mxq_mxfp4_pack_mma(const void *x, uint8_t *codes4, uint8_t *scales_mma, int 
                        const uint8_t *floor_tab_host, void *stream) {
   if (rows == 0 || k == 0) return MXQ_OK;
   if (!x || !codes4 || !scales_mma || !floor_tab_host) return MXQ_ERR_NULL;
-  if (rows < 0 || k < 0 || k % 64) return MXQ_ERR_SHAPE;
+  if (rows < 0 || k < 0 || k % 128) return MXQ_ERR_SHAPE;
   if (reinterpret_cast<uintptr_t>(codes4) & 31u) return MXQ_ERR_ALIGN;
   const Log2Tab tab = load_tab(floor_tab_host);
   cudaStream_t st = (cudaStream_t)stream;
-  const int64_t k_chunks = (k + 127) / 128;
-  const int64_t sf_bytes = ((rows + 255) / 256) * 2 * k_chunks * 512;
-  // scale bytes of K blocks past the end of a row must be finite (see mxq_mxfp_pack_mma)
-  if (k % 128 && cudaMemsetAsync(scales_mma, 0, sf_bytes, st) != cudaSuccess) return MXQ_ERR_LAUNCH;
+  const int64_t k_chunks = k / 128;
   const int64_t n_blocks = rows * (k / 32);
   if (in_dtype == MXQ_F32)
     mxfp4_pack_mma_kernel<float><<<grid_for(n_blocks, kThreads), kThreads, 0, st>>>((const float *)x, codes4, scales_mma,

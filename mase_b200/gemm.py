@@ -147,8 +147,8 @@ def mma_supported(exp_bits: int, frac_bits: int, block_size: int, k: int) -> boo
 
 
 def fp4_supported(exp_bits: int, frac_bits: int, k: int) -> bool:
-    """Weights that can be kept as nibble-packed MXFP4: E2M1 elements and rows of whole 32-byte groups."""
-    return exp_bits == 2 and frac_bits == 1 and k % 64 == 0
+    """Weights that can be kept as nibble-packed MXFP4: E2M1 elements and rows of whole 128-element chunks."""
+    return exp_bits == 2 and frac_bits == 1 and k % 128 == 0
 
 
 def pack_mx_operand(x: Tensor, exp_bits: int, frac_bits: int, fp4: bool = False) -> MXOperand:
@@ -168,7 +168,7 @@ def pack_mx_operand(x: Tensor, exp_bits: int, frac_bits: int, fp4: bool = False)
     scales = torch.empty((int(lib.mxq_mma_scale_bytes(rows, k)),), dtype=torch.uint8, device=x.device)
     if fp4:
         if not fp4_supported(exp_bits, frac_bits, k):
-            raise NotImplementedError("nibble-packed operands need E2M1 elements and K divisible by 64")
+            raise NotImplementedError("nibble-packed operands need E2M1 elements and K divisible by 128")
         codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
         with _on_device(x):
             rc = lib.mxq_mxfp4_pack_mma(xc.data_ptr(), codes.data_ptr(), scales.data_ptr(), _DT[x.dtype], rows, k,

@@ -203,7 +203,7 @@ def test_transposed_small_m_kernel_vs_oracle_and_regular_tiles(shape):
     assert rel_err(d16, ref) <= 4e-3 and rel_err(d32, ref) <= REL_TOL
 
 
-@pytest.mark.parametrize("shape", [(1, 4096, 4096), (16, 1024, 1000), (100, 4032, 768), (128, 512, 512), (300, 1024, 260),
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (16, 1024, 1000), (100, 3968, 768), (128, 512, 512), (300, 1024, 260),
                                    (512, 2048, 1024), (2048, 4096, 4096), (1000, 11008, 1304)])
 def test_nibble_packed_mxfp4_weight_matches_e4m3_bytes(shape):
     """MXFP4 weights stored two codes per byte (the copy engine expands them on the way into shared memory) give the
