@@ -479,14 +479,14 @@ def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
         ws = [(torch.randn(n, k, generator=gen, device=device) * 0.02).to(torch.bfloat16)
               for (n, k) in ((ffn, hidden), (ffn, hidden), (hidden, ffn))]
         stack.append(tpmod.build_tp_gated_mlp(mb.LinearMXFP, ws[0], ws[1], ws[2], cfg, tp, device=device,
-                                              reduce="scatter_gather"))
+                                              reduce=os.environ.get("MXQ_BENCH_TP_REDUCE", "fused")))
         del ws
     x0 = torch.randn(M, hidden, generator=gen, device=device).to(torch.bfloat16)
 
     results = {}
     for micro in ((1,) if world == 1 else (1, 2, 4)):
         def step():
-            return tpmod.run_mlp_stack(stack, x0, micro_batches=micro)
+            return tpmod.run_mlp_stack(stack, x0, micro_batches=micro, comm_sms=int(os.environ.get("MXQ_BENCH_COMM_SMS", 32)))
 
         for _ in range(2):
             step()

@@ -227,6 +227,40 @@ int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint
                         int F, const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status,
                         const mxq_gemm_options *options, void *stream);
 
+/*
+ * Row-parallel Linear over the GPUs of one node (tensor parallelism).  The reference reaches this point through
+ * DTensor redistribution (chop/distributed/tensor/_redistribute.py:189-245: partial -> replicate = all-reduce); here
+ * the reduction is part of the GEMM and of one small kernel, over peer memory.  All buffers are symmetric
+ * allocations of the caller: `*_ptrs` are HOST arrays of `world` device pointers, entry r = the buffer of GPU r as
+ * mapped in this process; the calling process owns GPU `rank`.
+ *
+ *   slots    fp32 [world][M / world][N] per GPU: slot s of GPU r receives GPU s's partial sums of GPU r's row slice
+ *   out      [M][N] of out_dtype per GPU: every GPU's copy of the reduced result
+ *   flags    uint32 [world] per GPU, zero before the first barrier; `epoch` grows by one per barrier
+ *
+ * Sequence on every GPU, one stream: mxq_gemm_mxf8_scatter, mxq_peer_barrier(epoch), mxq_reduce_gather,
+ * mxq_peer_barrier(epoch + 1); afterwards `out` is complete on every GPU.
+ */
+
+/* Block-scaled GEMM of this GPU's K shard whose epilogue stores every fp32 tile directly into the slot of the GPU
+ * that owns the tile's rows (bulk tensor stores over NVLink; no multicast, no collective): the reduce-scatter
+ * travels under the MMAs.  Needs (M / world) % 256 == 0; MXQ_ERR_UNSUPPORTED otherwise (use a collective). */
+int mxq_gemm_mxf8_scatter(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_codes, const uint8_t *b_scales,
+                          int b_format, void *const *slot_ptrs, int world, int rank, int64_t M, int64_t N, int64_t K,
+                          int *status, const mxq_gemm_options *options, void *stream);
+
+/* Every GPU publishes `epoch` to all others (after a system-wide fence: its earlier stores are visible) and waits
+ * until it has received theirs.  The wait is bounded (wait_limit_ns, 0 = one second): when a GPU does not arrive the
+ * kernel stores 7 in the status word and returns.  One warp. */
+int mxq_peer_barrier(void *const *flag_ptrs, int world, int rank, uint32_t epoch, int *status, int64_t wait_limit_ns,
+                     void *stream);
+
+/* This GPU's row slice: sum of its `world` slots in rank order (repeatable) + bias, one rounding to out_dtype,
+ * written to rows [rank * rows, (rank + 1) * rows) of every GPU's `out` (peer stores): reduce + all-gather.
+ * n % 8 == 0.  max_ctas caps the grid (0 = no cap) so that it can run beside a GEMM. */
+int mxq_reduce_gather(const void *slots, int world, int rank, int64_t rows, int64_t n, const void *bias, int bias_dtype,
+                      void *const *out_ptrs, int out_dtype, int max_ctas, void *stream);
+
 /* Allocation-free variant of mxq_mx_linear.  It has no counterpart in the reference.
  *
  * Some callers are not in a position to hand over scratch memory: code that runs where the allocator must not be

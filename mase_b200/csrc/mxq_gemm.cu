@@ -260,6 +260,15 @@ struct Params {
   int drop_last_load;   // test hook: CTA 0 never loads the last K chunk of its first tile
   uint32_t b_fp4;       // block-scaled kind: B holds E2M1 elements (two per byte in global memory) instead of E4M3 bytes
   uint32_t tx_less;     // a 4-bit box counts its packed bytes on the barrier, half of what lands in shared memory
+  // Row-parallel GEMM fused with the reduce-scatter (CTA-pair kernel): rows [r * scatter_rows, (r + 1) * scatter_rows)
+  // of the fp32 result go to store map r, which covers a buffer in GPU r's memory.  0 = one output, map 0.
+  int scatter_rows;
+};
+
+// Store maps of the CTA-pair kernel: one output, or one slot buffer per GPU of a tensor-parallel group.
+constexpr int kMaxPeers = 8;
+struct StoreMaps {
+  CUtensorMap m[kMaxPeers];
 };
 
 // Epilogue of one tile for one warp: drains the warp's 32 TMEM lanes (= 32 tile rows starting at row0) of the
@@ -720,7 +729,7 @@ template <int kKind>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                      const __grid_constant__ CUtensorMap map_d, const Params p) {
+                      const __grid_constant__ StoreMaps maps_d, const Params p) {
   constexpr bool kScaled = kKind == kMxf8;
   using L = PairLayout<kScaled>;
   constexpr int BN = 256;
@@ -787,7 +796,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfa) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfb) : "memory");
       }
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&maps_d.m[0]) : "memory");
     }
     const uint32_t lead_full0 = map_to_cta(full_bar(0), 0);  // the leader's full[0] as a shared::cluster address
     uint32_t sa = s_base, ssf = s_base + L::kSfBase, full = full_bar(0), lead_full = lead_full0, empty = empty_bar(0);
@@ -913,10 +922,13 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait, p.wait_ns)) break;
       tc_fence_after();
+      // with a reduce-scatter fused in, the tile goes to the slot buffer of the GPU that owns its rows
+      const int owner = p.scatter_rows ? (m_blk * BM) / p.scatter_rows : 0;
       drain_accumulator<BN, kOverlap, kStoreBufs>(
-          p, &map_d, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride),
+          p, &maps_d.m[owner], tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride),
           kOverlap && acc == 0 ? BN / 32 - 2 : 0,
-          m_blk * BM + quarter * 32, n_blk * BN, lane, stage_buf, buf, [&] { mbar_arrive_cluster(lead_overlap); });
+          m_blk * BM - owner * p.scatter_rows + quarter * 32, n_blk * BN, lane, stage_buf, buf,
+          [&] { mbar_arrive_cluster(lead_overlap); });
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(acc), 0));
@@ -1368,6 +1380,7 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   p.wait_ns = o.wait_ns, p.drop_last_load = !kSplit && o.test_hook == MXQ_TEST_DROP_LAST_LOAD;
   p.b_fp4 = o.b_fp4 ? 1u : 0u;
   p.tx_less = o.b_fp4 ? BN * (kRowBytes / 2) : 0;
+  p.scatter_rows = 0;
   CUtensorMap msa = ma, msb = ma;  // unused by the dense kinds
   if constexpr (kKind == kMxf8) {
     rc = make_sf_map(&msa, sfa, ((M + 255) / 256) * 2 * p.k_chunks);
@@ -1406,7 +1419,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
                        cudaStream_t st) {
   using L = PairLayout<kKind == kMxf8>;
   constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
-  CUtensorMap ma, mb, msa, msb, md;
+  CUtensorMap ma, mb, msa, msb;
   int rc = make_map(&ma, a, kKind, M, K, BM);
   if (rc) return rc;
   rc = o.b_fp4 ? make_map_fp4(&mb, b, N, K, 128) : make_map(&mb, b, kKind, N, K, 128);
@@ -1421,11 +1434,18 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   }
   const bool out_bf16 = out_dtype == MXQ_BF16;
   const bool tma_store = (N * (out_bf16 ? 2 : 4)) % 16 == 0;
-  if (tma_store) {
-    rc = make_store_map(&md, d, out_bf16, M, N);
+  StoreMaps maps;
+  for (int r = 0; r < kMaxPeers; ++r) maps.m[r] = ma;  // placeholders
+  if (o.scatter_world > 0) {
+    // one fp32 slot buffer [scatter_rows, N] per GPU of the group; d is unused
+    if (!tma_store || out_bf16 || M % o.scatter_world || (M / o.scatter_world) % 256) return MXQ_ERR_UNSUPPORTED;
+    for (int r = 0; r < o.scatter_world; ++r) {
+      rc = make_store_map(&maps.m[r], o.scatter_dst[r], false, M / o.scatter_world, N);
+      if (rc) return rc;
+    }
+  } else if (tma_store) {
+    rc = make_store_map(&maps.m[0], d, out_bf16, M, N);
     if (rc) return rc;
-  } else {
-    md = ma;  // unused by the kernel
   }
   Params p;
   p.sfa = sfa, p.sfb = sfb, p.d = d, p.bias = bias, p.status = status;
@@ -1436,6 +1456,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   p.wait_ns = o.wait_ns, p.drop_last_load = 0;
   p.b_fp4 = o.b_fp4 ? 1u : 0u;
   p.tx_less = o.b_fp4 ? 2 * 128 * (kRowBytes / 2) : 0;  // the B boxes of both CTAs
+  p.scatter_rows = o.scatter_world > 0 ? (int)(M / o.scatter_world) : 0;
   static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
   bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {
@@ -1450,7 +1471,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   if (2 * tiles < grid) grid = (int)(2 * tiles);
   grid &= ~1;
   if (grid < 2) return MXQ_ERR_UNSUPPORTED;
-  const cudaError_t err = launch_dependent(umma_gemm_pair_kernel<kKind>, grid, kThreads, L::kTotal, st, 0, ma, mb, msa, msb, md, p);
+  const cudaError_t err = launch_dependent(umma_gemm_pair_kernel<kKind>, grid, kThreads, L::kTotal, st, 0, ma, mb, msa, msb, maps, p);
   if (err != cudaSuccess) {
     cudaGetLastError();  // clear it: the caller falls back to single-CTA tiles
     return MXQ_ERR_LAUNCH;
@@ -1528,6 +1549,8 @@ static int launch_any(const void *a, const void *b, const uint8_t *sfa, const ui
                       cudaStream_t st) {
   const int64_t tiles_m = (M + BM - 1) / BM;
   const int sms = sm_count();
+  if (o.scatter_world > 0)  // reduce-scatter fused into the epilogue: CTA pairs only
+    return launch_pair<kKind>(a, b, sfa, sfb, d, bias, out_dtype, bias_dtype, M, N, K, status, o, st);
   if (M <= BM && o.transposed && o.test_hook == 0) {
     // few rows: the weight streams through as the 128-row operand (a context that cannot place the clusters falls
     // back to the tiles below)

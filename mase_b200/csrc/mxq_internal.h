@@ -20,6 +20,9 @@ struct Opts {
   unsigned long long wait_ns = kDefaultWaitNs;
   int test_hook = 0;
   bool b_fp4 = false;  // block-scaled kind: B (the weight) holds E2M1 elements, two per byte
+  // reduce-scatter fused into the GEMM: fp32 slot buffer of every GPU of the group (rows M / scatter_world each)
+  int scatter_world = 0;
+  void *scatter_dst[8] = {};
 };
 
 Opts make_opts(const mxq_gemm_options *o);

@@ -33,6 +33,7 @@ _STATUS_TEXT = {
     3: "MMA issuer: wait for a free accumulator ran out",
     4: "epilogue: wait for a finished accumulator ran out",
     5: "CTA pair: the two CTAs got different tensor-memory addresses",
+    7: "peer barrier: a GPU of the tensor-parallel group did not arrive within the wait limit",
 }
 
 

@@ -12,6 +12,10 @@ hand-placed tensor parallelism; for the MX path only two placements matter, so t
 
 The collective plumbing is torch.distributed only, so the same code runs under the gloo backend on CPU ranks with an
 injected local layer (tests) and under NCCL with the CUDA layers of this package.
+
+reduce="fused" takes the collective library off the data path of the row-parallel layer: the GEMM's epilogue stores
+each fp32 tile into the memory of the GPU that owns its rows (symmetric memory, peer stores over NVLink), and one small
+kernel per GPU sums its slice in rank order, rounds once and writes the slice into every GPU's output (`PeerReducer`).
 """
 
 from __future__ import annotations
@@ -95,6 +99,94 @@ class ColumnParallelLinear(nn.Module):
         return torch.cat(parts, dim=-1)
 
 
+class PeerReducer:
+    """Symmetric buffers and launches of the fused row-parallel reduction (mxq_gemm_mxf8_scatter, mxq_peer_barrier,
+    mxq_reduce_gather of include/mxq.h) for one tensor-parallel group on one GPU.
+
+    Buffers are allocated once per (rows, columns, output type, tag) through torch's symmetric memory and exchanged
+    with the other ranks (a collective call: every rank must ask for the same buffers in the same order).  `tag`
+    separates reductions that are in flight at the same time (micro-batches).  The barrier epoch is a plain counter
+    that every rank advances in lockstep."""
+
+    _instances: dict = {}
+
+    @classmethod
+    def for_group(cls, tp: TPGroup, device) -> "PeerReducer":
+        key = (id(tp.group), torch.device(device).index)
+        if key not in cls._instances:
+            cls._instances[key] = cls(tp, device)
+        return cls._instances[key]
+
+    def __init__(self, tp: TPGroup, device):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.tp, self.device = tp, torch.device(device)
+        self._symm = symm_mem
+        self._group = tp.group if tp.group is not None else dist.group.WORLD
+        self._plans: dict = {}
+        self._ctypes = ctypes
+        self.epoch = 0
+        self.flags, self.flag_ptrs = self._alloc(64, torch.int32)
+        self.flags.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=tp.group)  # every rank's flags are zero before anyone publishes an epoch
+
+    @staticmethod
+    def available(tp: TPGroup, device) -> bool:
+        if tp.world < 2 or tp.world > 8 or torch.device(device).type != "cuda":
+            return False
+        try:
+            import torch.distributed._symmetric_memory  # noqa: F401
+        except Exception:
+            return False
+        return dist.get_backend(tp.group) == "nccl"
+
+    def _alloc(self, numel: int, dtype):
+        t = self._symm.empty(numel, dtype=dtype, device=self.device)
+        hdl = self._symm.rendezvous(t, self._group)
+        ptrs = (self._ctypes.c_void_p * self.tp.world)(*[int(p) for p in hdl.buffer_ptrs])
+        return t, ptrs
+
+    def plan(self, rows: int, cols: int, out_dtype, tag: int = 0) -> dict:
+        key = (rows, cols, out_dtype, tag)
+        if key not in self._plans:
+            slots, slot_ptrs = self._alloc(rows * cols, torch.float32)
+            out, out_ptrs = self._alloc(rows * cols, out_dtype)
+            self._plans[key] = {"slots": slots, "slot_ptrs": slot_ptrs, "out": out.view(rows, cols), "out_ptrs": out_ptrs}
+        return self._plans[key]
+
+    def barrier(self, status: Tensor, stream) -> None:
+        from . import _lib
+
+        self.epoch += 1
+        rc = _lib.lib().mxq_peer_barrier(self.flag_ptrs, self.tp.world, self.tp.rank, self.epoch & 0xFFFFFFFF,
+                                         status.data_ptr(), 0, stream)
+        _lib.check(rc, "mxq_peer_barrier")
+
+    def scatter_gemm(self, a_op, w_op, plan: dict, status: Tensor, options_ptr, stream) -> None:
+        """This rank's partial product, stored tile by tile into the owners' slots."""
+        from . import _lib
+
+        rc = _lib.lib().mxq_gemm_mxf8_scatter(a_op.codes.data_ptr(), a_op.scales.data_ptr(), w_op.codes.data_ptr(),
+                                              w_op.scales.data_ptr(), w_op.format, plan["slot_ptrs"], self.tp.world,
+                                              self.tp.rank, a_op.rows, w_op.rows, a_op.k, status.data_ptr(), options_ptr,
+                                              stream)
+        _lib.check(rc, "mxq_gemm_mxf8_scatter")
+
+    def reduce_gather(self, plan: dict, bias: Tensor | None, max_ctas: int, stream) -> None:
+        from . import _lib
+        from .quantizers import _DT
+
+        rows, cols = plan["out"].shape
+        b = None if bias is None else bias.contiguous()
+        rc = _lib.lib().mxq_reduce_gather(plan["slots"].data_ptr(), self.tp.world, self.tp.rank, rows // self.tp.world, cols,
+                                          0 if b is None else b.data_ptr(), 0 if b is None else _DT[b.dtype],
+                                          plan["out_ptrs"], _DT[plan["out"].dtype], max_ctas, stream)
+        _lib.check(rc, "mxq_reduce_gather")
+
+
 class RowParallelLinear(nn.Module):
     """Input features split over the ranks.  `inner` maps this rank's [..., K/G] slice to a float32 partial
     [..., N] (bias-free); the partials are summed across ranks in float32, then the bias is added and the sum is
@@ -103,14 +195,21 @@ class RowParallelLinear(nn.Module):
     reduce="all_reduce": one float32 all-reduce.  reduce="scatter_gather": float32 reduce-scatter over rows, cast,
     all-gather in the output dtype (fewer bytes on the wire; needs rows divisible by the number of ranks and falls
     back to the all-reduce otherwise).  Measured on 8 B200 for [8192, 8192]: 0.72 ms vs 0.62 ms.
+    reduce="fused": no collective on the data path (see `PeerReducer`): the inner layer's GEMM stores its fp32 tiles
+    into the owning GPUs' memory, then barrier, reduce + all-gather kernel, barrier.  Needs a LinearMXFP inner layer on
+    the block-scaled path, rows divisible by 256 x ranks and NCCL ranks on one node; anything else takes the
+    scatter_gather route.  The result of a fused call lives in a buffer that the next call with the same shape and
+    `tag` overwrites: `forward` returns a copy, `finish(handle, keep=True)` the buffer itself.
 
     `start(x)` / `finish(handle)` split the call so that a caller can overlap the collective (issued on a side
     stream) with other work; `forward` is `finish(start(x))`."""
 
-    def __init__(self, inner: nn.Module, tp: TPGroup, bias: Tensor | None = None, reduce: str = "all_reduce"):
+    def __init__(self, inner: nn.Module, tp: TPGroup, bias: Tensor | None = None, reduce: str = "all_reduce",
+                 reduce_ctas: int = 0):
         super().__init__()
-        assert reduce in ("all_reduce", "scatter_gather")
+        assert reduce in ("all_reduce", "scatter_gather", "fused")
         self.inner, self.tp, self.reduce = inner, tp, reduce
+        self.reduce_ctas = reduce_ctas  # grid cap of the fused reduce + all-gather kernel (0 = whole GPU)
         if hasattr(inner, "output_dtype"):
             inner.output_dtype = torch.float32
         self.bias = None if bias is None else nn.Parameter(bias, requires_grad=False)
@@ -121,18 +220,56 @@ class RowParallelLinear(nn.Module):
             self._comm_stream = torch.cuda.Stream(device=device)
         return self._comm_stream
 
-    def start_gated(self, gate: Tensor, up: Tensor):
+    # ---- fused route ------------------------------------------------------------------------------------------------
+    def _fused_applies(self, like: Tensor) -> bool:
+        if self.reduce != "fused" or self.tp.world == 1 or not like.is_cuda:
+            return False
+        inner = self.inner
+        rows = like.numel() // like.shape[-1]
+        return (hasattr(inner, "_uses_packed_path") and inner._uses_packed_path(like) and inner.bias is None
+                and rows % (256 * self.tp.world) == 0 and inner.out_features % 8 == 0
+                and PeerReducer.available(self.tp, like.device))
+
+    def _start_fused(self, a_op, like: Tensor, tag: int):
+        from . import gemm
+
+        red = PeerReducer.for_group(self.tp, like.device)
+        plan = red.plan(a_op.rows, self.inner.out_features, like.dtype, tag)
+        status = gemm._status(like.device)
+        cur = torch.cuda.current_stream(like.device)
+        red.scatter_gemm(a_op, self.inner._packed_weight(), plan, status, gemm._options_ptr(), cur.cuda_stream)
+        side = self._side_stream(like.device)
+        side.wait_stream(cur)
+        red.barrier(status, side.cuda_stream)          # every GPU's tiles have landed
+        red.reduce_gather(plan, self.bias, self.reduce_ctas, side.cuda_stream)
+        red.barrier(status, side.cuda_stream)          # every GPU's slice has landed
+        ev = torch.cuda.Event()
+        ev.record(side)
+        a_op.codes.record_stream(side)
+        return (plan["out"], ev, like.dtype, like.shape[:-1], "fused")
+
+    def start_gated(self, gate: Tensor, up: Tensor, tag: int = 0):
         """`start(silu(gate) * up)` for a gated MLP; the product goes straight into the inner layer's quantized
         operand when that layer can take it (`forward_gated`)."""
+        if self._fused_applies(gate):
+            from . import gemm
+
+            _, _, x_exp, x_frac = self.inner._input_format()
+            k = gate.shape[-1]
+            a_op = gemm.pack_gated_operand(gate.reshape(-1, k), up.reshape(-1, k), x_exp, x_frac)
+            return self._start_fused(a_op, gate, tag)
         if hasattr(self.inner, "forward_gated"):
             k = gate.shape[-1]
             return self.start(None, partial=self.inner.forward_gated(gate.reshape(-1, k), up.reshape(-1, k)),
                               like=gate)
         return self.start(torch.nn.functional.silu(gate) * up)
 
-    def start(self, x_shard: Tensor | None, partial: Tensor | None = None, like: Tensor | None = None):
+    def start(self, x_shard: Tensor | None, partial: Tensor | None = None, like: Tensor | None = None, tag: int = 0):
         """Local GEMM on the current stream, collective on a side stream; returns a handle for `finish`."""
         like = x_shard if like is None else like
+        if partial is None and self._fused_applies(like):
+            a_op, _ = self.inner.quantize_input(x_shard.reshape(-1, x_shard.shape[-1]))
+            return self._start_fused(a_op, like, tag)
         out_dtype = like.dtype
         lead = like.shape[:-1]
         p = partial if partial is not None else self.inner(x_shard.reshape(-1, x_shard.shape[-1]))
@@ -141,7 +278,7 @@ class RowParallelLinear(nn.Module):
         if self.tp.world == 1:
             return (p, None, out_dtype, lead, None)
         rows = p.shape[0]
-        use_sg = self.reduce == "scatter_gather" and rows % self.tp.world == 0
+        use_sg = self.reduce in ("scatter_gather", "fused") and rows % self.tp.world == 0
         if not p.is_cuda:  # CPU ranks (gloo): no streams, plain all-reduce
             dist.all_reduce(p, op=dist.ReduceOp.SUM, group=self.tp.group)
             return (p, None, out_dtype, lead, None)
@@ -165,10 +302,13 @@ class RowParallelLinear(nn.Module):
         p.record_stream(side)
         return (result, ev, out_dtype, lead, done_bias)
 
-    def finish(self, handle) -> Tensor:
+    def finish(self, handle, keep: bool = False) -> Tensor:
         y, ev, out_dtype, lead, done_bias = handle
         if ev is not None:
             torch.cuda.current_stream(y.device).wait_event(ev)
+        if done_bias == "fused":  # y is the reducer's output buffer, already biased and rounded
+            y = y if keep else y.clone()
+            return y.reshape(*lead, y.shape[-1])
         if not done_bias and self.bias is not None:
             y = y + self.bias.float()
         return y.to(out_dtype).reshape(*lead, y.shape[-1])
@@ -223,12 +363,13 @@ class TPGatedMLP(nn.Module):
         half = gu.shape[-1] // 2
         return gu[..., :half], gu[..., half:]
 
-    def start(self, x: Tensor):
+    def start(self, x: Tensor, tag: int = 0):
         """Both column-parallel GEMMs, SiLU * mul and the row-parallel GEMM on the current stream, the reduction on
-        the down layer's side stream; `self.down.finish(handle)` gives the layer's output."""
+        the down layer's side stream; `self.down.finish(handle)` gives the layer's output.  `tag` names the
+        micro-batch (reductions in flight at the same time must not share buffers)."""
         gate, up = self.gate_and_up(x)
         if hasattr(self.down, "start_gated"):
-            return self.down.start_gated(gate, up)
+            return self.down.start_gated(gate, up, tag)
         return self.down.start(torch.nn.functional.silu(gate) * up)
 
     def forward(self, x: Tensor) -> Tensor:
@@ -256,13 +397,14 @@ def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, c
     """x -> layer_1 -> ... -> layer_L.  With micro_batches > 1 the rows are split and the cross-GPU reduction of one
     micro-batch (side stream) overlaps the GEMMs of the next one, within and across layers.  The GEMM kernels are
     persistent and fill every SM, so while the pipeline runs they are capped to leave `comm_sms` SMs to the
-    collective kernels (otherwise those only start when a GEMM ends and nothing overlaps)."""
-    if micro_batches <= 1 or x.shape[0] < micro_batches or not hasattr(layers[0].down, "start"):
+    reduction's kernels (otherwise those only start when a GEMM ends and nothing overlaps); 0 = no cap."""
+    if not hasattr(layers[0].down, "start"):
         for layer in layers:
             x = layer(x)
         return x
+    micro_batches = max(1, min(micro_batches, x.shape[0]))
     ctx = contextlib.nullcontext()
-    if x.is_cuda and comm_sms > 0:
+    if x.is_cuda and comm_sms > 0 and micro_batches > 1:
         from . import gemm
 
         sms = torch.cuda.get_device_properties(x.device).multi_processor_count
@@ -274,8 +416,10 @@ def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, c
         for layer in layers:
             for i in range(len(parts)):
                 # a part waits only for its own reduction of the previous layer; the other parts' reductions stay
-                # in flight underneath this part's GEMMs
-                inp = parts[i] if prev_layer is None else prev_layer.down.finish(handles[i])
-                handles[i] = layer.start(inp)
+                # in flight underneath this part's GEMMs.  keep=True: the previous layer's result is consumed here,
+                # before anything can overwrite the reducer's buffer it may live in.
+                inp = parts[i] if prev_layer is None else prev_layer.down.finish(handles[i], keep=True)
+                handles[i] = layer.start(inp, tag=i)
             prev_layer = layer
-        return torch.cat([prev_layer.down.finish(h) for h in handles], dim=0)
+        outs = [prev_layer.down.finish(h, keep=True) for h in handles]
+        return torch.cat(outs, dim=0) if len(outs) > 1 else outs[0].clone()

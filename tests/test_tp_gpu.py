@@ -42,6 +42,20 @@ def _worker(rank, world, port, results):
         fused = tpmod.build_tp_gated_mlp(mb.LinearMXFP, wg, wu, wd, CFG, tp, device=dev, reduce="scatter_gather")
         y3 = fused(x.to(dev))
         y4 = tpmod.run_mlp_stack([fused], x.to(dev), micro_batches=4)
+        # the reduction fused into the GEMM (peer stores + reduce/all-gather kernel), rows divisible by 256 x ranks
+        m2 = 1024
+        x2 = torch.randn(m2, h, generator=g).bfloat16().to(dev)
+        nccl = tpmod.build_tp_gated_mlp(mb.LinearMXFP, wg, wu, wd, CFG, tp, device=dev, reduce="scatter_gather")
+        peer = tpmod.build_tp_gated_mlp(mb.LinearMXFP, wg, wu, wd, CFG, tp, device=dev, reduce="fused")
+        assert peer.down._fused_applies(torch.empty(m2, ffn // world, dtype=torch.bfloat16, device=dev))
+        z_nccl = nccl(x2)
+        z_peer = peer(x2)
+        z_peer2 = tpmod.run_mlp_stack([peer, peer], x2, micro_batches=2)
+        z_nccl2 = nccl(nccl(x2))
+        z_peer3 = tpmod.run_mlp_stack([peer, peer], x2, micro_batches=1)
+        torch.cuda.synchronize()
+        assert torch.equal(z_peer, z_nccl), "fused reduction differs from reduce-scatter + all-gather"
+        assert torch.equal(z_peer2, z_nccl2) and torch.equal(z_peer3, z_nccl2)
         torch.cuda.synchronize()
         assert torch.equal(y, y2) and torch.equal(y3, y4)
         assert float((y3.float() - y.float()).abs().max() / y.float().abs().max()) <= 8e-3  # bf16 output rounding
