@@ -484,7 +484,7 @@ def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
     x0 = torch.randn(M, hidden, generator=gen, device=device).to(torch.bfloat16)
 
     results = {}
-    for micro in ((1,) if world == 1 else (1, 2, 4)):
+    for micro in ((1,) if world == 1 else (1, 2)):
         def step():
             return tpmod.run_mlp_stack(stack, x0, micro_batches=micro, comm_sms=int(os.environ.get("MXQ_BENCH_COMM_SMS", 32)))
 
@@ -538,7 +538,10 @@ def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
             "ms_per_step": sec_step * 1e3, "TFLOPs_aggregate": ach, "n_gpus": world,
             "scaling": "strong", "micro_batches": micro,
             "ms_per_step_by_micro_batches": {str(k): v * 1e3 for k, v in results.items()},
-            "reduction": "fp32 reduce-scatter + bf16 all-gather on a side stream",
+            "reduction": "fused: GEMM epilogue stores fp32 tiles into the owning GPU's memory (peer stores over NVLink), "
+                         "bounded peer barrier, reduce + bf16 all-gather kernel over peer stores; no collective library "
+                         "on the data path" if os.environ.get("MXQ_BENCH_TP_REDUCE", "fused") == "fused"
+                         else "fp32 reduce-scatter + bf16 all-gather (NCCL) on a side stream",
             "parity_max_rel_err": parity,
             "parity_check": "layer 1, rows 0/1171/4097/8191, against the CPU oracle (bf16 roundings of gate, up and "
                             "SiLU*mul as torch does them)",

@@ -21,6 +21,7 @@ kernel per GPU sums its slice in rank order, rounds once and writes the slice in
 from __future__ import annotations
 
 import contextlib
+import importlib
 import math
 from dataclasses import dataclass
 
@@ -120,8 +121,7 @@ class PeerReducer:
     def __init__(self, tp: TPGroup, device):
         import ctypes
 
-        import torch.distributed._symmetric_memory as symm_mem
-
+        symm_mem = importlib.import_module("torch.distributed._symmetric_memory")
         self.tp, self.device = tp, torch.device(device)
         self._symm = symm_mem
         self._group = tp.group if tp.group is not None else dist.group.WORLD
@@ -138,7 +138,7 @@ class PeerReducer:
         if tp.world < 2 or tp.world > 8 or torch.device(device).type != "cuda":
             return False
         try:
-            import torch.distributed._symmetric_memory  # noqa: F401
+            importlib.import_module("torch.distributed._symmetric_memory")
         except Exception:
             return False
         return dist.get_backend(tp.group) == "nccl"
@@ -210,8 +210,8 @@ class RowParallelLinear(nn.Module):
         assert reduce in ("all_reduce", "scatter_gather", "fused")
         self.inner, self.tp, self.reduce = inner, tp, reduce
         self.reduce_ctas = reduce_ctas  # grid cap of the fused reduce + all-gather kernel (0 = whole GPU)
-        if hasattr(inner, "output_dtype"):
-            inner.output_dtype = torch.float32
+        if hasattr(inner, "output_dtype") and tp.world > 1:
+            inner.output_dtype = torch.float32  # partial sums stay fp32 until they have been added up
         self.bias = None if bias is None else nn.Parameter(bias, requires_grad=False)
         self._comm_stream = None
 
@@ -273,10 +273,10 @@ class RowParallelLinear(nn.Module):
         out_dtype = like.dtype
         lead = like.shape[:-1]
         p = partial if partial is not None else self.inner(x_shard.reshape(-1, x_shard.shape[-1]))
+        if self.tp.world == 1:  # nothing to add up: the inner layer's result in its own dtype
+            return (p, None, out_dtype, lead, None)
         if p.dtype != torch.float32:
             p = p.float()
-        if self.tp.world == 1:
-            return (p, None, out_dtype, lead, None)
         rows = p.shape[0]
         use_sg = self.reduce in ("scatter_gather", "fused") and rows % self.tp.world == 0
         if not p.is_cuda:  # CPU ranks (gloo): no streams, plain all-reduce
@@ -310,7 +310,7 @@ class RowParallelLinear(nn.Module):
             y = y if keep else y.clone()
             return y.reshape(*lead, y.shape[-1])
         if not done_bias and self.bias is not None:
-            y = y + self.bias.float()
+            y = (y.float() + self.bias.float())
         return y.to(out_dtype).reshape(*lead, y.shape[-1])
 
     def forward(self, x_shard: Tensor) -> Tensor:
