@@ -210,8 +210,8 @@ class RowParallelLinear(nn.Module):
         assert reduce in ("all_reduce", "scatter_gather", "fused")
         self.inner, self.tp, self.reduce = inner, tp, reduce
         self.reduce_ctas = reduce_ctas  # grid cap of the fused reduce + all-gather kernel (0 = whole GPU)
-        if hasattr(inner, "output_dtype") and tp.world > 1:
-            inner.output_dtype = torch.float32  # partial sums stay fp32 until they have been added up
+        if hasattr(inner, "output_dtype") and (tp.world > 1 or bias is not None):
+            inner.output_dtype = torch.float32  # fp32 until the partial sums and the bias have been added: one rounding
         self.bias = None if bias is None else nn.Parameter(bias, requires_grad=False)
         self._comm_stream = None
 
