@@ -673,15 +673,17 @@ def run_ours(args) -> None:
 
 
 def run_linear(args) -> None:
-    """`--workload linear`: MXFP8 Linear forward 4096 -> 4096 at M = --m (single GPU), one JSON line.  Used for the
-    tensor-core roofline and for profiler captures of the GEMM and activation-pack kernels."""
+    """`--workload linear`: MX Linear forward 4096 -> 4096 at M = --m (single GPU), one JSON line.  Used for the
+    tensor-core roofline and for profiler captures of the GEMM and activation-pack kernels.  `--wfmt e2m1` stores
+    the weight as nibble-packed MXFP4 (activations stay MXFP8)."""
     import mase_b200 as mb
     from mase_b200 import gemm, synthetic
 
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
     M, K, N = args.m, 4096, 4096
-    cfg = {"weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3,
+    we, wf = (2, 1) if args.wfmt == "e2m1" else (4, 3)
+    cfg = {"weight_block_size": 32, "weight_exponent_width": we, "weight_frac_width": wf,
            "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
     x, w = synthetic.linear_operands(M, K, N, seed=2)
     x = x.to(device)
@@ -695,23 +697,21 @@ def run_linear(args) -> None:
     sec_gemm = time_region(lambda: gemm.mx_gemm(xp, wp, None, torch.bfloat16), args.steps, 1, device)
     gemm.check_status()
     flops = 2.0 * M * N * K
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
-            bf16_peak, src = float(json.load(fh)["bf16_tflops"]), "2 x measured bf16 cuBLAS burst"
-    except Exception:
-        bf16_peak, src = 1590.0, "2 x fallback bf16"
+    bf16_peak, _, src = measured_bf16_tflops()
     peak = 2.0 * bf16_peak
     ach = flops * args.steps / sec_gemm / 1e12
     print(json.dumps({
         "metric": "mx_linear_forward_TFLOPs", "value": flops * args.steps / sec / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": sec / args.steps * 1e3,
-        "higher_is_better": True, "dtype": "mxfp8 (E4M3 x E4M3, E8M0 scales), fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"LinearMXFP 4096->4096 forward, M={M}, bf16 in/out, W and A MXFP8 block 32"},
+        "higher_is_better": True, "dtype": f"mxfp8 activations x {args.wfmt} weights, E8M0 scales, fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": f"LinearMXFP 4096->4096 forward, M={M}, bf16 in/out, W {args.wfmt} / A e4m3, block 32"},
         "gpu_launches": 2 * args.steps,  # activation pack + GEMM
         "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
-                     "peak_source": src + " (no block-scaled FP8 entry in MEASURED_PEAKS.json; nominal 4500)",
-                     "kernel": "mxq::gemm::umma_gemm_pair_kernel (cta_group::2, 256x256 tiles)" if M >= 1024
-                     else "mxq::gemm::umma_gemm_kernel<mxf8,64>", "traffic": None},
+                     "peak_source": f"2 x {src} bf16 cuBLAS burst (the default run measures the library FP8 GEMM instead)",
+                     "kernel": "mxq::gemm::umma_gemm_pair_kernel (cta_group::2, 256x256 tiles)" if M > 128
+                     else "mxq::gemm::umma_gemm_swap_kernel (weight as the 128-row operand, K split over a cluster)",
+                     "traffic": None},
         "gemm_only_ms": sec_gemm / args.steps * 1e3,
     }))
 
@@ -728,6 +728,7 @@ def main() -> None:
     ap.add_argument("--workload", default="quant", choices=["quant", "linear"],
                     help="quant: the headline quantizer benchmark; linear: MXFP8 Linear forward (profiling aid)")
     ap.add_argument("--m", type=int, default=8192, help="tokens for --workload linear")
+    ap.add_argument("--wfmt", default="e4m3", choices=["e4m3", "e2m1"], help="weight format for --workload linear")
     args = ap.parse_args()
     if args.workload == "linear" and args.impl == "ours":
         run_linear(args)

@@ -26,6 +26,9 @@ from .quantizers import (  # noqa: F401
     quantizer_map,
 )
 from .modules import (  # noqa: F401
+    EmbeddingMXFP,
+    EmbeddingMXInt,
+    RMSNormMinifloat,
     LinearBlockFP,
     LinearMXFP,
     LinearMXInt,
@@ -34,8 +37,8 @@ from .modules import (  # noqa: F401
     quantized_module_map,
 )
 from .functional import (  # noqa: F401
-    bmm_mxfp, bmm_mxint, kv_cache_mxfp, kv_cache_mxint, matmul_mxfp, matmul_mxint, rope_mxfp, rope_mxint, silu_mxfp,
-    silu_mxint, softmax_mxfp, softmax_mxint,
+    bmm_mxfp, bmm_mxint, kv_cache_mxfp, kv_cache_mxint, matmul_mxfp, matmul_mxint, rope_minifloat, rope_mxfp, rope_mxint,
+    silu_minifloat, silu_mxfp, silu_mxint, softmax_minifloat, softmax_mxfp, softmax_mxint,
 )
 from .patch import patch  # noqa: F401
 

@@ -6,9 +6,13 @@
     silu_mxfp / silu_mxint                              chop/nn/quantized/functional/silu.py:10-40
     rope_mxfp / rope_mxint                              chop/nn/quantized/functional/rope.py:30-77
 
+    softmax_minifloat / silu_minifloat / rope_minifloat chop/nn/quantized/functional/softmax.py:42-57, silu.py:43-58,
+                                                        rope.py:78-101
+
 Both operands are fake-quantized along their last dimension (x[..., M, K] along K, y[..., K, N] along N, as the
-reference does) and multiplied.  A two-dimensional y goes through this package's tensor-core GEMM (exact products of
-the quantized values, fp32 accumulation); a batched y is multiplied by torch.matmul / torch.bmm per the reference.
+reference does) and multiplied on this package's tensor-core GEMM (exact products of the quantized values, fp32
+accumulation): a two-dimensional y in one launch over all rows of x, a batched y in one launch per batch element.
+Only `bypass` configurations, which the reference leaves unquantized, go to torch.matmul / torch.bmm.
 """
 
 from __future__ import annotations
@@ -17,13 +21,29 @@ import torch
 from torch import Tensor
 
 from .gemm import linear_forward
-from .quantizers import mxfp_quantizer, mxint_quantizer
+from .quantizers import MinifloatMeta, minifloat_quantizer_sim, mxfp_quantizer, mxint_quantizer
 
 
 def _product(x: Tensor, y: Tensor, style: str) -> Tensor:
-    if style == "matmul" and y.dim() == 2 and x.dim() >= 2 and x.shape[-1] % 8 == 0:
+    """x @ y for already-quantized operands.  y[..., K, N] is brought to the K-major [N, K] form the GEMM reads."""
+    if style == "bmm" and (x.dim() != 3 or y.dim() != 3):
+        raise RuntimeError(f"batch1 and batch2 must be 3D tensors, got {x.dim()}D and {y.dim()}D")
+    if x.dim() < 2 or y.dim() < 2:  # vector operands: as torch.matmul defines them
+        xv, yv = (x.unsqueeze(0) if x.dim() == 1 else x), (y.unsqueeze(-1) if y.dim() == 1 else y)
+        out = _product(xv, yv, "matmul")
+        if x.dim() == 1:
+            out = out.squeeze(-2)
+        return out.squeeze(-1) if y.dim() == 1 else out
+    if y.dim() == 2:
         return linear_forward(x, y.t().contiguous(), None, x.dtype)
-    return torch.bmm(x, y) if style == "bmm" else torch.matmul(x, y)
+    # batched y: broadcast the batch dimensions, then one GEMM launch per batch element
+    batch = torch.broadcast_shapes(x.shape[:-2], y.shape[:-2])
+    xb = x.expand(*batch, *x.shape[-2:]).reshape(-1, *x.shape[-2:])
+    yt = y.expand(*batch, *y.shape[-2:]).reshape(-1, *y.shape[-2:]).transpose(-1, -2).contiguous()  # [B, N, K]
+    out = torch.empty((xb.shape[0], x.shape[-2], y.shape[-1]), dtype=x.dtype, device=x.device)
+    for b in range(xb.shape[0]):
+        out[b] = linear_forward(xb[b], yt[b], None, x.dtype)
+    return out.reshape(*batch, x.shape[-2], y.shape[-1])
 
 
 def _generic_matmul_mxfp(x: Tensor, y: Tensor, config: dict, style: str) -> Tensor:
@@ -66,6 +86,12 @@ def _x_mxfp(config: dict):
                                     element_frac_bits=config["data_in_frac_width"], block_dim=-1)
 
 
+def _x_minifloat(config: dict):
+    meta = MinifloatMeta(exp_bits=config["data_in_exponent_width"], frac_bits=config["data_in_frac_width"],
+                         is_finite=config.get("data_in_is_finite", True), round_mode=config.get("data_in_round_mode", "rn"))
+    return lambda t: minifloat_quantizer_sim(t, minifloat_meta=meta)
+
+
 def _x_mxint(config: dict):
     return lambda t: mxint_quantizer(t, block_size=config["data_in_block_size"], element_bits=config["data_in_width"],
                                      block_dim=-1)
@@ -89,6 +115,15 @@ def softmax_mxfp(x: Tensor, config: dict = None, dim: int = -1) -> Tensor:
 def softmax_mxint(x: Tensor, config: dict = None, dim: int = -1) -> Tensor:
     x = _x_mxint(config)(x)
     return torch.nn.functional.softmax(x.to(torch.float32), dim=dim).to(x.dtype)
+
+
+def softmax_minifloat(x: Tensor, config: dict = None, dim: int = -1) -> Tensor:
+    x = _x_minifloat(config)(x)
+    return torch.nn.functional.softmax(x.to(torch.float32), dim=dim).to(x.dtype)
+
+
+def silu_minifloat(x: Tensor, config: dict = None) -> Tensor:
+    return torch.nn.functional.silu(_x_minifloat(config)(x))
 
 
 def silu_mxfp(x: Tensor, config: dict = None) -> Tensor:
@@ -122,6 +157,11 @@ def rope_mxint(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor, config: dict = No
     return _apply_rope(q, k, quant(cos), quant(sin), unsqueeze_dim)
 
 
+def rope_minifloat(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor, config: dict = None, unsqueeze_dim: int = 1):
+    quant = _x_minifloat(config)
+    return _apply_rope(q, k, quant(cos), quant(sin), unsqueeze_dim)
+
+
 quantized_func_map = {
     "kv_cache_mxfp": kv_cache_mxfp,
     "kv_cache_mxint": kv_cache_mxint,
@@ -131,6 +171,9 @@ quantized_func_map = {
     "silu_mxint": silu_mxint,
     "rope_mxfp": rope_mxfp,
     "rope_mxint": rope_mxint,
+    "softmax_minifloat": softmax_minifloat,
+    "silu_minifloat": silu_minifloat,
+    "rope_minifloat": rope_minifloat,
     "matmul_mxfp": matmul_mxfp,
     "matmul_mxint": matmul_mxint,
     "bmm_mxfp": bmm_mxfp,

@@ -345,6 +345,89 @@ class LinearBlockFP(_LinearBase):
         return linearBlockFP(x, self.weight, self.bias, self.config, self.output_dtype)
 
 
+class _EmbeddingMX(torch.nn.Embedding):
+    """Embedding whose weight is MX-quantized along the embedding dimension at forward time
+    (chop/nn/quantized/modules/embedding.py:9-71).  The reference quantizes the whole table on every call and then
+    looks the rows up; blocks run along a row, so when a row is a whole number of blocks the quantized rows do not
+    depend on one another and this class looks up first and quantizes only the rows that were asked for -- the same
+    values for a fraction of the work.  Tables whose rows are not whole blocks (flattened blocks straddle rows) and
+    lookups with `max_norm` (which rewrites the table) take the reference's order."""
+
+    def __init__(self, num_embeddings, embedding_dim, config=None, **kwargs):
+        super().__init__(num_embeddings, embedding_dim, **kwargs)
+        self.config = config or {}
+        self.bypass = self.config.get("bypass", False)
+
+    def _quantize(self, rows: Tensor) -> Tensor:
+        raise NotImplementedError
+
+    @torch.no_grad()
+    def forward(self, input: Tensor) -> Tensor:
+        if self.bypass:
+            return super().forward(input)
+        args = (self.padding_idx, self.max_norm, self.norm_type, self.scale_grad_by_freq, self.sparse)
+        if self.max_norm is not None or self.embedding_dim % self.config["weight_block_size"]:
+            return torch.nn.functional.embedding(input, self._quantize(self.weight), *args)
+        rows = torch.nn.functional.embedding(input, self.weight, *args)
+        return self._quantize(rows.reshape(-1, self.embedding_dim)).reshape(rows.shape)
+
+
+class EmbeddingMXFP(_EmbeddingMX):
+    def _quantize(self, rows: Tensor) -> Tensor:
+        cfg = self.config
+        return mxfp_quantizer(rows, block_size=cfg["weight_block_size"], element_exp_bits=cfg["weight_exponent_width"],
+                              element_frac_bits=cfg["weight_frac_width"], block_dim=1)
+
+
+class EmbeddingMXInt(_EmbeddingMX):
+    def _quantize(self, rows: Tensor) -> Tensor:
+        cfg = self.config
+        return mxint_quantizer(rows, block_size=cfg["weight_block_size"], element_bits=cfg["weight_width"], block_dim=1)
+
+
+class RMSNormMinifloat(torch.nn.Module):
+    """RMSNorm with minifloat-quantized input and weight, quantized at forward time: the arithmetic of
+    LlamaRMSNormMinifloat (chop/nn/quantized/modules/llama/rms_norm.py:34-84) without the dependency on a
+    `transformers` model config.  `RMSNormMinifloat(hidden_size, eps, q_config)`, or `from_config(config, layer_idx,
+    q_config)` with the reference's constructor arguments."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-6, q_config: dict | None = None, layer_idx=None, device=None,
+                 dtype=None):
+        super().__init__()
+        self.weight = torch.nn.Parameter(torch.ones(hidden_size, device=device, dtype=dtype))
+        self.variance_epsilon = eps
+        self.layer_idx = layer_idx
+        self.q_config = q_config or {}
+        self.bypass = self.q_config.get("bypass", False)
+        self.weight_bypass = self.q_config.get("weight_bypass", False)
+        self.data_in_bypass = self.q_config.get("data_in_bypass", False)
+
+    @classmethod
+    def from_config(cls, config=None, layer_idx=None, q_config: dict | None = None):
+        return cls(config.hidden_size, config.rms_norm_eps, q_config, layer_idx)
+
+    def _meta(self, prefix: str):
+        from .quantizers import MinifloatMeta
+
+        q = self.q_config
+        return MinifloatMeta(exp_bits=q[prefix + "_exponent_width"], frac_bits=q[prefix + "_frac_width"],
+                             is_finite=q.get(prefix + "_is_finite", True), round_mode=q.get(prefix + "_round_mode", "rn"))
+
+    def forward(self, hidden_states: Tensor) -> Tensor:
+        from .quantizers import minifloat_quantizer_sim
+
+        input_dtype = hidden_states.dtype
+        if not self.bypass and not self.data_in_bypass:
+            hidden_states = minifloat_quantizer_sim(hidden_states, self._meta("data_in"))
+        hidden_states = hidden_states.to(torch.float32)
+        variance = hidden_states.pow(2).mean(-1, keepdim=True)
+        hidden_states = hidden_states * torch.rsqrt(variance + self.variance_epsilon)
+        weight = self.weight
+        if not self.bypass and not self.weight_bypass:
+            weight = minifloat_quantizer_sim(self.weight.data, self._meta("weight"))
+        return weight * hidden_states.to(input_dtype)
+
+
 # entries of chop.nn.quantized.modules.quantized_module_map (nn/quantized/modules/__init__.py:241-246)
 quantized_module_map = {
     "linear_mxfp": LinearMXFP,

@@ -47,6 +47,13 @@ def patch(chop=None) -> list[str]:
             done.append(f"chop.nn.quantized.modules.quantized_module_map[{key!r}]")
         for cls in modules.quantized_module_map.values():
             setattr(mm, cls.__name__, cls)
+        for cls in (modules.EmbeddingMXFP, modules.EmbeddingMXInt):  # exported by the package, not in its map
+            setattr(mm, cls.__name__, cls)
+            done.append(f"chop.nn.quantized.modules.{cls.__name__}")
+    me = _maybe("chop.nn.quantized.modules.embedding")
+    if me is not None:
+        me.EmbeddingMXFP, me.EmbeddingMXInt = modules.EmbeddingMXFP, modules.EmbeddingMXInt
+        done.append("chop.nn.quantized.modules.embedding")
     ml = _maybe("chop.nn.quantized.modules.linear")
     if ml is not None:
         for cls in modules.quantized_module_map.values():

@@ -1,0 +1,95 @@
+"""MX functional ops, Embedding and RMSNorm wrappers on the GPU against the same ops built from the CPU oracle."""
+
+import pytest
+import torch
+
+import mase_b200 as mb
+from mase_b200 import gemm
+from conftest import assert_bits_equal
+from oracle import mx_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+FP_CFG = {"data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3,
+          "weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3}
+INT_CFG = {"data_in_block_size": 32, "data_in_width": 8, "weight_block_size": 32, "weight_width": 8}
+
+
+def rel_err(y, ref):
+    return float((y.float().cpu() - ref.float()).abs().max() / ref.float().abs().max())
+
+
+@pytest.mark.parametrize("kind", ["mxfp", "mxint"])
+def test_batched_products_run_on_the_tensor_core_gemm(kind):
+    """bmm_* and matmul_* with a batched second operand: one GEMM launch per batch element, no library GEMM."""
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(6, 40, 64, generator=g).bfloat16()
+    y = torch.randn(6, 64, 96, generator=g).bfloat16()
+    if kind == "mxfp":
+        xq, yq = O.mxfp_fake(x, 32, 4, 3), O.mxfp_fake(y, 32, 4, 3)
+        fn_b, fn_m, cfg = mb.bmm_mxfp, mb.matmul_mxfp, FP_CFG
+    else:
+        xq, yq = O.mxint_fake(x, 32, 8), O.mxint_fake(y, 32, 8)
+        fn_b, fn_m, cfg = mb.bmm_mxint, mb.matmul_mxint, INT_CFG
+    ref = torch.bmm(xq.float(), yq.float())
+    out = fn_b(x.to(DEV), y.to(DEV), cfg)
+    assert out.shape == ref.shape and out.dtype == torch.bfloat16
+    assert rel_err(out, ref) <= 4e-3
+    # matmul with broadcast batch dimensions and with a 2-D second operand
+    x4 = x.view(2, 3, 40, 64)
+    out4 = fn_m(x4.to(DEV), y[:3].to(DEV), cfg)
+    ref4 = torch.matmul(xq.view(2, 3, 40, 64).float(), yq[:3].float())
+    assert out4.shape == ref4.shape and rel_err(out4, ref4) <= 4e-3
+    out2 = fn_m(x.to(DEV), y[0].to(DEV), cfg)
+    assert rel_err(out2, torch.matmul(xq.float(), yq[0].float())) <= 4e-3
+    gemm.check_status()
+    with pytest.raises(RuntimeError):
+        fn_b(x[0].to(DEV), y.to(DEV), cfg)
+
+
+def test_minifloat_functional_wrappers():
+    g = torch.Generator().manual_seed(32)
+    cfg = {"data_in_exponent_width": 4, "data_in_frac_width": 3}
+    x = (torch.randn(4, 8, 16, 32, generator=g) * 3).bfloat16()
+    xq = O.minifloat_fake(x, 4, 3)
+    assert_bits_equal(mb.silu_minifloat(x.to(DEV), cfg), torch.nn.functional.silu(xq.to(DEV)), "silu_minifloat")
+    ref = torch.nn.functional.softmax(xq.to(DEV).float(), dim=-1).to(torch.bfloat16)
+    assert_bits_equal(mb.softmax_minifloat(x.to(DEV), cfg), ref, "softmax_minifloat")
+    q, k = x[:, :, :, :32], (x * 0.5)
+    cos, sin = torch.rand(4, 16, 32, generator=g).bfloat16(), torch.rand(4, 16, 32, generator=g).bfloat16()
+    rq, rk = mb.rope_minifloat(q.to(DEV), k.to(DEV), cos.to(DEV), sin.to(DEV), cfg)
+    cq, sq = O.minifloat_fake(cos, 4, 3).to(DEV).unsqueeze(1), O.minifloat_fake(sin, 4, 3).to(DEV).unsqueeze(1)
+    rot = lambda t: torch.cat((-t[..., 16:], t[..., :16]), dim=-1)  # noqa: E731
+    qd = q.to(DEV)
+    assert_bits_equal(rq, qd * cq + rot(qd) * sq, "rope_minifloat q")
+
+
+@pytest.mark.parametrize("cls,cfg,fake", [
+    (mb.EmbeddingMXFP, {"weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3},
+     lambda w: O.mxfp_fake(w, 32, 4, 3, 1)),
+    (mb.EmbeddingMXInt, {"weight_block_size": 32, "weight_width": 8}, lambda w: O.mxint_fake(w, 32, 8, 1)),
+])
+def test_embedding_looks_up_then_quantizes(cls, cfg, fake):
+    g = torch.Generator().manual_seed(33)
+    for dim in (128, 48):  # 48: rows are not whole blocks, the whole table is quantized as in the reference
+        emb = cls(1000, dim, config=cfg, padding_idx=0, dtype=torch.bfloat16, device=DEV)
+        w = torch.randn(1000, dim, generator=g).bfloat16()
+        emb.weight.data.copy_(w)
+        idx = torch.randint(0, 1000, (7, 33), generator=g)
+        out = emb(idx.to(DEV))
+        ref = torch.nn.functional.embedding(idx, fake(w))
+        assert_bits_equal(out, ref, f"{cls.__name__} dim {dim}")
+    assert cls(10, 32, config={"bypass": True}, device=DEV).bypass
+
+
+def test_rms_norm_minifloat():
+    g = torch.Generator().manual_seed(34)
+    qc = {"weight_exponent_width": 4, "weight_frac_width": 3, "data_in_exponent_width": 5, "data_in_frac_width": 2}
+    norm = mb.RMSNormMinifloat(256, 1e-6, qc, device=DEV, dtype=torch.bfloat16)
+    norm.weight.data.copy_((torch.rand(256, generator=g) + 0.5).bfloat16())
+    x = torch.randn(3, 17, 256, generator=g).bfloat16()
+    y = norm(x.to(DEV))
+    xq = O.minifloat_fake(x, 5, 2).float()
+    h = xq * torch.rsqrt(xq.pow(2).mean(-1, keepdim=True) + 1e-6)
+    ref = O.minifloat_fake(norm.weight.data.cpu(), 4, 3) * h.to(torch.bfloat16)
+    assert y.dtype == torch.bfloat16 and rel_err(y, ref) <= 8e-3  # rsqrt and the mean round differently on the two devices
