@@ -500,37 +500,48 @@ def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
     y1 = stack[0](x0)
     gemm.check_status()
     parity = cpu = None
+    weights_ok = None
     if rank == 0:
         from oracle import mx_oracle as O
 
+        # Layer 1 on four rows, unsharded: activations quantized by the CPU oracle; the three full weights are
+        # regenerated from the seed and fake-quantized on the device, with 64 rows of each checked bit for bit against
+        # the oracle (quantizing all 700 M weight elements on the host would take minutes); the reference products run
+        # in fp32 (torch.matmul as the checker, outside every timed region).
         rows = torch.tensor([0, 1171, 4097, M - 1])
         g1 = torch.Generator(device=device).manual_seed(4)
         wq = []
+        weights_ok = True
         for (n, k) in ((ffn, hidden), (ffn, hidden), (hidden, ffn)):
-            w = (torch.randn(n, k, generator=g1, device=device) * 0.02).to(torch.bfloat16).cpu()
-            wq.append(oracle_quantize_weight(w, 2, 1))
+            w = (torch.randn(n, k, generator=g1, device=device) * 0.02).to(torch.bfloat16)
+            q = mb.mxfp_quantizer(w, 32, 2, 1, 1)
+            idx = torch.arange(0, n, max(1, n // 64), device=device)
+            weights_ok &= torch.equal(q[idx].cpu().view(torch.int16), O.mxfp_fake(w[idx].cpu(), 32, 2, 1, 1).view(torch.int16))
+            wq.append(q)
             del w
         xs = x0[rows.to(device)].cpu()
-        xq = O.mxfp_fake(xs, 32, 4, 3).float()
+        xq = O.mxfp_fake(xs, 32, 4, 3).to(device).float()
         gate = (xq @ wq[0].float().t()).bfloat16()
         up = (xq @ wq[1].float().t()).bfloat16()
-        h = torch.nn.functional.silu(gate) * up
-        ref = O.mxfp_fake(h, 32, 4, 3).float() @ wq[2].float().t()
+        h = (torch.nn.functional.silu(gate) * up).cpu()
+        ref = (O.mxfp_fake(h, 32, 4, 3).to(device).float() @ wq[2].float().t()).cpu()
         got = y1[rows.to(device)].float().cpu()
         parity = float((got - ref).abs().max() / ref.abs().max())
         # CPU baseline: one layer the way MASE's modules run it (quantize, F.linear in bf16) on a sample of the rows
         qs, kind = cpu_quantizers()
         sample = 64
         xc = x0[:sample].cpu()
+        wc = [q.cpu() for q in wq]
+        del wq
         torch.set_num_threads(os.cpu_count() or 1)
         t0 = time.perf_counter()
         xq16 = qs["mxfp"](xc, 32, 4, 3)
-        hc = torch.nn.functional.silu(torch.nn.functional.linear(xq16, wq[0])) * torch.nn.functional.linear(xq16, wq[1])
-        torch.nn.functional.linear(qs["mxfp"](hc, 32, 4, 3), wq[2])
+        hc = torch.nn.functional.silu(torch.nn.functional.linear(xq16, wc[0])) * torch.nn.functional.linear(xq16, wc[1])
+        torch.nn.functional.linear(qs["mxfp"](hc, 32, 4, 3), wc[2])
         t_cpu = time.perf_counter() - t0
         cpu = {"value": 3 * 2.0 * sample * hidden * ffn / t_cpu / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
                "kind": kind, "sample": f"one layer (gate, up, SiLU*mul, down) on {sample} of {M} rows, unsharded"}
-        del wq
+        del wc
     del stack, y1
     torch.cuda.empty_cache()
     ach = flops / sec_step / 1e12
@@ -543,8 +554,10 @@ def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
                          "on the data path" if os.environ.get("MXQ_BENCH_TP_REDUCE", "fused") == "fused"
                          else "fp32 reduce-scatter + bf16 all-gather (NCCL) on a side stream",
             "parity_max_rel_err": parity,
-            "parity_check": "layer 1, rows 0/1171/4097/8191, against the CPU oracle (bf16 roundings of gate, up and "
-                            "SiLU*mul as torch does them)",
+            "parity_check": "layer 1, rows 0/1171/4097/8191: activations quantized by the CPU oracle, weights quantized on "
+                            "the device with 64 rows of each checked bit for bit against the oracle, fp32 reference "
+                            "products, bf16 roundings of gate, up and SiLU*mul as torch does them",
+            "parity_weight_rows_match_oracle": weights_ok,
             "roofline": {"bound": "tensor", "achieved": ach, "peak": world * peaks["fp8_used"], "unit": "TFLOP/s",
                          "frac": ach / (world * peaks["fp8_used"]),
                          "peak_source": f"{world} x " + peaks["fp8_used_source"]},
