@@ -35,14 +35,14 @@ def _product(x: Tensor, y: Tensor, style: str) -> Tensor:
             out = out.squeeze(-2)
         return out.squeeze(-1) if y.dim() == 1 else out
     if y.dim() == 2:
-        return linear_forward(x, y.t().contiguous(), None, x.dtype)
+        return linear_forward(x, y.t().contiguous(), None, x.dtype, fp32_exact=True)
     # batched y: broadcast the batch dimensions, then one GEMM launch per batch element
     batch = torch.broadcast_shapes(x.shape[:-2], y.shape[:-2])
     xb = x.expand(*batch, *x.shape[-2:]).reshape(-1, *x.shape[-2:])
     yt = y.expand(*batch, *y.shape[-2:]).reshape(-1, *y.shape[-2:]).transpose(-1, -2).contiguous()  # [B, N, K]
     out = torch.empty((xb.shape[0], x.shape[-2], y.shape[-1]), dtype=x.dtype, device=x.device)
     for b in range(xb.shape[0]):
-        out[b] = linear_forward(xb[b], yt[b], None, x.dtype)
+        out[b] = linear_forward(xb[b], yt[b], None, x.dtype, fp32_exact=True)
     return out.reshape(*batch, x.shape[-2], y.shape[-1])
 
 

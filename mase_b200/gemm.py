@@ -90,9 +90,19 @@ def _bias_args(bias: Tensor | None):
     return bias.contiguous(), _DT[bias.dtype]
 
 
-def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None, out_dtype: torch.dtype | None = None) -> Tensor:
-    """x[..., K] @ weight[N, K]^T + bias, output in x.dtype (or `out_dtype`); bf16 operands use kind::f16, fp32
-    operands kind::tf32."""
+def _tf32_split(t: Tensor) -> tuple[Tensor, Tensor]:
+    """t = hi + lo with hi holding the top 11 significant bits (exact in tf32) and lo the rest (exact in fp32)."""
+    hi = (t.view(torch.int32) & -8192).view(torch.float32)  # clear the low 13 mantissa bits
+    return hi, t - hi
+
+
+def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None, out_dtype: torch.dtype | None = None,
+                   fp32_exact: bool = False) -> Tensor:
+    """x[..., K] @ weight[N, K]^T + bias, output in x.dtype (or `out_dtype`); bf16 operands use kind::f16 (exact
+    products), fp32 operands kind::tf32.  tf32 keeps 11 significant bits: callers whose fp32 operands are known to fit
+    (MX / block-fp values of at most 11 significant bits) pass `fp32_exact=True`; any other fp32 operands (bypassed
+    layers, weights that were never quantized) are split into a tf32-exact high part and a remainder and multiplied as
+    hi*hi + hi*lo + lo*hi in one GEMM over 3K, which recovers fp32-level products (error ~2**-21 per product)."""
     _require_cuda(x, "linear_forward")
     if x.dtype != weight.dtype:
         raise RuntimeError(f"expected input and weight to have the same dtype, got {x.dtype} and {weight.dtype}")
@@ -107,6 +117,11 @@ def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None, out_dtype: to
         a = a.contiguous().clone() if a.data_ptr() % 16 else a.contiguous()
     w = weight if weight.is_contiguous() else weight.contiguous()
     M = a.shape[0]
+    if x.dtype == torch.float32 and not fp32_exact:
+        a_hi, a_lo = _tf32_split(a)
+        w_hi, w_lo = _tf32_split(w)
+        a, w = torch.cat([a_hi, a_hi, a_lo], dim=1), torch.cat([w_hi, w_lo, w_hi], dim=1)
+        K = 3 * K
     need = 8 if x.dtype == torch.bfloat16 else 4
     if K % need:
         # rows must be multiples of 16 bytes for the tensor maps: pad K with zeros (contributes nothing)

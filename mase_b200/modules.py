@@ -75,6 +75,7 @@ class LinearMXFP(_LinearBase):
         if self.bypass or self.gptq:
             return result
         cfg = self.config
+        self._weight_quantized = True  # from here on `weight` holds MX values: exact on the tf32 tensor cores
         self._pack_weight_for_tensor_cores()  # from the unquantized weight: quantizing twice is not idempotent
         self.weight.data.copy_(
             mxfp_quantizer(
@@ -215,7 +216,8 @@ class LinearMXFP(_LinearBase):
         if isinstance(xq, MXOperand):
             out_dtype = self.output_dtype or self.weight.dtype
             return mx_gemm(xq, self._packed_weight(), self.bias, out_dtype).reshape(*lead, self.out_features)
-        return linear_forward(xq, self.weight, self.bias, self.output_dtype)
+        return linear_forward(xq, self.weight, self.bias, self.output_dtype,
+                              fp32_exact=not self.bypass and getattr(self, "_weight_quantized", False))
 
     @torch.no_grad()
     def forward_gated(self, gate: Tensor, up: Tensor) -> Tensor:
@@ -244,6 +246,7 @@ class LinearMXInt(_LinearBase):
         if self.bypass or self.gptq:
             return result
         cfg = self.config
+        self._weight_quantized = True  # from here on `weight` holds MX values: exact on the tf32 tensor cores
         self.weight.data.copy_(
             mxint_quantizer(self.weight.data, block_size=cfg["weight_block_size"], element_bits=cfg["weight_width"],
                             block_dim=1, quantile_search=self.clip_search)
@@ -264,6 +267,8 @@ class LinearMXInt(_LinearBase):
         x_block, x_bits = cfg.get("data_in_block_size"), cfg.get("data_in_width")
         if x_block is not None and x_bits is not None:
             x = mxint_quantizer(x, block_size=x_block, element_bits=x_bits, block_dim=-1)
+            return linear_forward(x, self.weight, self.bias, self.output_dtype,
+                                  fp32_exact=getattr(self, "_weight_quantized", False))
         return linear_forward(x, self.weight, self.bias, self.output_dtype)
 
 
@@ -280,7 +285,8 @@ class LinearMXInt(_LinearBase):
 
     @torch.no_grad()
     def forward_quantized(self, quantized) -> Tensor:
-        return linear_forward(quantized[0], self.weight, self.bias, self.output_dtype)
+        return linear_forward(quantized[0], self.weight, self.bias, self.output_dtype,
+                              fp32_exact=not self.bypass and getattr(self, "_weight_quantized", False))
 
 
 def forward_siblings(layers, x: Tensor) -> list[Tensor]:
@@ -329,7 +335,9 @@ def linearBlockFP(x: Tensor, weight: Tensor, bias: Tensor = None, config: dict =
     x = x_quantizer(x)
     weight = w_quantizer(weight)
     bias = b_quantizer(bias) if bias is not None else None
-    return linear_forward(x, weight, bias, out_dtype)
+    # width counts the sign: up to 12 means at most 11 significant bits, which tf32 multiplies exactly
+    return linear_forward(x, weight, bias, out_dtype,
+                          fp32_exact=config["weight_width"] <= 12 and config["data_in_width"] <= 12)
 
 
 class LinearBlockFP(_LinearBase):

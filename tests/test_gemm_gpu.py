@@ -33,7 +33,7 @@ def test_dense_gemm_matches_fp32_reference(shape, dtype):
     M, K, N = shape
     xq, wq = quantized_operands(M, K, N, seed=M + K + N, dtype=dtype)
     ref = xq.float() @ wq.float().t()
-    y = gemm.linear_forward(xq.to(DEV), wq.to(DEV), None)
+    y = gemm.linear_forward(xq.to(DEV), wq.to(DEV), None, fp32_exact=True)
     gemm.check_status()
     assert y.dtype == dtype and y.shape == (M, N)
     tol = REL_TOL if dtype == torch.float32 else 4e-3  # bf16 output rounding: half an ulp = 2**-9 of the value
@@ -54,7 +54,7 @@ def test_dense_gemm_bias_and_leading_dims():
     gemm.check_status()
     assert y.shape == (2, 3, 40, 96)
     assert rel_err(y, ref) <= 4e-3
-    y32 = gemm.linear_forward(x.float().to(DEV), w.float().to(DEV), b.float().to(DEV))
+    y32 = gemm.linear_forward(x.float().to(DEV), w.float().to(DEV), b.float().to(DEV), fp32_exact=True)
     assert rel_err(y32, ref) <= REL_TOL
 
 
@@ -107,9 +107,9 @@ def test_dense_gemm_cta_pairs_match_single_cta(shape, dtype):
     g = torch.Generator().manual_seed(6)
     b = torch.randn(N, generator=g).to(dtype).to(DEV)
     with gemm.options(tiles=_lib.TILES_SINGLE):
-        single = gemm.linear_forward(x.to(DEV), w.to(DEV), b)
+        single = gemm.linear_forward(x.to(DEV), w.to(DEV), b, fp32_exact=True)
     with gemm.options(tiles=_lib.TILES_PAIRS):
-        pair = gemm.linear_forward(x.to(DEV), w.to(DEV), b)
+        pair = gemm.linear_forward(x.to(DEV), w.to(DEV), b, fp32_exact=True)
     gemm.check_status()
     assert torch.equal(single, pair)
     ref = x.float() @ w.float().t() + b.float().cpu()
@@ -194,7 +194,7 @@ def test_transposed_small_m_kernel_vs_oracle_and_regular_tiles(shape):
     with gemm.options(no_transposed=1):
         y_tiles = gemm.mx_gemm(xp, wp, b, torch.float32)
     d16 = gemm.linear_forward(xq.to(DEV), wq.to(DEV), b)
-    d32 = gemm.linear_forward(xq.float().to(DEV), wq.float().to(DEV), b.float())
+    d32 = gemm.linear_forward(xq.float().to(DEV), wq.float().to(DEV), b.float(), fp32_exact=True)
     gemm.check_status()
     assert torch.equal(y1, y2)
     assert rel_err(y1, ref) <= REL_TOL and rel_err(y_unsplit, ref) <= REL_TOL and rel_err(y_tiles, ref) <= REL_TOL
@@ -232,3 +232,25 @@ def test_nibble_packed_mxfp4_weight_matches_e4m3_bytes(shape):
         gemm.check_status()
         assert torch.equal(y8, y4), fields
         assert rel_err(y4, ref) <= REL_TOL and rel_err(y4_16, ref) <= 4e-3, fields
+
+
+@pytest.mark.parametrize("shape", [(64, 512, 256), (300, 1000, 520), (2048, 1024, 1024)])
+def test_unquantized_fp32_operands_keep_fp32_level_products(shape):
+    """fp32 operands that are not MX values (bypassed layers, weights that were never quantized): the tf32 tensor cores
+    keep 11 significant bits, so the operands are split into a tf32-exact part and a remainder and multiplied as three
+    products in one GEMM.  Against a float64 reference the result is within 2e-6 of max, where plain tf32 is ~1e-3."""
+    M, K, N = shape
+    g = torch.Generator().manual_seed(14)
+    x = torch.randn(M, K, generator=g)
+    w = torch.randn(N, K, generator=g) * 0.05
+    b = torch.randn(N, generator=g)
+    ref = (x.double() @ w.double().t() + b.double()).float()
+    y = gemm.linear_forward(x.to(DEV), w.to(DEV), b.to(DEV))
+    plain = gemm.linear_forward(x.to(DEV), w.to(DEV), b.to(DEV), fp32_exact=True)  # what tf32 alone would give
+    gemm.check_status()
+    assert rel_err(y, ref) <= 2e-6
+    assert rel_err(plain, ref) > rel_err(y, ref)
+    layer = mb.LinearMXFP(K, N, bias=True, device=DEV, dtype=torch.float32,
+                          config={"bypass": True, "weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3})
+    layer.load_state_dict({"weight": w.to(DEV), "bias": b.to(DEV)}, strict=False)
+    assert rel_err(layer(x.to(DEV)), ref) <= 2e-6
