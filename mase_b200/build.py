@@ -62,5 +62,44 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+EXT_NAME = "_mxq_torch"
+
+
+def ext_path() -> str:
+    import sysconfig
+
+    return os.path.join(LIB_DIR, EXT_NAME + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+
+
+def build_torch_binding(force: bool = False, verbose: bool = False) -> str:
+    """Compile csrc/torch_binding.cpp (host code only, g++) into mase_b200/lib/_mxq_torch*.so, linked against
+    libmxq.so and torch.  Optional: the package issues the same C calls through ctypes when it is absent."""
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension
+
+    build()
+    src = os.path.join(CSRC, "torch_binding.cpp")
+    out = ext_path()
+    deps = [src, os.path.join(ROOT, "include", "mxq.h")]
+    if not force and os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(d) for d in deps):
+        return out
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    inc = cpp_extension.include_paths() + [sysconfig.get_paths()["include"], os.path.join(ROOT, "include"),
+                                           os.path.join(cuda_home, "include")]
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=" + EXT_NAME,
+           "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           *["-I" + i for i in inc], src, "-o", out,
+           "-L" + torch_lib, "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10", "-lc10_cuda", "-ltorch_cuda",
+           "-L" + LIB_DIR, "-l:libmxq.so", "-Wl,-rpath," + torch_lib, "-Wl,-rpath,$ORIGIN"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.run(cmd, check=True)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_torch_binding(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -38,6 +38,28 @@ _STATUS_TEXT = {
 
 
 _TLS = threading.local()
+_EXT = None
+
+
+def _ext():
+    """The compiled torch binding (mase_b200/lib/_mxq_torch*.so, `python -m mase_b200.build`) or False when it has not
+    been built: it issues the same C calls as the ctypes path below with a fraction of the per-call host cost."""
+    global _EXT
+    if _EXT is None:
+        _EXT = False
+        if os.environ.get("MXQ_NO_TORCH_BINDING", "0") != "1":
+            from . import build
+
+            path = build.ext_path()
+            if os.path.exists(path):
+                import importlib.util
+
+                _lib.lib()  # libmxq.so first: the binding links against it
+                spec = importlib.util.spec_from_file_location(build.EXT_NAME, path)
+                mod = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(mod)
+                _EXT = mod
+    return _EXT
 
 
 @contextlib.contextmanager
@@ -111,6 +133,14 @@ def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None, out_dtype: to
     N, K = weight.shape
     if x.shape[-1] != K:
         raise RuntimeError(f"mat1 and mat2 shapes cannot be multiplied ({tuple(x.shape)} and {K}x{N})")
+    ext = _ext()
+    if ext and (x.dtype == torch.bfloat16 or fp32_exact) and K % (8 if x.dtype == torch.bfloat16 else 4) == 0:
+        if bias is not None and bias.dtype not in _DT:
+            raise NotImplementedError(f"bias dtype {bias.dtype} is not supported")
+        out = ext.dense_linear(x, weight, bias, out_dtype, _status(x.device), _options_ptr() or 0)
+        if _CHECK_EVERY_CALL:
+            check_status(x.device)
+        return out
     lead = x.shape[:-1]
     a = x.reshape(-1, K)
     if not a.is_contiguous() or a.data_ptr() % 16:
@@ -282,6 +312,15 @@ def mx_linear(x: Tensor, weight: MXOperand, bias: Tensor | None, exp_bits: int, 
         raise NotImplementedError(f"mx_linear: dtype {x.dtype} is not supported")
     K = x.shape[-1]
     assert K == weight.k
+    ext = _ext()
+    if ext:
+        if bias is not None and bias.dtype not in _DT:
+            raise NotImplementedError(f"bias dtype {bias.dtype} is not supported")
+        out = ext.mx_linear(x, weight.codes, weight.scales, weight.format, weight.rows, bias, exp_bits, frac_bits, out_dtype,
+                            _floor_tab_ptr(), _status(x.device), _options_ptr() or 0)
+        if _CHECK_EVERY_CALL:
+            check_status(x.device)
+        return out
     lead = x.shape[:-1]
     a = x.reshape(-1, K)
     if not a.is_contiguous() or a.data_ptr() % 16:

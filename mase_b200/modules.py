@@ -132,8 +132,13 @@ class LinearMXFP(_LinearBase):
         return out
 
     def _operand(self, codes: Tensor, scales: Tensor) -> MXOperand:
+        cached = self.__dict__.get("_mx_operand")
+        if cached is not None and cached.codes is codes and cached.scales is scales:
+            return cached
         fp4 = codes.shape[1] * 2 == self.in_features and codes.shape[1] != self.in_features
-        return MXOperand(codes, scales, codes.shape[0], self.in_features, fp4)
+        op = MXOperand(codes, scales, codes.shape[0], self.in_features, fp4)
+        self.__dict__["_mx_operand"] = op
+        return op
 
     def _packed_weight(self) -> MXOperand | None:
         """The tensor-core copy of the weight, or None when there is none or `weight` has changed since it was made.
