@@ -227,6 +227,17 @@ int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint
                         int F, const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status,
                         const mxq_gemm_options *options, void *stream);
 
+/* Rotary position embedding y = x * cos + rotate_half(x) * sin in one pass.  Replaces _apply_rope
+ * (chop/nn/quantized/functional/rope.py:17-28; the rope_mxfp / rope_mxint / rope_minifloat wrappers quantize the
+ * tables first and then call it).  x, y: [batch, heads, seq, dim] of `dtype` with a contiguous last dimension and the
+ * element strides given (y has x's layout and must not overlap x); cos, sin:
+ * [batch or 1, seq, dim] of `table_dtype` (table_stride_b = 0 for tables shared by the batch).  dim % 16 == 0.
+ * Tables of the tensor's dtype: each product and the sum are rounded to it, as the framework's elementwise kernels
+ * do; fp32 tables with a bf16 tensor: evaluated in fp32 and rounded once. */
+int mxq_rope(const void *x, void *y, const void *cos, const void *sin, int dtype, int table_dtype, int64_t batch,
+             int64_t heads, int64_t seq, int64_t dim, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s,
+             int64_t table_stride_b, int64_t table_stride_s, void *stream);
+
 /*
  * Row-parallel Linear over the GPUs of one node (tensor parallelism).  The reference reaches this point through
  * DTensor redistribution (chop/distributed/tensor/_redistribute.py:189-245: partial -> replicate = all-reduce); here

@@ -139,7 +139,45 @@ def _rotate_half(x: Tensor) -> Tensor:
     return torch.cat((-x[..., half:], x[..., :half]), dim=-1)
 
 
+def rope_apply(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor | None:
+    """x * cos + rotate_half(x) * sin in one kernel (mxq_rope) for x[batch, heads, seq, dim] on a CUDA device with
+    tables [seq, dim] or [batch, seq, dim]; the result has x's memory layout.  Returns None for layouts the kernel does
+    not take (the caller then composes the elementwise ops)."""
+    from . import _lib
+    from .quantizers import _DT, _on_device, _stream
+
+    if not (x.is_cuda and x.dim() == 4 and x.dtype in _DT and cos.dtype in _DT and cos.dtype == sin.dtype
+            and cos.shape == sin.shape and cos.dim() in (2, 3)):
+        return None
+    if x.dtype == torch.float32 and cos.dtype != torch.float32:
+        return None
+    b, h, s, d = x.shape
+    if d % 16 or x.stride(3) != 1 or cos.shape[-1] != d or cos.shape[-2] < s:
+        return None
+    if cos.dim() == 3 and cos.shape[0] not in (1, b):
+        return None
+    cos, sin = cos.contiguous(), sin.contiguous()
+    tb = cos.stride(0) if cos.dim() == 3 and cos.shape[0] == b and b > 1 else 0
+    ts = cos.stride(-2)
+    y = torch.empty_like(x)  # keeps the strides of a dense, possibly permuted x
+    if y.stride() != x.stride():
+        x = x.contiguous()
+        y = torch.empty_like(x)
+    with _on_device(x):
+        rc = _lib.lib().mxq_rope(x.data_ptr(), y.data_ptr(), cos.data_ptr(), sin.data_ptr(), _DT[x.dtype], _DT[cos.dtype],
+                                 b, h, s, d, x.stride(0), x.stride(1), x.stride(2), tb, ts, _stream(x))
+    if rc in (-2, -4):  # strides or alignment the kernel does not take
+        return None
+    _lib.check(rc, "mxq_rope")
+    return y
+
+
 def _apply_rope(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor, unsqueeze_dim: int):
+    if unsqueeze_dim == 1 and cos.dtype == q.dtype == k.dtype:
+        rq = rope_apply(q, cos, sin)
+        rk = rope_apply(k, cos, sin) if rq is not None else None
+        if rk is not None:
+            return rq, rk
     cos, sin = cos.unsqueeze(unsqueeze_dim), sin.unsqueeze(unsqueeze_dim)
     seq_len = q.size(-2)
     cos, sin = cos[..., :seq_len, :], sin[..., :seq_len, :]

@@ -96,8 +96,14 @@ class DecoderLayer(torch.nn.Module):
     def _rope(self, t):  # t: [B, heads, S, head_dim]
         s, d = t.shape[-2], t.shape[-1]
         cos, sin = self._rope_tables(s, d, t.device)
+        if t.is_cuda:  # one pass over t (the tables are fp32: products and sum in fp32, one rounding)
+            from .functional import rope_apply
+
+            out = rope_apply(t, cos, sin)
+            if out is not None:
+                return out
         rot = torch.cat([-t[..., d // 2:], t[..., : d // 2]], -1)
-        return torch.addcmul(t * cos, rot, sin).to(t.dtype)  # the tables are fp32: products and sum in fp32
+        return torch.addcmul(t * cos, rot, sin).to(t.dtype)
 
     def forward(self, x):  # [B, S, hidden]
         b, s, h = x.shape

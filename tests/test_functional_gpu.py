@@ -93,3 +93,37 @@ def test_rms_norm_minifloat():
     h = xq * torch.rsqrt(xq.pow(2).mean(-1, keepdim=True) + 1e-6)
     ref = O.minifloat_fake(norm.weight.data.cpu(), 4, 3) * h.to(torch.bfloat16)
     assert y.dtype == torch.bfloat16 and rel_err(y, ref) <= 8e-3  # rsqrt and the mean round differently on the two devices
+
+
+def test_rope_kernel_equals_the_elementwise_sequence():
+    """mxq_rope against torch's own elementwise ops on the same device: bit for bit with tables of the tensor's dtype
+    (every product and the sum rounded to it); with fp32 tables and a bf16 tensor both evaluate in fp32 and round once,
+    so they agree up to the last fp32 bit before that rounding.  Permuted and batched layouts."""
+    from mase_b200 import functional as Fn
+
+    g = torch.Generator().manual_seed(35)
+    b, h, s, d = 3, 8, 70, 128
+    base = torch.randn(b, s, h, d, generator=g).bfloat16().to(DEV)
+    q = base.transpose(1, 2)  # [b, h, s, d] view of [b, s, h, d] memory, as attention code produces it
+    cos, sin = torch.rand(b, s, d, generator=g).bfloat16().to(DEV), torch.rand(b, s, d, generator=g).bfloat16().to(DEV)
+    rot = lambda t: torch.cat((-t[..., d // 2:], t[..., : d // 2]), dim=-1)  # noqa: E731
+    ref = q * cos.unsqueeze(1) + rot(q) * sin.unsqueeze(1)
+    out = Fn.rope_apply(q, cos, sin)
+    assert out is not None and out.shape == q.shape
+    assert_bits_equal(out, ref, "bf16 tables, batched")
+    out2 = Fn.rope_apply(q.contiguous(), cos[0], sin[0])
+    assert_bits_equal(out2, q * cos[0] + rot(q) * sin[0], "bf16 tables, shared")
+    c32, s32 = cos[0].float() * 1.001, sin[0].float() * 0.999
+    out3 = Fn.rope_apply(q, c32, s32)
+    ref3 = torch.addcmul(q * c32, rot(q), s32).to(torch.bfloat16)
+    assert float((out3.float() - ref3.float()).abs().max() / ref3.float().abs().max()) <= 2.0 ** -7
+    assert float((out3 != ref3).float().mean()) < 1e-3
+    qf = q.float().contiguous()
+    outf = Fn.rope_apply(qf, c32, s32)
+    assert_bits_equal(outf, qf * c32 + rot(qf) * s32, "fp32")
+    # the functional wrappers go through it
+    cfg = {"data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    rq, rk = mb.rope_mxfp(q, q * 0.5, cos, sin, cfg)
+    cq, sq = mb.mxfp_quantizer(cos, 32, 4, 3), mb.mxfp_quantizer(sin, 32, 4, 3)
+    assert_bits_equal(rq, q * cq.unsqueeze(1) + rot(q) * sq.unsqueeze(1), "rope_mxfp q")
+    assert Fn.rope_apply(q[..., :24], cos[..., :24], sin[..., :24]) is None  # dim not a multiple of 16: composed ops
