@@ -341,7 +341,7 @@ def extras(device, x, peaks: dict) -> dict:
     return out
 
 
-def decoder_layer_extras(device, peaks: dict) -> dict:
+def decoder_layer_extras(device, peaks: dict, steps: int = 10) -> dict:
     """Llama-style decoder layer, hidden 4096, 32 heads, FFN 11008, batch 8 x sequence 512 (4096 tokens), bf16:
     q/k/v/o MXINT8 weights and activations (exact bf16 tensor-core GEMM of the quantized values), gate/up/down MXFP4
     weights x MXFP8 activations (block-scaled GEMM); norms, RoPE, attention and SiLU unquantized."""
@@ -359,7 +359,7 @@ def decoder_layer_extras(device, peaks: dict) -> dict:
     x = torch.randn(8, 512, 4096, generator=g).bfloat16()
     xd = x.to(device)
     with torch.no_grad():
-        t = 1.0 / quick_gbs(lambda: layer(xd), 1, calls=10) / 1e9
+        t = 1.0 / quick_gbs(lambda: layer(xd), 1, calls=steps) / 1e9
     gemm.check_status(device)
     flops = layer.linear_flops(tokens)
     flops_int = 2.0 * tokens * 4 * layer.hidden * layer.hidden   # q/k/v/o on the bf16 kind
@@ -729,6 +729,20 @@ def run_linear(args) -> None:
     }))
 
 
+def run_decoder(args) -> None:
+    """`--workload decoder`: the mixed-precision decoder layer alone (single GPU), one JSON line; for launch lists."""
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    peaks = {"bf16_tflops": measured_bf16_tflops()[0]}
+    peaks["fp8_used"], peaks["fp8_used_source"] = 2.0 * peaks["bf16_tflops"], "2 x measured bf16 (no FP8 GEMM measured in this mode)"
+    out = decoder_layer_extras(device, peaks, steps=args.steps)
+    print(json.dumps({"metric": "decoder_layer_linear_TFLOPs", "value": out["linear_TFLOPs"], "unit": "TFLOP/s", "n_gpus": 1,
+                      "steps": args.steps, "ms_per_step": out["ms_per_forward"], "higher_is_better": True,
+                      "config": {"workload": "Llama-style decoder layer, hidden 4096, FFN 11008, 8 x 512 tokens, MXINT8 "
+                                             "attention projections, MXFP4-weight / MXFP8-activation FFN"},
+                      "roofline": out["roofline"], "cpu_baseline": out["cpu_baseline"]}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -738,13 +752,17 @@ def main() -> None:
     ap.add_argument("--no-extra", action="store_true", help="skip the untimed extra measurements")
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the [rows, 8192] tensor (default: the full workload)")
     ap.add_argument("--kernel-only", action="store_true", help="only the device-resident timed region (for profilers)")
-    ap.add_argument("--workload", default="quant", choices=["quant", "linear"],
-                    help="quant: the headline quantizer benchmark; linear: MXFP8 Linear forward (profiling aid)")
+    ap.add_argument("--workload", default="quant", choices=["quant", "linear", "decoder"],
+                    help="quant: the headline quantizer benchmark; linear: MX Linear forward; decoder: the mixed-precision "
+                         "decoder layer (both profiling aids)")
     ap.add_argument("--m", type=int, default=8192, help="tokens for --workload linear")
     ap.add_argument("--wfmt", default="e4m3", choices=["e4m3", "e2m1"], help="weight format for --workload linear")
     args = ap.parse_args()
     if args.workload == "linear" and args.impl == "ours":
         run_linear(args)
+        return
+    if args.workload == "decoder" and args.impl == "ours":
+        run_decoder(args)
         return
     if args.impl == "reference":
         run_reference(args)
