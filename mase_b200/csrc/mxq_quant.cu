@@ -380,7 +380,7 @@ __device__ __forceinline__ uint4 silu_mul_vec(const uint4 &g, const uint4 &u) {
   return make_uint4(silu_mul_pair(g.x, u.x), silu_mul_pair(g.y, u.y), silu_mul_pair(g.z, u.z), silu_mul_pair(g.w, u.w));
 }
 template <int E, int F>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 4)
 silu_mul_pack_mma_kernel(const __nv_bfloat16 *__restrict__ gate, const __nv_bfloat16 *__restrict__ up, int64_t ld,
                          uint8_t *__restrict__ codes, uint8_t *__restrict__ scales, int64_t n_unit,
                          uint32_t unit_per_row, int64_t k_chunks, const __grid_constant__ Log2Tab tab) {
