@@ -465,6 +465,8 @@ def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
     reduction.  Strong scaling (total work fixed); every rank runs it.  Outside the timed region rank 0 recomputes a
     few output rows of the first layer on the CPU with the oracle (weights regenerated from the seed and quantized by
     the oracle) and reports the largest deviation, so the multi-GPU result is checked in the run that times it."""
+    import torch.distributed as dist
+
     import mase_b200 as mb
     from mase_b200 import gemm, tp as tpmod
 
@@ -472,27 +474,68 @@ def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
     cfg = {"weight_block_size": 32, "weight_exponent_width": 2, "weight_frac_width": 1,
            "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
     tp = tpmod.TPGroup(rank, world, None)
-    gen = torch.Generator(device=device).manual_seed(4)
-    stack = []
-    for _ in range(layers):
-        # every rank draws the same full weights (same seed) and keeps its shards
-        ws = [(torch.randn(n, k, generator=gen, device=device) * 0.02).to(torch.bfloat16)
-              for (n, k) in ((ffn, hidden), (ffn, hidden), (hidden, ffn))]
-        stack.append(tpmod.build_tp_gated_mlp(mb.LinearMXFP, ws[0], ws[1], ws[2], cfg, tp, device=device,
-                                              reduce=os.environ.get("MXQ_BENCH_TP_REDUCE", "fused")))
-        del ws
-    x0 = torch.randn(M, hidden, generator=gen, device=device).to(torch.bfloat16)
+    reduce_mode = os.environ.get("MXQ_BENCH_TP_REDUCE", "fused")
 
-    results = {}
-    for micro in ((1,) if world == 1 else (1, 2)):
-        def step():
-            return tpmod.run_mlp_stack(stack, x0, micro_batches=micro, comm_sms=int(os.environ.get("MXQ_BENCH_COMM_SMS", 32)))
+    def build_stack(mode: str):
+        gen = torch.Generator(device=device).manual_seed(4)
+        stack = []
+        for _ in range(layers):
+            # every rank draws the same full weights (same seed) and keeps its shards
+            ws = [(torch.randn(n, k, generator=gen, device=device) * 0.02).to(torch.bfloat16)
+                  for (n, k) in ((ffn, hidden), (ffn, hidden), (hidden, ffn))]
+            stack.append(tpmod.build_tp_gated_mlp(mb.LinearMXFP, ws[0], ws[1], ws[2], cfg, tp, device=device, reduce=mode))
+            del ws
+        return stack, torch.randn(M, hidden, generator=gen, device=device).to(torch.bfloat16)
 
-        for _ in range(2):
-            step()
-        steps = 3
-        results[micro] = time_region(step, steps, world, device) / steps
-    gemm.check_status()
+    def time_stack(stack, x0):
+        res = {}
+        for micro in ((1,) if world == 1 else (1, 2)):
+            def step():
+                return tpmod.run_mlp_stack(stack, x0, micro_batches=micro, comm_sms=int(os.environ.get("MXQ_BENCH_COMM_SMS", 32)))
+
+            for _ in range(2):
+                step()
+            steps = 3
+            res[micro] = time_region(step, steps, world, device) / steps
+        gemm.check_status()
+        return res
+
+    stack, x0 = build_stack(reduce_mode)
+    fallback_note = None
+    by_mode = {}
+    if reduce_mode == "fused" and world > 1:
+        # the fused reduction needs symmetric memory and peer access between all ranks: try one step, and let every
+        # rank fall back to the collective route together if any of them could not run it
+        ok, why = 1, ""
+        try:
+            tpmod.run_mlp_stack(stack, x0)
+            gemm.check_status()
+        except Exception as exc:  # noqa: BLE001 - reported in the JSON line
+            ok, why = 0, f"{type(exc).__name__}: {exc}"[:200]
+        flag = torch.tensor([ok], device=device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            reduce_mode = "scatter_gather"
+            fallback_note = "fused reduction unavailable on this run" + (f" ({why})" if why else "")
+        else:
+            by_mode["fused"] = time_stack(stack, x0)
+        # The peer-store route and the collective route are both measured: small stores over NVLink favour the fused
+        # route on few GPUs and the collective on many.  The faster one is the reported configuration.
+        del stack
+        torch.cuda.empty_cache()
+        stack, x0 = build_stack("scatter_gather")
+        by_mode["scatter_gather"] = time_stack(stack, x0)
+        if "fused" in by_mode and min(by_mode["fused"].values()) <= min(by_mode["scatter_gather"].values()):
+            del stack
+            torch.cuda.empty_cache()
+            reduce_mode = "fused"
+            stack, x0 = build_stack("fused")
+        else:
+            reduce_mode = "scatter_gather"
+        results = by_mode[reduce_mode]
+    else:
+        results = time_stack(stack, x0)
+        by_mode[reduce_mode] = results
     micro, sec_step = min(results.items(), key=lambda kv: kv[1])
     flops = layers * 3 * 2.0 * M * hidden * ffn
 
@@ -549,10 +592,12 @@ def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
             "ms_per_step": sec_step * 1e3, "TFLOPs_aggregate": ach, "n_gpus": world,
             "scaling": "strong", "micro_batches": micro,
             "ms_per_step_by_micro_batches": {str(k): v * 1e3 for k, v in results.items()},
+            "ms_per_step_by_reduction": {m: {str(k): v * 1e3 for k, v in r.items()} for m, r in by_mode.items()},
             "reduction": "fused: GEMM epilogue stores fp32 tiles into the owning GPU's memory (peer stores over NVLink), "
                          "bounded peer barrier, reduce + bf16 all-gather kernel over peer stores; no collective library "
-                         "on the data path" if os.environ.get("MXQ_BENCH_TP_REDUCE", "fused") == "fused"
+                         "on the data path" if reduce_mode == "fused"
                          else "fp32 reduce-scatter + bf16 all-gather (NCCL) on a side stream",
+            "reduction_note": fallback_note,
             "parity_max_rel_err": parity,
             "parity_check": "layer 1, rows 0/1171/4097/8191: activations quantized by the CPU oracle, weights quantized on "
                             "the device with 64 rows of each checked bit for bit against the oracle, fp32 reference "

@@ -202,7 +202,8 @@ def test_weight_only_storage_round_trip():
     layer.drop_dense_weight()
     assert layer.weight.numel() == 0
     packed_bytes = layer.weight_codes.numel() + layer.weight_scales.numel()
-    assert packed_bytes <= 0.55 * dense_bytes
+    assert layer.weight_codes.shape == (768, 512)  # MXFP4: two codes per byte
+    assert packed_bytes <= 0.28 * dense_bytes       # 0.53 bytes per element against 2
     assert torch.equal(layer(x.to(DEV)), y0)
     state = layer.state_dict()
     assert "weight_codes" in state and "weight_scales" in state
@@ -212,6 +213,22 @@ def test_weight_only_storage_round_trip():
     gemm.check_status()
     with pytest.raises(RuntimeError):
         fresh(x.to(DEV).float())
+    # a checkpoint whose packed weight does not fit the layer is refused instead of reaching the GEMM
+    other = mb.LinearMXFP(1024, 512, bias=False, device=DEV, dtype=torch.bfloat16, config=dict(cfg))
+    with pytest.raises(RuntimeError, match="do not fit"):
+        other.load_state_dict(state)
+    # MXFP8 weights keep one byte per element
+    cfg8 = dict(cfg, weight_exponent_width=4, weight_frac_width=3)
+    l8 = mb.LinearMXFP(1024, 768, bias=False, device=DEV, dtype=torch.bfloat16, config=cfg8)
+    l8.load_state_dict({"weight": w.to(DEV)}, strict=False)
+    y8 = l8(x.to(DEV))
+    l8.drop_dense_weight()
+    assert l8.weight_codes.shape == (768, 1024) and torch.equal(l8(x.to(DEV)), y8)
+    # an update of the dense weight through .data (no version bump) on a moved layer: the packed copy follows .to()
+    moved = mb.LinearMXFP(1024, 768, bias=False, device=DEV, dtype=torch.bfloat16, config=dict(cfg))
+    moved.load_state_dict({"weight": w.to(DEV)}, strict=False)
+    moved.to(DEV)
+    assert moved._packed_weight() is not None
 
 
 def test_functional_elementwise_mx_ops_vs_oracle():
