@@ -333,24 +333,24 @@ __device__ __forceinline__ void drain_accumulator(const Params &p, const CUtenso
         }
         buf = (buf + 1) % kStoreBufs;
       } else {
+        // fp32: one box of 32 columns (128 bytes per row, 128-byte swizzle) per chunk.  It takes both of the warp's
+        // staging buffers, so the previous box must have been read out first; rows of 128 bytes matter when the
+        // destination is another GPU (64-byte rows reached a quarter of the link's bandwidth).
+        static_assert(kStoreBufs == 2, "the fp32 box spans both staging buffers");
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+        uint8_t *dst = stage_buf + lane * 128;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {  // fp32: two boxes of 16 columns (64 bytes per row) per chunk
-          if (n0 + c + 16 * h >= p.N) break;
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStoreBufs - 1) : "memory");
-          __syncwarp();
-          uint8_t *dst = stage_buf + buf * 2048 + lane * 64;
-#pragma unroll
-          for (int t = 0; t < 4; ++t)
-            *reinterpret_cast<uint4 *>(dst + ((t ^ ((lane >> 1) & 3)) << 4)) =
-                make_uint4(v[16 * h + 4 * t], v[16 * h + 4 * t + 1], v[16 * h + 4 * t + 2], v[16 * h + 4 * t + 3]);
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(map_d, smem_u32(stage_buf + buf * 2048), n0 + c + 16 * h, row0);
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          }
-          buf = (buf + 1) % kStoreBufs;
+        for (int t = 0; t < 8; ++t)  // 16-byte chunk t of this row lands at chunk t ^ (row & 7)
+          *reinterpret_cast<uint4 *>(dst + ((t ^ (lane & 7)) << 4)) =
+              make_uint4(v[4 * t], v[4 * t + 1], v[4 * t + 2], v[4 * t + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(map_d, smem_u32(stage_buf), n0 + c, row0);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
+        buf = 0;
       }
     } else if (row0 + lane < p.M) {
       const size_t off = (size_t)(row0 + lane) * p.N + n0 + c;
@@ -1267,18 +1267,19 @@ static int make_map_fp4(CUtensorMap *map, const void *ptr, int64_t rows, int64_t
   return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_UNSUPPORTED;
 }
 
-// tensor map of the output [rows, n] for stores of 32-row x 64-byte boxes, 64-byte swizzle
+// tensor map of the output [rows, n] for stores of 32-row x 32-column boxes: 64-byte rows with 64-byte swizzle for
+// bf16, 128-byte rows with 128-byte swizzle for fp32
 static int make_store_map(CUtensorMap *map, void *ptr, bool bf16, int64_t rows, int64_t n) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return MXQ_ERR_UNSUPPORTED;
   const int es = bf16 ? 2 : 4;
   cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)n * es};
-  cuuint32_t box[2] = {(cuuint32_t)(64 / es), 32};
+  cuuint32_t box[2] = {32, 32};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, bf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_LAUNCH;
 }
 
