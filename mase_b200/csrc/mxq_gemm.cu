@@ -263,6 +263,10 @@ struct Params {
   // Row-parallel GEMM fused with the reduce-scatter (CTA-pair kernel): rows [r * scatter_rows, (r + 1) * scatter_rows)
   // of the fp32 result go to store map r, which covers a buffer in GPU r's memory.  0 = one output, map 0.
   int scatter_rows;
+  // Rows of 256-row tiles by which the CTA-pair kernel's tile order is rotated.  With a scatter every GPU of the group
+  // starts with the rows of a different owner (its successor's), so that at any time the GPUs store into different
+  // peers instead of all into the same one.
+  int m_rotate;
 };
 
 // Store maps of the CTA-pair kernel: one output, or one slot buffer per GPU of a tensor-parallel group.
@@ -805,7 +809,8 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     int issued = 0;
     bool ok = true;
     for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
-      const int m_blk = (tile / tiles_n) * 2 + (int)rank;      // 128-row block of A and of the A scales
+      // (row of tiles, rotated when the epilogue scatters to other GPUs: see Params::m_rotate)
+      const int m_blk = ((tile / tiles_n + p.m_rotate) % tiles_m) * 2 + (int)rank;  // 128-row block of A and its scales
       const int n_blk = (tile % tiles_n) * 2;                  // first of the tile's two 128-column blocks
       const int row_a = m_blk * BM, row_b = (n_blk + (int)rank) * 128;
       int chunk_a = m_blk * p.k_chunks, chunk_b = n_blk * p.k_chunks;
@@ -917,7 +922,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     int buf = 0;
     int local = 0;
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++local) {
-      const int m_blk = (tile / tiles_n) * 2 + (int)rank, n_blk = tile % tiles_n;
+      const int m_blk = ((tile / tiles_n + p.m_rotate) % tiles_m) * 2 + (int)rank, n_blk = tile % tiles_n;
       const int acc = local & 1;
       const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait, p.wait_ns)) break;
@@ -1381,7 +1386,7 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   p.wait_ns = o.wait_ns, p.drop_last_load = !kSplit && o.test_hook == MXQ_TEST_DROP_LAST_LOAD;
   p.b_fp4 = o.b_fp4 ? 1u : 0u;
   p.tx_less = o.b_fp4 ? BN * (kRowBytes / 2) : 0;
-  p.scatter_rows = 0;
+  p.scatter_rows = 0, p.m_rotate = 0;
   CUtensorMap msa = ma, msb = ma;  // unused by the dense kinds
   if constexpr (kKind == kMxf8) {
     rc = make_sf_map(&msa, sfa, ((M + 255) / 256) * 2 * p.k_chunks);
@@ -1458,6 +1463,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   p.b_fp4 = o.b_fp4 ? 1u : 0u;
   p.tx_less = o.b_fp4 ? 2 * 128 * (kRowBytes / 2) : 0;  // the B boxes of both CTAs
   p.scatter_rows = o.scatter_world > 0 ? (int)(M / o.scatter_world) : 0;
+  p.m_rotate = o.scatter_world > 0 ? (int)((((int64_t)o.scatter_rank + 1) % o.scatter_world) * (M / o.scatter_world / 256)) : 0;
   static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
   bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {

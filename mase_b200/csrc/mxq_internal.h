@@ -22,6 +22,7 @@ struct Opts {
   bool b_fp4 = false;  // block-scaled kind: B (the weight) holds E2M1 elements, two per byte
   // reduce-scatter fused into the GEMM: fp32 slot buffer of every GPU of the group (rows M / scatter_world each)
   int scatter_world = 0;
+  int scatter_rank = 0;
   void *scatter_dst[8] = {};
 };
 

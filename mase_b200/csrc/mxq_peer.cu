@@ -122,6 +122,7 @@ int mxq_gemm_mxf8_scatter(const uint8_t *a_codes, const uint8_t *a_scales, const
   mxq::gemm::Opts o = mxq::gemm::make_opts(options);
   o.b_fp4 = b_format == MXQ_CODES_E2M1X2;
   o.scatter_world = world;
+  o.scatter_rank = rank;
   const int64_t slot_bytes = (M / world) * N * 4;  // this rank's slot inside every GPU's buffer
   for (int r = 0; r < world; ++r) {
     if (!slot_ptrs[r] || (reinterpret_cast<uintptr_t>(slot_ptrs[r]) & 15u)) return MXQ_ERR_ALIGN;
