@@ -272,6 +272,15 @@ int mxq_peer_barrier(void *const *flag_ptrs, int world, int rank, uint32_t epoch
 int mxq_reduce_gather(const void *slots, int world, int rank, int64_t rows, int64_t n, const void *bias, int bias_dtype,
                       void *const *out_ptrs, int out_dtype, int max_ctas, void *stream);
 
+/* mxq_reduce_gather for an output that the next layer consumes as an MXFP(E, F) activation (blocks of 32 along n):
+ * the reduced slice is rounded to bf16 -- the value a separate output tensor would hold -- quantized exactly as
+ * mxq_mxfp_pack_mma quantizes that tensor, and written as E4M3 bytes [world * rows, n] + scale chunks
+ * (mxq_mma_scale_bytes(world * rows, n)) into every GPU's operand buffers; with out_ptrs != NULL the bf16 rows are
+ * written as well.  Half the all-gather bytes, and the consumer needs no pack.  n % 128 == 0. */
+int mxq_reduce_gather_pack(const void *slots, int world, int rank, int64_t rows, int64_t n, const void *bias,
+                           int bias_dtype, void *const *codes_ptrs, void *const *scales_ptrs, void *const *out_ptrs, int E,
+                           int F, const uint8_t *floor_tab_host, int max_ctas, void *stream);
+
 /* Allocation-free variant of mxq_mx_linear.  It has no counterpart in the reference.
  *
  * Some callers are not in a position to hand over scratch memory: code that runs where the allocator must not be

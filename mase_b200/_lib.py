@@ -43,6 +43,8 @@ _PROTOTYPES = {
                               c_int64, c_void_p, c_void_p, c_void_p],
     "mxq_peer_barrier": [c_void_p, c_int, c_int, ctypes.c_uint32, c_void_p, c_int64, c_void_p],
     "mxq_reduce_gather": [c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+    "mxq_reduce_gather_pack": [c_void_p, c_int, c_int, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                               c_int, c_void_p, c_int, c_void_p],
     "mxq_mx_linear_static": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
                              c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "mxq_bfp_fake_tiles": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,

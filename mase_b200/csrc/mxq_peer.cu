@@ -17,6 +17,7 @@
 
 #include "mxq.h"
 #include "mxq_internal.h"
+#include "mxq_pack.cuh"
 
 namespace mxq {
 namespace peer {
@@ -105,6 +106,76 @@ reduce_gather_kernel(const float *__restrict__ slots, int world, int rank, int64
   }
 }
 
+// byte offset of the E8M0 scale of (row, block kb of 32 along K) in the tensor-core scale layout
+__device__ __forceinline__ int64_t scale_offset(int64_t row, int64_t kb, int64_t k_chunks) {
+  return ((row >> 7) * k_chunks + (kb >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kb & 3);
+}
+
+// The same reduction, but what goes to every GPU is the next layer's activation operand: the reduced row slice is
+// rounded to bf16 (the value a separate output tensor would hold), MXFP(E, F)-quantized in blocks of 32 along the row
+// exactly as the activation pack does, and written as E4M3 bytes + E8M0 scale chunks into every GPU's operand buffers
+// (and, when out.p[0] is set, also as bf16 into every GPU's output).  Half the all-gather bytes and no pack kernel in
+// the consumer.  Each thread: 16 consecutive columns (half a block) of one row; the two lanes of a block are neighbours.
+template <int E, int F>
+__global__ void __launch_bounds__(256)
+reduce_gather_pack_kernel(const float *__restrict__ slots, int world, int rank, int64_t rows, int64_t n, const void *bias,
+                          int bias_bf16, PeerPtrs codes, PeerPtrs scales, PeerPtrs out,
+                          const __grid_constant__ mxq::Log2Tab tab) {
+  const int64_t unit_per_row = n / 16;
+  const int64_t total = rows * unit_per_row;
+  const int64_t slot_elems = rows * n;
+  const int64_t k_chunks = (n + 127) / 128;
+  const int64_t padded = ((total + 31) / 32) * 32;  // whole warps run the shuffles inside pack_bf16
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < padded; i += (int64_t)gridDim.x * blockDim.x) {
+    const bool live = i < total;
+    const int64_t row = live ? i / unit_per_row : 0, col = live ? (i - row * unit_per_row) * 16 : 0;
+    const int64_t off = row * n + col;
+    float acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+    if (live) {
+      for (int s = 0; s < world; ++s) {  // rank order: the sum does not depend on arrival times
+        const float4 *q = reinterpret_cast<const float4 *>(slots + s * slot_elems + off);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const float4 a = __ldcs(q + v);
+          if (s == 0)
+            acc[4 * v] = a.x, acc[4 * v + 1] = a.y, acc[4 * v + 2] = a.z, acc[4 * v + 3] = a.w;
+          else
+            acc[4 * v] += a.x, acc[4 * v + 1] += a.y, acc[4 * v + 2] += a.z, acc[4 * v + 3] += a.w;
+        }
+      }
+      if (bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          acc[j] += bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(bias)[col + j])
+                              : reinterpret_cast<const float *>(bias)[col + j];
+      }
+    }
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      w[j] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+    const uint4 lo = make_uint4(w[0], w[1], w[2], w[3]), hi = make_uint4(w[4], w[5], w[6], w[7]);
+    int scale;
+    const uint4 c16 = mxq::pack_bf16<E, F>(lo, hi, tab, scale);  // all lanes take part (shuffle inside)
+    if (!live) continue;
+    const int64_t grow = (int64_t)rank * rows + row;  // row in the full [world * rows, n] matrix
+    const int64_t dst = grow * n + col;
+    const int64_t sdst = scale_offset(grow, col >> 5, k_chunks);
+    for (int g = 0; g < world; ++g) {
+      *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(codes.p[g]) + dst) = c16;
+      if ((threadIdx.x & 1) == 0) reinterpret_cast<uint8_t *>(scales.p[g])[sdst] = (uint8_t)scale;
+      if (out.p[0] != nullptr) {
+        uint4 *q = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(out.p[g]) + dst);
+        q[0] = lo, q[1] = hi;
+      }
+    }
+  }
+}
+
 }  // namespace peer
 }  // namespace mxq
 
@@ -171,6 +242,41 @@ int mxq_reduce_gather(const void *slots, int world, int rank, int64_t rows, int6
     reduce_gather_kernel<float><<<(int)grid, 256, 0, st>>>((const float *)slots, world, rank, rows, n, bias,
                                                            bias_dtype == MXQ_BF16, out);
   return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;
+}
+
+int mxq_reduce_gather_pack(const void *slots, int world, int rank, int64_t rows, int64_t n, const void *bias,
+                           int bias_dtype, void *const *codes_ptrs, void *const *scales_ptrs, void *const *out_ptrs, int E,
+                           int F, const uint8_t *floor_tab_host, int max_ctas, void *stream) {
+  if (rows == 0 || n == 0) return MXQ_OK;
+  if (!slots || !codes_ptrs || !scales_ptrs || !floor_tab_host) return MXQ_ERR_NULL;
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || rows < 0 || n < 0 || n % 128) return MXQ_ERR_SHAPE;
+  if (bias && bias_dtype != MXQ_F32 && bias_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
+  if (reinterpret_cast<uintptr_t>(slots) & 15u) return MXQ_ERR_ALIGN;
+  PeerPtrs codes = {}, scales = {}, out = {};
+  for (int r = 0; r < world; ++r) {
+    if (!codes_ptrs[r] || !scales_ptrs[r] || (reinterpret_cast<uintptr_t>(codes_ptrs[r]) & 15u)) return MXQ_ERR_ALIGN;
+    codes.p[r] = codes_ptrs[r], scales.p[r] = scales_ptrs[r];
+    if (out_ptrs) {
+      if (!out_ptrs[r] || (reinterpret_cast<uintptr_t>(out_ptrs[r]) & 15u)) return MXQ_ERR_ALIGN;
+      out.p[r] = out_ptrs[r];
+    }
+  }
+  mxq::Log2Tab tab;
+  for (int i = 0; i < 256; ++i) tab.t[i] = floor_tab_host[i];
+  const int64_t total = rows * (n / 16);
+  int64_t grid = (total + 255) / 256;
+  const int64_t cap = max_ctas > 0 ? max_ctas : (int64_t)mxq::gemm::sm_count() * 4;
+  if (grid > cap) grid = cap;
+  cudaStream_t st = (cudaStream_t)stream;
+#define MXQ_RGP(e, f)                                                                                                  \
+  if (E == e && F == f) {                                                                                              \
+    reduce_gather_pack_kernel<e, f><<<(int)grid, 256, 0, st>>>((const float *)slots, world, rank, rows, n, bias,       \
+                                                               bias_dtype == MXQ_BF16, codes, scales, out, tab);       \
+    return cudaGetLastError() == cudaSuccess ? MXQ_OK : MXQ_ERR_LAUNCH;                                                \
+  }
+  MXQ_RGP(4, 3) MXQ_RGP(2, 3) MXQ_RGP(3, 2) MXQ_RGP(2, 1) MXQ_RGP(1, 2)
+#undef MXQ_RGP
+  return MXQ_ERR_FORMAT;
 }
 
 }  // extern "C"

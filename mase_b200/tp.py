@@ -91,8 +91,9 @@ class ColumnParallelLinear(nn.Module):
                              "all-gather takes equal shards")
         self.inner, self.tp, self.gather_output = inner, tp, gather_output
 
-    def forward(self, x: Tensor) -> Tensor:
-        y = self.inner(x)
+    def forward(self, x) -> Tensor:
+        # x: a tensor, or the (operand, leading shape) pair a fused row-parallel layer delivers with `emit_packed`
+        y = self.inner.forward_quantized(x) if isinstance(x, tuple) else self.inner(x)
         if not self.gather_output or self.tp.world == 1:
             return y
         parts = [torch.empty_like(y) for _ in range(self.tp.world)]
@@ -149,13 +150,20 @@ class PeerReducer:
         ptrs = (self._ctypes.c_void_p * self.tp.world)(*[int(p) for p in hdl.buffer_ptrs])
         return t, ptrs
 
-    def plan(self, rows: int, cols: int, out_dtype, tag: int = 0) -> dict:
+    def plan(self, rows: int, cols: int, out_dtype, tag: int = 0, packed: bool = False) -> dict:
         key = (rows, cols, out_dtype, tag)
         if key not in self._plans:
             slots, slot_ptrs = self._alloc(rows * cols, torch.float32)
             out, out_ptrs = self._alloc(rows * cols, out_dtype)
             self._plans[key] = {"slots": slots, "slot_ptrs": slot_ptrs, "out": out.view(rows, cols), "out_ptrs": out_ptrs}
-        return self._plans[key]
+        plan = self._plans[key]
+        if packed and "codes" not in plan:  # operand buffers for a consumer that takes the result as MXFP codes
+            from . import _lib
+
+            codes, code_ptrs = self._alloc(rows * cols, torch.uint8)
+            scales, scale_ptrs = self._alloc(int(_lib.lib().mxq_mma_scale_bytes(rows, cols)), torch.uint8)
+            plan.update({"codes": codes.view(rows, cols), "code_ptrs": code_ptrs, "scales": scales, "scale_ptrs": scale_ptrs})
+        return plan
 
     def barrier(self, status: Tensor, stream) -> None:
         from . import _lib
@@ -175,12 +183,21 @@ class PeerReducer:
                                               stream)
         _lib.check(rc, "mxq_gemm_mxf8_scatter")
 
-    def reduce_gather(self, plan: dict, bias: Tensor | None, max_ctas: int, stream) -> None:
+    def reduce_gather(self, plan: dict, bias: Tensor | None, max_ctas: int, stream, pack: tuple | None = None) -> None:
+        """Sum this rank's slice and write it into every rank's output; with `pack=(E, F)` into every rank's MXFP
+        operand buffers instead (the next layer's activation, already quantized)."""
         from . import _lib
-        from .quantizers import _DT
+        from .quantizers import _DT, _floor_tab_ptr
 
         rows, cols = plan["out"].shape
         b = None if bias is None else bias.contiguous()
+        if pack is not None:
+            rc = _lib.lib().mxq_reduce_gather_pack(plan["slots"].data_ptr(), self.tp.world, self.tp.rank,
+                                                   rows // self.tp.world, cols, 0 if b is None else b.data_ptr(),
+                                                   0 if b is None else _DT[b.dtype], plan["code_ptrs"], plan["scale_ptrs"],
+                                                   None, pack[0], pack[1], _floor_tab_ptr(), max_ctas, stream)
+            _lib.check(rc, "mxq_reduce_gather_pack")
+            return
         rc = _lib.lib().mxq_reduce_gather(plan["slots"].data_ptr(), self.tp.world, self.tp.rank, rows // self.tp.world, cols,
                                           0 if b is None else b.data_ptr(), 0 if b is None else _DT[b.dtype],
                                           plan["out_ptrs"], _DT[plan["out"].dtype], max_ctas, stream)
@@ -230,34 +247,40 @@ class RowParallelLinear(nn.Module):
                 and rows % (256 * self.tp.world) == 0 and inner.out_features % 8 == 0
                 and PeerReducer.available(self.tp, like.device))
 
-    def _start_fused(self, a_op, like: Tensor, tag: int):
+    def _start_fused(self, a_op, like: Tensor, tag: int, emit_packed: tuple | None = None):
         from . import gemm
 
         red = PeerReducer.for_group(self.tp, like.device)
-        plan = red.plan(a_op.rows, self.inner.out_features, like.dtype, tag)
+        if emit_packed is not None and (like.dtype != torch.bfloat16 or self.inner.out_features % 128):
+            emit_packed = None
+        plan = red.plan(a_op.rows, self.inner.out_features, like.dtype, tag, packed=emit_packed is not None)
         status = gemm._status(like.device)
         cur = torch.cuda.current_stream(like.device)
         red.scatter_gemm(a_op, self.inner._packed_weight(), plan, status, gemm._options_ptr(), cur.cuda_stream)
         side = self._side_stream(like.device)
         side.wait_stream(cur)
         red.barrier(status, side.cuda_stream)          # every GPU's tiles have landed
-        red.reduce_gather(plan, self.bias, self.reduce_ctas, side.cuda_stream)
+        red.reduce_gather(plan, self.bias, self.reduce_ctas, side.cuda_stream, pack=emit_packed)
         red.barrier(status, side.cuda_stream)          # every GPU's slice has landed
         ev = torch.cuda.Event()
         ev.record(side)
         a_op.codes.record_stream(side)
+        if emit_packed is not None:
+            op = gemm.MXOperand(plan["codes"], plan["scales"], a_op.rows, self.inner.out_features)
+            return (op, ev, like.dtype, like.shape[:-1], "fused_packed")
         return (plan["out"], ev, like.dtype, like.shape[:-1], "fused")
 
-    def start_gated(self, gate: Tensor, up: Tensor, tag: int = 0):
+    def start_gated(self, gate: Tensor, up: Tensor, tag: int = 0, emit_packed: tuple | None = None):
         """`start(silu(gate) * up)` for a gated MLP; the product goes straight into the inner layer's quantized
-        operand when that layer can take it (`forward_gated`)."""
+        operand when that layer can take it (`forward_gated`).  `emit_packed=(E, F)` (fused route only): deliver the
+        result as the MXFP operand of a consumer that quantizes it with that format, see `finish`."""
         if self._fused_applies(gate):
             from . import gemm
 
             _, _, x_exp, x_frac = self.inner._input_format()
             k = gate.shape[-1]
             a_op = gemm.pack_gated_operand(gate.reshape(-1, k), up.reshape(-1, k), x_exp, x_frac)
-            return self._start_fused(a_op, gate, tag)
+            return self._start_fused(a_op, gate, tag, emit_packed)
         if hasattr(self.inner, "forward_gated"):
             k = gate.shape[-1]
             return self.start(None, partial=self.inner.forward_gated(gate.reshape(-1, k), up.reshape(-1, k)),
@@ -305,7 +328,9 @@ class RowParallelLinear(nn.Module):
     def finish(self, handle, keep: bool = False) -> Tensor:
         y, ev, out_dtype, lead, done_bias = handle
         if ev is not None:
-            torch.cuda.current_stream(y.device).wait_event(ev)
+            torch.cuda.current_stream().wait_event(ev)
+        if done_bias == "fused_packed":  # y is an MXOperand in the reducer's buffers: (operand, leading shape)
+            return (y, lead)
         if done_bias == "fused":  # y is the reducer's output buffer, already biased and rounded
             y = y if keep else y.clone()
             return y.reshape(*lead, y.shape[-1])
@@ -363,14 +388,26 @@ class TPGatedMLP(nn.Module):
         half = gu.shape[-1] // 2
         return gu[..., :half], gu[..., half:]
 
-    def start(self, x: Tensor, tag: int = 0):
+    def start(self, x, tag: int = 0, emit_packed: tuple | None = None):
         """Both column-parallel GEMMs, SiLU * mul and the row-parallel GEMM on the current stream, the reduction on
         the down layer's side stream; `self.down.finish(handle)` gives the layer's output.  `tag` names the
-        micro-batch (reductions in flight at the same time must not share buffers)."""
+        micro-batch (reductions in flight at the same time must not share buffers); `emit_packed` asks the down
+        layer to deliver its result as the next layer's quantized activation (fused route only)."""
         gate, up = self.gate_and_up(x)
         if hasattr(self.down, "start_gated"):
-            return self.down.start_gated(gate, up, tag)
+            return self.down.start_gated(gate, up, tag, emit_packed)
         return self.down.start(torch.nn.functional.silu(gate) * up)
+
+    def packed_input_format(self, like: Tensor) -> tuple | None:
+        """(E, F) when this layer's first GEMM takes its input as MXFP tensor-core operands (then a preceding fused
+        row-parallel layer can deliver exactly that), else None."""
+        if self.gate_up is None:
+            return None
+        inner = getattr(self.gate_up, "inner", None)
+        if inner is None or not hasattr(inner, "_uses_packed_path") or not inner._uses_packed_path(like):
+            return None
+        _, _, x_exp, x_frac = inner._input_format()
+        return (x_exp, x_frac)
 
     def forward(self, x: Tensor) -> Tensor:
         gate, up = self.gate_and_up(x)
@@ -413,13 +450,17 @@ def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, c
         parts = list(x.chunk(micro_batches, dim=0))
         handles = [None] * len(parts)
         prev_layer = None
-        for layer in layers:
+        for li, layer in enumerate(layers):
+            # a layer whose successor quantizes its input to MXFP anyway delivers that quantized operand directly
+            # (fused route): half the all-gather bytes and no pack in the successor
+            nxt = layers[li + 1] if li + 1 < len(layers) else None
+            emit = nxt.packed_input_format(parts[0]) if nxt is not None and hasattr(nxt, "packed_input_format") else None
             for i in range(len(parts)):
                 # a part waits only for its own reduction of the previous layer; the other parts' reductions stay
                 # in flight underneath this part's GEMMs.  keep=True: the previous layer's result is consumed here,
                 # before anything can overwrite the reducer's buffer it may live in.
                 inp = parts[i] if prev_layer is None else prev_layer.down.finish(handles[i], keep=True)
-                handles[i] = layer.start(inp, tag=i)
+                handles[i] = layer.start(inp, tag=i, emit_packed=emit)
             prev_layer = layer
         outs = [prev_layer.down.finish(h, keep=True) for h in handles]
         return torch.cat(outs, dim=0) if len(outs) > 1 else outs[0].clone()

@@ -63,6 +63,40 @@ def test_scatter_gemm_then_reduce_gather_equals_unsharded(world, M, K, N, fp4):
             assert e <= 1e-3, (r, s, e)
 
 
+def test_reduce_gather_pack_equals_pack_of_the_reduced_output():
+    """The reduction that delivers the next layer's activation operand: its E4M3 bytes and scales are those of packing
+    the bf16 output of the plain reduction, on every emulated rank's buffers."""
+    lib = _lib.lib()
+    world, rows, N = 4, 256, 1024
+    M = world * rows
+    g = torch.Generator().manual_seed(15)
+    slots = [(torch.randn(world, rows, N, generator=g) * torch.exp2(torch.randint(-6, 6, (world, rows, 1), generator=g).float())).to(DEV)
+             for _ in range(world)]
+    bias = torch.randn(N, generator=g).to(DEV)
+    outs = [torch.zeros(M, N, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+    codes = [torch.zeros(M, N, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    nsc = int(lib.mxq_mma_scale_bytes(M, N))
+    scales = [torch.zeros(nsc, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    stream = torch.cuda.current_stream().cuda_stream
+    from mase_b200.quantizers import _floor_tab_ptr
+
+    for rank in range(world):
+        assert lib.mxq_reduce_gather(slots[rank].data_ptr(), world, rank, rows, N, bias.data_ptr(), _DT[bias.dtype],
+                                     ptr_array(outs), _DT[torch.bfloat16], 0, stream) == 0
+        assert lib.mxq_reduce_gather_pack(slots[rank].data_ptr(), world, rank, rows, N, bias.data_ptr(), _DT[bias.dtype],
+                                          ptr_array(codes), ptr_array(scales), None, 4, 3, _floor_tab_ptr(), 0, stream) == 0
+    torch.cuda.synchronize()
+    ref = gemm.pack_mx_operand(outs[0], 4, 3)
+    for r in range(world):
+        assert torch.equal(outs[r], outs[0])
+        assert torch.equal(codes[r], ref.codes), f"codes on rank {r}"
+        assert torch.equal(scales[r], ref.scales), f"scales on rank {r}"
+    # and the bf16 values themselves: fp32 sum in rank order + bias, one rounding
+    want = (torch.stack([sum(slots[r][s] for s in range(world)) for r in range(world)])
+            .reshape(M, N) + bias).bfloat16()
+    assert torch.equal(outs[0], want)
+
+
 def test_peer_barrier_wait_runs_out_without_a_peer():
     """A rank that never arrives: the wait is bounded, the status word reports it, the stream stays usable."""
     lib = _lib.lib()
