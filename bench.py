@@ -459,7 +459,7 @@ def oracle_quantize_weight(w: torch.Tensor, e: int, f: int, rows_per_chunk: int 
     return torch.cat([O.mxfp_fake(w[r:r + rows_per_chunk], 32, e, f, 1) for r in range(0, w.shape[0], rows_per_chunk)])
 
 
-def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
+def tp_stack_extras(device, rank: int, world: int, peaks: dict, reduce_mode: str = "fused", comm_sms: int = 32) -> dict:
     """Tensor-parallel Linear stack at the 70B shape: hidden 8192, FFN 28672, 4 gated-MLP layers, M = 8192 tokens,
     MXFP4 (E2M1) weights / MXFP8 (E4M3) activations, gate/up column parallel, down row parallel with an fp32
     reduction.  Strong scaling (total work fixed); every rank runs it.  Outside the timed region rank 0 recomputes a
@@ -474,7 +474,6 @@ def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
     cfg = {"weight_block_size": 32, "weight_exponent_width": 2, "weight_frac_width": 1,
            "data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
     tp = tpmod.TPGroup(rank, world, None)
-    reduce_mode = os.environ.get("MXQ_BENCH_TP_REDUCE", "fused")
 
     def build_stack(mode: str):
         gen = torch.Generator(device=device).manual_seed(4)
@@ -491,7 +490,7 @@ def tp_stack_extras(device, rank: int, world: int, peaks: dict) -> dict:
         res = {}
         for micro in ((1,) if world == 1 else (1, 2)):
             def step():
-                return tpmod.run_mlp_stack(stack, x0, micro_batches=micro, comm_sms=int(os.environ.get("MXQ_BENCH_COMM_SMS", 32)))
+                return tpmod.run_mlp_stack(stack, x0, micro_batches=micro, comm_sms=comm_sms)
 
             for _ in range(2):
                 step()
@@ -689,7 +688,7 @@ def run_ours(args) -> None:
         del x
         torch.cuda.empty_cache()
         peaks = tensor_peaks(device)
-        tp_extra = tp_stack_extras(device, rank, world, peaks)
+        tp_extra = tp_stack_extras(device, rank, world, peaks, args.tp_reduce, args.comm_sms)
         x = synthetic.device_student_t3(ROWS, COLS, seed=1 + rank, device=device)
 
     if rank == 0:
@@ -801,6 +800,11 @@ def main() -> None:
                     help="quant: the headline quantizer benchmark; linear: MX Linear forward; decoder: the mixed-precision "
                          "decoder layer (both profiling aids)")
     ap.add_argument("--m", type=int, default=8192, help="tokens for --workload linear")
+    ap.add_argument("--tp-reduce", default="fused", choices=["fused", "scatter_gather", "all_reduce"],
+                    help="reduction of the row-parallel layers of the tensor-parallel extra; with 'fused' the collective "
+                         "route is timed as well and the faster one is reported")
+    ap.add_argument("--comm-sms", type=int, default=32,
+                    help="SMs the GEMMs leave to the reduction's kernels when micro-batches overlap (tensor-parallel extra)")
     ap.add_argument("--wfmt", default="e4m3", choices=["e4m3", "e2m1"], help="weight format for --workload linear")
     args = ap.parse_args()
     if args.workload == "linear" and args.impl == "ours":

@@ -976,8 +976,8 @@ struct SwapLayout {
   static constexpr int kSf = kScaled ? 1024 : 0;  // weight chunk, activation chunk
   // partial sums of the other CTAs of the cluster land here in the first CTA: [rank - 1][column][row] fp32
   static constexpr int kXbufBytes = (kMaxSplit - 1) * BNX * BM * 4;
-  static constexpr int kBudget = 200 * 1024 - kXbufBytes;
-  static constexpr int kFit = kBudget / (kWX + kSf);
+  static constexpr int kRingSpace = 200 * 1024 - kXbufBytes;
+  static constexpr int kFit = kRingSpace / (kWX + kSf);
   static constexpr int kStages = kFit < 10 ? kFit : 10;
   static constexpr int kSfBase = kStages * kWX;
   static constexpr int kXbuf = (kStages * (kWX + kSf) + 1023) & ~1023;
