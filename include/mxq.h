@@ -227,6 +227,15 @@ int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint
                         int F, const uint8_t *floor_tab_host, void *workspace, int64_t workspace_bytes, int *status,
                         const mxq_gemm_options *options, void *stream);
 
+/* Softmax over the last dimension of rows that are MX-quantized first, in one pass: replaces softmax_mxfp /
+ * softmax_mxint / softmax_minifloat (chop/nn/quantized/functional/softmax.py:10-57: quantize along the last dimension,
+ * softmax in fp32, cast back).  x, y: [rows, cols] of `dtype`, contiguous.  quantizer: 0 = MXFP (p0 = E, p1 = F, floor
+ * table), 1 = MXINT (p0 = bits, ceil table of x's dtype), 2 = element-wise minifloat (p0 = E, p1 = F, no table, block
+ * ignored).  cols % block == 0 and cols <= 12288 (the row is kept in shared memory), else MXQ_ERR_SHAPE /
+ * MXQ_ERR_UNSUPPORTED. */
+int mxq_softmax_quant(const void *x, void *y, int dtype, int64_t rows, int64_t cols, int quantizer, int block, int p0,
+                      int p1, const uint8_t *tab_host, void *stream);
+
 /* Rotary position embedding y = x * cos + rotate_half(x) * sin in one pass.  Replaces _apply_rope
  * (chop/nn/quantized/functional/rope.py:17-28; the rope_mxfp / rope_mxint / rope_minifloat wrappers quantize the
  * tables first and then call it).  x, y: [batch, heads, seq, dim] of `dtype` with a contiguous last dimension and the

@@ -107,17 +107,54 @@ def kv_cache_mxint(key_states: Tensor, value_states: Tensor, config: dict = None
     return q(key_states), q(value_states)
 
 
+def _fused_softmax(x: Tensor, dim: int, quantizer: int, block: int, p0: int, p1: int) -> Tensor | None:
+    """Quantize along the last dimension + softmax over it in one kernel (mxq_softmax_quant); None when the kernel does
+    not take the case (softmax over another dimension, rows that are not whole blocks or too long for shared memory,
+    autograd), and the caller composes quantizer and softmax instead."""
+    from . import _lib
+    from .quantizers import _DT, _ceil_tab_ptr, _floor_tab_ptr, _on_device, _stream
+
+    if not x.is_cuda or x.dtype not in _DT or x.dim() < 1 or dim not in (-1, x.dim() - 1):
+        return None
+    if x.requires_grad and torch.is_grad_enabled():
+        return None
+    cols = x.shape[-1]
+    if cols == 0 or cols > 12288 or (quantizer != 2 and cols % block):
+        return None
+    xc = x.contiguous()
+    y = torch.empty_like(xc)
+    tab = 0 if quantizer == 2 else (_floor_tab_ptr() if quantizer == 0 else _ceil_tab_ptr(x.dtype))
+    with _on_device(xc):
+        rc = _lib.lib().mxq_softmax_quant(xc.data_ptr(), y.data_ptr(), _DT[x.dtype], xc.numel() // cols, cols, quantizer,
+                                          block, p0, p1, tab, _stream(xc))
+    if rc == -7:
+        return None
+    _lib.check(rc, "mxq_softmax_quant")
+    return y
+
+
 def softmax_mxfp(x: Tensor, config: dict = None, dim: int = -1) -> Tensor:
+    out = _fused_softmax(x, dim, 0, config["data_in_block_size"], config["data_in_exponent_width"],
+                         config["data_in_frac_width"])
+    if out is not None:
+        return out
     x = _x_mxfp(config)(x)
     return torch.nn.functional.softmax(x.to(torch.float32), dim=dim).to(x.dtype)
 
 
 def softmax_mxint(x: Tensor, config: dict = None, dim: int = -1) -> Tensor:
+    out = _fused_softmax(x, dim, 1, config["data_in_block_size"], config["data_in_width"], 0)
+    if out is not None:
+        return out
     x = _x_mxint(config)(x)
     return torch.nn.functional.softmax(x.to(torch.float32), dim=dim).to(x.dtype)
 
 
 def softmax_minifloat(x: Tensor, config: dict = None, dim: int = -1) -> Tensor:
+    if config.get("data_in_is_finite", True) and config.get("data_in_round_mode", "rn") == "rn":
+        out = _fused_softmax(x, dim, 2, 1, config["data_in_exponent_width"], config["data_in_frac_width"])
+        if out is not None:
+            return out
     x = _x_minifloat(config)(x)
     return torch.nn.functional.softmax(x.to(torch.float32), dim=dim).to(x.dtype)
 

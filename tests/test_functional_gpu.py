@@ -127,3 +127,35 @@ def test_rope_kernel_equals_the_elementwise_sequence():
     cq, sq = mb.mxfp_quantizer(cos, 32, 4, 3), mb.mxfp_quantizer(sin, 32, 4, 3)
     assert_bits_equal(rq, q * cq.unsqueeze(1) + rot(q) * sq.unsqueeze(1), "rope_mxfp q")
     assert Fn.rope_apply(q[..., :24], cos[..., :24], sin[..., :24]) is None  # dim not a multiple of 16: composed ops
+
+
+def test_softmax_fused_with_its_quantizer():
+    """softmax_mxfp / softmax_mxint / softmax_minifloat in one kernel against quantizer + torch softmax on the same
+    device: the quantized values are the quantizer's own (bit-exact elsewhere), so the results may differ only by the
+    order of the fp32 sum before the one rounding to bf16."""
+    g = torch.Generator().manual_seed(36)
+    cfp = {"data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    cint = {"data_in_block_size": 32, "data_in_width": 8}
+    cmf = {"data_in_exponent_width": 4, "data_in_frac_width": 3}
+    for shape in ((2, 4, 48, 64), (3, 1000, 512), (5, 4096), (2, 7, 96)):
+        for dtype in (torch.bfloat16, torch.float32):
+            x = (torch.randn(*shape, generator=g) * 4).to(dtype).to(DEV)
+            for fn, quant in ((mb.softmax_mxfp, lambda t: mb.mxfp_quantizer(t, 32, 4, 3)),
+                              (mb.softmax_mxint, lambda t: mb.mxint_quantizer(t, 32, 8)),
+                              (mb.softmax_minifloat, lambda t: mb.minifloat_quantizer_sim(t, mb.MinifloatMeta(4, 3, True, "rn")))):
+                cfg = cfp if fn is mb.softmax_mxfp else (cint if fn is mb.softmax_mxint else cmf)
+                out = fn(x, cfg)
+                ref = torch.softmax(quant(x).float(), -1).to(dtype)
+                assert out.shape == x.shape and out.dtype == dtype
+                tol = 2.0 ** -7 if dtype == torch.bfloat16 else 1e-6
+                rel = ((out.float() - ref.float()).abs() / ref.float().clamp_min(1e-30)).max()
+                assert float(rel) <= tol, (shape, dtype, fn.__name__, float(rel))
+                if dtype == torch.bfloat16:
+                    assert float((out != ref).float().mean()) < 5e-3
+                assert float((out.float().sum(-1) - 1).abs().max()) < 2e-2
+    # a softmax over another dimension, or rows that are not whole blocks, takes the composed route with the same values
+    x = torch.randn(4, 64, 48, generator=g).bfloat16().to(DEV)
+    ref = torch.softmax(mb.mxfp_quantizer(x, 32, 4, 3).float(), 1).to(torch.bfloat16)
+    assert torch.equal(mb.softmax_mxfp(x, cfp, dim=1), ref)
+    ref_last = torch.softmax(mb.mxfp_quantizer(x, 32, 4, 3).float(), -1).to(torch.bfloat16)
+    assert torch.equal(mb.softmax_mxfp(x, cfp), ref_last)  # 48 columns: blocks straddle rows
