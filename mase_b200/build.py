@@ -57,8 +57,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 print(" ".join(cmd), flush=True)
             subprocess.run(cmd, check=True)
         objs.append(obj)
-    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB_PATH, *objs, "-lcudart"]
+    tmp = LIB_PATH + ".tmp"  # link under another name, then swap: a reader never sees a half-written library
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", tmp, *objs, "-lcudart"]
     subprocess.run(cmd, check=True)
+    os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 
@@ -91,12 +93,13 @@ def build_torch_binding(force: bool = False, verbose: bool = False) -> str:
     torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
     cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=" + EXT_NAME,
            "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
-           *["-I" + i for i in inc], src, "-o", out,
+           *["-I" + i for i in inc], src, "-o", out + ".tmp",
            "-L" + torch_lib, "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10", "-lc10_cuda", "-ltorch_cuda",
            "-L" + LIB_DIR, "-l:libmxq.so", "-Wl,-rpath," + torch_lib, "-Wl,-rpath,$ORIGIN"]
     if verbose:
         print(" ".join(cmd), flush=True)
     subprocess.run(cmd, check=True)
+    os.replace(out + ".tmp", out)
     return out
 
 

@@ -93,9 +93,34 @@ at::Tensor dense_linear(const at::Tensor &x, const at::Tensor &weight, const c10
   return out.reshape(shape);
 }
 
+// MXFP / MXINT quantize-dequantize of a tensor that already is a run of blocks (contiguous, blocks along the last
+// dimension).  kind 0: MXFP (p0 = E, p1 = F, floor table); kind 1: MXINT (p0 = bits, ceil table of x's dtype).
+at::Tensor mx_fake(const at::Tensor &x, int64_t kind, int64_t block, int64_t p0, int64_t p1,
+                   c10::optional<at::ScalarType> out_dtype, int64_t tab_ptr) {
+  TORCH_CHECK(x.is_cuda(), "mx_fake: tensor is on '", x.device(), "'; mase_b200 runs on CUDA devices only");
+  TORCH_CHECK(x.is_contiguous() && reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0, "mx_fake: contiguous, aligned input");
+  const int64_t n = x.numel();
+  TORCH_CHECK(block > 0 && n % block == 0, "Input tensor size ", n, " is not divisible by block size ", block, ".");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const at::ScalarType odt = out_dtype.value_or(x.scalar_type());
+  at::Tensor y = at::empty(x.sizes(), x.options().dtype(odt));
+  void *stream = at::cuda::getCurrentCUDAStream(x.device().index()).stream();
+  const uint8_t *tab = reinterpret_cast<const uint8_t *>(tab_ptr);
+  int rc;
+  if (kind == 0)
+    rc = mxq_mxfp_fake(x.data_ptr(), y.data_ptr(), dtype_code(x.scalar_type()), dtype_code(odt), n / block, (int)block,
+                       (int)p0, (int)p1, tab, stream);
+  else
+    rc = mxq_mxint_fake(x.data_ptr(), y.data_ptr(), dtype_code(x.scalar_type()), dtype_code(odt), n / block, (int)block,
+                        (int)p0, tab, stream);
+  check_rc(rc, kind == 0 ? "mxq_mxfp_fake" : "mxq_mxint_fake");
+  return y;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("mx_fake", &mx_fake, "MXFP / MXINT quantize-dequantize of a contiguous run of blocks");
   m.def("mx_linear", &mx_linear, "LinearMXFP forward on packed weights (mxq_mx_linear)");
   m.def("dense_linear", &dense_linear, "F.linear of quantized bf16 / fp32 operands (mxq_gemm_dense)");
 }

@@ -134,6 +134,20 @@ def _dtype_code(dt: torch.dtype, what: str) -> int:
     return _DT[dt]
 
 
+_BINDING = None
+
+
+def _binding():
+    """The compiled torch binding when it is built and has the quantizer entry (see mase_b200.gemm._ext), else False."""
+    global _BINDING
+    if _BINDING is None:
+        from . import gemm
+
+        ext = gemm._ext()
+        _BINDING = ext if ext and hasattr(ext, "mx_fake") else False
+    return _BINDING
+
+
 def _stream(t: Tensor) -> int:
     return torch._C._cuda_getCurrentRawStream(t.device.index)
 
@@ -228,6 +242,9 @@ def _mxint_fake_flat(flat: Tensor, meta: MXIntMeta, out_dtype: torch.dtype) -> T
     di = _dtype_code(flat.dtype, "mxint")
     do = _dtype_code(out_dtype, "mxint")
     flat = _flat_contiguous(flat)
+    ext = _binding()
+    if ext:
+        return ext.mx_fake(flat, 1, B, meta.element_bits, 0, out_dtype, _ceil_tab_ptr(flat.dtype))
     y = torch.empty(flat.shape, dtype=out_dtype, device=flat.device)
     with _on_device(flat):
         rc = _lib.lib().mxq_mxint_fake(flat.data_ptr(), y.data_ptr(), di, do, flat.numel() // B, B, meta.element_bits,
@@ -462,6 +479,9 @@ def _mxfp_fake_flat(flat: Tensor, meta: MXFPMeta, out_dtype: torch.dtype) -> Ten
     di = _dtype_code(flat.dtype, "mxfp")
     do = _dtype_code(out_dtype, "mxfp")
     flat = _flat_contiguous(flat)
+    ext = _binding()
+    if ext:
+        return ext.mx_fake(flat, 0, B, meta.element_exp_bits, meta.element_frac_bits, out_dtype, _floor_tab_ptr())
     y = torch.empty(flat.shape, dtype=out_dtype, device=flat.device)
     with _on_device(flat):
         rc = _lib.lib().mxq_mxfp_fake(flat.data_ptr(), y.data_ptr(), di, do, flat.numel() // B, B,
