@@ -131,6 +131,21 @@ class LinearMXFP(_LinearBase):
             self._mx_weight_key = (self.weight.data_ptr(), tuple(self.weight.shape), self.weight.dtype)
         return out
 
+    def __deepcopy__(self, memo):
+        """copy.deepcopy: the copy's packed weight belongs to the copy's `weight` (new storage, same values)."""
+        import copy
+
+        valid = self._buffers.get("_mx_w_codes") is not None and self._packed_weight() is not None
+        new = self.__class__.__new__(self.__class__)
+        memo[id(self)] = new
+        for k, v in self.__dict__.items():
+            if k != "_mx_operand":
+                new.__dict__[k] = copy.deepcopy(v, memo)
+        if valid:
+            new._mx_weight_version = new.weight._version
+            new._mx_weight_key = (new.weight.data_ptr(), tuple(new.weight.shape), new.weight.dtype)
+        return new
+
     def _operand(self, codes: Tensor, scales: Tensor) -> MXOperand:
         cached = self.__dict__.get("_mx_operand")
         if cached is not None and cached.codes is codes and cached.scales is scales:

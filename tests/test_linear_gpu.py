@@ -229,6 +229,14 @@ def test_weight_only_storage_round_trip():
     moved.load_state_dict({"weight": w.to(DEV)}, strict=False)
     moved.to(DEV)
     assert moved._packed_weight() is not None
+    import copy
+
+    twin = copy.deepcopy(moved)
+    assert twin._packed_weight() is not None and twin._packed_weight().codes.data_ptr() != moved._packed_weight().codes.data_ptr()
+    assert torch.equal(twin(x.to(DEV)), moved(x.to(DEV)))
+    twin.weight.data.mul_(2)  # in-place through .data: no version bump, same pointer -> documented: repack by hand
+    twin.weight.mul_(1)       # a tracked in-place op invalidates the packed copy
+    assert twin._packed_weight() is None
 
 
 def test_functional_elementwise_mx_ops_vs_oracle():
