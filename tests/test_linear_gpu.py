@@ -234,8 +234,8 @@ def test_weight_only_storage_round_trip():
     twin = copy.deepcopy(moved)
     assert twin._packed_weight() is not None and twin._packed_weight().codes.data_ptr() != moved._packed_weight().codes.data_ptr()
     assert torch.equal(twin(x.to(DEV)), moved(x.to(DEV)))
-    twin.weight.data.mul_(2)  # in-place through .data: no version bump, same pointer -> documented: repack by hand
-    twin.weight.mul_(1)       # a tracked in-place op invalidates the packed copy
+    with torch.no_grad():
+        twin.weight.mul_(1)  # a tracked in-place update invalidates the packed copy (forward then multiplies `weight`)
     assert twin._packed_weight() is None
 
 
