@@ -71,6 +71,23 @@ int mxq_mxint_extract(const void *x, int8_t *mant, uint8_t *scales, int in_dtype
 int mxq_mxint_compose(const int8_t *mant, const uint8_t *scales, void *y, int out_dtype, int64_t n_blocks,
                       int block, int bits, void *stream);
 
+/* MXINT clipping search.  Replaces the quantile_search branch of mxint_quantizer_sim without activations
+ * (mxint/mxint.py:40-136): per block, eleven candidate exponents from the quantiles 1.0, 0.995, 0.99, 0.97, 0.95,
+ * 0.93, 0.90, 0.80, 0.70, 0.60, 0.50 of |x| (linear interpolation), the one with the smallest 2-norm error wins
+ * (the first of equals).  x, y: n_blocks*32 elements of `dtype`; choice (may be NULL): uint8 [n_blocks], index of
+ * the winning quantile.  block must be 32 (MXQ_ERR_UNSUPPORTED otherwise). */
+int mxq_mxint_clip_search(const void *x, void *y, uint8_t *choice, int dtype, int64_t n_blocks, int block, int bits,
+                          const uint8_t *ceil_tab_host, void *stream);
+
+/* MXFP clipping search.  Replaces the quantile_search branch of mxfp_quantizer_sim without activations
+ * (mxfp/mxfp.py:40-104), including its error measure (raw code bytes scaled in uint8 arithmetic) and its strict
+ * "better than everything before" acceptance.  candidate < 0: search; 0..10: evaluate only that quantile
+ * (extract_mxfp_components with percentile, mxfp/fake.py:57).  y: dequantized result in out_dtype; metric (may be
+ * NULL): in_dtype [n_blocks*32], the values the error compares with x; choice (may be NULL): uint8 [n_blocks]. */
+int mxq_mxfp_clip_search(const void *x, void *y, void *metric, uint8_t *choice, int in_dtype, int out_dtype,
+                         int64_t n_blocks, int block, int E, int F, int candidate, const uint8_t *floor_tab_host,
+                         void *stream);
+
 /* MXFP quantize-dequantize with E exponent and F fraction bits per element, E8M0 shared scale.
  * Replaces chop/nn/quantizers/mxfp/mxfp.py:14-115 (mxfp_quantizer_sim, non-search branch) =
  * extract_mxfp_components + compose_mxfp_tensor (mxfp/fake.py:12-104) with the element codec of

@@ -18,6 +18,9 @@ _PROTOTYPES = {
     "mxq_mxint_fake": [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_void_p, c_void_p],
     "mxq_mxint_extract": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p],
     "mxq_mxint_compose": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p],
+    "mxq_mxint_clip_search": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p],
+    "mxq_mxfp_clip_search": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int, c_int,
+                             c_void_p, c_void_p],
     "mxq_mxfp_fake": [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p],
     "mxq_mxfp_extract": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p],
     "mxq_mxfp_compose": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p],

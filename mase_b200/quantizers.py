@@ -12,10 +12,12 @@ Drop-in counterparts of (paths inside the MASE repository, `src/chop/nn/quantize
 
 Same names, parameter names, defaults, return types and error behaviour.  Tensors must live on a CUDA
 device: there is no CPU path.  fp32 and bf16 inputs are supported; other dtypes raise
-NotImplementedError rather than silently computing something else.  The calibration-time options
-of MXINT (`quantile_search=True`, `percentile != 1.0`, `act_tensor`) are not part of the inference path: they run as
-plain tensor operations on the tensor's device.  The MXFP search raises NotImplementedError (the reference's version
-measures its error on raw code bytes and wraps its uint8 scales, so there is no meaningful behaviour to keep).
+NotImplementedError rather than silently computing something else.  The calibration-time clipping search
+(`quantile_search=True`) runs as one kernel per tensor for blocks of 32 along a contiguous last dimension without
+activations (what the quantized Linear layers and GPTQ ask for); its other forms (`act_tensor`, other block sizes or
+dimensions, MXINT `percentile != 1.0`) run as tensor operations on the tensor's device around the kernels.  The MXFP
+search keeps the reference's own error measure: raw code bytes scaled by a power of two evaluated in uint8
+arithmetic, so for tensors of ordinary magnitude it returns the plain quantization.
 """
 
 from __future__ import annotations
@@ -323,6 +325,8 @@ def mxint_quantizer_sim(
     """Quantize-dequantize along `block_dim` (mxint/mxint.py:14-171, non-search branch)."""
     _require_cuda(tensor, "mxint_quantizer_sim")
     if quantile_search:
+        if act_tensor is None and mxint_meta.block_size == 32 and _is_last_dim_contiguous(tensor, block_dim):
+            return mxint_clip_search(tensor, mxint_meta)[0]
         out = _mxint_clip_search(tensor, block_dim, mxint_meta, act_tensor, cali_batch_size)
         return out.to(tensor.dtype)
     ori_shape = tuple(tensor.shape)
@@ -335,9 +339,30 @@ def mxint_quantizer_sim(
     return permute_for_dequantize(y, ori_shape, block_dim)
 
 
-# Calibration-time clipping search (mxint/mxint.py:40-136): not on the inference path, so it is the reference's own
-# sequence of tensor operations on the tensor's device.  The one exception is the shared exponent, which uses the
-# same host-derived table as the kernels instead of the device's log2.
+def mxint_clip_search(tensor: Tensor, mxint_meta: MXIntMeta) -> tuple[Tensor, Tensor]:
+    """The clipping search of mxint_quantizer_sim(quantile_search=True) without activations (mxint/mxint.py:40-136)
+    for blocks of 32 along a contiguous last dimension, in one kernel.  Returns (fake-quantized tensor, uint8 index
+    of the winning quantile per block)."""
+    _require_cuda(tensor, "mxint_clip_search")
+    dt = _dtype_code(tensor.dtype, "mxint")
+    if mxint_meta.scale_bits != 8:
+        raise NotImplementedError("mxint: only scale_bits=8 is supported")
+    assert mxint_meta.block_size == 32 and tensor.numel() % 32 == 0
+    flat = _flat_contiguous(tensor)
+    n = flat.numel() // 32
+    y = torch.empty_like(flat)
+    choice = torch.empty((n,), dtype=torch.uint8, device=tensor.device)
+    with _on_device(tensor):
+        rc = _lib.lib().mxq_mxint_clip_search(flat.data_ptr(), y.data_ptr(), choice.data_ptr(), dt, n, 32,
+                                              mxint_meta.element_bits, _ceil_tab_ptr(tensor.dtype), _stream(tensor))
+    _lib.check(rc, "mxq_mxint_clip_search")
+    return y.view(tensor.shape), choice
+
+
+# The other forms of the calibration-time clipping search (mxint/mxint.py:40-136: with activations, block sizes other
+# than 32, blocks along another dimension) are not on the inference path and run as the reference's own sequence of
+# tensor operations on the tensor's device.  The one exception is the shared exponent, which uses the same
+# host-derived table as the kernels instead of the device's log2.
 _SEARCH_PERCENTILES = (1.0, 0.995, 0.99, 0.97, 0.95, 0.93, 0.90, 0.80, 0.70, 0.60, 0.50)
 
 
@@ -437,7 +462,9 @@ def extract_mxfp_components(tensor: Tensor, mxfp_meta: MXFPMeta, percentile: flo
     """(scales uint8 [n_blocks,1], elements uint8 [n_blocks,B]) (mxfp/fake.py:12-72)."""
     _require_cuda(tensor, "extract_mxfp_components")
     if percentile != 1.0:
-        raise NotImplementedError("percentile clipping is a calibration-time option and is not provided")
+        raise NotImplementedError("extract_mxfp_components: percentile clipping returns no codes here; "
+                                  "mxfp_clip_search(flat, meta, candidate=i) gives the dequantized blocks of the "
+                                  "reference's clipping quantiles")
     _check_mxfp_meta(mxfp_meta)
     B = mxfp_meta.block_size
     assert tensor.numel() % B == 0
@@ -502,9 +529,8 @@ def mxfp_quantizer_sim(
 ) -> Tensor:
     """Quantize-dequantize along `block_dim` (mxfp/mxfp.py:14-115, non-search branch)."""
     _require_cuda(tensor, "mxfp_quantizer_sim")
-    if quantile_search or act_tensor is not None:
-        raise NotImplementedError("mxfp: the clipping search is not provided (the reference measures its error on raw code "
-                                  "bytes and wraps its uint8 scales)")
+    if quantile_search:
+        return _mxfp_clip_search(tensor, block_dim, mxfp_meta, act_tensor, dtype, cali_batch_size)
     ori_shape = tuple(tensor.shape)
     ndim = len(ori_shape)
     assert block_dim < ndim and block_dim >= -ndim
@@ -513,6 +539,81 @@ def mxfp_quantizer_sim(
     flat = flatten_for_quantize(tensor, block_dim)
     y = _mxfp_fake_flat(flat, mxfp_meta, dtype or tensor.dtype)
     return permute_for_dequantize(y, ori_shape, block_dim)
+
+
+def mxfp_clip_search(flat: Tensor, mxfp_meta: MXFPMeta, out_dtype: torch.dtype | None = None, candidate: int = -1,
+                     want_metric: bool = False):
+    """One launch of the MXFP search kernel on a flat run of blocks of 32.  candidate < 0: the search of
+    mxfp_quantizer_sim(quantile_search=True) without activations (mxfp/mxfp.py:40-104); 0..10: only that clipping
+    quantile.  Returns (dequantized flat tensor, uint8 winner per block, metric or None); `metric` holds what the
+    reference's error compares with the tensor (raw code bytes scaled in uint8 arithmetic)."""
+    _require_cuda(flat, "mxfp_clip_search")
+    _check_mxfp_meta(mxfp_meta)
+    if mxfp_meta.block_size != 32 or mxfp_meta.scale_exp_bits != 8:
+        raise NotImplementedError("mxfp: the clipping search is provided for blocks of 32 with 8-bit scales")
+    di = _dtype_code(flat.dtype, "mxfp")
+    do = _dtype_code(out_dtype or flat.dtype, "mxfp")
+    flat = _flat_contiguous(flat)
+    assert flat.numel() % 32 == 0
+    n = flat.numel() // 32
+    y = torch.empty(flat.shape, dtype=out_dtype or flat.dtype, device=flat.device)
+    choice = torch.empty((n,), dtype=torch.uint8, device=flat.device)
+    metric = torch.empty_like(flat) if want_metric else None
+    with _on_device(flat):
+        rc = _lib.lib().mxq_mxfp_clip_search(flat.data_ptr(), y.data_ptr(), metric.data_ptr() if want_metric else None,
+                                             choice.data_ptr(), di, do, n, 32, mxfp_meta.element_exp_bits,
+                                             mxfp_meta.element_frac_bits, candidate, _floor_tab_ptr(), _stream(flat))
+    _lib.check(rc, "mxq_mxfp_clip_search")
+    return y, choice, metric
+
+
+def _mxfp_clip_search(tensor: Tensor, block_dim: int, meta: MXFPMeta, act_tensor: Tensor | None,
+                      dtype: torch.dtype | None, cali_batch_size: int) -> Tensor:
+    ori_shape = tuple(tensor.shape)
+    ndim = len(ori_shape)
+    assert block_dim < ndim and block_dim >= -ndim
+    in_order = _is_last_dim_contiguous(tensor, block_dim)
+    flat = tensor.reshape(-1) if in_order else flatten_for_quantize(tensor, block_dim)
+    restore = (lambda y: y.view(ori_shape)) if in_order else (lambda y: permute_for_dequantize(y, ori_shape, block_dim))
+    if act_tensor is None and in_order:
+        return restore(mxfp_clip_search(flat, meta, dtype)[0])
+    # with activations, or with blocks along another dimension (the reference then compares against the tensor in
+    # its original element order): one launch per candidate, errors and the running best as tensor operations
+    B = meta.block_size
+    target = tensor.flatten().reshape(-1, B)
+    n_blocks = target.shape[0]
+    best = torch.full([n_blocks], float("inf"), device=tensor.device, dtype=tensor.dtype)
+    best_y = None
+    if act_tensor is not None and act_tensor.shape[-1] != B:
+        assert act_tensor.shape[-1] % B == 0
+        act_tensor = act_tensor.view(*act_tensor.shape[:-1], act_tensor.shape[-1] // B, B)
+    for i in range(len(_SEARCH_PERCENTILES)):
+        y, _, metric = mxfp_clip_search(flat, meta, dtype, candidate=i, want_metric=True)
+        y, q = y.view(n_blocks, B), metric.view(n_blocks, B)
+        if best_y is None:
+            best_y = y.clone()
+        if act_tensor is not None:
+            err = torch.zeros(n_blocks, device=tensor.device, dtype=tensor.dtype)
+            for b in range(0, act_tensor.shape[0], cali_batch_size):
+                act_b = act_tensor[b : b + cali_batch_size]
+                diff = _act_product(act_b, q) - _act_product(act_b, target)
+                err += torch.norm(diff, p=2, dim=tuple(range(diff.dim() - 1)))
+        else:
+            d = (q - target).abs_()
+            err = torch.sum(d * d, 1)
+        better = err < best
+        best = torch.where(better, err, best)
+        best_y[better] = y[better]
+    return restore(best_y.reshape(-1))
+
+
+def _act_product(act: Tensor, blocks: Tensor) -> Tensor:
+    """act [..., B] @ blocks[n, B]^T on the package's own GEMM (the reduction is one block long)."""
+    from .gemm import linear_forward
+
+    lead = act.shape[:-1]
+    a2 = act.reshape(-1, act.shape[-1]).to(blocks.dtype).contiguous()
+    return linear_forward(a2, blocks.contiguous(), None, blocks.dtype).reshape(*lead, blocks.shape[0])
 
 
 class MXFPQuantize(torch.autograd.Function):

@@ -22,6 +22,9 @@ Reference locations (paths inside the MASE repository, `src/chop/...`):
   nn/quantizers/block_fp.py:7-82             _block_fp_quantize
   nn/quantized/modules/linear.py:817-972     LinearMXFP / LinearMXInt
   nn/quantized/functional/linear.py:220-278  linearBlockFP
+  nn/quantizers/mxint/mxint.py:40-136        MXINT clipping search
+  nn/quantizers/mxfp/mxfp.py:40-104          MXFP clipping search
+  passes/module/transforms/gptq/gptq.py      GPTQ with an MX inner quantizer
 """
 
 from __future__ import annotations
@@ -75,12 +78,9 @@ def mxint_scale_exponent(x_blocks: Tensor) -> Tensor:
     return torch.log2(amax).ceil().to(_I32)
 
 
-def mxint_extract(x: Tensor, block: int, bits: int, scale_bits: int = 8) -> tuple[Tensor, Tensor]:
-    """Returns (scale [n,1], mantissa [n,block]) in x.dtype, integer valued (mxint/fake.py:45-56)."""
-    assert x.numel() % block == 0, "numel must be divisible by the block size"
-    dt = x.dtype
-    xb = x.reshape(-1, block)
-    s = mxint_scale_exponent(xb)
+def _mxint_codes_for_exponent(xb: Tensor, s: Tensor, bits: int, scale_bits: int = 8) -> tuple[Tensor, Tensor]:
+    """(scale [n,1], mantissa [n,block]) of blocks xb for shared exponents s (int32 [n,1])."""
+    dt = xb.dtype
     half = 1 << (bits - 1)
     xd = xb.to(torch.float64)
     # x / 2**s * 2**(bits-1): exact power-of-two scalings (results below the dtype's normal range only
@@ -93,6 +93,13 @@ def mxint_extract(x: Tensor, block: int, bits: int, scale_bits: int = 8) -> tupl
     bias = (1 << (scale_bits - 1)) - 1
     sc = (s + bias).clamp(0, (1 << scale_bits) - 1)
     return sc.to(dt), m.to(dt)
+
+
+def mxint_extract(x: Tensor, block: int, bits: int, scale_bits: int = 8) -> tuple[Tensor, Tensor]:
+    """Returns (scale [n,1], mantissa [n,block]) in x.dtype, integer valued (mxint/fake.py:45-56)."""
+    assert x.numel() % block == 0, "numel must be divisible by the block size"
+    xb = x.reshape(-1, block)
+    return _mxint_codes_for_exponent(xb, mxint_scale_exponent(xb), bits, scale_bits)
 
 
 def mxint_compose(scale: Tensor, mant: Tensor, bits: int, scale_bits: int = 8) -> Tensor:
@@ -179,22 +186,29 @@ def minifloat_fake(x: Tensor, E: int, F: int, out_dtype=None) -> Tensor:
 # --------------------------------------------------------------------------------------------------
 # MXFP (mxfp/fake.py:12-104)
 # --------------------------------------------------------------------------------------------------
-def mxfp_extract(x: Tensor, block: int, E: int, F: int) -> tuple[Tensor, Tensor]:
-    """Returns (scales uint8 [n,1], codes uint8 [n,block])."""
+def mxfp_extract(x: Tensor, block: int, E: int, F: int, percentile: float = 1.0) -> tuple[Tensor, Tensor]:
+    """Returns (scales uint8 [n,1], codes uint8 [n,block]).  `percentile` < 1 takes that quantile of |x| per block
+    (linear interpolation between order statistics, `torch.quantile`) in place of the block maximum
+    (mxfp/fake.py:57)."""
     assert x.numel() % block == 0
     xf = x.to(torch.float32).reshape(-1, block).contiguous()
     bits = xf.view(_I32)
     flushed = (bits & 0x7F800000) == 0
     xf = torch.where(flushed, torch.zeros_like(xf), xf)
-    amax = xf.abs().amax(dim=1, keepdim=True)
+    if percentile == 1.0:
+        amax = xf.abs().amax(dim=1, keepdim=True)
+    else:
+        amax = xf.abs().quantile(percentile, dim=1, keepdim=True)
     all_zero = flushed.all(dim=1, keepdim=True)
+    zero_q = amax == 0
     bias = (1 << (E - 1)) - 1
     emax_b = ((1 << E) - 1) - bias
-    # floor(log2(amax)) in fp32; amax == 0 only for all-zero blocks whose scale is forced to 0 below
-    lf = torch.log2(torch.where(all_zero, torch.ones_like(amax), amax)).floor().to(_I32)
+    # floor(log2(amax)) in fp32
+    lf = torch.log2(torch.where(zero_q, torch.ones_like(amax), amax)).floor().to(_I32)
     sh = (lf - emax_b).clamp(-127, 128)
-    # an all-zero block: log2(0) = -inf whose int32 conversion saturates low; the clamp gives -127
-    sh = torch.where(all_zero, torch.full_like(sh, -127), sh)
+    # amax == 0: log2(0) = -inf converts to the lowest int32, the subtraction of emax wraps around and the clamp
+    # returns the top, 128.  The block is then divided by exp2(128) = inf and every element becomes +0.
+    sh = torch.where(zero_q, torch.full_like(sh, 128), sh)
     scale = torch.where(all_zero, torch.zeros_like(sh), sh + 127).to(torch.uint8)
     # the reference divides in fp32 by exp2(sh) (a subnormal divisor for sh = -127)
     v = xf / torch.exp2(sh.to(torch.float32))
@@ -217,6 +231,111 @@ def mxfp_fake(x: Tensor, block: int, E: int, F: int, block_dim: int = -1, out_dt
     sc, co = mxfp_extract(flat, block, E, F)
     y = mxfp_compose(sc, co, E, F, out_dtype or x.dtype)
     return unflatten_blocks(y, tuple(x.shape), block_dim)
+
+
+# --------------------------------------------------------------------------------------------------
+# calibration-time clipping search (mxint/mxint.py:40-136, mxfp/mxfp.py:40-104)
+# --------------------------------------------------------------------------------------------------
+SEARCH_PERCENTILES = (1.0, 0.995, 0.99, 0.97, 0.95, 0.93, 0.90, 0.80, 0.70, 0.60, 0.50)
+
+
+def mxint_clip_search(x: Tensor, block: int, bits: int, block_dim: int = -1) -> tuple[Tensor, Tensor]:
+    """Per block, the candidate among eleven clipping quantiles with the smallest 2-norm error
+    (mxint/mxint.py:40-136 without activations).  Returns (fake-quantized tensor, index of the chosen candidate
+    per block).  Intermediates live in x.dtype as in the reference; the error is taken against the tensor in its
+    original element order."""
+    dt = x.dtype
+    target = x.reshape(-1, block)
+    xb = flatten_blocks(x, block_dim).reshape(-1, block)
+    errs, cands = [], []
+    for p in SEARCH_PERCENTILES:
+        q = torch.tensor([p], dtype=torch.float32)
+        x_max = xb.abs().to(torch.float32).quantile(q, dim=1, keepdim=True)[0].to(dt).clamp(min=torch.finfo(dt).tiny)
+        s = torch.log2(x_max).ceil().to(_I32)
+        sc, m = _mxint_codes_for_exponent(xb, s, bits)
+        cand = mxint_compose(sc, m, bits).reshape(-1, block)
+        cands.append(cand)
+        errs.append(torch.norm(cand - target, p=2, dim=-1))
+    best = torch.argmin(torch.stack(errs), dim=0)
+    chosen = torch.stack(cands)[best, torch.arange(xb.shape[0])]
+    return unflatten_blocks(chosen.reshape(-1), tuple(x.shape), block_dim).to(dt), best
+
+
+def mxfp_search_metric(scales: Tensor, codes: Tensor, F: int, dt) -> Tensor:
+    """The per-element values the reference's MXFP search compares with the tensor (mxfp/mxfp.py:57-63): the raw
+    code bytes divided by 2**(F-1), times 2**(scale - 127) evaluated in uint8 arithmetic, i.e. 2**k for
+    k = (scale - 127) mod 256 below 8 and 0 otherwise."""
+    k = (scales.to(_I32) - 127) & 255
+    pw = torch.where(k < 8, torch.ones_like(k) << k.clamp(max=7), torch.zeros_like(k))
+    return (codes.to(torch.float32) / 2 ** (F - 1) * pw.to(torch.float32)).to(dt)
+
+
+def mxfp_clip_search(x: Tensor, block: int, E: int, F: int, block_dim: int = -1, out_dtype=None) -> tuple[Tensor, Tensor]:
+    """mxfp_quantizer_sim(quantile_search=True) without activations (mxfp/mxfp.py:40-104): candidates in the order of
+    SEARCH_PERCENTILES, each accepted only if its error is strictly below the best before it; the first candidate is
+    the initial answer.  Returns (fake-quantized tensor, chosen candidate per block)."""
+    dt = x.dtype
+    target = x.flatten().reshape(-1, block)
+    flat = flatten_blocks(x, block_dim)
+    best_err = torch.full([target.shape[0]], float("inf"), dtype=dt)
+    best_sc, best_co = mxfp_extract(flat, block, E, F, 1.0)
+    best_sc, best_co = best_sc.clone(), best_co.clone()
+    chosen = torch.zeros(target.shape[0], dtype=torch.int64)
+    for i, p in enumerate(SEARCH_PERCENTILES):
+        sc, co = mxfp_extract(flat, block, E, F, p)
+        d = mxfp_search_metric(sc, co, F, dt)
+        d = (d - target).abs()
+        err = (d * d).sum(1)
+        better = err < best_err
+        best_err = torch.where(better, err, best_err)
+        best_sc[better], best_co[better], chosen[better] = sc[better], co[better], i
+    y = mxfp_compose(best_sc, best_co, E, F, out_dtype or dt)
+    return unflatten_blocks(y, tuple(x.shape), block_dim), chosen
+
+
+# --------------------------------------------------------------------------------------------------
+# GPTQ with an MX inner quantizer (passes/module/transforms/gptq/gptq.py:17-123)
+# --------------------------------------------------------------------------------------------------
+def gptq_hessian(batches) -> Tensor:
+    """Running average of 2/n * X^T X over calibration batches [b, s, in] (gptq.py:28-38)."""
+    H, n = None, 0
+    for x in batches:
+        x = x.unsqueeze(0) if x.dim() == 2 else x
+        b = x.shape[0]
+        x2 = x.reshape(-1, x.shape[-1]).t()
+        if H is None:
+            H = torch.zeros(x2.shape[0], x2.shape[0])
+        H *= n / (n + b)
+        n += b
+        x2 = (2 / n) ** 0.5 * x2.float()
+        H += x2.matmul(x2.t())
+    return H
+
+
+def gptq_quantize(w: Tensor, hessian: Tensor, quantize_block, block: int, percdamp: float = 0.01) -> Tensor:
+    """Column blocks of `block` weights are quantized left to right; the error of each block, weighted by the
+    inverse Hessian's Cholesky factor, is fed forward into the columns not yet quantized (gptq.py:40-118).
+    `quantize_block(W1)` is the inner fake-quantizer of a [rows, block] slice."""
+    W = w.clone()
+    H = hessian.clone()
+    cols = W.shape[1]
+    dead = torch.diag(H) == 0
+    H[dead, dead] = 1
+    W[:, dead] = 0
+    idx = torch.arange(cols)
+    H[idx, idx] += percdamp * torch.mean(torch.diag(H))
+    H = torch.linalg.cholesky(H)
+    H = torch.cholesky_inverse(H)
+    Hinv = torch.linalg.cholesky(H, upper=True)
+    Q = torch.zeros_like(W)
+    for c0 in range(0, cols, block):
+        c1 = min(c0 + block, cols)
+        W1 = W[:, c0:c1].clone()
+        Q1 = quantize_block(W1)
+        err = (W1 - Q1) / torch.diag(Hinv[c0:c1, c0:c1]).unsqueeze(0)
+        Q[:, c0:c1] = Q1
+        W[:, c1:] -= err.matmul(Hinv[c0:c1, c1:])
+    return Q
 
 
 # --------------------------------------------------------------------------------------------------

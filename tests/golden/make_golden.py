@@ -245,6 +245,56 @@ def main(root: str) -> None:
             arrays[f"mxint_search/{dt_name}/w{nbits}/p97_mant"] = bits(mant)
             index.append({"kind": "mxint_search", "dtype": dt_name, "bits": nbits, "block": 32})
 
+    # MXFP clipping search: ordinary weights (the search returns the plain result), large magnitudes (the reference's
+    # error on raw code bytes is non-zero there) and sparse rows (zero quantiles)
+    from chop.nn.quantizers.mxfp.mxfp import mxfp_quantizer_sim
+    from chop.nn.quantizers.mxfp.meta import MXFPMeta
+
+    g = torch.Generator().manual_seed(321)
+    parts = []
+    for magnitude in (0.02, 1.0, 40.0, 300.0, 3000.0):
+        w = torch.randn(16, 128, generator=g) * magnitude
+        w[torch.rand(16, 128, generator=g) < 0.03] *= 20
+        parts.append(w)
+    sparse = torch.randn(16, 128, generator=g) * 200
+    sparse[torch.rand(16, 128, generator=g) < 0.6] = 0
+    sparse[3] = 0
+    parts.append(sparse)
+    w32 = torch.cat(parts)
+    for dt_name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        w = w32.to(dt)
+        arrays[f"mxfp_search/{dt_name}/x"] = bits(w)
+        for E, F in ((4, 3), (2, 1), (3, 2)):
+            meta = MXFPMeta(block_size=32, scale_exp_bits=8, element_exp_bits=E, element_frac_bits=F,
+                            element_is_finite=True, round_mode="rn")
+            arrays[f"mxfp_search/{dt_name}/e{E}m{F}/fake"] = bits(mxfp_quantizer_sim(w, 1, meta, quantile_search=True))
+            index.append({"kind": "mxfp_search", "dtype": dt_name, "E": E, "F": F, "block": 32})
+
+    # GPTQ (passes/module/transforms/gptq/gptq.py): one small Linear, Hessian from seeded activations, MXFP4 / MXINT4
+    # inner quantizer with and without the clipping search
+    pkg = types.ModuleType("chop.passes.module.transforms.gptq")
+    pkg.__path__ = [root + "/passes/module/transforms/gptq"]
+    sys.modules["chop.passes.module.transforms.gptq"] = pkg
+    from chop.passes.module.transforms.gptq.gptq import GPTQ
+
+    g = torch.Generator().manual_seed(77)
+    lin = torch.nn.Linear(128, 48, bias=False)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(48, 128, generator=g) * 0.05)
+    acts = torch.randn(6, 40, 128, generator=g) * (1 + 3 * torch.rand(128, generator=g))
+    arrays["gptq/w"] = bits(lin.weight.data)
+    arrays["gptq/acts"] = bits(acts)
+    for fmt, cfg in (("mxfp", {"weight_block_size": 32, "weight_exponent_width": 2, "weight_frac_width": 1}),
+                     ("mxint", {"weight_block_size": 32, "weight_width": 4})):
+        for search in (False, True):
+            solver = GPTQ(lin)
+            for i in range(acts.shape[0]):
+                solver.add_batch(acts[i : i + 1], None)
+            arrays[f"gptq/{fmt}/search{int(search)}/hessian"] = bits(solver.H.clone())
+            arrays[f"gptq/{fmt}/search{int(search)}/q"] = bits(
+                solver.fasterquant(None, fmt, cfg, percdamp=0.01, quant_search=search))
+            index.append({"kind": "gptq", "format": fmt, "search": search})
+
     np.savez_compressed(os.path.join(HERE, "reference_vectors.npz"), **arrays)
     with open(os.path.join(HERE, "reference_vectors.json"), "w") as fh:
         json.dump({"torch": torch.__version__, "cases": index}, fh, indent=1)

@@ -13,7 +13,8 @@ def _cases(golden, kind):
 
 def test_fixture_inventory(golden):
     kinds = {c["kind"] for c in golden.cases}
-    assert kinds == {"mxint", "mxfp", "minifloat", "bfp", "bfp_tiles", "blockdim", "linear", "mxint_search"}
+    assert kinds == {"mxint", "mxfp", "minifloat", "bfp", "bfp_tiles", "blockdim", "linear", "mxint_search",
+                     "mxfp_search", "gptq"}
     assert len(golden.cases) >= 200
 
 
@@ -139,3 +140,36 @@ def test_oracle_vs_live_reference_random():
         assert_bits_equal(O.mxfp_fake(xd, 32, 4, 3), q.mxfp_quantizer(xd, 32, 4, 3), "mxfp e4m3")
         assert_bits_equal(O.mxfp_fake(xd, 32, 2, 1), q.mxfp_quantizer(xd, 32, 2, 1), "mxfp e2m1")
         assert_bits_equal(O.bfp_fake_rows(xd, 8, 8, 127, 32), q.block_fp_quantizer(xd, 8, 8, 127, [1, 32], True), "bfp")
+
+
+def test_clip_search_oracles_match_reference(golden):
+    """The clipping searches of both formats, bit for bit (NaN blocks of zero-quantile candidates included)."""
+    for c in _cases(golden, "mxfp_search"):
+        dt, E, F = c["dtype"], c["E"], c["F"]
+        x = golden.tensor(f"mxfp_search/{dt}/x", dt)
+        y, chosen = O.mxfp_clip_search(x, 32, E, F, 1)
+        assert_bits_equal(y.contiguous(), golden.tensor(f"mxfp_search/{dt}/e{E}m{F}/fake", dt), f"mxfp search {dt} E{E}M{F}")
+        assert int(chosen.max()) > 0  # the large-magnitude rows do leave the first candidate
+    for c in _cases(golden, "mxint_search"):
+        dt, nbits = c["dtype"], c["bits"]
+        x = golden.tensor(f"mxint_search/{dt}/x", dt)
+        y, _ = O.mxint_clip_search(x, 32, nbits, 1)
+        assert_bits_equal(y.contiguous(), golden.tensor(f"mxint_search/{dt}/w{nbits}/fake", dt), f"mxint search {dt} w{nbits}")
+
+
+def test_gptq_oracle_matches_reference(golden):
+    """Hessian accumulation and the block-wise GPTQ sweep with MXFP4 / MXINT4 inner quantizers, with and without
+    the clipping search, against the reference's own output on one 128 -> 48 layer."""
+    w, acts = golden.tensor("gptq/w"), golden.tensor("gptq/acts")
+    H = O.gptq_hessian([acts[i : i + 1] for i in range(acts.shape[0])])
+    inner = {
+        ("mxfp", False): lambda W1: O.mxfp_fake(W1, 32, 2, 1, 1),
+        ("mxfp", True): lambda W1: O.mxfp_clip_search(W1, 32, 2, 1, 1)[0],
+        ("mxint", False): lambda W1: O.mxint_fake(W1, 32, 4, 1),
+        ("mxint", True): lambda W1: O.mxint_clip_search(W1, 32, 4, 1)[0],
+    }
+    for c in _cases(golden, "gptq"):
+        tag = f"gptq/{c['format']}/search{int(c['search'])}"
+        assert_bits_equal(H, golden.tensor(tag + "/hessian"), tag + " hessian")
+        Q = O.gptq_quantize(w, H, inner[(c["format"], c["search"])], 32)
+        assert_bits_equal(Q, golden.tensor(tag + "/q"), tag + " q")
