@@ -193,7 +193,9 @@ def cpu_quantizers():
 
         q = stage_reference.import_staged_quantizers()
         return {"mxfp": lambda x, block, e, f: q.mxfp_quantizer(x, block, e, f),
-                "mxint": lambda x, block, bits: q.mxint_quantizer(x, block, bits)}, "reference"
+                "mxint": lambda x, block, bits: q.mxint_quantizer(x, block, bits),
+                "mxfp_search": lambda x, block, e, f: q.mxfp_quantizer(x, block, e, f, -1, 8, True),
+                "mxint_search": lambda x, block, bits: q.mxint_quantizer(x, block, bits, -1, 8, True)}, "reference"
     except Exception:
         from oracle import mx_oracle as O
 
@@ -339,6 +341,73 @@ def extras(device, x, peaks: dict) -> dict:
         out[f"mxfp8_bf16_{shape[0]}x{shape[1]}_us"] = xx.numel() * 4 / g / 1e3
     out["linear_mxfp8_4096x4096"] = linear_extras(device, peaks)
     out["decoder_layer_mixed_precision"] = decoder_layer_extras(device, peaks)
+    try:
+        out["calibration"] = calibration_extras(device)
+    except Exception as exc:  # calibration is off the timed path: report instead of losing the line
+        out["calibration"] = {"error": repr(exc)}
+    return out
+
+
+def calibration_extras(device) -> dict:
+    """Calibration-time work on one 4096 x 4096 weight: the clipping search of both formats (one kernel each) and a
+    GPTQ sweep with the MXINT4 search inside, each with the CPU implementation timed on a bounded slice (the
+    reference's own quantizers when staged, else the port; GPTQ always the port, on a 1024 x 1024 layer)."""
+    import mase_b200 as mb
+    from mase_b200 import gptq
+    from oracle import mx_oracle as O
+
+    out = {}
+    g = torch.Generator().manual_seed(3)
+    w = torch.randn(4096, 4096, generator=g) * 0.02
+    w[torch.rand(4096, 4096, generator=g) < 0.01] *= 20
+    wd = w.to(device).bfloat16()
+    qs, kind = cpu_quantizers()
+    torch.set_num_threads(os.cpu_count() or 1)
+    int_meta, fp_meta = mb.MXIntMeta(32, 8, 4), mb.MXFPMeta(32, 8, 2, 1, True, "rn")
+    rows = 256
+    for name, gpu_fn, cpu_fn in (
+            ("mxint4", lambda: mb.mxint_quantizer_sim(wd, 1, int_meta, quantile_search=True),
+             (lambda x: qs["mxint_search"](x, 32, 4)) if "mxint_search" in qs else (lambda x: O.mxint_clip_search(x, 32, 4, 1))),
+            ("mxfp4_e2m1", lambda: mb.mxfp_quantizer_sim(wd, 1, fp_meta, quantile_search=True),
+             (lambda x: qs["mxfp_search"](x, 32, 2, 1)) if "mxfp_search" in qs else (lambda x: O.mxfp_clip_search(x, 32, 2, 1, 1)))):
+        gbs = quick_gbs(gpu_fn, wd.numel() * 4)
+        xs = w[:rows].bfloat16()
+        cpu_fn(xs[:8])
+        t0 = time.perf_counter()
+        cpu_fn(xs)
+        cpu_s = (time.perf_counter() - t0) * (4096 / rows)
+        out[f"{name}_clip_search_bf16_4096x4096"] = {
+            "us": wd.numel() * 4 / gbs / 1e3, "GBps": gbs,
+            "cpu_baseline": {"value": cpu_s * 1e6, "unit": "us (scaled from the sample)", "kind": kind,
+                             "cores": torch.get_num_threads(), "sample": f"{rows} of 4096 rows"}}
+
+    def gptq_layer(n: int, tokens: int):
+        lin = torch.nn.Linear(n, n, bias=False, device=device)
+        lin.weight.data.copy_(w[:n, :n])
+        acts = torch.randn(4, tokens // 4, n, generator=g) * (0.5 + 2 * torch.rand(n, generator=g))
+        acts_d = acts.to(device)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        solver = gptq.GPTQ(lin)
+        for i in range(4):
+            solver.add_batch(acts_d[i : i + 1])
+        q = solver.fasterquant(None, "mxint", {"weight_block_size": 32, "weight_width": 4}, quant_search=True)
+        torch.cuda.synchronize()
+        return time.perf_counter() - t0, acts, q
+
+    gptq_layer(256, 512)  # warm-up: kernels, the solver library
+    t_big, _, _ = gptq_layer(4096, 8192)
+    t_small, acts, q = gptq_layer(1024, 2048)
+    ws = w[:1024, :1024].clone()
+    t0 = time.perf_counter()
+    q_ref = O.gptq_quantize(ws, O.gptq_hessian([acts[i : i + 1] for i in range(4)]),
+                            lambda W1: O.mxint_clip_search(W1, 32, 4, 1)[0], 32)
+    t_cpu = time.perf_counter() - t0
+    out["gptq_mxint4_search"] = {
+        "layer_4096x4096_8192_tokens_ms": t_big * 1e3, "layer_1024x1024_2048_tokens_ms": t_small * 1e3,
+        "weights_equal_to_cpu_port_1024": float((q.cpu() == q_ref).float().mean()),
+        "cpu_baseline": {"value": t_cpu * 1e3, "unit": "ms", "kind": "port", "cores": torch.get_num_threads(),
+                         "sample": "the 1024 x 1024 layer, 2048 tokens"}}
     return out
 
 

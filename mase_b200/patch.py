@@ -76,4 +76,19 @@ def patch(chop=None) -> list[str]:
         fl.linearBlockFP = modules.linearBlockFP
         fl.block_fp_quantizer = quantizers.block_fp_quantizer
         done.append("chop.nn.quantized.functional.linear")
+    # the GPTQ pre-pass is looked up as `..gptq.run_gptq` when the quantize pass runs
+    # (chop/passes/module/transforms/quantize/quantize.py:134-138); its package only imports where the reference's
+    # dataset loaders do
+    gp = _maybe("chop.passes.module.transforms.gptq")
+    if gp is not None:
+        from . import gptq
+
+        gp.run_gptq = gptq.run_gptq
+        for name in ("chop.passes.module.transforms.gptq.gptq", "chop.passes.module.transforms.gptq.quantize_dispatch"):
+            sub = _maybe(name)
+            if sub is not None:
+                if hasattr(sub, "GPTQ"):
+                    sub.GPTQ = gptq.GPTQ
+                sub.quantize_tensor = gptq.quantize_tensor
+        done.append("chop.passes.module.transforms.gptq.run_gptq")
     return done

@@ -1,0 +1,122 @@
+"""GPTQ on the GPU against the reference's own output (one 128 -> 48 layer, fixtures made by running the reference)
+and against the oracle on a larger layer, plus the whole-model pass with per-layer checkpoints on a small decoder.
+
+GPTQ feeds rounding errors forward through an inverse-Hessian factor, so a product rounded differently (the GEMM here
+splits fp32 operands into tf32 parts; the factorisation runs in a different library on the device) can move a weight
+across a rounding boundary.  Bars: Hessian within 1e-5 of its largest entry; at least 98 % of the quantized weights
+identical to the reference's; the layer's output error within 2 % of the reference result's and clearly below plain
+rounding."""
+
+import pytest
+import torch
+
+import mase_b200 as mb
+from mase_b200 import gptq
+from oracle import mx_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+MXFP4 = {"weight_block_size": 32, "weight_exponent_width": 2, "weight_frac_width": 1}
+MXINT4 = {"weight_block_size": 32, "weight_width": 4}
+
+
+def output_error(acts: torch.Tensor, w: torch.Tensor, q: torch.Tensor) -> float:
+    x = acts.reshape(-1, acts.shape[-1]).double()
+    return float((x @ (w.double() - q.double()).t()).norm())
+
+
+def test_single_layer_matches_reference_vectors(golden):
+    w, acts = golden.tensor("gptq/w"), golden.tensor("gptq/acts")
+    for case in (c for c in golden.cases if c["kind"] == "gptq"):
+        fmt, search = case["format"], case["search"]
+        tag = f"gptq/{fmt}/search{int(search)}"
+        lin = torch.nn.Linear(128, 48, bias=False, device=DEV)
+        lin.weight.data.copy_(w)
+        solver = gptq.GPTQ(lin)
+        for i in range(acts.shape[0]):
+            solver.add_batch(acts[i : i + 1].to(DEV), None)
+        h_ref = golden.tensor(tag + "/hessian")
+        assert float((solver.H.cpu() - h_ref).abs().max() / h_ref.abs().max()) <= 1e-5
+        q = solver.fasterquant(None, fmt, MXFP4 if fmt == "mxfp" else MXINT4, percdamp=0.01, quant_search=search).cpu()
+        q_ref = golden.tensor(tag + "/q")
+        assert float((q == q_ref).float().mean()) >= 0.98, (tag, float((q == q_ref).float().mean()))
+        e, e_ref = output_error(acts, w, q), output_error(acts, w, q_ref)
+        assert e <= 1.02 * e_ref, (tag, e, e_ref)
+
+
+def test_larger_layer_beats_plain_rounding_and_tracks_the_oracle():
+    g = torch.Generator().manual_seed(3)
+    K, N = 512, 256
+    w = torch.randn(N, K, generator=g) * 0.05
+    acts = torch.randn(8, 64, K, generator=g) * (0.5 + 4 * torch.rand(K, generator=g))
+    lin = torch.nn.Linear(K, N, bias=False, device=DEV)
+    lin.weight.data.copy_(w)
+    solver = gptq.GPTQ(lin)
+    for i in range(0, 8, 2):
+        solver.add_batch(acts[i : i + 2].to(DEV), None)
+    H = O.gptq_hessian([acts[i : i + 2] for i in range(0, 8, 2)])
+    assert float((solver.H.cpu() - H).abs().max() / H.abs().max()) <= 1e-5
+    q = solver.fasterquant(None, "mxfp", MXFP4, quant_search=False).cpu()
+    q_ref = O.gptq_quantize(w, H, lambda W1: O.mxfp_fake(W1, 32, 2, 1, 1), 32)
+    assert float((q == q_ref).float().mean()) >= 0.98
+    # every row block of the result is a fixed point of the plain quantizer: the values are MXFP4 values
+    assert torch.equal(O.mxfp_fake(q, 32, 2, 1, 1), q)
+    rtn = O.mxfp_fake(w, 32, 2, 1, 1)
+    e, e_ref, e_rtn = output_error(acts, w, q), output_error(acts, w, q_ref), output_error(acts, w, rtn)
+    assert e <= 1.02 * e_ref and e < 0.9 * e_rtn, (e, e_ref, e_rtn)
+
+
+def tiny_llama(seed: int = 0):
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(seed)
+    cfg = LlamaConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                      num_key_value_heads=4, vocab_size=97, max_position_embeddings=64)
+    return LlamaForCausalLM(cfg).eval()
+
+
+def test_run_gptq_over_a_small_decoder_with_checkpoint_resume(tmp_path):
+    g = torch.Generator().manual_seed(9)
+    data = [torch.randint(0, 97, (1, 32), generator=g) for _ in range(6)]
+    base = tiny_llama()
+    original = {n: p.detach().clone() for n, p in base.named_parameters()}
+    cfg = {"device": DEV, "format": "mxint", "weight_config": MXINT4, "quantile_search": True,
+           "calibration_data": data, "nsamples": 6}
+    straight = gptq.run_gptq(tiny_llama(), dict(cfg))
+    found = gptq.find_qlayers(straight.model.layers[0], layers=[torch.nn.Linear])
+    assert set(found) == {"self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+                          "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj"}
+    changed = 0
+    for n, p in straight.named_parameters():
+        if ".layers." in n and n.endswith("_proj.weight"):
+            changed += 1
+            assert not torch.equal(p.detach().cpu(), original[n])
+            # at most 16 levels per block of 32 (4-bit mantissas, one shared exponent)
+            levels = max(len(torch.unique(b)) for b in p.detach().cpu().reshape(-1, 32)[:64])
+            assert levels <= 16
+        else:
+            assert torch.equal(p.detach().cpu(), original[n]), n  # embeddings, norms and the head are untouched
+    assert changed == 3 * 7
+    # stop after one layer, then resume from the checkpoints: the same weights as the straight run
+    ckpt = str(tmp_path / "ckpt")
+    part = gptq.run_gptq(tiny_llama(), dict(cfg, checkpoint_dir=ckpt, max_layers=1))
+    assert gptq.detect_quantized_layers(ckpt).keys() == {0}
+    assert torch.equal(part.model.layers[1].mlp.down_proj.weight.cpu(), original["model.layers.1.mlp.down_proj.weight"])
+    resumed = gptq.run_gptq(tiny_llama(), dict(cfg, checkpoint_dir=ckpt))
+    assert gptq.detect_quantized_layers(ckpt).keys() == {0, 1, 2}
+    for (n, a), (_, b) in zip(straight.named_parameters(), resumed.named_parameters()):
+        assert torch.equal(a.detach().cpu(), b.detach().cpu()), n
+    # everything saved: a further call has nothing left to do
+    again = gptq.run_gptq(tiny_llama(), dict(cfg, checkpoint_dir=ckpt))
+    assert torch.equal(again.model.layers[2].mlp.up_proj.weight.cpu(), straight.model.layers[2].mlp.up_proj.weight.cpu())
+
+
+def test_quantize_tensor_dispatch():
+    x = torch.randn(8, 64, device=DEV)
+    y = gptq.quantize_tensor(x, 1, "mxfp", MXFP4, quantile_search=False)
+    assert torch.equal(y, mb.mxfp_quantizer(x, 32, 2, 1, 1))
+    y = gptq.quantize_tensor(x, 1, "mxint", MXINT4, quantile_search=False)
+    assert torch.equal(y, mb.mxint_quantizer(x, 32, 4, 1))
+    with pytest.raises(ValueError):
+        gptq.quantize_tensor(x, 1, "int8", MXINT4, quantile_search=False)

@@ -187,3 +187,42 @@ def test_mxint_clipping_search_matches_reference_vectors(golden):
         cand = Q._mxint_candidates(blocks, meta, torch.tensor(Q._SEARCH_PERCENTILES, dtype=torch.float32))
         hit = (cand.view(11, -1, 32) == y.reshape(1, -1, 32)).all(dim=2).any(dim=0)
         assert bool(hit.all())
+
+
+def test_gptq_checkpoints_and_layer_discovery(tmp_path):
+    """Host-side parts of the GPTQ pass: Linear discovery, per-layer checkpoint files and the resume rule (only a
+    consecutive run of layers starting at 0 is loaded; a damaged file ends it)."""
+    import pytest
+    from mase_b200 import gptq
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.self_attn = torch.nn.ModuleDict({"q_proj": torch.nn.Linear(8, 8, bias=False)})
+            self.mlp = torch.nn.ModuleDict({"up_proj": torch.nn.Linear(8, 16, bias=False)})
+            self.norm = torch.nn.LayerNorm(8)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.model = torch.nn.Module()
+            self.model.layers = torch.nn.ModuleList([Block() for _ in range(4)])
+
+    torch.manual_seed(0)
+    src, dst = Net(), Net()
+    assert set(gptq.find_qlayers(src.model.layers[0])) == {"self_attn.q_proj", "mlp.up_proj"}
+    ckpt = tmp_path / "c"
+    for i in (0, 1, 3):  # layer 2 is missing: the resume stops after layer 1
+        gptq.save_layer_checkpoint(src, i, str(ckpt))
+    assert set(gptq.detect_quantized_layers(str(ckpt))) == {0, 1, 3}
+    assert gptq.auto_load_quantized_layers(dst, str(ckpt)) == 1
+    for i, same in ((0, True), (1, True), (3, False)):
+        a, b = src.model.layers[i].mlp["up_proj"].weight, dst.model.layers[i].mlp["up_proj"].weight
+        assert torch.equal(a, b) == same
+    (ckpt / "quantized_model_layer_1.safetensors").write_bytes(b"not a checkpoint")
+    assert gptq.auto_load_quantized_layers(Net(), str(ckpt)) == 0
+    assert gptq.auto_load_quantized_layers(Net(), str(tmp_path / "absent")) == -1
+    with pytest.raises(RuntimeError):
+        gptq.GPTQ(torch.nn.Linear(8, 8))  # a CPU layer: no CPU path
+    with pytest.raises(ValueError):
+        gptq.run_gptq(Net(), {"format": "mxint", "weight_config": {}})
