@@ -486,7 +486,7 @@ def linear_extras(device, peaks: dict) -> dict:
         t_fwd = 1.0 / quick_gbs(lambda: layer(x), 1, calls=calls) / 1e9   # seconds per call
         xp = gemm.pack_mx_operand(x, 4, 3)
         wp = layer._packed_weight()
-        t_gemm = 1.0 / quick_gbs(lambda: gemm.mx_gemm(xp, wp, None, torch.bfloat16), 1, calls=calls) / 1e9
+        t_gemm = 1.0 / quick_gbs(lambda: gemm.mx_gemm(xp, wp, None, torch.bfloat16, static_b=True), 1, calls=calls) / 1e9
         xq = mb.mxfp_quantizer(x, 32, 4, 3)
         t_dense = 1.0 / quick_gbs(lambda: gemm.linear_forward(xq, layer.weight, None), 1, calls=calls) / 1e9
         # the same forward replayed from a CUDA graph: device time without the per-call host work.  Small problems are
@@ -506,7 +506,7 @@ def linear_extras(device, peaks: dict) -> dict:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 for r in range(reps):
-                    gemm.mx_gemm(xp, wps[r], None, torch.bfloat16)
+                    gemm.mx_gemm(xp, wps[r], None, torch.bfloat16, static_b=True)  # a layer's weight: packed at load
             t_gemm = min(t_gemm, 1.0 / quick_gbs(graph.replay, 1, calls=calls) / 1e9 / reps)
             del graph
         if M <= 128:

@@ -156,7 +156,14 @@ typedef struct mxq_gemm_options {
    * partial sums over through distributed shared memory in a fixed order (repeatable results).  0 = let the library
    * decide, 1 = never. */
   int32_t no_split_k;
-  int32_t reserved;  /* leave 0 */
+  /* Bit flags.
+   *   MXQ_GEMM_STATIC_B   operand B (the weight) was complete before the launch of every kernel that may still be
+   *                       running on the stream -- packed at load time, say.  The small-M kernel then fetches it
+   *                       ahead of the stream dependency, under the tail of the previous kernel.  Without the flag
+   *                       nothing is read before the previous kernel of the stream has finished.  mxq_mx_linear,
+   *                       mxq_mx_gated_linear and mxq_mx_linear_static imply it: their weight argument is by contract
+   *                       a weight packed earlier, not the product of a kernel in flight. */
+  int32_t flags;
   /* Limit of every device-side wait in nanoseconds; 0 = one second.  When a wait runs out the kernel stores a
    * non-zero code in the status word, lets its copies in flight land, frees its tensor memory and returns. */
   int64_t wait_limit_ns;
@@ -170,6 +177,7 @@ typedef struct mxq_gemm_options {
   int32_t no_transposed;
 } mxq_gemm_options;
 
+#define MXQ_GEMM_STATIC_B 1
 #define MXQ_TILES_AUTO 0
 #define MXQ_TILES_SINGLE 1
 #define MXQ_TILES_PAIRS 2

@@ -61,11 +61,12 @@ class GemmOptions(ctypes.Structure):
     """`mxq_gemm_options` of include/mxq.h: per-call settings of the GEMM entry points (all zero = defaults)."""
 
     _fields_ = [("max_ctas", ctypes.c_int32), ("tiles", ctypes.c_int32), ("no_split_k", ctypes.c_int32),
-                ("reserved", ctypes.c_int32), ("wait_limit_ns", ctypes.c_int64), ("test_hook", ctypes.c_int32),
+                ("flags", ctypes.c_int32), ("wait_limit_ns", ctypes.c_int64), ("test_hook", ctypes.c_int32),
                 ("no_transposed", ctypes.c_int32)]
 
 
 TILES_AUTO, TILES_SINGLE, TILES_PAIRS = 0, 1, 2
+GEMM_STATIC_B = 1  # bit of GemmOptions.flags
 CODES_E4M3, CODES_E2M1X2 = 0, 1
 TEST_DROP_LAST_LOAD = 1
 

@@ -996,6 +996,7 @@ struct SwapParams {
   int out_bf16, bias_bf16;
   uint32_t w_fp4;    // block-scaled kind: the weight holds E2M1 elements, two per byte in global memory
   uint32_t tx_less;  // a 4-bit box counts its packed bytes on the barrier, half of what lands in shared memory
+  uint32_t early_w;  // the weight was complete before anything still running on the stream: fetch it ahead of the wait
   unsigned long long wait_ns;
 };
 
@@ -1027,6 +1028,10 @@ umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   constexpr int kElem = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
   constexpr int kBlockK = kRowBytes / kElem;
   constexpr int kSfCol = 128;          // scale factors behind the (at most 128) accumulator columns
+  // The next kernel of the stream may be scheduled from here on (it waits on the device before it touches anything
+  // this launch reads or writes): its CTAs take over an SM the moment this launch's CTA leaves it and, for a launch of
+  // this kernel with a static weight, start pulling the weight without waiting for the rest of this grid.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int kSwapTmemCols = 256;
 
   extern __shared__ uint8_t smem_raw[];
@@ -1063,6 +1068,7 @@ umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
+    if (!p.early_w) grid_dependency_wait();  // the weight may be the product of a kernel that is still running
     for (int i = 0; i < first_pass; ++i) {
       if (elect_one()) {
         const int kc = kc_begin + i;
@@ -1311,6 +1317,7 @@ Opts make_opts(const mxq_gemm_options *o) {
     r.transposed = o->no_transposed == 0;
     if (o->wait_limit_ns > 0) r.wait_ns = (unsigned long long)o->wait_limit_ns;
     r.test_hook = o->test_hook;
+    r.static_b = (o->flags & MXQ_GEMM_STATIC_B) != 0;
   }
   return r;
 }
@@ -1518,16 +1525,17 @@ static int launch_swap(const void *a, const void *b, const uint8_t *sfa, const u
   p.out_bf16 = out_dtype == MXQ_BF16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.wait_ns = o.wait_ns;
   p.w_fp4 = o.b_fp4 ? 1u : 0u;
   p.tx_less = o.b_fp4 ? BM * (kRowBytes / 2) : 0;
+  p.early_w = o.static_b ? 1u : 0u;
   static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
   bool &attr_set = attr_done[current_device() & 63];
   if (!attr_set) {
-    if (cudaFuncSetAttribute(umma_gemm_swap_kernel<kKind, BNX>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(umma_gemm_swap_kernel<kKind, BNX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             L::kTotal) != cudaSuccess)
       return MXQ_ERR_LAUNCH;
     attr_set = true;
   }
-  const cudaError_t err = launch_dependent(umma_gemm_swap_kernel<kKind, BNX>, (int)(tiles * split), kThreads, L::kTotal, st,
-                                           split, mw, mx, msw, msx, p);
+  const cudaError_t err = launch_dependent(umma_gemm_swap_kernel<kKind, BNX>, (int)(tiles * split), kThreads,
+                                           L::kTotal, st, split, mw, mx, msw, msx, p);
   if (err != cudaSuccess) {
     cudaGetLastError();
     return MXQ_ERR_LAUNCH;

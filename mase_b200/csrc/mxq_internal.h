@@ -20,6 +20,7 @@ struct Opts {
   unsigned long long wait_ns = kDefaultWaitNs;
   int test_hook = 0;
   bool b_fp4 = false;  // block-scaled kind: B (the weight) holds E2M1 elements, two per byte
+  bool static_b = false;  // B was complete before anything still running on the stream (MXQ_GEMM_STATIC_B)
   // reduce-scatter fused into the GEMM: fp32 slot buffer of every GPU of the group (rows M / scatter_world each)
   int scatter_world = 0;
   int scatter_rank = 0;
@@ -38,5 +39,13 @@ int gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t *b_
 
 }  // namespace gemm
 
+// The activation packs behind mxq_mxfp_pack_mma / mxq_silu_mul_pack_mma.  chained = launched with programmatic stream
+// serialization from inside a fused Linear call: the kernel lets the GEMM behind it start at once and itself waits on
+// the device for the kernel before it.  The plain entry points never chain: what they write may be a weight, which a
+// GEMM that is told its weight is static fetches before any wait.
+int pack_mxfp_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k, int E, int F,
+                  const uint8_t *floor_tab_host, cudaStream_t st, bool chained);
+int pack_silu_mul_mma(const void *gate, const void *up, int64_t ld, uint8_t *codes, uint8_t *scales_mma, int64_t rows,
+                      int64_t k, int E, int F, const uint8_t *floor_tab_host, cudaStream_t st, bool chained);
 
 }  // namespace mxq

@@ -1,16 +1,27 @@
 // Forward of an MX Linear layer in one call: quantize the activations to MXFP along K into a caller-provided
 // workspace (E4M3 bytes + E8M0 scale chunks), then run the block-scaled tensor-core GEMM against a weight that was
-// packed once with mxq_mxfp_pack_mma.  Both steps are enqueued on the caller's stream; the GEMM is launched with
-// programmatic stream serialization, so its set-up (and, for few rows, its weight loads) runs under the pack's tail.
+// packed once with mxq_mxfp_pack_mma.  Both kernels are launched with programmatic stream serialization on the
+// caller's stream: the pack may start under the tail of the previous kernel (it waits for it on the device) and lets
+// the GEMM start at once; the GEMM sets up -- and, for few rows, fetches its weight, which by contract is older than
+// anything in flight -- while the pack runs, and waits on the device for the packed activations.
 
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "mxq.h"
+#include "mxq_internal.h"
 
 #include <mutex>
 
 static inline int64_t align256(int64_t v) { return (v + 255) & ~(int64_t)255; }
+
+// The weight of a Linear layer was packed at load time: the small-M GEMM may fetch it before the stream dependency.
+static mxq_gemm_options with_static_weight(const mxq_gemm_options *options) {
+  mxq_gemm_options o = {};
+  if (options) o = *options;
+  o.flags |= MXQ_GEMM_STATIC_B;
+  return o;
+}
 
 // Scratch for mxq_mx_linear_static.  The array lives in the device image of this library: every GPU that loads
 // libmxq holds MXQ_STATIC_SCRATCH_BYTES of its memory from the first use of the library until the process exits.
@@ -55,10 +66,11 @@ int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uin
   if (workspace_bytes < need) return MXQ_ERR_SHAPE;
   uint8_t *a_codes = static_cast<uint8_t *>(workspace);
   uint8_t *a_scales = a_codes + align256(M * K);
-  const int rc = mxq_mxfp_pack_mma(x, a_codes, a_scales, in_dtype, M, K, E, F, floor_tab_host, stream);
+  const int rc = mxq::pack_mxfp_mma(x, a_codes, a_scales, in_dtype, M, K, E, F, floor_tab_host, (cudaStream_t)stream, true);
   if (rc != MXQ_OK) return rc;
-  return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, w_format, d, bias, out_dtype, bias_dtype, M, N, K, status,
-                       options, stream);
+  const mxq_gemm_options o = with_static_weight(options);
+  return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, w_format, d, bias, out_dtype, bias_dtype, M, N, K, status, &o,
+                       stream);
 }
 
 int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint8_t *w_codes, const uint8_t *w_scales,
@@ -73,10 +85,12 @@ int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint
   if (workspace_bytes < need) return MXQ_ERR_SHAPE;
   uint8_t *a_codes = static_cast<uint8_t *>(workspace);
   uint8_t *a_scales = a_codes + align256(M * K);
-  const int rc = mxq_silu_mul_pack_mma(gate, up, ld, a_codes, a_scales, M, K, E, F, floor_tab_host, stream);
+  const int rc = mxq::pack_silu_mul_mma(gate, up, ld, a_codes, a_scales, M, K, E, F, floor_tab_host, (cudaStream_t)stream,
+                                         true);
   if (rc != MXQ_OK) return rc;
-  return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, w_format, d, bias, out_dtype, bias_dtype, M, N, K, status,
-                       options, stream);
+  const mxq_gemm_options o = with_static_weight(options);
+  return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, w_format, d, bias, out_dtype, bias_dtype, M, N, K, status, &o,
+                       stream);
 }
 
 int mxq_mx_linear_static(const void *x, int in_dtype, const uint8_t *w_codes, const uint8_t *w_scales, int w_format, void *d,

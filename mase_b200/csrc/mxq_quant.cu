@@ -314,11 +314,16 @@ template <int E, int F, bool kWide, typename I>
 __global__ void __launch_bounds__(kThreads, 4)
 mxfp_pack_mma_bf16_kernel(const __nv_bfloat16 *__restrict__ x, uint8_t *__restrict__ codes,
                           uint8_t *__restrict__ scales, int64_t n_unit64, uint32_t unit_per_row, int64_t k_chunks,
-                          UnitStep jump, UnitStep stride, const __grid_constant__ Log2Tab tab) {
+                          UnitStep jump, UnitStep stride, const __grid_constant__ Log2Tab tab, uint32_t chained) {
   constexpr int kU = 2;
-  // the GEMM that follows in the stream may be launched from now on: it sets up its barriers and tensor memory while
-  // this kernel finishes and waits for the operands on the device (griddepcontrol.wait)
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Inside a fused Linear call: the GEMM that follows in the stream may be launched from now on (it sets up its
+  // barriers and tensor memory, and may fetch its weight, while this kernel runs, and waits on the device for the
+  // operands written here); this kernel itself may have been launched under the tail of the previous one and waits
+  // for it before reading x or writing the scratch that kernel may still be reading.
+  if (chained) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
   const I n_unit = (I)n_unit64;
   const I step = (I)gridDim.x * kThreads * kU;
   I base = (I)blockIdx.x * kThreads * kU;
@@ -383,8 +388,11 @@ template <int E, int F>
 __global__ void __launch_bounds__(kThreads, 4)
 silu_mul_pack_mma_kernel(const __nv_bfloat16 *__restrict__ gate, const __nv_bfloat16 *__restrict__ up, int64_t ld,
                          uint8_t *__restrict__ codes, uint8_t *__restrict__ scales, int64_t n_unit,
-                         uint32_t unit_per_row, int64_t k_chunks, const __grid_constant__ Log2Tab tab) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+                         uint32_t unit_per_row, int64_t k_chunks, const __grid_constant__ Log2Tab tab, uint32_t chained) {
+  if (chained) {  // see mxfp_pack_mma_bf16_kernel
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
   const int64_t step = (int64_t)gridDim.x * kThreads;
   for (int64_t base = (int64_t)blockIdx.x * kThreads; base < n_unit; base += step) {
     const int64_t j = base + threadIdx.x;
@@ -883,13 +891,40 @@ int mxq_mxfp_extract(const void *x, uint8_t *codes, uint8_t *scales, int in_dtyp
 
 int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k, int E, int F,
                       const uint8_t *floor_tab_host, void *stream) {
+  return mxq::pack_mxfp_mma(x, codes, scales_mma, in_dtype, rows, k, E, F, floor_tab_host, (cudaStream_t)stream, false);
+}
+
+int mxq_silu_mul_pack_mma(const void *gate, const void *up, int64_t ld, uint8_t *codes, uint8_t *scales_mma,
+                          int64_t rows, int64_t k, int E, int F, const uint8_t *floor_tab_host, void *stream) {
+  return mxq::pack_silu_mul_mma(gate, up, ld, codes, scales_mma, rows, k, E, F, floor_tab_host, (cudaStream_t)stream,
+                                false);
+}
+
+}  // extern "C"
+
+namespace mxq {
+
+// Plain launch, or (chained) one with programmatic stream serialization: the kernel may then start under the tail of
+// the previous kernel of the stream and waits for it on the device.
+template <typename... KArgs, typename... Args>
+static void launch_pack(void (*kernel)(KArgs...), int grid, cudaStream_t st, bool chained, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid), cfg.blockDim = dim3((unsigned)kThreads), cfg.dynamicSmemBytes = 0, cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = chained ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, args..., (uint32_t)(chained ? 1 : 0));
+}
+
+int pack_mxfp_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k, int E, int F,
+                  const uint8_t *floor_tab_host, cudaStream_t st, bool chained) {
   if (rows == 0 || k == 0) return MXQ_OK;
   if (!x || !codes || !scales_mma || !floor_tab_host) return MXQ_ERR_NULL;
   if (rows < 0 || k < 0 || k % 32) return MXQ_ERR_SHAPE;
   if (!legal_ef(E, F) || E > 4 || F > 3) return MXQ_ERR_FORMAT;
   if (!aligned16(x) || !aligned16(codes)) return MXQ_ERR_ALIGN;
   const Log2Tab tab = load_tab(floor_tab_host);
-  cudaStream_t st = (cudaStream_t)stream;
   const int64_t k_chunks = (k + 127) / 128;
   const int64_t sf_bytes = ((rows + 255) / 256) * 2 * k_chunks * 512;
   // Scales of K blocks past the end of a row (K not a multiple of 128) must be finite: the codes there read as zero,
@@ -917,17 +952,17 @@ int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in
     // 32-bit indices: unit numbers (with a grid step of headroom) and scale offsets stay below 2**31
     const bool small = n_unit + step < (1ll << 31) && sf_bytes < (1ll << 31);
 #define MXQ_PACK_ARGS (const __nv_bfloat16 *)x, codes, scales_mma, n_unit, upr, k_chunks, jump, stride, tab
-#define MXQ_PACK(e, f)                                                                                     \
-  if (E == e && F == f) {                                                                                  \
-    if (wide && small)                                                                                     \
-      mxfp_pack_mma_bf16_kernel<e, f, true, uint32_t><<<grid, kThreads, 0, st>>>(MXQ_PACK_ARGS);           \
-    else if (wide)                                                                                         \
-      mxfp_pack_mma_bf16_kernel<e, f, true, int64_t><<<grid, kThreads, 0, st>>>(MXQ_PACK_ARGS);            \
-    else if (small)                                                                                        \
-      mxfp_pack_mma_bf16_kernel<e, f, false, uint32_t><<<grid, kThreads, 0, st>>>(MXQ_PACK_ARGS);          \
-    else                                                                                                   \
-      mxfp_pack_mma_bf16_kernel<e, f, false, int64_t><<<grid, kThreads, 0, st>>>(MXQ_PACK_ARGS);           \
-    return check_launch();                                                                                 \
+#define MXQ_PACK(e, f)                                                                                   \
+  if (E == e && F == f) {                                                                                \
+    if (wide && small)                                                                                   \
+      launch_pack(mxfp_pack_mma_bf16_kernel<e, f, true, uint32_t>, grid, st, chained, MXQ_PACK_ARGS);    \
+    else if (wide)                                                                                       \
+      launch_pack(mxfp_pack_mma_bf16_kernel<e, f, true, int64_t>, grid, st, chained, MXQ_PACK_ARGS);     \
+    else if (small)                                                                                      \
+      launch_pack(mxfp_pack_mma_bf16_kernel<e, f, false, uint32_t>, grid, st, chained, MXQ_PACK_ARGS);   \
+    else                                                                                                 \
+      launch_pack(mxfp_pack_mma_bf16_kernel<e, f, false, int64_t>, grid, st, chained, MXQ_PACK_ARGS);    \
+    return check_launch();                                                                               \
   }
     MXQ_PACK(4, 3) MXQ_PACK(2, 3) MXQ_PACK(3, 2) MXQ_PACK(2, 1) MXQ_PACK(1, 2)
   } else {
@@ -937,6 +972,10 @@ int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in
 #undef MXQ_PACK_ARGS
   return MXQ_ERR_FORMAT;
 }
+
+}  // namespace mxq
+
+extern "C" {
 
 int mxq_mxfp4_pack_mma(const void *x, uint8_t *codes4, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k,
                        const uint8_t *floor_tab_host, void *stream) {
@@ -959,15 +998,17 @@ int mxq_mxfp4_pack_mma(const void *x, uint8_t *codes4, uint8_t *scales_mma, int 
   return check_launch();
 }
 
-int mxq_silu_mul_pack_mma(const void *gate, const void *up, int64_t ld, uint8_t *codes, uint8_t *scales_mma,
-                          int64_t rows, int64_t k, int E, int F, const uint8_t *floor_tab_host, void *stream) {
+}  // extern "C"
+
+int mxq::pack_silu_mul_mma(const void *gate, const void *up, int64_t ld, uint8_t *codes, uint8_t *scales_mma, int64_t rows,
+                           int64_t k, int E, int F, const uint8_t *floor_tab_host, cudaStream_t st, bool chained) {
+  using namespace mxq;
   if (rows == 0 || k == 0) return MXQ_OK;
   if (!gate || !up || !codes || !scales_mma || !floor_tab_host) return MXQ_ERR_NULL;
   if (rows < 0 || k < 0 || k % 32 || ld < k || ld % 8) return MXQ_ERR_SHAPE;
   if (!legal_ef(E, F) || E > 4 || F > 3) return MXQ_ERR_FORMAT;
   if (!aligned16(gate) || !aligned16(up) || !aligned16(codes)) return MXQ_ERR_ALIGN;
   const Log2Tab tab = load_tab(floor_tab_host);
-  cudaStream_t st = (cudaStream_t)stream;
   const int64_t k_chunks = (k + 127) / 128;
   const int64_t sf_bytes = ((rows + 255) / 256) * 2 * k_chunks * 512;
   // scale bytes of K blocks past the end of a row must be finite (see mxq_mxfp_pack_mma)
@@ -975,17 +1016,18 @@ int mxq_silu_mul_pack_mma(const void *gate, const void *up, int64_t ld, uint8_t 
   const int64_t n_unit = rows * k / 16;
   const uint32_t upr = (uint32_t)(k / 16);
   const int grid = grid_for(n_unit, kThreads);
-#define MXQ_PACK(e, f)                                                                                         \
-  if (E == e && F == f) {                                                                                      \
-    silu_mul_pack_mma_kernel<e, f><<<grid, kThreads, 0, st>>>((const __nv_bfloat16 *)gate,                     \
-                                                              (const __nv_bfloat16 *)up, ld, codes, scales_mma, \
-                                                              n_unit, upr, k_chunks, tab);                     \
-    return check_launch();                                                                                     \
+#define MXQ_PACK(e, f)                                                                                          \
+  if (E == e && F == f) {                                                                                       \
+    launch_pack(silu_mul_pack_mma_kernel<e, f>, grid, st, chained, (const __nv_bfloat16 *)gate,                 \
+                (const __nv_bfloat16 *)up, ld, codes, scales_mma, n_unit, upr, k_chunks, tab);                  \
+    return check_launch();                                                                                      \
   }
   MXQ_PACK(4, 3) MXQ_PACK(2, 3) MXQ_PACK(3, 2) MXQ_PACK(2, 1) MXQ_PACK(1, 2)
 #undef MXQ_PACK
   return MXQ_ERR_FORMAT;
 }
+
+extern "C" {
 
 int mxq_mxfp_compose(const uint8_t *codes, const uint8_t *scales, void *y, int out_dtype, int64_t n_blocks, int block,
                      int E, int F, void *stream) {

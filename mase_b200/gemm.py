@@ -66,7 +66,7 @@ def _ext():
 def options(**fields):
     """Per-call GEMM options (`mxq_gemm_options` of include/mxq.h) for every GEMM this thread issues inside the
     `with` block: `max_ctas` (leave SMs to a concurrent kernel), `tiles` (_lib.TILES_AUTO / TILES_SINGLE /
-    TILES_PAIRS), `no_split_k`, `no_transposed`, `wait_limit_ns`, `test_hook`.  The options travel with each call into
+    TILES_PAIRS), `no_split_k`, `no_transposed`, `wait_limit_ns`, `test_hook`, `flags` (_lib.GEMM_STATIC_B).  The options travel with each call into
     the library, which keeps no settings of its own; other threads are not affected.  Blocks nest: inner fields
     override outer ones."""
     prev = getattr(_TLS, "opts", None)
@@ -79,9 +79,23 @@ def options(**fields):
         _TLS.opts = prev
 
 
-def _options_ptr():
+_STATIC_B_ONLY = _lib.GemmOptions(flags=_lib.GEMM_STATIC_B)
+
+
+def _options_ptr(static_b: bool = False):
+    """Address of the options struct of this thread's `options(...)` block (None outside one).  static_b adds
+    MXQ_GEMM_STATIC_B: operand B is a weight packed long ago, which the small-M kernel may fetch ahead of the stream
+    dependency."""
     cur = getattr(_TLS, "opts", None)
-    return None if cur is None else ctypes.addressof(cur[0])
+    if not static_b:
+        return None if cur is None else ctypes.addressof(cur[0])
+    if cur is None:
+        return ctypes.addressof(_STATIC_B_ONLY)
+    if len(cur) < 3:
+        fields = dict(cur[1])
+        fields["flags"] = fields.get("flags", 0) | _lib.GEMM_STATIC_B
+        cur = _TLS.opts = (cur[0], cur[1], _lib.GemmOptions(**fields))
+    return ctypes.addressof(cur[2])
 
 
 def _status(device: torch.device) -> Tensor:
@@ -287,8 +301,10 @@ def mx_gated_linear(gate: Tensor, up: Tensor, weight: MXOperand, bias: Tensor | 
     return out.reshape(*lead, N)
 
 
-def mx_gemm(a: MXOperand, b: MXOperand, bias: Tensor | None, out_dtype: torch.dtype) -> Tensor:
-    """[a.rows, b.rows] = a @ b^T (+ bias) with block-scaled MXFP8 tensor-core MMAs, fp32 accumulation."""
+def mx_gemm(a: MXOperand, b: MXOperand, bias: Tensor | None, out_dtype: torch.dtype, static_b: bool = False) -> Tensor:
+    """[a.rows, b.rows] = a @ b^T (+ bias) with block-scaled MXFP8 tensor-core MMAs, fp32 accumulation.
+    static_b: b was packed before any kernel that may still be running on the stream was launched (a layer's weight);
+    never set it for an operand that the stream is still producing."""
     assert a.k == b.k and not a.fp4, "the first operand is always E4M3 bytes"
     out = torch.empty((a.rows, b.rows), dtype=out_dtype, device=a.codes.device)
     bb, bdt = _bias_args(bias)
@@ -296,7 +312,7 @@ def mx_gemm(a: MXOperand, b: MXOperand, bias: Tensor | None, out_dtype: torch.dt
     with _on_device(a.codes):
         rc = _lib.lib().mxq_gemm_mxf8(a.codes.data_ptr(), a.scales.data_ptr(), b.codes.data_ptr(), b.scales.data_ptr(),
                                       b.format, out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[out_dtype], bdt, a.rows,
-                                      b.rows, a.k, st.data_ptr(), _options_ptr(), _stream(a.codes))
+                                      b.rows, a.k, st.data_ptr(), _options_ptr(static_b), _stream(a.codes))
     _lib.check(rc, "mxq_gemm_mxf8")
     if _CHECK_EVERY_CALL:
         check_status(a.codes.device)

@@ -235,7 +235,7 @@ class LinearMXFP(_LinearBase):
         xq, lead = quantized
         if isinstance(xq, MXOperand):
             out_dtype = self.output_dtype or self.weight.dtype
-            return mx_gemm(xq, self._packed_weight(), self.bias, out_dtype).reshape(*lead, self.out_features)
+            return mx_gemm(xq, self._packed_weight(), self.bias, out_dtype, static_b=True).reshape(*lead, self.out_features)
         return linear_forward(xq, self.weight, self.bias, self.output_dtype,
                               fp32_exact=not self.bypass and getattr(self, "_weight_quantized", False))
 

@@ -321,3 +321,31 @@ def test_sibling_projections_share_one_activation_quantization():
     # layers that cannot share (different classes) are simply called one by one
     mixed = forward_siblings([layers[0], torch.nn.Linear(512, 64, dtype=torch.bfloat16, device=DEV)], x)
     assert mixed[1].shape == (3, 50, 64)
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (5, 160, 96), (16, 11008, 512), (16, 4096, 4096), (9, 1024, 200)])
+@pytest.mark.parametrize("fp4", [False, True])
+def test_decode_sized_forward_matches_its_parts(shape, fp4):
+    """Up to 16 rows: the fused call (activation pack chained to the GEMM, the weight fetched ahead of the stream
+    dependency) must give the bits of packing x and multiplying the packed operands as separate calls, with and
+    without bias, bf16 and fp32 output; K not a multiple of 128, K shares that wrap the operand ring, N not a
+    multiple of 128."""
+    M, K, N = shape
+    if fp4 and K % 128:
+        pytest.skip("nibble-packed weights need K % 128 == 0")
+    x, w = synthetic.linear_operands(M, K, N, seed=M + K)
+    x[0, :32] = 0  # an all-zero block
+    x[M - 1, 32:64] *= 300  # a block whose top element takes the E4M3 code that the hardware reads as NaN
+    xd = x.to(DEV)
+    we, wf = (2, 1) if fp4 else (4, 3)
+    wp = gemm.pack_mx_operand(w.to(DEV), we, wf, fp4=fp4)
+    bias = torch.randn(N, device=DEV).bfloat16()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        for b in (None, bias):
+            fused = gemm.mx_linear(xd, wp, b, 4, 3, out_dtype)
+            parts = gemm.mx_gemm(gemm.pack_mx_operand(xd, 4, 3), wp, b, out_dtype)
+            gemm.check_status()
+            assert torch.equal(fused, parts), (shape, fp4, out_dtype, b is not None)
+    ref = O.mxfp_fake(x, 32, 4, 3).float() @ O.mxfp_fake(w, 32, we, wf, 1).float().t()
+    err = float((gemm.mx_linear(xd, wp, None, 4, 3, torch.float32).cpu() - ref).abs().max() / ref.abs().max())
+    assert err <= 1e-3, (shape, fp4, err)
