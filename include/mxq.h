@@ -192,6 +192,17 @@ int mxq_gemm_options_size(void);
 int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int in_dtype, int out_dtype, int bias_dtype,
                    int64_t M, int64_t N, int64_t K, int *status, const mxq_gemm_options *options, void *stream);
 
+/* A batch of independent dense products D[i] = A[i] B[i]^T, i < batch, in one launch: A[i] = a + i * stride_a is
+ * [M, K], B[i] = b + i * stride_b is [N, K], D[i] = d + i * stride_d is [M, N], all row-major (strides in elements,
+ * at least one matrix apart; rows and the strides of a and b must be multiples of 16 bytes).  Element types and
+ * accumulation as mxq_gemm_dense; no bias.  Replaces the torch.matmul / torch.bmm behind the quantized matmul and bmm
+ * wrappers (chop/nn/quantized/functional/matmul.py:437-512) and behind the quantized attention products
+ * (chop/nn/quantized/modules/llama/attention.py:334-394) once both operands are fake-quantized.  The tensor maps carry
+ * the matrix index as a third coordinate, so tiles at a matrix edge read zeros and store nothing beyond it. */
+int mxq_gemm_dense_batched(const void *a, const void *b, void *d, int in_dtype, int out_dtype, int64_t batch, int64_t M,
+                           int64_t N, int64_t K, int64_t stride_a, int64_t stride_b, int64_t stride_d, int *status,
+                           const mxq_gemm_options *options, void *stream);
+
 /* Size in bytes of the scale array that mxq_mxfp_pack_mma writes for a [rows, k] operand. */
 int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k);
 

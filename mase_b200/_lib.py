@@ -27,6 +27,8 @@ _PROTOTYPES = {
     "mxq_minifloat_fake": [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_void_p],
     "mxq_gemm_dense": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_void_p,
                        c_void_p, c_void_p],
+    "mxq_gemm_dense_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
+                               c_int64, c_int64, c_void_p, c_void_p, c_void_p],
     "mxq_mma_scale_bytes": [c_int64, c_int64],
     "mxq_gemm_options_size": [],
     "mxq_mxfp_pack_mma": [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p],

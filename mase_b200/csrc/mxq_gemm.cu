@@ -97,6 +97,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
+// the same with a third coordinate: (k, row, matrix of a batch)
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
@@ -105,6 +112,11 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
 // ---- thread-block clusters ----
@@ -267,6 +279,10 @@ struct Params {
   // starts with the rows of a different owner (its successor's), so that at any time the GPUs store into different
   // peers instead of all into the same one.
   int m_rotate;
+  // Batch of independent products (single-CTA kernel, dense kinds): the maps of A, B and D carry the matrix index as a
+  // third coordinate, tiles are numbered matrix by matrix.  0 = one product, two-dimensional maps.
+  int batch = 0;
+  long long d_batch_stride = 0;  // elements between consecutive outputs (direct stores)
 };
 
 // Store maps of the CTA-pair kernel: one output, or one slot buffer per GPU of a tensor-parallel group.
@@ -287,7 +303,7 @@ struct NoCombine {
 template <int BN, bool kOverlap, int kStoreBufs, typename F, typename C = NoCombine>
 __device__ __forceinline__ void drain_accumulator(const Params &p, const CUtensorMap *map_d, uint32_t t_acc, int first,
                                                   int row0, int n0, int lane, uint8_t *stage_buf, int &buf,
-                                                  F shared_columns_read, C combine = C()) {
+                                                  F shared_columns_read, C combine = C(), int z = -1) {
   // two chunks in flight: the TMEM load of chunk c+1 is issued before chunk c is converted and stored
   // chunk order: with overlapping accumulators the 64 shared columns go first (the last two chunks of
   // accumulator 0, the first two of accumulator 1)
@@ -332,7 +348,10 @@ __device__ __forceinline__ void drain_accumulator(const Params &p, const CUtenso
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(map_d, smem_u32(stage_buf + buf * 2048), n0 + c, row0);
+          if (z >= 0)
+            tma_store_3d(map_d, smem_u32(stage_buf + buf * 2048), n0 + c, row0, z);
+          else
+            tma_store_2d(map_d, smem_u32(stage_buf + buf * 2048), n0 + c, row0);
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
         buf = (buf + 1) % kStoreBufs;
@@ -351,13 +370,16 @@ __device__ __forceinline__ void drain_accumulator(const Params &p, const CUtenso
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(map_d, smem_u32(stage_buf), n0 + c, row0);
+          if (z >= 0)
+            tma_store_3d(map_d, smem_u32(stage_buf), n0 + c, row0, z);
+          else
+            tma_store_2d(map_d, smem_u32(stage_buf), n0 + c, row0);
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
         buf = 0;
       }
     } else if (row0 + lane < p.M) {
-      const size_t off = (size_t)(row0 + lane) * p.N + n0 + c;
+      const size_t off = (size_t)(row0 + lane) * p.N + n0 + c + (z > 0 ? (size_t)z * (size_t)p.d_batch_stride : 0);
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         if (n0 + c + j < p.N) {
@@ -419,7 +441,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   const int warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;  // warp: provably uniform
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
-  const int n_tiles = tiles_m * tiles_n;
+  const int tiles_mn = tiles_m * tiles_n;
+  const int n_tiles = tiles_mn * (p.batch > 0 ? p.batch : 1);
   // Split K (small problems, launched as clusters of two with one tile per cluster): CTA `rank` of the cluster takes
   // the K chunks [kc_begin, kc_end) of tile blockIdx.x / 2; rank 1 hands its accumulator to rank 0, which stores.
   const int rank = kSplit ? (int)cluster_rank() : 0;
@@ -473,7 +496,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     int issued = 0;
     bool ok = true;
     for (int tile = first_tile; tile < n_tiles && ok; tile += tile_step) {
-      const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
+      const int z = tile / tiles_mn, in_z = tile - z * tiles_mn;  // matrix of the batch, tile inside it
+      const int m_blk = in_z / tiles_n, n_blk = in_z % tiles_n;
       const int row_a = m_blk * BM, row_b = n_blk * BN;
       // rows of the scale maps
       int chunk_a = m_blk * p.k_chunks + kc_begin, chunk_b = ((n_blk * BN) / 128) * p.k_chunks + kc_begin;
@@ -487,8 +511,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (p.drop_last_load && blockIdx.x == 0 && tile == first_tile && kc == kc_end - 1) break;
         if (elect_one()) {
           mbar_expect_tx(full, L::kStage - L::kA + p.a_box_bytes - p.tx_less);
-          tma_load_2d(sa, &map_a, full, k0, row_a);
-          tma_load_2d(sa + L::kA, &map_b, full, k0, row_b);
+          if (p.batch > 0) {
+            tma_load_3d(sa, &map_a, full, k0, row_a, z);
+            tma_load_3d(sa + L::kA, &map_b, full, k0, row_b, z);
+          } else {
+            tma_load_2d(sa, &map_a, full, k0, row_a);
+            tma_load_2d(sa + L::kA, &map_b, full, k0, row_b);
+          }
           if constexpr (kScaled) {
             tma_load_2d(ssf, &map_sfa, full, 0, chunk_a);
 #pragma unroll
@@ -581,7 +610,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     int local = 0;
     if constexpr (!kSplit) {
       for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++local) {
-        const int m_blk = tile / tiles_n, n_blk = tile % tiles_n;
+        const int z = tile / tiles_mn, in_z = tile - z * tiles_mn;
+        const int m_blk = in_z / tiles_n, n_blk = in_z % tiles_n;
         const int acc = local % kAccStages;
         const uint32_t acc_phase = (uint32_t)(local / kAccStages) & 1u;
         if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, kErrEpilogueWait, p.wait_ns)) break;
@@ -589,7 +619,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         drain_accumulator<BN, kOverlap, kStoreBufs>(
             p, &map_d, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * kAccStride),
             kOverlap && acc == 0 ? BN / 32 - 2 : 0, m_blk * BM + quarter * 32, n_blk * BN, lane, stage_buf, buf,
-            [&] { mbar_arrive(overlap_bar); });
+            [&] { mbar_arrive(overlap_bar); }, NoCombine(), p.batch > 0 ? z : -1);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty_bar(acc));
@@ -1361,30 +1391,67 @@ static cudaError_t launch_dependent(void (*kernel)(KArgs...), int grid, int bloc
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// Batches of matrices: the same boxes with the matrix index as a third coordinate (box extent 1), so that loads fill
+// with zeros and stores clip at the edge of each matrix, not of the whole allocation.  Strides in elements.
+struct Batch {
+  int64_t count = 0;  // 0 = one product, two-dimensional maps
+  int64_t stride_a = 0, stride_b = 0, stride_d = 0;
+};
+static int make_map3(CUtensorMap *map, const void *ptr, int kind, int64_t rows, int64_t k, int box_rows, int64_t batch,
+                     int64_t stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return MXQ_ERR_UNSUPPORTED;
+  const int es = kind == kBf16 ? 2 : 4;
+  cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)k * es, (cuuint64_t)stride * es};
+  cuuint32_t box[3] = {(cuuint32_t)(kRowBytes / es), (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, kind == kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                  const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_LAUNCH;
+}
+static int make_store_map3(CUtensorMap *map, void *ptr, bool bf16, int64_t rows, int64_t n, int64_t batch, int64_t stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return MXQ_ERR_UNSUPPORTED;
+  const int es = bf16 ? 2 : 4;
+  cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)n * es, (cuuint64_t)stride * es};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ptr, dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, bf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MXQ_OK : MXQ_ERR_LAUNCH;
+}
+
 template <int kKind, int BN, bool kSplit = false>
 static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_t *sfb, void *d, const void *bias,
                   int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K, int *status, const Opts &o,
-                  cudaStream_t st) {
+                  cudaStream_t st, const Batch &bt = Batch()) {
   using L = Layout<BN, kKind == kMxf8, kSplit>;
+  if (bt.count > 0 && (kKind == kMxf8 || kSplit)) return MXQ_ERR_UNSUPPORTED;
   constexpr int es = kKind == kBf16 ? 2 : (kKind == kTf32 ? 4 : 1);
   CUtensorMap ma, mb, md;
   // With fewer than 128 rows the A load fetches only the rows that exist (rounded up to the 8-row swizzle atom): the
   // remaining rows of the tile in shared memory stay as they are, and the accumulator rows they produce are never
   // stored.  (Letting TMA zero-fill them costs time: M = 16 ran slower than M = 128.)
   const int a_rows = M < BM ? (int)((M + 7) / 8 * 8) : BM;
-  int rc = make_map(&ma, a, kKind, M, K, a_rows);
+  int rc = bt.count > 0 ? make_map3(&ma, a, kKind, M, K, a_rows, bt.count, bt.stride_a) : make_map(&ma, a, kKind, M, K, a_rows);
   if (rc) return rc;
-  rc = o.b_fp4 ? make_map_fp4(&mb, b, N, K, BN) : make_map(&mb, b, kKind, N, K, BN);
+  rc = bt.count > 0 ? make_map3(&mb, b, kKind, N, K, BN, bt.count, bt.stride_b)
+                    : (o.b_fp4 ? make_map_fp4(&mb, b, N, K, BN) : make_map(&mb, b, kKind, N, K, BN));
   if (rc) return rc;
   const bool out_bf16 = out_dtype == MXQ_BF16;
-  const bool tma_store = (N * (out_bf16 ? 2 : 4)) % 16 == 0;
+  const bool tma_store = (N * (out_bf16 ? 2 : 4)) % 16 == 0 && (bt.count == 0 || (bt.stride_d * (out_bf16 ? 2 : 4)) % 16 == 0);
   if (tma_store) {
-    rc = make_store_map(&md, d, out_bf16, M, N);
+    rc = bt.count > 0 ? make_store_map3(&md, d, out_bf16, M, N, bt.count, bt.stride_d) : make_store_map(&md, d, out_bf16, M, N);
     if (rc) return rc;
   } else {
     md = ma;  // unused by the kernel
   }
   Params p;
+  p.batch = (int)bt.count, p.d_batch_stride = bt.stride_d;
   p.sfa = sfa, p.sfb = sfb, p.d = d, p.bias = bias, p.status = status;
   p.M = (int)M, p.N = (int)N, p.K = (int)K;
   p.k_chunks = (int)((K * es + kRowBytes - 1) / kRowBytes);
@@ -1409,7 +1476,9 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
       return MXQ_ERR_LAUNCH;
     attr_set = true;
   }
-  const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
+  const int64_t tiles64 = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * (bt.count > 0 ? bt.count : 1);
+  if (tiles64 > INT32_MAX) return MXQ_ERR_SHAPE;
+  const int tiles = (int)tiles64;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (o.max_ctas > 0 && grid > o.max_ctas) grid = o.max_ctas;
   if (kSplit) {  // one tile per cluster of two; the caller checked that 2 * tiles CTAs fit
@@ -1597,6 +1666,15 @@ static int launch_any(const void *a, const void *b, const uint8_t *sfa, const ui
   return MXQ_ERR_UNSUPPORTED;
 }
 
+template <int kKind>
+static int launch_batched(const void *a, const void *b, void *d, int out_dtype, int64_t M, int64_t N, int64_t K, int *status,
+                          const Opts &o, cudaStream_t st, const Batch &bt) {
+  // tile width by the output's width: the batch supplies the parallelism
+  if (N > 128) return launch<kKind, 256>(a, b, nullptr, nullptr, d, nullptr, out_dtype, MXQ_F32, M, N, K, status, o, st, bt);
+  if (N > 32) return launch<kKind, 64>(a, b, nullptr, nullptr, d, nullptr, out_dtype, MXQ_F32, M, N, K, status, o, st, bt);
+  return launch<kKind, 32>(a, b, nullptr, nullptr, d, nullptr, out_dtype, MXQ_F32, M, N, K, status, o, st, bt);
+}
+
 }  // namespace gemm
 }  // namespace mxq
 
@@ -1611,6 +1689,29 @@ int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k) {
   const int64_t row_chunks = ((rows + 255) / 256) * 2;  // padded to whole 256-row tiles
   const int64_t k_chunks = (k + 127) / 128;
   return row_chunks * k_chunks * 512;
+}
+
+int mxq_gemm_dense_batched(const void *a, const void *b, void *d, int in_dtype, int out_dtype, int64_t batch, int64_t M,
+                           int64_t N, int64_t K, int64_t stride_a, int64_t stride_b, int64_t stride_d, int *status,
+                           const mxq_gemm_options *options, void *stream) {
+  if (batch == 0 || M == 0 || N == 0) return MXQ_OK;
+  if (!a || !b || !d) return MXQ_ERR_NULL;
+  Opts o = make_opts(options);
+  o.test_hook = 0;
+  if (batch < 0 || M < 0 || N < 0 || K <= 0 || batch > INT32_MAX || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
+    return MXQ_ERR_SHAPE;
+  if (stride_a < M * K || stride_b < N * K || stride_d < M * N) return MXQ_ERR_SHAPE;
+  if (out_dtype != MXQ_F32 && out_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
+  if (in_dtype != MXQ_F32 && in_dtype != MXQ_BF16) return MXQ_ERR_DTYPE;
+  const int es = in_dtype == MXQ_BF16 ? 2 : 4;
+  if ((K * es) % 16 || (stride_a * es) % 16 || (stride_b * es) % 16) return MXQ_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d)) & 15u)
+    return MXQ_ERR_ALIGN;
+  Batch bt;
+  bt.count = batch, bt.stride_a = stride_a, bt.stride_b = stride_b, bt.stride_d = stride_d;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (in_dtype == MXQ_BF16) return launch_batched<kBf16>(a, b, d, out_dtype, M, N, K, status, o, st, bt);
+  return launch_batched<kTf32>(a, b, d, out_dtype, M, N, K, status, o, st, bt);
 }
 
 int mxq_gemm_dense(const void *a, const void *b, void *d, const void *bias, int in_dtype, int out_dtype, int bias_dtype,

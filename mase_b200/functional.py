@@ -11,7 +11,8 @@
 
 Both operands are fake-quantized along their last dimension (x[..., M, K] along K, y[..., K, N] along N, as the
 reference does) and multiplied on this package's tensor-core GEMM (exact products of the quantized values, fp32
-accumulation): a two-dimensional y in one launch over all rows of x, a batched y in one launch per batch element.
+accumulation): a two-dimensional y in one launch over all rows of x, a batched y in one launch over the whole batch
+(`mxq_gemm_dense_batched`).
 Only `bypass` configurations, which the reference leaves unquantized, go to torch.matmul / torch.bmm.
 """
 
@@ -20,7 +21,7 @@ from __future__ import annotations
 import torch
 from torch import Tensor
 
-from .gemm import linear_forward
+from .gemm import batched_product, linear_forward
 from .quantizers import MinifloatMeta, minifloat_quantizer_sim, mxfp_quantizer, mxint_quantizer
 
 
@@ -36,13 +37,11 @@ def _product(x: Tensor, y: Tensor, style: str) -> Tensor:
         return out.squeeze(-1) if y.dim() == 1 else out
     if y.dim() == 2:
         return linear_forward(x, y.t().contiguous(), None, x.dtype, fp32_exact=True)
-    # batched y: broadcast the batch dimensions, then one GEMM launch per batch element
+    # batched y: broadcast the batch dimensions, then one batched GEMM launch
     batch = torch.broadcast_shapes(x.shape[:-2], y.shape[:-2])
     xb = x.expand(*batch, *x.shape[-2:]).reshape(-1, *x.shape[-2:])
     yt = y.expand(*batch, *y.shape[-2:]).reshape(-1, *y.shape[-2:]).transpose(-1, -2).contiguous()  # [B, N, K]
-    out = torch.empty((xb.shape[0], x.shape[-2], y.shape[-1]), dtype=x.dtype, device=x.device)
-    for b in range(xb.shape[0]):
-        out[b] = linear_forward(xb[b], yt[b], None, x.dtype, fp32_exact=True)
+    out = batched_product(xb, yt, x.dtype)  # one launch for the whole batch
     return out.reshape(*batch, x.shape[-2], y.shape[-1])
 
 

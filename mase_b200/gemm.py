@@ -186,6 +186,40 @@ def linear_forward(x: Tensor, weight: Tensor, bias: Tensor | None, out_dtype: to
     return out.reshape(*lead, N)
 
 
+def batched_product(a: Tensor, b: Tensor, out_dtype: torch.dtype | None = None, fp32_exact: bool = True) -> Tensor:
+    """out[i] = a[i] @ b[i]^T for a[B, M, K] and b[B, N, K] in one launch: the GEMM's tensor maps carry the batch index
+    as a third coordinate.  bf16 products are exact; fp32 operands run as tf32, which is exact for MX / block-fp values
+    (`fp32_exact=True`); other fp32 operands are split into tf32-exact parts first, as in `linear_forward`."""
+    _require_cuda(a, "batched_product")
+    if a.dtype != b.dtype or a.dtype not in _DT:
+        raise NotImplementedError(f"batched_product: dtypes {a.dtype} / {b.dtype} are not supported")
+    assert a.dim() == 3 and b.dim() == 3 and a.shape[0] == b.shape[0] and a.shape[2] == b.shape[2]
+    B, M, K = a.shape
+    N = b.shape[1]
+    if a.dtype == torch.float32 and not fp32_exact:
+        a_hi, a_lo = _tf32_split(a)
+        b_hi, b_lo = _tf32_split(b)
+        a, b, K = torch.cat([a_hi, a_hi, a_lo], dim=2), torch.cat([b_hi, b_lo, b_hi], dim=2), 3 * K
+    need = 8 if a.dtype == torch.bfloat16 else 4
+    if K % need:  # rows must be multiples of 16 bytes for the tensor maps: pad K with zeros (contributes nothing)
+        pad = need - K % need
+        a, b, K = torch.nn.functional.pad(a, (0, pad)), torch.nn.functional.pad(b, (0, pad)), K + pad
+    a = a if a.is_contiguous() and a.data_ptr() % 16 == 0 else a.contiguous().clone()
+    b = b if b.is_contiguous() and b.data_ptr() % 16 == 0 else b.contiguous().clone()
+    out = torch.empty((B, M, N), dtype=out_dtype or a.dtype, device=a.device)
+    if B == 0 or M == 0 or N == 0:
+        return out
+    sa, sb = M * K, N * K  # multiples of 16 bytes because K is
+    st = _status(a.device)
+    with _on_device(a):
+        rc = _lib.lib().mxq_gemm_dense_batched(a.data_ptr(), b.data_ptr(), out.data_ptr(), _DT[a.dtype], _DT[out.dtype], B, M,
+                                               N, K, sa, sb, M * N, st.data_ptr(), _options_ptr(), _stream(a))
+    _lib.check(rc, "mxq_gemm_dense_batched")
+    if _CHECK_EVERY_CALL:
+        check_status(a.device)
+    return out
+
+
 @dataclass
 class MXOperand:
     """A [rows, K] matrix as tensor-core operands: hardware E4M3 bytes and E8M0 scales in the MMA chunk layout."""

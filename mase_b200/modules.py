@@ -419,9 +419,11 @@ class RMSNormMinifloat(torch.nn.Module):
     `transformers` model config.  `RMSNormMinifloat(hidden_size, eps, q_config)`, or `from_config(config, layer_idx,
     q_config)` with the reference's constructor arguments."""
 
-    def __init__(self, hidden_size: int, eps: float = 1e-6, q_config: dict | None = None, layer_idx=None, device=None,
-                 dtype=None):
+    def __init__(self, hidden_size: int | None = None, eps: float = 1e-6, q_config: dict | None = None, layer_idx=None,
+                 device=None, dtype=None, config=None):
         super().__init__()
+        if config is not None:  # the call of the quantize pass: (config=..., layer_idx=..., q_config=...)
+            hidden_size, eps = config.hidden_size, config.rms_norm_eps
         self.weight = torch.nn.Parameter(torch.ones(hidden_size, device=device, dtype=dtype))
         self.variance_epsilon = eps
         self.layer_idx = layer_idx

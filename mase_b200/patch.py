@@ -76,6 +76,18 @@ def patch(chop=None) -> list[str]:
         fl.linearBlockFP = modules.linearBlockFP
         fl.block_fp_quantizer = quantizers.block_fp_quantizer
         done.append("chop.nn.quantized.functional.linear")
+    # attention / MLP wrappers of the Llama family: looked up as quantized_module_map[f"{prefix}_{name}"] and built with
+    # (config, layer_idx, q_config) (chop/passes/module/module_modify_helper.py:265-275)
+    if mm is not None and hasattr(mm, "quantized_module_map"):
+        from . import attention
+
+        for key, cls in (("llama_self_attention_mxfp", attention.AttentionMXFP),
+                         ("llama_self_attention_mxint", attention.AttentionMXInt),
+                         ("llama_mlp_mxfp", attention.GatedMLPMX), ("llama_mlp_mxint", attention.GatedMLPMX),
+                         ("llama_rms_norm_minifloat", modules.RMSNormMinifloat)):
+            if key in mm.quantized_module_map:
+                mm.quantized_module_map[key] = cls
+                done.append(f"chop.nn.quantized.modules.quantized_module_map[{key!r}]")
     # the GPTQ pre-pass is looked up as `..gptq.run_gptq` when the quantize pass runs
     # (chop/passes/module/transforms/quantize/quantize.py:134-138); its package only imports where the reference's
     # dataset loaders do

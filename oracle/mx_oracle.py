@@ -25,6 +25,8 @@ Reference locations (paths inside the MASE repository, `src/chop/...`):
   nn/quantizers/mxint/mxint.py:40-136        MXINT clipping search
   nn/quantizers/mxfp/mxfp.py:40-104          MXFP clipping search
   passes/module/transforms/gptq/gptq.py      GPTQ with an MX inner quantizer
+  nn/quantized/modules/llama/attention.py:130-457   quantized attention (MXFP / MXINT operands, minifloat rope and softmax)
+  nn/quantized/modules/llama/mlp.py:48-77    gated MLP with a minifloat SiLU input
 """
 
 from __future__ import annotations
@@ -436,3 +438,55 @@ def linear_block_fp(x: Tensor, w: Tensor, bias, cfg: dict) -> Tensor:
         bq = bfp_fake_rows(bias, cfg["bias_width"], cfg["bias_exponent_width"], cfg["bias_exponent_bias"],
                            cfg["bias_block_size"][-1]).float()
     return torch.nn.functional.linear(xq.float(), wq.float(), bq)
+
+
+# --------------------------------------------------------------------------------------------------
+# quantized attention and gated MLP (nn/quantized/modules/llama/attention.py:130-457, mlp.py:48-77)
+# --------------------------------------------------------------------------------------------------
+def _operand_quantizer(fmt: str, cfg: dict):
+    if fmt == "mxfp":
+        return lambda t: mxfp_fake(t, cfg["data_in_block_size"], cfg["data_in_exponent_width"], cfg["data_in_frac_width"], -1)
+    return lambda t: mxint_fake(t, cfg["data_in_block_size"], cfg["data_in_width"], -1)
+
+
+def _minifloat(t: Tensor, cfg: dict) -> Tensor:
+    return minifloat_fake(t, cfg["data_in_exponent_width"], cfg["data_in_frac_width"])
+
+
+def _rotate_half(t: Tensor) -> Tensor:
+    half = t.shape[-1] // 2
+    return torch.cat((-t[..., half:], t[..., :half]), dim=-1)
+
+
+def attention_mx(hidden: Tensor, weights: dict, cos: Tensor, sin: Tensor, mask, fmt: str, q_config: dict, heads: int,
+                 kv_heads: int, cached: bool) -> tuple[Tensor, Tensor]:
+    """Forward of the reference's MX attention block with plain Linear projections: minifloat cos / sin in the rotary
+    embedding, MX key / value states when a cache is attached, MX queries into Q K^T, scaling, mask, minifloat input
+    of an fp32 softmax, MX probabilities into P V (attention.py:148-214, 334-394).  Returns (output, probabilities)."""
+    B, S, _ = hidden.shape
+    lin = torch.nn.functional.linear
+    q = lin(hidden, weights["q_proj.weight"]).view(B, S, heads, -1).transpose(1, 2)
+    k = lin(hidden, weights["k_proj.weight"]).view(B, S, kv_heads, -1).transpose(1, 2)
+    v = lin(hidden, weights["v_proj.weight"]).view(B, S, kv_heads, -1).transpose(1, 2)
+    c, s_ = _minifloat(cos, q_config["rope"]).unsqueeze(1), _minifloat(sin, q_config["rope"]).unsqueeze(1)
+    q, k = q * c + _rotate_half(q) * s_, k * c + _rotate_half(k) * s_
+    if cached:
+        kv_q = _operand_quantizer(fmt, q_config["kv_cache"])
+        k, v = kv_q(k), kv_q(v)
+    rep = heads // kv_heads
+    k = k[:, :, None].expand(B, kv_heads, rep, S, k.shape[-1]).reshape(B, heads, S, -1)
+    v = v[:, :, None].expand(B, kv_heads, rep, S, v.shape[-1]).reshape(B, heads, S, -1)
+    q = _operand_quantizer(fmt, q_config["qk_matmul"])(q)
+    scores = torch.matmul(q, k.transpose(2, 3)) * (q.shape[-1] ** -0.5)
+    if mask is not None:
+        scores = scores + mask[:, :, :, :S]
+    probs = torch.softmax(_minifloat(scores, q_config["softmax"]).to(torch.float32), dim=-1).to(scores.dtype)
+    probs = _operand_quantizer(fmt, q_config["av_matmul"])(probs)
+    out = torch.matmul(probs, v).transpose(1, 2).contiguous().reshape(B, S, -1)
+    return lin(out, weights["o_proj.weight"]), probs
+
+
+def gated_mlp_minifloat(x: Tensor, gate_w: Tensor, up_w: Tensor, down_w: Tensor, cfg: dict) -> Tensor:
+    """down(silu(minifloat(gate(x))) * up(x)) (mlp.py:56-61 with functional/silu.py:43-58)."""
+    lin = torch.nn.functional.linear
+    return lin(torch.nn.functional.silu(_minifloat(lin(x, gate_w), cfg)) * lin(x, up_w), down_w)

@@ -295,6 +295,65 @@ def main(root: str) -> None:
                 solver.fasterquant(None, fmt, cfg, percdamp=0.01, quant_search=search))
             index.append({"kind": "gptq", "format": fmt, "search": search})
 
+    # Quantized Llama attention and MLP wrappers (nn/quantized/modules/llama/{attention,mlp}.py): one small block in
+    # bf16 and fp32 with a causal mask, with and without a key/value cache
+    for name in ("chop.nn.quantized", "chop.nn.quantized.modules", "chop.nn.quantized.modules.llama"):
+        if name not in sys.modules or not hasattr(sys.modules[name], "__path__"):
+            m = types.ModuleType(name)
+            m.__path__ = [root + name[len("chop"):].replace(".", "/")]
+            sys.modules[name] = m
+    from chop.nn.quantized.modules.llama.attention import LlamaAttentionMXFP, LlamaAttentionMXInt
+    from chop.nn.quantized.modules.llama.mlp import LlamaMLPMXFP
+    from transformers import LlamaConfig
+    from transformers.cache_utils import DynamicCache
+    from transformers.models.llama.modeling_llama import LlamaRotaryEmbedding
+
+    hf = LlamaConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=1, num_attention_heads=4,
+                     num_key_value_heads=2, vocab_size=64, max_position_embeddings=128)
+    hf._attn_implementation = "eager"
+    fp_cfg = {"data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    int_cfg = {"data_in_block_size": 32, "data_in_width": 8}
+    mini = {"data_in_exponent_width": 5, "data_in_frac_width": 10}
+    q_fp = {"qk_matmul": fp_cfg, "av_matmul": fp_cfg, "rope": mini, "softmax": mini, "kv_cache": fp_cfg}
+    q_int = {"qk_matmul": int_cfg, "av_matmul": int_cfg, "rope": mini, "softmax": mini, "kv_cache": int_cfg}
+    g = torch.Generator().manual_seed(2024)
+    B, S = 2, 64
+    hidden32 = torch.randn(B, S, 128, generator=g)
+    weights32 = {n: torch.randn(shape, generator=g) * 0.06 for n, shape in
+                 (("q_proj.weight", (128, 128)), ("k_proj.weight", (64, 128)), ("v_proj.weight", (64, 128)),
+                  ("o_proj.weight", (128, 128)))}
+    causal = torch.ones(S, S, dtype=torch.bool).triu(1)[None, None].expand(B, 1, S, S)
+    pos = torch.arange(S)[None].expand(B, S)
+    for dt_name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        hidden = hidden32.to(dt)
+        cos, sin = LlamaRotaryEmbedding(hf)(hidden, pos)
+        arrays[f"attention/{dt_name}/hidden"] = bits(hidden)
+        arrays[f"attention/{dt_name}/cos"] = bits(cos)
+        arrays[f"attention/{dt_name}/sin"] = bits(sin)
+        # additive mask the way the model builds it: the most negative finite value of the dtype (an infinite score is
+        # outside the minifloat quantizer's domain)
+        mask = torch.zeros(B, 1, S, S, dtype=dt).masked_fill(causal, torch.finfo(dt).min)
+        arrays[f"attention/{dt_name}/mask"] = bits(mask)
+        for wname, w in weights32.items():
+            arrays[f"attention/{dt_name}/{wname}"] = bits(w.to(dt))
+        for fmt, cls, qc in (("mxfp", LlamaAttentionMXFP, q_fp), ("mxint", LlamaAttentionMXInt, q_int)):
+            for cached in (False, True):
+                attn = cls(hf, 0, qc).to(dt).eval()
+                attn.load_state_dict({n: w.to(dt) for n, w in weights32.items()})
+                with torch.no_grad():
+                    out, probs = attn(hidden, (cos, sin), mask, past_key_value=DynamicCache() if cached else None,
+                                      cache_position=torch.arange(S))
+                arrays[f"attention/{dt_name}/{fmt}/cache{int(cached)}/out"] = bits(out)
+                arrays[f"attention/{dt_name}/{fmt}/cache{int(cached)}/probs"] = bits(probs)
+                index.append({"kind": "attention", "dtype": dt_name, "format": fmt, "cached": cached})
+        mlp = LlamaMLPMXFP(hf, 0, mini).to(dt).eval()
+        with torch.no_grad():
+            for n, prm in mlp.named_parameters():
+                prm.copy_((torch.randn(prm.shape, generator=g) * 0.06).to(dt))
+                arrays[f"mlp/{dt_name}/{n}"] = bits(prm.data)
+            arrays[f"mlp/{dt_name}/out"] = bits(mlp(hidden))
+        index.append({"kind": "mlp", "dtype": dt_name})
+
     np.savez_compressed(os.path.join(HERE, "reference_vectors.npz"), **arrays)
     with open(os.path.join(HERE, "reference_vectors.json"), "w") as fh:
         json.dump({"torch": torch.__version__, "cases": index}, fh, indent=1)

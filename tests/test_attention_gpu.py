@@ -1,0 +1,128 @@
+"""The quantized attention block and gated MLP against outputs of the reference's own classes
+(LlamaAttentionMXFP / LlamaAttentionMXInt / LlamaMLPMXFP run on the CPU when the fixtures were made) and against the
+oracle on a larger block.  The projections are plain Linear layers (torch), everything between them runs on this
+package's kernels.  Bars: fp32 outputs within 2e-4 of the largest value, bf16 within 2e-2 (a chain of five bf16
+roundings whose inputs differ in the last bit between host and device); at least 97 % of the quantized probabilities
+identical and none further than one quantization step of its block."""
+
+import pytest
+import torch
+
+from mase_b200 import attention, gemm
+from oracle import mx_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+FP = {"data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+INT = {"data_in_block_size": 32, "data_in_width": 8}
+MINI = {"data_in_exponent_width": 5, "data_in_frac_width": 10}
+QCFG = {"mxfp": {"qk_matmul": FP, "av_matmul": FP, "rope": MINI, "softmax": MINI, "kv_cache": FP},
+        "mxint": {"qk_matmul": INT, "av_matmul": INT, "rope": MINI, "softmax": MINI, "kv_cache": INT}}
+CLS = {"mxfp": attention.AttentionMXFP, "mxint": attention.AttentionMXInt}
+WEIGHTS = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight")
+
+
+class ListCache:
+    """The part of a key/value cache the block uses: update() appends along the sequence and returns everything."""
+
+    def __init__(self):
+        self.k, self.v = {}, {}
+
+    def update(self, k, v, layer_idx, cache_kwargs=None):
+        self.k[layer_idx] = k if layer_idx not in self.k else torch.cat([self.k[layer_idx], k], dim=-2)
+        self.v[layer_idx] = v if layer_idx not in self.v else torch.cat([self.v[layer_idx], v], dim=-2)
+        return self.k[layer_idx], self.v[layer_idx]
+
+
+def check(out, probs, ref_out, ref_probs, dt, what):
+    tol = 2e-4 if dt == "fp32" else 2e-2
+    err = float((out.float().cpu() - ref_out.float()).abs().max() / ref_out.float().abs().max())
+    assert err <= tol, (what, err)
+    p, r = probs.float().cpu(), ref_probs.float()
+    assert float((p == r).float().mean()) >= 0.97, (what, float((p == r).float().mean()))
+    step = r.reshape(-1, 32).abs().amax(dim=1, keepdim=True) / 8  # coarser than any element's own step
+    assert bool(((p - r).reshape(-1, 32).abs() <= step + 1e-12).all()), what
+
+
+def test_attention_matches_reference_vectors(golden):
+    cases = [c for c in golden.cases if c["kind"] == "attention"]
+    assert len(cases) == 8
+    for c in cases:
+        dt, fmt, cached = c["dtype"], c["format"], c["cached"]
+        t = lambda n: golden.tensor(f"attention/{dt}/{n}", dt).to(DEV)  # noqa: E731
+        dtype = torch.float32 if dt == "fp32" else torch.bfloat16
+        block = CLS[fmt](None, 0, QCFG[fmt], hidden_size=128, num_heads=4, num_kv_heads=2, device=DEV, dtype=dtype)
+        block.load_state_dict({n: t(n) for n in WEIGHTS})
+        with torch.no_grad():
+            out, probs = block(t("hidden"), (t("cos"), t("sin")), t("mask"), past_key_value=ListCache() if cached else None,
+                               cache_position=torch.arange(64, device=DEV))
+        gemm.check_status()
+        tag = f"attention/{dt}/{fmt}/cache{int(cached)}"
+        check(out, probs, golden.tensor(tag + "/out", dt), golden.tensor(tag + "/probs", dt), dt, tag)
+
+
+def test_gated_mlp_matches_reference_vectors(golden):
+    for c in (c for c in golden.cases if c["kind"] == "mlp"):
+        dt = c["dtype"]
+        dtype = torch.float32 if dt == "fp32" else torch.bfloat16
+        mlp = attention.GatedMLPMX(None, 0, MINI, hidden_size=128, intermediate_size=256, device=DEV, dtype=dtype)
+        mlp.load_state_dict({n: golden.tensor(f"mlp/{dt}/{n}", dt).to(DEV)
+                             for n in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")})
+        with torch.no_grad():
+            out = mlp(golden.tensor(f"attention/{dt}/hidden", dt).to(DEV))
+        ref = golden.tensor(f"mlp/{dt}/out", dt)
+        err = float((out.float().cpu() - ref.float()).abs().max() / ref.float().abs().max())
+        assert err <= (2e-4 if dt == "fp32" else 2e-2), (dt, err)
+
+
+def test_larger_block_vs_oracle_and_construction_from_a_config():
+    """hidden 512, 8 heads of 64 over 4 key/value heads, 2 x 160 tokens (a key length that is not a multiple of the
+    GEMM tile), bf16; built the way the quantize pass builds it (config object, layer index, q_config) and through
+    from_attention."""
+    class Cfg:
+        hidden_size, num_attention_heads, num_key_value_heads, attention_bias, attention_dropout = 512, 8, 4, False, 0.0
+
+    g = torch.Generator().manual_seed(8)
+    B, S = 2, 160
+    hidden = torch.randn(B, S, 512, generator=g).bfloat16()
+    w = {n: (torch.randn(shape, generator=g) * 0.04).bfloat16() for n, shape in
+         zip(WEIGHTS, ((512, 512), (256, 512), (256, 512), (512, 512)))}
+    pos = torch.arange(S, dtype=torch.float32)
+    inv = 1.0 / (10000 ** (torch.arange(0, 64, 2, dtype=torch.float32) / 64))
+    ang = torch.cat([pos[:, None] * inv[None], pos[:, None] * inv[None]], dim=-1)
+    cos, sin = ang.cos()[None].expand(B, S, 64).bfloat16(), ang.sin()[None].expand(B, S, 64).bfloat16()
+    mask = torch.zeros(B, 1, S, S, dtype=torch.bfloat16).masked_fill(
+        torch.ones(S, S, dtype=torch.bool).triu(1)[None, None], torch.finfo(torch.bfloat16).min)
+    block = attention.AttentionMXFP(Cfg(), 3, QCFG["mxfp"]).to(device=DEV, dtype=torch.bfloat16)
+    assert block.layer_idx == 3 and block.head_dim == 64 and block.num_key_value_groups == 2
+    block.load_state_dict(w)
+    again = attention.AttentionMXFP.from_attention(block, QCFG["mxfp"])
+    with torch.no_grad():
+        out, probs = block(hidden.to(DEV), (cos.to(DEV), sin.to(DEV)), mask.to(DEV))
+        out2, _ = again(hidden.to(DEV), (cos.to(DEV), sin.to(DEV)), mask.to(DEV))
+    gemm.check_status()
+    assert torch.equal(out, out2)
+    ref_out, ref_probs = O.attention_mx(hidden, w, cos, sin, mask, "mxfp", QCFG["mxfp"], 8, 4, False)
+    check(out, probs, ref_out, ref_probs, "bf16", "larger block")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(3, 70, 40, 96), (16, 128, 256, 64), (5, 200, 24, 8), (2, 33, 130, 36)])
+def test_batched_product_vs_fp64(dtype, shape):
+    """The batched GEMM: ragged M, N and K against an fp64 product; matrices at the end of the batch must not leak
+    into their neighbours (tiles at a matrix edge)."""
+    B, M, N, K = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    a = torch.randn(B, M, K, generator=g).to(dtype)
+    b = torch.randn(B, N, K, generator=g).to(dtype)
+    ref = torch.einsum("bmk,bnk->bmn", a.double(), b.double())
+    out = gemm.batched_product(a.to(DEV), b.to(DEV), torch.float32, fp32_exact=False)
+    gemm.check_status()
+    err = float((out.double().cpu() - ref).abs().max() / ref.abs().max())
+    assert err <= 2e-5, (shape, dtype, err)
+    # the same values as one launch per matrix
+    out_same = gemm.batched_product(a.to(DEV), b.to(DEV), dtype, fp32_exact=False)
+    loop = torch.stack([gemm.linear_forward(a[i].to(DEV), b[i].to(DEV), None, dtype) for i in range(B)])
+    tol = 2e-5 if dtype == torch.float32 else 1e-2  # bf16: the two routes may round an output differently
+    assert float((out_same.float() - loop.float()).abs().max()) <= tol * float(ref.abs().max())

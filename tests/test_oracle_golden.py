@@ -14,7 +14,7 @@ def _cases(golden, kind):
 def test_fixture_inventory(golden):
     kinds = {c["kind"] for c in golden.cases}
     assert kinds == {"mxint", "mxfp", "minifloat", "bfp", "bfp_tiles", "blockdim", "linear", "mxint_search",
-                     "mxfp_search", "gptq"}
+                     "mxfp_search", "gptq", "attention", "mlp"}
     assert len(golden.cases) >= 200
 
 
@@ -173,3 +173,27 @@ def test_gptq_oracle_matches_reference(golden):
         assert_bits_equal(H, golden.tensor(tag + "/hessian"), tag + " hessian")
         Q = O.gptq_quantize(w, H, inner[(c["format"], c["search"])], 32)
         assert_bits_equal(Q, golden.tensor(tag + "/q"), tag + " q")
+
+
+def test_attention_and_mlp_oracles_match_reference(golden):
+    """The attention block (MXFP and MXINT operands, minifloat rotary tables and softmax input, with and without a
+    key/value cache) and the gated MLP with a minifloat SiLU input against the reference's own classes, bit for bit."""
+    fp = {"data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    it = {"data_in_block_size": 32, "data_in_width": 8}
+    mini = {"data_in_exponent_width": 5, "data_in_frac_width": 10}
+    qc = {"mxfp": {"qk_matmul": fp, "av_matmul": fp, "rope": mini, "softmax": mini, "kv_cache": fp},
+          "mxint": {"qk_matmul": it, "av_matmul": it, "rope": mini, "softmax": mini, "kv_cache": it}}
+    for c in _cases(golden, "attention"):
+        dt, fmt = c["dtype"], c["format"]
+        t = lambda n: golden.tensor(f"attention/{dt}/{n}", dt)  # noqa: E731
+        w = {n: t(n) for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight")}
+        out, probs = O.attention_mx(t("hidden"), w, t("cos"), t("sin"), t("mask"), fmt, qc[fmt], 4, 2, c["cached"])
+        tag = f"attention/{dt}/{fmt}/cache{int(c['cached'])}"
+        assert_bits_equal(out, golden.tensor(tag + "/out", dt), tag + " out")
+        assert_bits_equal(probs, golden.tensor(tag + "/probs", dt), tag + " probs")
+    for c in _cases(golden, "mlp"):
+        dt = c["dtype"]
+        t = lambda n: golden.tensor(f"mlp/{dt}/{n}", dt)  # noqa: E731
+        out = O.gated_mlp_minifloat(golden.tensor(f"attention/{dt}/hidden", dt), t("gate_proj.weight"), t("up_proj.weight"),
+                                    t("down_proj.weight"), mini)
+        assert_bits_equal(out, t("out"), f"mlp {dt}")

@@ -52,3 +52,32 @@ def test_patch_replaces_the_entries_the_pass_reads(chop_modules):
     out, _ = run_pass(model, {"by": "type", "linear": {"config": dict(cfg, bypass=True)}})
     assert isinstance(out[0], mb.LinearMXFP) and isinstance(out[2], mb.LinearMXFP)
     assert out[0].config["weight_exponent_width"] == 4
+
+
+def test_patch_registers_the_llama_wrappers_and_the_gptq_entry(chop_modules):
+    """The family wrappers are looked up as quantized_module_map[f"{prefix}_{name}"] and built with
+    (config, layer_idx, q_config): the entries are this package's classes and accept that call."""
+    from mase_b200 import attention, gptq
+
+    _, qm, _ = chop_modules
+    mb.patch()
+    assert qm.quantized_module_map["llama_self_attention_mxfp"] is attention.AttentionMXFP
+    assert qm.quantized_module_map["llama_self_attention_mxint"] is attention.AttentionMXInt
+    assert qm.quantized_module_map["llama_mlp_mxfp"] is attention.GatedMLPMX
+    assert qm.quantized_module_map["llama_rms_norm_minifloat"] is mb.RMSNormMinifloat
+
+    class Cfg:
+        hidden_size, intermediate_size, num_attention_heads, num_key_value_heads = 64, 128, 4, 2
+        attention_bias, mlp_bias, attention_dropout, rms_norm_eps = False, False, 0.0, 1e-5
+
+    attn = qm.quantized_module_map["llama_self_attention_mxfp"](config=Cfg(), layer_idx=2, q_config={"rope": {"bypass": True}})
+    assert attn.layer_idx == 2 and attn.rope_bypass and not attn.qk_bypass
+    assert attn.k_proj.out_features == 32 and attn.num_key_value_groups == 2
+    assert set(attn.state_dict()) == {"q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight"}
+    mlp = qm.quantized_module_map["llama_mlp_mxint"](config=Cfg(), layer_idx=2, q_config={"bypass": True})
+    assert mlp.bypass and mlp.down_proj.in_features == 128
+    norm = qm.quantized_module_map["llama_rms_norm_minifloat"](config=Cfg(), layer_idx=2, q_config={"bypass": True})
+    assert norm.variance_epsilon == 1e-5 and norm.weight.shape == (64,)
+    gp = sys.modules.get("chop.passes.module.transforms.gptq")
+    if gp is not None:
+        assert gp.run_gptq is gptq.run_gptq
