@@ -106,7 +106,8 @@ int mxq_mxfp_compose(const uint8_t *codes, const uint8_t *scales, void *y, int o
                      int block, int E, int F, void *stream);
 
 /* Element-wise minifloat quantize-dequantize.  Replaces minifloat_quantizer_sim
- * (_minifloat_mx/minifloat.py:12-33) for is_finite=True, round-to-nearest. */
+ * (_minifloat_mx/minifloat.py:12-33) for is_finite=True, round-to-nearest.  E >= 1, F >= 1, E + F <= 15 (the range of
+ * the reference's MinifloatMeta: 8-bit formats as well as fp16-like E5M10 or bf16-like E8M7). */
 int mxq_minifloat_fake(const void *x, void *y, int in_dtype, int out_dtype, int64_t n, int E, int F, void *stream);
 
 /* Block floating point with tiles of `bs` consecutive elements of the last dimension (a ragged last tile is

@@ -1051,7 +1051,7 @@ int mxq_minifloat_fake(const void *x, void *y, int in_dtype, int out_dtype, int6
   if (n == 0) return MXQ_OK;
   if (!x || !y) return MXQ_ERR_NULL;
   if (n < 0) return MXQ_ERR_SHAPE;
-  if (E < 1 || F < 1 || E + F > 7) return MXQ_ERR_FORMAT;
+  if (E < 1 || F < 1 || E + F > 15) return MXQ_ERR_FORMAT;  // the reference's range: fewer than 16 bits after the sign
   const int grid = grid_for(n, kThreads);
 #define CALL(TI, TO)                                                                                        \
   minifloat_kernel<TI, TO><<<grid, kThreads, 0, (cudaStream_t)stream>>>((const TI *)x, (TO *)y, n, E, F); \

@@ -123,7 +123,7 @@ extern "C" int mxq_softmax_quant(const void *x, void *y, int dtype, int64_t rows
   if (rows < 0 || cols < 0) return MXQ_ERR_SHAPE;
   if (quantizer < kMxfp || quantizer > kMinifloat) return MXQ_ERR_FORMAT;
   if (quantizer != kMinifloat && (!tab_host || block < 1 || cols % block)) return MXQ_ERR_SHAPE;
-  if (quantizer == kMxint ? (p0 < 2 || p0 > 8) : (p0 < 1 || p1 < 1 || p0 + p1 > 7)) return MXQ_ERR_FORMAT;
+  if (quantizer == kMxint ? (p0 < 2 || p0 > 8) : (p0 < 1 || p1 < 1 || p0 + p1 > (quantizer == kMinifloat ? 15 : 7))) return MXQ_ERR_FORMAT;
   if (cols * (int64_t)sizeof(float) > 48 * 1024) return MXQ_ERR_UNSUPPORTED;  // the row lives in shared memory
   mxq::Log2Tab tab;
   for (int i = 0; i < 256; ++i) tab.t[i] = tab_host ? tab_host[i] : 0;

@@ -661,8 +661,6 @@ def minifloat_quantizer_sim(tensor: Tensor, minifloat_meta: MinifloatMeta, outpu
     _require_cuda(tensor, "minifloat_quantizer_sim")
     if not minifloat_meta.is_finite or minifloat_meta.round_mode != "rn":
         raise NotImplementedError("minifloat: only is_finite=True with round_mode='rn' is provided")
-    if minifloat_meta.exp_bits + minifloat_meta.frac_bits > 7:
-        raise NotImplementedError("minifloat: at most 8 bits per element")
     out_dtype = output_dtype or tensor.dtype
     di = _dtype_code(tensor.dtype, "minifloat")
     do = _dtype_code(out_dtype, "minifloat")

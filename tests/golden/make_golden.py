@@ -144,7 +144,7 @@ def main(root: str) -> None:
                     arrays[f"{tag}/codes"] = bits(co)
                     arrays[f"{tag}/fake"] = bits(y)
                     index.append({"kind": "mxfp", "input": key, "tag": tag, "block": block, "E": E, "F": F})
-            for E, F in ((4, 3), (2, 1)):
+            for E, F in ((4, 3), (2, 1), (5, 10), (8, 7), (3, 12)):  # 8-bit, fp16-like, bf16-like, a long fraction
                 y = minifloat_quantizer_sim(x, MinifloatMeta(exp_bits=E, frac_bits=F, is_finite=True, round_mode="rn"))
                 tag = f"{key}/minifloat_e{E}m{F}"
                 arrays[f"{tag}/fake"] = bits(y)

@@ -35,10 +35,13 @@ class ListCache:
         return self.k[layer_idx], self.v[layer_idx]
 
 
-def check(out, probs, ref_out, ref_probs, dt, what):
-    tol = 2e-4 if dt == "fp32" else 2e-2
-    err = float((out.float().cpu() - ref_out.float()).abs().max() / ref_out.float().abs().max())
+def check(out, probs, ref_out, ref_probs, dt, what, tol=None):
+    tol = tol or (2e-4 if dt == "fp32" else 2e-2)
+    diff = out.float().cpu() - ref_out.float()
+    err = float(diff.abs().max() / ref_out.float().abs().max())
     assert err <= tol, (what, err)
+    rms = float(diff.pow(2).mean().sqrt() / ref_out.float().pow(2).mean().sqrt())
+    assert rms <= tol / 4, (what, rms)
     p, r = probs.float().cpu(), ref_probs.float()
     assert float((p == r).float().mean()) >= 0.97, (what, float((p == r).float().mean()))
     step = r.reshape(-1, 32).abs().amax(dim=1, keepdim=True) / 8  # coarser than any element's own step
@@ -104,7 +107,9 @@ def test_larger_block_vs_oracle_and_construction_from_a_config():
     gemm.check_status()
     assert torch.equal(out, out2)
     ref_out, ref_probs = O.attention_mx(hidden, w, cos, sin, mask, "mxfp", QCFG["mxfp"], 8, 4, False)
-    check(out, probs, ref_out, ref_probs, "bf16", "larger block")
+    # 160 keys per row: more probabilities sit on a rounding boundary of their block than in the small fixtures, and
+    # one that flips moves an output by a bf16 step or two
+    check(out, probs, ref_out, ref_probs, "bf16", "larger block", tol=4e-2)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
