@@ -873,6 +873,31 @@ def run_decoder(args) -> None:
                       "roofline": out["roofline"], "cpu_baseline": out["cpu_baseline"]}))
 
 
+def run_search(args) -> None:
+    """`--workload search`: the clipping search of both formats on a bf16 [4096, 4096] weight (single GPU), one JSON
+    line; for profiler captures of the search kernels."""
+    import mase_b200 as mb
+
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    g = torch.Generator().manual_seed(3)
+    w = torch.randn(4096, 4096, generator=g) * 0.02
+    w[torch.rand(4096, 4096, generator=g) < 0.01] *= 20
+    wd = w.to(device).bfloat16()
+    int_meta, fp_meta = mb.MXIntMeta(32, 8, 4), mb.MXFPMeta(32, 8, 2, 1, True, "rn")
+
+    def step():
+        mb.mxint_quantizer_sim(wd, 1, int_meta, quantile_search=True)
+        mb.mxfp_quantizer_sim(wd, 1, fp_meta, quantile_search=True)
+
+    for _ in range(max(args.warmup, 1)):
+        step()
+    sec = time_region(step, args.steps, 1, device)
+    print(json.dumps({"metric": "clip_search_pair_ms", "value": sec / args.steps * 1e3, "unit": "ms", "n_gpus": 1,
+                      "steps": args.steps, "higher_is_better": False,
+                      "config": {"workload": "MXINT4 + MXFP4 (E2M1) clipping search of a bf16 [4096, 4096] weight, block 32"}}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -882,7 +907,7 @@ def main() -> None:
     ap.add_argument("--no-extra", action="store_true", help="skip the untimed extra measurements")
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the [rows, 8192] tensor (default: the full workload)")
     ap.add_argument("--kernel-only", action="store_true", help="only the device-resident timed region (for profilers)")
-    ap.add_argument("--workload", default="quant", choices=["quant", "linear", "decoder"],
+    ap.add_argument("--workload", default="quant", choices=["quant", "linear", "decoder", "search"],
                     help="quant: the headline quantizer benchmark; linear: MX Linear forward; decoder: the mixed-precision "
                          "decoder layer (both profiling aids)")
     ap.add_argument("--m", type=int, default=8192, help="tokens for --workload linear")
@@ -896,6 +921,8 @@ def main() -> None:
     if args.workload == "linear" and args.impl == "ours":
         run_linear(args)
         return
+    if args.workload == "search" and args.impl == "ours":
+        return run_search(args)
     if args.workload == "decoder" and args.impl == "ours":
         run_decoder(args)
         return
