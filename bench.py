@@ -341,10 +341,12 @@ def extras(device, x, peaks: dict) -> dict:
         out[f"mxfp8_bf16_{shape[0]}x{shape[1]}_us"] = xx.numel() * 4 / g / 1e3
     out["linear_mxfp8_4096x4096"] = linear_extras(device, peaks)
     out["decoder_layer_mixed_precision"] = decoder_layer_extras(device, peaks)
-    try:
-        out["calibration"] = calibration_extras(device)
-    except Exception as exc:  # calibration is off the timed path: report instead of losing the line
-        out["calibration"] = {"error": repr(exc)}
+    for name, fn in (("calibration", lambda: calibration_extras(device)),
+                     ("attention_block_mxfp8", lambda: attention_extras(device, peaks))):
+        try:
+            out[name] = fn()
+        except Exception as exc:  # off the timed path: report instead of losing the line
+            out[name] = {"error": repr(exc)}
     return out
 
 
@@ -409,6 +411,60 @@ def calibration_extras(device) -> dict:
         "cpu_baseline": {"value": t_cpu * 1e3, "unit": "ms", "kind": "port", "cores": torch.get_num_threads(),
                          "sample": "the 1024 x 1024 layer, 2048 tokens"}}
     return out
+
+
+def attention_extras(device, peaks: dict) -> dict:
+    """The quantized attention block (MXFP8 queries and probabilities, minifloat rotary tables and softmax input) at
+    hidden 4096, 32 heads, 8 x 512 tokens, bf16, and its two batched products alone; the CPU restatement of the same
+    block timed on one sequence."""
+    from mase_b200 import attention, gemm
+    from oracle import mx_oracle as O
+
+    fp = {"data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    mini = {"data_in_exponent_width": 5, "data_in_frac_width": 10}
+    qc = {"qk_matmul": fp, "av_matmul": fp, "rope": mini, "softmax": mini, "kv_cache": fp}
+    B, S, H, D = 8, 512, 32, 128
+    g = torch.Generator().manual_seed(5)
+    block = attention.AttentionMXFP(None, 0, qc, hidden_size=H * D, num_heads=H, num_kv_heads=H, device=device,
+                                    dtype=torch.bfloat16)
+    for prm in block.parameters():
+        prm.data.copy_((torch.randn(prm.shape, generator=g) * 0.02).to(device))
+    hidden = torch.randn(B, S, H * D, generator=g).bfloat16()
+    pos = torch.arange(S, dtype=torch.float32)
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = torch.cat([pos[:, None] * inv[None], pos[:, None] * inv[None]], dim=-1)
+    cos, sin = ang.cos()[None].expand(B, S, D).bfloat16(), ang.sin()[None].expand(B, S, D).bfloat16()
+    mask = torch.zeros(B, 1, S, S, dtype=torch.bfloat16).masked_fill(
+        torch.ones(S, S, dtype=torch.bool).triu(1)[None, None], torch.finfo(torch.bfloat16).min)
+    hd, cd, sd, md = hidden.to(device), cos.to(device), sin.to(device), mask.to(device)
+    with torch.no_grad():
+        t_block = 1.0 / quick_gbs(lambda: block(hd, (cd, sd), md), 1, calls=5) / 1e9
+        q = torch.randn(B * H, S, D, device=device).bfloat16()
+        k = torch.randn(B * H, S, D, device=device).bfloat16()
+        p = torch.rand(B * H, S, S, device=device).bfloat16()
+        vt = torch.randn(B * H, D, S, device=device).bfloat16()
+        t_qk = 1.0 / quick_gbs(lambda: gemm.batched_product(q, k), 1, calls=10) / 1e9
+        t_pv = 1.0 / quick_gbs(lambda: gemm.batched_product(p, vt), 1, calls=10) / 1e9
+    flops = 2.0 * B * H * S * S * D
+    w = {n: prm.detach().cpu() for n, prm in block.named_parameters()}
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    O.attention_mx(hidden[:1], w, cos[:1], sin[:1], mask[:1], "mxfp", qc, H, H, False)
+    t_cpu = time.perf_counter() - t0
+    hbm, hbm_kind = measured_peaks()
+    # bytes each product has to move: both operands once, the result once (bf16)
+    qk_bytes = 2.0 * B * H * (S * D + S * D + S * S)
+    pv_bytes = 2.0 * B * H * (S * S + D * S + S * D)
+    return {"block_ms": t_block * 1e3, "qk_batched_us": t_qk * 1e6, "pv_batched_us": t_pv * 1e6,
+            "qk_TFLOPs": flops / t_qk / 1e12, "pv_TFLOPs": flops / t_pv / 1e12,
+            "roofline": {"bound": "hbm", "unit": "GB/s", "peak": hbm, "peak_source": f"{hbm_kind} copy bandwidth",
+                         "qk_achieved": qk_bytes / t_qk / 1e9, "qk_frac": qk_bytes / t_qk / 1e9 / hbm,
+                         "pv_achieved": pv_bytes / t_pv / 1e9, "pv_frac": pv_bytes / t_pv / 1e9 / hbm,
+                         "algorithmic_bytes": {"qk": qk_bytes, "pv": pv_bytes},
+                         "timed": "256 products of 512 x 512 x 128 (Q K^T) and 512 x 128 x 512 (P V) per launch; 200 MB "
+                                  "per launch, more than L2"},
+            "cpu_baseline": {"value": t_cpu * B * 1e3, "unit": "ms (scaled from the sample)", "kind": "port",
+                             "cores": torch.get_num_threads(), "sample": "1 of 8 sequences"}}
 
 
 def decoder_layer_extras(device, peaks: dict, steps: int = 10) -> dict:
