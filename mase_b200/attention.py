@@ -33,12 +33,28 @@ def repeat_kv(x: Tensor, n_rep: int) -> Tensor:
     return x[:, :, None, :, :].expand(b, h, n_rep, s, d).reshape(b, h * n_rep, s, d)
 
 
+class HeadRMSNorm(nn.Module):
+    """weight * x / sqrt(mean(x^2) + eps) over the last dimension, evaluated in fp32 and cast back before the weight
+    is applied (the RMS norm of the transformers library's Llama / Qwen3 models)."""
+
+    def __init__(self, dim: int, eps: float = 1e-6, device=None, dtype=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
+        self.variance_epsilon = eps
+
+    def forward(self, x: Tensor) -> Tensor:
+        dt = x.dtype
+        x = x.to(torch.float32)
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.variance_epsilon)
+        return self.weight * x.to(dt)
+
+
 class _AttentionMX(nn.Module):
-    _format = ""
+    _qk_norm = False
 
     def __init__(self, config=None, layer_idx: int = 0, q_config: dict | None = None, *, hidden_size: int | None = None,
                  num_heads: int | None = None, num_kv_heads: int | None = None, head_dim: int | None = None,
-                 bias: bool = False, attention_dropout: float = 0.0, device=None, dtype=None):
+                 bias: bool = False, attention_dropout: float = 0.0, rms_norm_eps: float = 1e-6, device=None, dtype=None):
         """Either `config` (an object with hidden_size, num_attention_heads, num_key_value_heads and optionally
         head_dim, attention_bias, attention_dropout -- the call the quantize pass makes,
         chop/passes/module/module_modify_helper.py:265-275) or the sizes as keywords."""
@@ -50,6 +66,7 @@ class _AttentionMX(nn.Module):
             head_dim = getattr(config, "head_dim", None)
             bias = getattr(config, "attention_bias", False)
             attention_dropout = getattr(config, "attention_dropout", 0.0)
+            rms_norm_eps = getattr(config, "rms_norm_eps", rms_norm_eps)
         self.config = config
         self.layer_idx = layer_idx
         self.num_heads = num_heads
@@ -63,6 +80,9 @@ class _AttentionMX(nn.Module):
         self.k_proj = nn.Linear(hidden_size, self.num_kv_heads * self.head_dim, bias=bias, **kw)
         self.v_proj = nn.Linear(hidden_size, self.num_kv_heads * self.head_dim, bias=bias, **kw)
         self.o_proj = nn.Linear(self.num_heads * self.head_dim, hidden_size, bias=bias, **kw)
+        if self._qk_norm:  # the Qwen3 family normalises queries and keys over the head dimension
+            self.q_norm = HeadRMSNorm(self.head_dim, rms_norm_eps, **kw)
+            self.k_norm = HeadRMSNorm(self.head_dim, rms_norm_eps, **kw)
         q_config = q_config or {}
         self.qk_config = q_config.get("qk_matmul", {})
         self.av_config = q_config.get("av_matmul", {})
@@ -90,9 +110,11 @@ class _AttentionMX(nn.Module):
         q, k = attention.q_proj, attention.k_proj
         head_dim = getattr(attention, "head_dim", None) or getattr(cfg, "head_dim", None) or \
             cfg.hidden_size // cfg.num_attention_heads
+        norm = getattr(attention, "q_norm", None)
         new = cls(None, getattr(attention, "layer_idx", 0), q_config, hidden_size=q.in_features,
                   num_heads=q.out_features // head_dim, num_kv_heads=k.out_features // head_dim, head_dim=head_dim,
                   bias=q.bias is not None, attention_dropout=getattr(attention, "attention_dropout", 0.0),
+                  rms_norm_eps=getattr(norm, "variance_epsilon", getattr(norm, "eps", None) or 1e-6),
                   device=q.weight.device, dtype=q.weight.dtype)
         new.load_state_dict(attention.state_dict(), strict=True)
         return new
@@ -108,8 +130,10 @@ class _AttentionMX(nn.Module):
         input_shape = hidden_states.shape[:-1]
         hidden_shape = (*input_shape, -1, self.head_dim)
         q, k, v = forward_siblings([self.q_proj, self.k_proj, self.v_proj], hidden_states)
-        query = q.view(hidden_shape).transpose(1, 2)
-        key = k.view(hidden_shape).transpose(1, 2)
+        q, k = q.view(hidden_shape), k.view(hidden_shape)
+        if self._qk_norm:
+            q, k = self.q_norm(q), self.k_norm(k)
+        query, key = q.transpose(1, 2), k.transpose(1, 2)
         value = v.view(hidden_shape).transpose(1, 2)
         cos, sin = position_embeddings
         if not self.rope_bypass:
@@ -198,5 +222,18 @@ class GatedMLPMX(nn.Module):
         return self.down_proj(F_mx.silu_minifloat(gate, self.q_config) * up)
 
 
+class Qwen3AttentionMXFP(AttentionMXFP):
+    """chop/nn/quantized/modules/qwen3/attention.py:20-120: the same block with RMS norms over the head dimension of
+    queries and keys before the rotary embedding (children `q_norm`, `k_norm`)."""
+
+    _qk_norm = True
+
+
+class Qwen3AttentionMXInt(AttentionMXInt):
+    """chop/nn/quantized/modules/qwen3/attention.py:127-227."""
+
+    _qk_norm = True
+
+
 LlamaAttentionMXFP, LlamaAttentionMXInt = AttentionMXFP, AttentionMXInt
-LlamaMLPMXFP = LlamaMLPMXInt = GatedMLPMX
+LlamaMLPMXFP = LlamaMLPMXInt = Qwen3MLPMXFP = Qwen3MLPMXInt = GatedMLPMX

@@ -84,7 +84,11 @@ def patch(chop=None) -> list[str]:
         for key, cls in (("llama_self_attention_mxfp", attention.AttentionMXFP),
                          ("llama_self_attention_mxint", attention.AttentionMXInt),
                          ("llama_mlp_mxfp", attention.GatedMLPMX), ("llama_mlp_mxint", attention.GatedMLPMX),
-                         ("llama_rms_norm_minifloat", modules.RMSNormMinifloat)):
+                         ("llama_rms_norm_minifloat", modules.RMSNormMinifloat),
+                         ("qwen3_self_attention_mxfp", attention.Qwen3AttentionMXFP),
+                         ("qwen3_self_attention_mxint", attention.Qwen3AttentionMXInt),
+                         ("qwen3_mlp_mxfp", attention.GatedMLPMX), ("qwen3_mlp_mxint", attention.GatedMLPMX),
+                         ("qwen3_rms_norm_minifloat", modules.RMSNormMinifloat)):
             if key in mm.quantized_module_map:
                 mm.quantized_module_map[key] = cls
                 done.append(f"chop.nn.quantized.modules.quantized_module_map[{key!r}]")

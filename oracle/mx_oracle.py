@@ -458,15 +458,26 @@ def _rotate_half(t: Tensor) -> Tensor:
     return torch.cat((-t[..., half:], t[..., :half]), dim=-1)
 
 
+def _head_rms_norm(x: Tensor, weight: Tensor, eps: float) -> Tensor:
+    xf = x.to(torch.float32)
+    xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return weight * xf.to(x.dtype)
+
+
 def attention_mx(hidden: Tensor, weights: dict, cos: Tensor, sin: Tensor, mask, fmt: str, q_config: dict, heads: int,
-                 kv_heads: int, cached: bool) -> tuple[Tensor, Tensor]:
+                 kv_heads: int, cached: bool, qk_norm_eps: float | None = None) -> tuple[Tensor, Tensor]:
     """Forward of the reference's MX attention block with plain Linear projections: minifloat cos / sin in the rotary
     embedding, MX key / value states when a cache is attached, MX queries into Q K^T, scaling, mask, minifloat input
-    of an fp32 softmax, MX probabilities into P V (attention.py:148-214, 334-394).  Returns (output, probabilities)."""
+    of an fp32 softmax, MX probabilities into P V (attention.py:148-214, 334-394).  `qk_norm_eps` adds the Qwen3
+    variant's RMS norms of queries and keys over the head dimension.  Returns (output, probabilities)."""
     B, S, _ = hidden.shape
     lin = torch.nn.functional.linear
-    q = lin(hidden, weights["q_proj.weight"]).view(B, S, heads, -1).transpose(1, 2)
-    k = lin(hidden, weights["k_proj.weight"]).view(B, S, kv_heads, -1).transpose(1, 2)
+    q = lin(hidden, weights["q_proj.weight"]).view(B, S, heads, -1)
+    k = lin(hidden, weights["k_proj.weight"]).view(B, S, kv_heads, -1)
+    if qk_norm_eps is not None:  # the Qwen3 variant (qwen3/attention.py:47-53)
+        q = _head_rms_norm(q, weights["q_norm.weight"], qk_norm_eps)
+        k = _head_rms_norm(k, weights["k_norm.weight"], qk_norm_eps)
+    q, k = q.transpose(1, 2), k.transpose(1, 2)
     v = lin(hidden, weights["v_proj.weight"]).view(B, S, kv_heads, -1).transpose(1, 2)
     c, s_ = _minifloat(cos, q_config["rope"]).unsqueeze(1), _minifloat(sin, q_config["rope"]).unsqueeze(1)
     q, k = q * c + _rotate_half(q) * s_, k * c + _rotate_half(k) * s_

@@ -346,6 +346,30 @@ def main(root: str) -> None:
                 arrays[f"attention/{dt_name}/{fmt}/cache{int(cached)}/out"] = bits(out)
                 arrays[f"attention/{dt_name}/{fmt}/cache{int(cached)}/probs"] = bits(probs)
                 index.append({"kind": "attention", "dtype": dt_name, "format": fmt, "cached": cached})
+        # the Qwen3 variant: RMS norms over the head dimension of queries and keys before the rotary embedding
+        # (nn/quantized/modules/qwen3/attention.py:20-120)
+        if "chop.nn.quantized.modules.qwen3" not in sys.modules:
+            m = types.ModuleType("chop.nn.quantized.modules.qwen3")
+            m.__path__ = [root + "/nn/quantized/modules/qwen3"]
+            sys.modules["chop.nn.quantized.modules.qwen3"] = m
+        from chop.nn.quantized.modules.qwen3.attention import Qwen3AttentionMXFP
+        from transformers import Qwen3Config
+
+        qw = Qwen3Config(hidden_size=128, intermediate_size=256, num_hidden_layers=1, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=32, vocab_size=64, max_position_embeddings=128)
+        qw._attn_implementation = "eager"
+        attn = Qwen3AttentionMXFP(qw, 0, q_fp).to(dt).eval()
+        state = {n: w.to(dt) for n, w in weights32.items()}
+        state["q_norm.weight"] = (1 + 0.2 * torch.randn(32, generator=g)).to(dt)
+        state["k_norm.weight"] = (1 + 0.2 * torch.randn(32, generator=g)).to(dt)
+        attn.load_state_dict(state)
+        with torch.no_grad():
+            out, probs = attn(hidden, (cos, sin), mask)
+        arrays[f"attention/{dt_name}/qwen3/q_norm.weight"] = bits(state["q_norm.weight"])
+        arrays[f"attention/{dt_name}/qwen3/k_norm.weight"] = bits(state["k_norm.weight"])
+        arrays[f"attention/{dt_name}/qwen3/out"] = bits(out)
+        arrays[f"attention/{dt_name}/qwen3/probs"] = bits(probs)
+        index.append({"kind": "attention_qwen3", "dtype": dt_name, "eps": qw.rms_norm_eps})
         mlp = LlamaMLPMXFP(hf, 0, mini).to(dt).eval()
         with torch.no_grad():
             for n, prm in mlp.named_parameters():

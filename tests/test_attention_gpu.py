@@ -69,6 +69,26 @@ def test_attention_matches_reference_vectors(golden):
         check(out, probs, golden.tensor(tag + "/out", dt), golden.tensor(tag + "/probs", dt), dt, tag)
 
 
+def test_qwen3_variant_matches_reference_vectors(golden):
+    """The same block with RMS norms over the head dimension of queries and keys (Qwen3AttentionMXFP)."""
+    for c in (c for c in golden.cases if c["kind"] == "attention_qwen3"):
+        dt = c["dtype"]
+        t = lambda n: golden.tensor(f"attention/{dt}/{n}", dt).to(DEV)  # noqa: E731
+        dtype = torch.float32 if dt == "fp32" else torch.bfloat16
+        block = attention.Qwen3AttentionMXFP(None, 0, QCFG["mxfp"], hidden_size=128, num_heads=4, num_kv_heads=2,
+                                             rms_norm_eps=c["eps"], device=DEV, dtype=dtype)
+        state = {n: t(n) for n in WEIGHTS}
+        state.update({n: t("qwen3/" + n) for n in ("q_norm.weight", "k_norm.weight")})
+        block.load_state_dict(state)
+        with torch.no_grad():
+            out, probs = block(t("hidden"), (t("cos"), t("sin")), t("mask"))
+        gemm.check_status()
+        check(out, probs, golden.tensor(f"attention/{dt}/qwen3/out", dt), golden.tensor(f"attention/{dt}/qwen3/probs", dt),
+              dt, f"qwen3 {dt}")
+        again = attention.Qwen3AttentionMXFP.from_attention(block, QCFG["mxfp"])
+        assert again.q_norm.variance_epsilon == c["eps"] and torch.equal(again.k_norm.weight, block.k_norm.weight)
+
+
 def test_gated_mlp_matches_reference_vectors(golden):
     for c in (c for c in golden.cases if c["kind"] == "mlp"):
         dt = c["dtype"]

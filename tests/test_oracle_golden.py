@@ -14,7 +14,8 @@ def _cases(golden, kind):
 def test_fixture_inventory(golden):
     kinds = {c["kind"] for c in golden.cases}
     assert kinds == {"mxint", "mxfp", "minifloat", "bfp", "bfp_tiles", "blockdim", "linear", "mxint_search",
-                     "mxfp_search", "gptq", "attention", "mlp"}
+                     "mxfp_search", "gptq", "attention", "mlp",
+                     "attention_qwen3"}
     assert len(golden.cases) >= 200
 
 
@@ -191,6 +192,14 @@ def test_attention_and_mlp_oracles_match_reference(golden):
         tag = f"attention/{dt}/{fmt}/cache{int(c['cached'])}"
         assert_bits_equal(out, golden.tensor(tag + "/out", dt), tag + " out")
         assert_bits_equal(probs, golden.tensor(tag + "/probs", dt), tag + " probs")
+    for c in _cases(golden, "attention_qwen3"):
+        dt = c["dtype"]
+        t = lambda n: golden.tensor(f"attention/{dt}/{n}", dt)  # noqa: E731
+        w = {n: t(n) for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight")}
+        w.update({n: t("qwen3/" + n) for n in ("q_norm.weight", "k_norm.weight")})
+        out, probs = O.attention_mx(t("hidden"), w, t("cos"), t("sin"), t("mask"), "mxfp", qc["mxfp"], 4, 2, False, c["eps"])
+        assert_bits_equal(out, t("qwen3/out"), f"qwen3 {dt} out")
+        assert_bits_equal(probs, t("qwen3/probs"), f"qwen3 {dt} probs")
     for c in _cases(golden, "mlp"):
         dt = c["dtype"]
         t = lambda n: golden.tensor(f"mlp/{dt}/{n}", dt)  # noqa: E731

@@ -65,6 +65,8 @@ def test_patch_registers_the_llama_wrappers_and_the_gptq_entry(chop_modules):
     assert qm.quantized_module_map["llama_self_attention_mxint"] is attention.AttentionMXInt
     assert qm.quantized_module_map["llama_mlp_mxfp"] is attention.GatedMLPMX
     assert qm.quantized_module_map["llama_rms_norm_minifloat"] is mb.RMSNormMinifloat
+    assert qm.quantized_module_map["qwen3_self_attention_mxfp"] is attention.Qwen3AttentionMXFP
+    assert qm.quantized_module_map["qwen3_mlp_mxint"] is attention.GatedMLPMX
 
     class Cfg:
         hidden_size, intermediate_size, num_attention_heads, num_key_value_heads = 64, 128, 4, 2
@@ -78,6 +80,10 @@ def test_patch_registers_the_llama_wrappers_and_the_gptq_entry(chop_modules):
     assert mlp.bypass and mlp.down_proj.in_features == 128
     norm = qm.quantized_module_map["llama_rms_norm_minifloat"](config=Cfg(), layer_idx=2, q_config={"bypass": True})
     assert norm.variance_epsilon == 1e-5 and norm.weight.shape == (64,)
+    qwen = qm.quantized_module_map["qwen3_self_attention_mxint"](config=Cfg(), layer_idx=0, q_config={})
+    assert set(qwen.state_dict()) == {"q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "q_norm.weight",
+                                      "k_norm.weight"}
+    assert qwen.q_norm.variance_epsilon == 1e-5 and qwen.q_norm.weight.shape == (16,)
     gp = sys.modules.get("chop.passes.module.transforms.gptq")
     if gp is not None:
         assert gp.run_gptq is gptq.run_gptq
