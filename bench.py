@@ -954,6 +954,18 @@ def run_search(args) -> None:
                       "config": {"workload": "MXINT4 + MXFP4 (E2M1) clipping search of a bf16 [4096, 4096] weight, block 32"}}))
 
 
+def run_attention(args) -> None:
+    """`--workload attention`: the quantized attention block alone (single GPU), one JSON line; for launch lists and
+    profiler captures of the batched products, the rotary and the softmax kernels."""
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    out = attention_extras(device, {"bf16_tflops": measured_bf16_tflops()[0]})
+    print(json.dumps({"metric": "attention_block_ms", "value": out["block_ms"], "unit": "ms", "n_gpus": 1,
+                      "steps": args.steps, "higher_is_better": False,
+                      "config": {"workload": "MXFP8 attention block, hidden 4096, 32 heads of 128, 8 x 512 tokens, bf16"},
+                      "roofline": out["roofline"], "cpu_baseline": out["cpu_baseline"], "extra": out}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -963,7 +975,7 @@ def main() -> None:
     ap.add_argument("--no-extra", action="store_true", help="skip the untimed extra measurements")
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the [rows, 8192] tensor (default: the full workload)")
     ap.add_argument("--kernel-only", action="store_true", help="only the device-resident timed region (for profilers)")
-    ap.add_argument("--workload", default="quant", choices=["quant", "linear", "decoder", "search"],
+    ap.add_argument("--workload", default="quant", choices=["quant", "linear", "decoder", "search", "attention"],
                     help="quant: the headline quantizer benchmark; linear: MX Linear forward; decoder: the mixed-precision "
                          "decoder layer (both profiling aids)")
     ap.add_argument("--m", type=int, default=8192, help="tokens for --workload linear")
@@ -979,6 +991,8 @@ def main() -> None:
         return
     if args.workload == "search" and args.impl == "ours":
         return run_search(args)
+    if args.workload == "attention" and args.impl == "ours":
+        return run_attention(args)
     if args.workload == "decoder" and args.impl == "ours":
         run_decoder(args)
         return

@@ -273,10 +273,28 @@ int mxq_mx_gated_linear(const void *gate, const void *up, int64_t ld, const uint
 int mxq_softmax_quant(const void *x, void *y, int dtype, int64_t rows, int64_t cols, int quantizer, int block, int p0,
                       int p1, const uint8_t *tab_host, void *stream);
 
+/* The softmax of an attention block with what surrounds it, one warp per row, one pass over HBM.  Replaces, with the
+ * roundings of the separate tensor operations (T = dtype),
+ *     s = matmul_result * scaling; s = s + causal_mask; p = softmax_minifloat(s) (or the fp32 softmax); p = quantizer(p)
+ * of chop/nn/quantized/modules/llama/attention.py:352-388:
+ *     s = round_T(x * scale) when use_scale; s = round_T(s + mask[b, 0, i, :]) when mask != NULL
+ *     q = quantizer(s): 0 MXFP(p0 = E, p1 = F), 1 MXINT(p0 = bits), 2 element-wise minifloat(p0 = E, p1 = F), 3 none
+ *     p = round_T(softmax over the row of fp32(q))
+ *     y = out_quantizer(p): 0 MXFP, 1 MXINT, 3 none
+ * x, y: [rows, cols] of dtype, rows = batch * heads * mask_rows in that order; mask: dtype [batch, 1, mask_rows, >= cols]
+ * with row stride mask_ld (elements) and batch stride mask_rows * mask_ld, finite values.  The MX quantizers work on
+ * blocks of 32 along the row (block / out_block must be 32) with the host log2 tables of the plain quantizers.
+ * cols % 32 == 0 and cols <= 2048, else MXQ_ERR_UNSUPPORTED (compose the operations instead). */
+int mxq_attention_softmax(const void *x, void *y, int dtype, int64_t rows, int64_t cols, int use_scale, float scale,
+                          const void *mask, int64_t mask_ld, int64_t mask_rows, int64_t heads, int quantizer, int block,
+                          int p0, int p1, const uint8_t *tab_host, int out_quantizer, int out_block, int out_p0,
+                          int out_p1, const uint8_t *out_tab_host, void *stream);
+
 /* Rotary position embedding y = x * cos + rotate_half(x) * sin in one pass.  Replaces _apply_rope
  * (chop/nn/quantized/functional/rope.py:17-28; the rope_mxfp / rope_mxint / rope_minifloat wrappers quantize the
- * tables first and then call it).  x, y: [batch, heads, seq, dim] of `dtype` with a contiguous last dimension and the
- * element strides given (y has x's layout and must not overlap x); cos, sin:
+ * tables first and then call it).  x: [batch, heads, seq, dim] of `dtype` with a contiguous last dimension and the
+ * element strides given (a transposed view of a [batch, seq, heads * dim] projection, for instance); y: the same shape,
+ * contiguous, not overlapping x -- the layout the attention products read; cos, sin:
  * [batch or 1, seq, dim] of `table_dtype` (table_stride_b = 0 for tables shared by the batch).  dim % 16 == 0.
  * Tables of the tensor's dtype: each product and the sum are rounded to it, as the framework's elementwise kernels
  * do; fp32 tables with a bf16 tensor: evaluated in fp32 and rounded once. */

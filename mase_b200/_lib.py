@@ -42,6 +42,8 @@ _PROTOTYPES = {
                               c_void_p],
     "mxq_mx_gated_linear": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64,
                             c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p],
+    "mxq_attention_softmax": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, ctypes.c_float, c_void_p, c_int64, c_int64,
+                              c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "mxq_softmax_quant": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "mxq_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                  c_int64, c_int64, c_int64, c_void_p],

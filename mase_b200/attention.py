@@ -51,6 +51,7 @@ class HeadRMSNorm(nn.Module):
 
 class _AttentionMX(nn.Module):
     _qk_norm = False
+    _format = ""  # "mxfp" / "mxint": the operand quantizer of queries, probabilities and cached keys / values
 
     def __init__(self, config=None, layer_idx: int = 0, q_config: dict | None = None, *, hidden_size: int | None = None,
                  num_heads: int | None = None, num_kv_heads: int | None = None, head_dim: int | None = None,
@@ -150,17 +151,30 @@ class _AttentionMX(nn.Module):
         if not self.qk_bypass:
             query = self._quantize(query, self.qk_config)
         # only the quantized operand is known to fit tf32; the other one takes the fp32 split
-        weights = self._product(query, key, exact=False) * self.scaling
-        if attention_mask is not None:
-            weights = weights + attention_mask[:, :, :, : key.shape[-2]]
-        if not self.softmax_bypass:
-            weights = F_mx.softmax_minifloat(weights, self.softmax_config, dim=-1)
+        weights = self._product(query, key, exact=False)
+        dropout = self.training and self.attention_dropout > 0
+        # scaling, mask, the softmax with its input quantizer and the quantizer of the probabilities: one kernel
+        fused = F_mx.attention_softmax(weights, self.scaling, attention_mask,
+                                       None if self.softmax_bypass else "minifloat", self.softmax_config,
+                                       None if self.av_bypass or dropout else self._format, self.av_config)
+        if fused is not None:
+            weights = fused
+            if dropout:
+                weights = nn.functional.dropout(weights, p=self.attention_dropout, training=True)
+                if not self.av_bypass:
+                    weights = self._quantize(weights, self.av_config)
         else:
-            weights = torch.softmax(weights.to(torch.float32), dim=-1).to(weights.dtype)
-        if self.training and self.attention_dropout > 0:
-            weights = nn.functional.dropout(weights, p=self.attention_dropout, training=True)
-        if not self.av_bypass:
-            weights = self._quantize(weights, self.av_config)
+            weights = weights * self.scaling
+            if attention_mask is not None:
+                weights = weights + attention_mask[:, :, :, : key.shape[-2]]
+            if not self.softmax_bypass:
+                weights = F_mx.softmax_minifloat(weights, self.softmax_config, dim=-1)
+            else:
+                weights = torch.softmax(weights.to(torch.float32), dim=-1).to(weights.dtype)
+            if dropout:
+                weights = nn.functional.dropout(weights, p=self.attention_dropout, training=True)
+            if not self.av_bypass:
+                weights = self._quantize(weights, self.av_config)
         out = self._product(weights, value.transpose(2, 3).contiguous(), exact=False)  # [B, H, S, D]
         out = out.transpose(1, 2).contiguous().reshape(*input_shape, -1)
         return self.o_proj(out), weights
@@ -168,6 +182,8 @@ class _AttentionMX(nn.Module):
 
 class AttentionMXFP(_AttentionMX):
     """chop/nn/quantized/modules/llama/attention.py:130-233 (LlamaAttentionMXFP)."""
+
+    _format = "mxfp"
 
     def _quantize(self, x, cfg):
         return mxfp_quantizer(x, block_size=cfg["data_in_block_size"], element_exp_bits=cfg["data_in_exponent_width"],
@@ -179,6 +195,8 @@ class AttentionMXFP(_AttentionMX):
 
 class AttentionMXInt(_AttentionMX):
     """chop/nn/quantized/modules/llama/attention.py:236-331 (LlamaAttentionMXInt)."""
+
+    _format = "mxint"
 
     def _quantize(self, x, cfg):
         return mxint_quantizer(x, block_size=cfg["data_in_block_size"], element_bits=cfg["data_in_width"], block_dim=-1)

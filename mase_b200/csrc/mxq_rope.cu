@@ -18,7 +18,7 @@ namespace rope {
 
 struct Shape {
   int64_t heads, seq, half;        // half = dim / 2
-  int64_t xs_b, xs_h, xs_s;        // element strides of x and y (the output has the input's layout)
+  int64_t xs_b, xs_h, xs_s;        // element strides of x; y is contiguous [batch, heads, seq, dim]
   int64_t ts_b, ts_s;              // element strides of the tables: [batch or 1, seq, dim]
   int64_t total;                   // batch * heads * seq * half / 8 groups of 8 element pairs
 };
@@ -81,7 +81,8 @@ rope_kernel(const T *__restrict__ x, T *__restrict__ y, const TT *__restrict__ c
         o_hi[j] = fmaf(lo[j], s_hi[j], hi[j] * c_hi[j]);
       }
     }
-    store8(y + xo, o_lo), store8(y + xo + s.half, o_hi);
+    const int64_t yo = row * (2 * s.half) + d;
+    store8(y + yo, o_lo), store8(y + yo + s.half, o_hi);
   }
 }
 

@@ -132,6 +132,63 @@ def _fused_softmax(x: Tensor, dim: int, quantizer: int, block: int, p0: int, p1:
     return y
 
 
+def _quantizer_code(fmt: str | None, cfg: dict | None, dtype: torch.dtype):
+    """(kind, block, p0, p1, table address) of a quantizer for the fused softmax kernel; kind 3 = none."""
+    from .quantizers import _ceil_tab_ptr, _floor_tab_ptr
+
+    if fmt is None or cfg is None or cfg.get("bypass", False):
+        return 3, 0, 0, 0, 0
+    if fmt == "mxfp":
+        return 0, cfg["data_in_block_size"], cfg["data_in_exponent_width"], cfg["data_in_frac_width"], _floor_tab_ptr()
+    if fmt == "mxint":
+        return 1, cfg["data_in_block_size"], cfg["data_in_width"], 0, _ceil_tab_ptr(dtype)
+    if fmt == "minifloat":
+        if not cfg.get("data_in_is_finite", True) or cfg.get("data_in_round_mode", "rn") != "rn":
+            return None
+        return 2, 1, cfg["data_in_exponent_width"], cfg["data_in_frac_width"], 0
+    raise ValueError(f"unknown quantizer {fmt!r}")
+
+
+def attention_softmax(scores: Tensor, scale: float | None, mask: Tensor | None, in_fmt: str | None, in_cfg: dict | None,
+                      out_fmt: str | None, out_cfg: dict | None) -> Tensor | None:
+    """softmax over the last dimension of scores[batch, heads, q_len, k_len] together with what surrounds it in an
+    attention block -- `scores * scale`, `+ mask[:, :, :, :k_len]`, the input quantizer of the softmax
+    (`in_fmt` "mxfp" / "mxint" / "minifloat" / None with its config), and the quantizer of the probabilities
+    (`out_fmt` "mxfp" / "mxint" / None) -- in one kernel (mxq_attention_softmax), with the roundings of the separate
+    tensor operations.  Returns None when the kernel does not take the case (the caller composes the operations)."""
+    from . import _lib
+    from .quantizers import _DT, _on_device, _stream
+
+    if not scores.is_cuda or scores.dtype not in _DT or scores.dim() != 4:
+        return None
+    if scores.requires_grad and torch.is_grad_enabled():
+        return None
+    b, h, sq, sk = scores.shape
+    if sk % 32 or sk > 2048 or scores.numel() == 0:
+        return None
+    qi, qo = _quantizer_code(in_fmt, in_cfg, scores.dtype), _quantizer_code(out_fmt, out_cfg, scores.dtype)
+    if qi is None or qo is None or (qi[0] in (0, 1) and qi[1] != 32) or (qo[0] in (0, 1) and qo[1] != 32) or qo[0] == 2:
+        return None
+    mask_ptr, mask_ld = 0, 0
+    if mask is not None:
+        mask = mask[:, :, :, :sk]
+        if (mask.dtype != scores.dtype or mask.dim() != 4 or mask.shape[0] != b or mask.shape[1] != 1 or mask.shape[2] != sq
+                or mask.stride(3) != 1 or (b > 1 and mask.stride(0) != sq * mask.stride(2))):
+            return None
+        mask_ptr, mask_ld = mask.data_ptr(), mask.stride(2)
+    x = scores.contiguous()
+    y = torch.empty_like(x)
+    with _on_device(x):
+        rc = _lib.lib().mxq_attention_softmax(x.data_ptr(), y.data_ptr(), _DT[x.dtype], b * h * sq, sk,
+                                              0 if scale is None else 1, 1.0 if scale is None else float(scale), mask_ptr,
+                                              mask_ld, sq, h, qi[0], qi[1], qi[2], qi[3], qi[4], qo[0], qo[1], qo[2], qo[3],
+                                              qo[4], _stream(x))
+    if rc == -7:
+        return None
+    _lib.check(rc, "mxq_attention_softmax")
+    return y
+
+
 def softmax_mxfp(x: Tensor, config: dict = None, dim: int = -1) -> Tensor:
     out = _fused_softmax(x, dim, 0, config["data_in_block_size"], config["data_in_exponent_width"],
                          config["data_in_frac_width"])
@@ -177,7 +234,8 @@ def _rotate_half(x: Tensor) -> Tensor:
 
 def rope_apply(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor | None:
     """x * cos + rotate_half(x) * sin in one kernel (mxq_rope) for x[batch, heads, seq, dim] on a CUDA device with
-    tables [seq, dim] or [batch, seq, dim]; the result has x's memory layout.  Returns None for layouts the kernel does
+    tables [seq, dim] or [batch, seq, dim]; x may be a strided view (transposed projection output), the result is
+    contiguous.  Returns None for layouts the kernel does
     not take (the caller then composes the elementwise ops)."""
     from . import _lib
     from .quantizers import _DT, _on_device, _stream
@@ -195,10 +253,7 @@ def rope_apply(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor | None:
     cos, sin = cos.contiguous(), sin.contiguous()
     tb = cos.stride(0) if cos.dim() == 3 and cos.shape[0] == b and b > 1 else 0
     ts = cos.stride(-2)
-    y = torch.empty_like(x)  # keeps the strides of a dense, possibly permuted x
-    if y.stride() != x.stride():
-        x = x.contiguous()
-        y = torch.empty_like(x)
+    y = torch.empty(x.shape, dtype=x.dtype, device=x.device)  # contiguous [b, h, s, d] whatever x's strides are
     with _on_device(x):
         rc = _lib.lib().mxq_rope(x.data_ptr(), y.data_ptr(), cos.data_ptr(), sin.data_ptr(), _DT[x.dtype], _DT[cos.dtype],
                                  b, h, s, d, x.stride(0), x.stride(1), x.stride(2), tb, ts, _stream(x))

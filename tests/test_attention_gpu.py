@@ -160,3 +160,45 @@ def test_batched_product_vs_fp64(dtype, shape):
     loop = torch.stack([gemm.linear_forward(a[i].to(DEV), b[i].to(DEV), None, dtype) for i in range(B)])
     tol = 2e-5 if dtype == torch.float32 else 1e-2  # bf16: the two routes may round an output differently
     assert float((out_same.float() - loop.float()).abs().max()) <= tol * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("cols", [32, 160, 512, 2048])
+def test_fused_attention_softmax_vs_composed_oracle(dtype, cols):
+    """mxq_attention_softmax against the separate operations on the CPU: scale, mask, minifloat / MXFP / MXINT / no
+    input quantizer, fp32 softmax, MXFP / MXINT / no quantizer of the probabilities.  The exponentials differ in the
+    last bit between device and host, so probabilities are compared to 2e-3 of the row maximum before the output
+    quantizer and by the share of identical values after it."""
+    from mase_b200 import functional as F
+
+    g = torch.Generator().manual_seed(cols)
+    B, H, S = 2, 3, 8
+    scores = (torch.randn(B, H, S, cols, generator=g) * 6).to(dtype)
+    mask = torch.zeros(B, 1, S, cols + 32, dtype=dtype)
+    mask[..., cols // 2:] = torch.finfo(dtype).min
+    mask[:, :, ::2, : cols // 2 + 7] = 0  # ragged visible lengths
+    fp = {"data_in_block_size": 32, "data_in_exponent_width": 4, "data_in_frac_width": 3}
+    it = {"data_in_block_size": 32, "data_in_width": 8}
+    mini = {"data_in_exponent_width": 5, "data_in_frac_width": 10}
+    quant = {"mxfp": lambda t: O.mxfp_fake(t, 32, 4, 3, -1), "mxint": lambda t: O.mxint_fake(t, 32, 8, -1),
+             "minifloat": lambda t: O.minifloat_fake(t, 5, 10), None: lambda t: t}
+    cfgs = {"mxfp": fp, "mxint": it, "minifloat": mini, None: None}
+    for in_fmt, out_fmt, scale, use_mask in (("minifloat", "mxfp", 0.125, True), ("minifloat", "mxint", 0.3, True),
+                                             (None, None, None, False), ("mxfp", None, 0.5, True),
+                                             ("mxint", "mxfp", None, False), ("minifloat", None, 0.125, False)):
+        got = F.attention_softmax(scores.to(DEV), scale, mask.to(DEV) if use_mask else None, in_fmt, cfgs[in_fmt],
+                                  out_fmt, cfgs[out_fmt])
+        assert got is not None, (in_fmt, out_fmt)
+        s = scores if scale is None else scores * scale
+        if use_mask:
+            s = s + mask[:, :, :, :cols]
+        p = torch.softmax(quant[in_fmt](s).to(torch.float32), dim=-1).to(dtype)
+        if out_fmt is None:
+            err = float((got.float().cpu() - p.float()).abs().max())
+            assert err <= 2e-3 * float(p.float().max()) + (0.0 if dtype == torch.float32 else 4e-3), (in_fmt, cols, err)
+        else:
+            ref = quant[out_fmt](p)
+            same = float((got.cpu() == ref).float().mean())
+            assert same >= 0.97, (in_fmt, out_fmt, cols, same)
+    # shapes the kernel does not take are declined, not mangled
+    assert F.attention_softmax(scores[..., :20].to(DEV), None, None, None, None, None, None) is None
