@@ -398,7 +398,7 @@ def calibration_extras(device) -> dict:
         return time.perf_counter() - t0, acts, q
 
     gptq_layer(256, 512)  # warm-up: kernels, the solver library
-    t_big, _, _ = gptq_layer(4096, 8192)
+    t_big = min(gptq_layer(4096, 8192)[0] for _ in range(2))  # host-driven (128 sweep steps): best of two
     t_small, acts, q = gptq_layer(1024, 2048)
     ws = w[:1024, :1024].clone()
     t0 = time.perf_counter()
