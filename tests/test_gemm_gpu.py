@@ -255,3 +255,24 @@ def test_unquantized_fp32_operands_keep_fp32_level_products(shape):
                           config={"bypass": True, "weight_block_size": 32, "weight_exponent_width": 4, "weight_frac_width": 3})
     layer.load_state_dict({"weight": w.to(DEV), "bias": b.to(DEV)}, strict=False)
     assert rel_err(layer(x.to(DEV)), ref) <= 2e-5
+
+
+@pytest.mark.parametrize("M", [1, 16, 128, 300])
+def test_static_weight_flag_changes_when_the_weight_is_fetched_not_the_result(M):
+    """MXQ_GEMM_STATIC_B lets the small-M kernel fetch the weight ahead of the stream dependency; results are the bits
+    of the unflagged call, also when calls are issued back to back on one stream (each launch may start under the
+    tail of the one before it) and for problems that do not use the small-M kernel at all."""
+    x, w = synthetic.linear_operands(M, 1024, 512, seed=M)
+    xp, wp = gemm.pack_mx_operand(x.to(DEV), 4, 3), gemm.pack_mx_operand(w.to(DEV), 4, 3)
+    torch.cuda.synchronize()  # the weight is complete before anything below is launched: the flag's precondition
+    plain = gemm.mx_gemm(xp, wp, None, torch.float32)
+    flagged = [gemm.mx_gemm(xp, wp, None, torch.float32, static_b=True) for _ in range(6)]
+    with gemm.options(max_ctas=64):  # the flag combines with other per-call options
+        flagged.append(gemm.mx_gemm(xp, wp, None, torch.float32, static_b=True))
+    gemm.check_status()
+    assert all(torch.equal(f, plain) for f in flagged)
+    # a weight packed immediately before an unflagged call: nothing is read before the pack has finished
+    for _ in range(3):
+        wp2 = gemm.pack_mx_operand(w.to(DEV), 4, 3)
+        assert torch.equal(gemm.mx_gemm(xp, wp2, None, torch.float32), plain)
+    gemm.check_status()
