@@ -163,7 +163,8 @@ typedef struct mxq_gemm_options {
    *                       ahead of the stream dependency, under the tail of the previous kernel.  Without the flag
    *                       nothing is read before the previous kernel of the stream has finished.  mxq_mx_linear,
    *                       mxq_mx_gated_linear and mxq_mx_linear_static imply it: their weight argument is by contract
-   *                       a weight packed earlier, not the product of a kernel in flight. */
+   *                       a weight packed earlier, not the product of a kernel in flight.
+   *   MXQ_GEMM_A_E5M2     mxq_gemm_mxf8: operand A holds E5M2 bytes (packed with E = 5, F = 2) instead of E4M3. */
   int32_t flags;
   /* Limit of every device-side wait in nanoseconds; 0 = one second.  When a wait runs out the kernel stores a
    * non-zero code in the status word, lets its copies in flight land, frees its tensor memory and returns. */
@@ -179,6 +180,7 @@ typedef struct mxq_gemm_options {
 } mxq_gemm_options;
 
 #define MXQ_GEMM_STATIC_B 1
+#define MXQ_GEMM_A_E5M2 4
 #define MXQ_TILES_AUTO 0
 #define MXQ_TILES_SINGLE 1
 #define MXQ_TILES_PAIRS 2
@@ -227,6 +229,7 @@ int mxq_mxfp4_pack_mma(const void *x, uint8_t *codes4, uint8_t *scales_mma, int 
 /* layout of the codes of a GEMM operand */
 #define MXQ_CODES_E4M3 0    /* one hardware E4M3 byte per element (mxq_mxfp_pack_mma) */
 #define MXQ_CODES_E2M1X2 1  /* two E2M1 nibbles per byte (mxq_mxfp4_pack_mma); B operand only */
+#define MXQ_CODES_E5M2 2    /* hardware E5M2 bytes (mxq_mxfp_pack_mma with E = 5, F = 2) */
 
 /* Block-scaled GEMM on operands produced by mxq_mxfp_pack_mma / mxq_mxfp4_pack_mma (kind::mxf8f6f4, one E8M0 scale
  * per 32 elements of K).  A is always E4M3 bytes; b_format says how B (the weight) is stored.  Replaces

@@ -70,8 +70,8 @@ class GemmOptions(ctypes.Structure):
 
 
 TILES_AUTO, TILES_SINGLE, TILES_PAIRS = 0, 1, 2
-GEMM_STATIC_B = 1  # bit of GemmOptions.flags
-CODES_E4M3, CODES_E2M1X2 = 0, 1
+GEMM_STATIC_B, GEMM_A_E5M2 = 1, 4  # bits of GemmOptions.flags
+CODES_E4M3, CODES_E2M1X2, CODES_E5M2 = 0, 1, 2
 TEST_DROP_LAST_LOAD = 1
 
 

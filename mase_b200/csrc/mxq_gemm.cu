@@ -221,6 +221,7 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
 
 // element format codes of the block-scaled kind's instruction descriptor (A: bits 7-9, B: bits 10-12); E4M3 is 0
 constexpr uint32_t kFormatE2M1 = 5;
+constexpr uint32_t kFormatE5M2 = 1;
 
 // instruction descriptor: fp32 accumulate, K-major A and B, M = 128, N = BN
 template <int kKind, int BN>
@@ -271,6 +272,7 @@ struct Params {
   unsigned long long wait_ns;  // limit of every wait
   int drop_last_load;   // test hook: CTA 0 never loads the last K chunk of its first tile
   uint32_t b_fp4;       // block-scaled kind: B holds E2M1 elements (two per byte in global memory) instead of E4M3 bytes
+  uint32_t fmt_bits = 0;  // block-scaled kind: element formats of A (bits 7-9) and B (bits 10-12) that are not E4M3 / E2M1
   uint32_t tx_less;     // a 4-bit box counts its packed bytes on the barrier, half of what lands in shared memory
   // Row-parallel GEMM fused with the reduce-scatter (CTA-pair kernel): rows [r * scatter_rows, (r + 1) * scatter_rows)
   // of the fp32 result go to store map r, which covers a buffer in GPU r's memory.  0 = one output, map 0.
@@ -543,7 +545,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    const uint32_t idesc = make_idesc<kKind, BN>() | (p.b_fp4 ? kFormatE2M1 << 10 : 0u);
+    const uint32_t idesc = make_idesc<kKind, BN>() | (p.b_fp4 ? kFormatE2M1 << 10 : 0u) | p.fmt_bits;
     uint32_t idk[4];  // per 32 bytes of K: byte k of each scale word
 #pragma unroll
     for (int k = 0; k < 4; ++k) idk[k] = kScaled ? idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4) : idesc;
@@ -883,7 +885,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       // ---------------- MMA issuer (leader only; warp-uniform loop, one elected lane issues) ----------------
       // the single-CTA descriptor with M = 256 (both CTAs) instead of 128
       const uint32_t idesc = (make_idesc<kKind, BN>() & ~(0x1Fu << 24)) | ((uint32_t)(256 >> 4) << 24) |
-                             (p.b_fp4 ? kFormatE2M1 << 10 : 0u);
+                             (p.b_fp4 ? kFormatE2M1 << 10 : 0u) | p.fmt_bits;
       uint32_t idk[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k)  // block-scaled: byte k of each scale word
@@ -1025,6 +1027,7 @@ struct SwapParams {
   int x_box_bytes;   // bytes one activation load delivers
   int out_bf16, bias_bf16;
   uint32_t w_fp4;    // block-scaled kind: the weight holds E2M1 elements, two per byte in global memory
+  uint32_t fmt_bits = 0;  // element formats other than E4M3 / E2M1: the weight's in bits 7-9, the activations' in bits 10-12
   uint32_t tx_less;  // a 4-bit box counts its packed bytes on the barrier, half of what lands in shared memory
   uint32_t early_w;  // the weight was complete before anything still running on the stream: fetch it ahead of the wait
   unsigned long long wait_ns;
@@ -1157,7 +1160,7 @@ umma_gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    const uint32_t idesc = make_idesc<kKind, BNX>() | (p.w_fp4 ? kFormatE2M1 << 7 : 0u);  // the weight is operand A here
+    const uint32_t idesc = make_idesc<kKind, BNX>() | (p.w_fp4 ? kFormatE2M1 << 7 : 0u) | p.fmt_bits;  // the weight is operand A here
     uint32_t idk[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) idk[k] = kScaled ? idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4) : idesc;
@@ -1348,6 +1351,7 @@ Opts make_opts(const mxq_gemm_options *o) {
     if (o->wait_limit_ns > 0) r.wait_ns = (unsigned long long)o->wait_limit_ns;
     r.test_hook = o->test_hook;
     r.static_b = (o->flags & MXQ_GEMM_STATIC_B) != 0;
+    r.a_e5m2 = (o->flags & MXQ_GEMM_A_E5M2) != 0;
   }
   return r;
 }
@@ -1459,6 +1463,7 @@ static int launch(const void *a, const void *b, const uint8_t *sfa, const uint8_
   p.a_box_bytes = a_rows * kRowBytes;
   p.wait_ns = o.wait_ns, p.drop_last_load = !kSplit && o.test_hook == MXQ_TEST_DROP_LAST_LOAD;
   p.b_fp4 = o.b_fp4 ? 1u : 0u;
+  p.fmt_bits = (o.a_e5m2 ? kFormatE5M2 << 7 : 0u) | (o.b_e5m2 ? kFormatE5M2 << 10 : 0u);
   p.tx_less = o.b_fp4 ? BN * (kRowBytes / 2) : 0;
   p.scatter_rows = 0, p.m_rotate = 0;
   CUtensorMap msa = ma, msb = ma;  // unused by the dense kinds
@@ -1537,6 +1542,7 @@ static int launch_pair(const void *a, const void *b, const uint8_t *sfa, const u
   p.a_box_bytes = BM * kRowBytes;
   p.wait_ns = o.wait_ns, p.drop_last_load = 0;
   p.b_fp4 = o.b_fp4 ? 1u : 0u;
+  p.fmt_bits = (o.a_e5m2 ? kFormatE5M2 << 7 : 0u) | (o.b_e5m2 ? kFormatE5M2 << 10 : 0u);
   p.tx_less = o.b_fp4 ? 2 * 128 * (kRowBytes / 2) : 0;  // the B boxes of both CTAs
   p.scatter_rows = o.scatter_world > 0 ? (int)(M / o.scatter_world) : 0;
   p.m_rotate = o.scatter_world > 0 ? (int)((((int64_t)o.scatter_rank + 1) % o.scatter_world) * (M / o.scatter_world / 256)) : 0;
@@ -1593,6 +1599,7 @@ static int launch_swap(const void *a, const void *b, const uint8_t *sfa, const u
   p.x_box_bytes = x_rows * kRowBytes;
   p.out_bf16 = out_dtype == MXQ_BF16, p.bias_bf16 = bias_dtype == MXQ_BF16, p.wait_ns = o.wait_ns;
   p.w_fp4 = o.b_fp4 ? 1u : 0u;
+  p.fmt_bits = (o.b_e5m2 ? kFormatE5M2 << 7 : 0u) | (o.a_e5m2 ? kFormatE5M2 << 10 : 0u);  // operands swapped
   p.tx_less = o.b_fp4 ? BM * (kRowBytes / 2) : 0;
   p.early_w = o.static_b ? 1u : 0u;
   static bool attr_done[64] = {};  // per device: function attributes belong to the device's context
@@ -1740,8 +1747,9 @@ int mxq_gemm_mxf8(const uint8_t *a_codes, const uint8_t *a_scales, const uint8_t
                   int b_format, void *d, const void *bias, int out_dtype, int bias_dtype, int64_t M, int64_t N, int64_t K,
                   int *status, const mxq_gemm_options *options, void *stream) {
   Opts o = make_opts(options);
-  if (b_format != MXQ_CODES_E4M3 && b_format != MXQ_CODES_E2M1X2) return MXQ_ERR_FORMAT;
+  if (b_format != MXQ_CODES_E4M3 && b_format != MXQ_CODES_E2M1X2 && b_format != MXQ_CODES_E5M2) return MXQ_ERR_FORMAT;
   o.b_fp4 = b_format == MXQ_CODES_E2M1X2;
+  o.b_e5m2 = b_format == MXQ_CODES_E5M2;
   return mxq::gemm::gemm_mxf8(a_codes, a_scales, b_codes, b_scales, d, bias, out_dtype, bias_dtype, M, N, K, status, o,
                               (cudaStream_t)stream);
 }

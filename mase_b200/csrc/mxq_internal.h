@@ -20,6 +20,7 @@ struct Opts {
   unsigned long long wait_ns = kDefaultWaitNs;
   int test_hook = 0;
   bool b_fp4 = false;  // block-scaled kind: B (the weight) holds E2M1 elements, two per byte
+  bool a_e5m2 = false, b_e5m2 = false;  // block-scaled kind: operand holds E5M2 bytes (MXQ_GEMM_A_E5M2 / MXQ_CODES_E5M2)
   bool static_b = false;  // B was complete before anything still running on the stream (MXQ_GEMM_STATIC_B)
   // reduce-scatter fused into the GEMM: fp32 slot buffer of every GPU of the group (rows M / scatter_world each)
   int scatter_world = 0;

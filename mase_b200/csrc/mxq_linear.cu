@@ -68,7 +68,8 @@ int mxq_mx_linear(const void *x, int in_dtype, const uint8_t *w_codes, const uin
   uint8_t *a_scales = a_codes + align256(M * K);
   const int rc = mxq::pack_mxfp_mma(x, a_codes, a_scales, in_dtype, M, K, E, F, floor_tab_host, (cudaStream_t)stream, true);
   if (rc != MXQ_OK) return rc;
-  const mxq_gemm_options o = with_static_weight(options);
+  mxq_gemm_options o = with_static_weight(options);
+  if (E == 5 && F == 2) o.flags |= MXQ_GEMM_A_E5M2;  // the pack wrote hardware E5M2 bytes
   return mxq_gemm_mxf8(a_codes, a_scales, w_codes, w_scales, w_format, d, bias, out_dtype, bias_dtype, M, N, K, status, &o,
                        stream);
 }

@@ -712,6 +712,48 @@ static bool legal_ef(int E, int F) {
          (E == 1 && F == 2);
 }
 // lanes sharing one block, or 0 when the fast path does not apply
+// MXFP8 with E5M2 elements as tensor-core operands: one thread per block of 32, the element codec of the generic path.
+// The hardware reads exponent code 31 as inf / nan while the reference uses it as a normal binade -- and its shared
+// exponent puts every block's maximum exactly there -- so each block is stored one scale step up with its values
+// halved (exponent codes one lower).  Halving is exact except for elements in the two lowest binades of the format
+// whose last fraction bit is set; those are rounded to nearest by the hardware conversion, an error of at most
+// 2**-17 of the block scale against a block maximum of at least 2**15.
+template <typename Tin>
+__global__ void __launch_bounds__(kThreads)
+mxfp_pack_mma_e5m2_kernel(const Tin *__restrict__ x, uint8_t *__restrict__ codes, uint8_t *__restrict__ scales,
+                          int64_t n_blocks, int64_t blocks_per_row, int64_t k_chunks, const __grid_constant__ Log2Tab tab) {
+  for (int64_t blk = (int64_t)blockIdx.x * kThreads + threadIdx.x; blk < n_blocks;
+       blk += (int64_t)gridDim.x * kThreads) {
+    const Tin *xb = x + blk * 32;
+    uint32_t bits[32];
+    uint32_t amax = 0;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      uint32_t b = __float_as_uint(load_scalar(xb + k));
+      if (((b & 0x7FFFFFFFu) >> 23) == 0) b = 0;  // zero and fp32-subnormal inputs are flushed
+      bits[k] = b;
+      amax = max(amax, b & 0x7FFFFFFFu);
+    }
+    const MxfpBlock p = mxfp_block(amax, 5, tab);
+    uint32_t w[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int k = 0; k < 4; k += 2) {
+        const float v0 = mxfp_decode(mxfp_encode(bits[4 * q + k], p.sh, 5, 2), 5, 2) * 0.5f;
+        const float v1 = mxfp_decode(mxfp_encode(bits[4 * q + k + 1], p.sh, 5, 2), 5, 2) * 0.5f;
+        word |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(v0, v1), __NV_SATFINITE, __NV_E5M2) << (8 * k);
+      }
+      w[q] = word;
+    }
+    uint4 *dst = reinterpret_cast<uint4 *>(codes + blk * 32);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]), dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    const int64_t row = blk / blocks_per_row, kb = blk - row * blocks_per_row;
+    scales[mma_scale_offset<int64_t>(row, kb, k_chunks)] = (uint8_t)(p.scale + 1);
+  }
+}
+
 template <typename Tin>
 static int fast_group(int block) {
   constexpr int N = Elem<Tin>::kVec;
@@ -922,7 +964,8 @@ int pack_mxfp_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in_dty
   if (rows == 0 || k == 0) return MXQ_OK;
   if (!x || !codes || !scales_mma || !floor_tab_host) return MXQ_ERR_NULL;
   if (rows < 0 || k < 0 || k % 32) return MXQ_ERR_SHAPE;
-  if (!legal_ef(E, F) || E > 4 || F > 3) return MXQ_ERR_FORMAT;
+  const bool e5m2 = E == 5 && F == 2;
+  if (!legal_ef(E, F) || (!e5m2 && (E > 4 || F > 3))) return MXQ_ERR_FORMAT;
   if (!aligned16(x) || !aligned16(codes)) return MXQ_ERR_ALIGN;
   const Log2Tab tab = load_tab(floor_tab_host);
   const int64_t k_chunks = (k + 127) / 128;
@@ -931,6 +974,19 @@ int pack_mxfp_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in_dty
   // and zero times an unset scale byte (0xFF is NaN) would poison valid outputs.  Scales of rows past the end only
   // reach accumulator rows that are never stored, so they may stay unset.
   if (k % 128 && cudaMemsetAsync(scales_mma, 0, sf_bytes, st) != cudaSuccess) return MXQ_ERR_LAUNCH;
+  if (e5m2) {  // hardware E5M2 bytes, every block at scale + 1: the element codec, one thread per block
+    const int64_t n_blocks = rows * (k / 32);
+    const int grid = grid_for(n_blocks, kThreads);
+    if (in_dtype == MXQ_F32)
+      mxfp_pack_mma_e5m2_kernel<float><<<grid, kThreads, 0, st>>>((const float *)x, codes, scales_mma, n_blocks, k / 32, k_chunks,
+                                                                tab);
+    else if (in_dtype == MXQ_BF16)
+      mxfp_pack_mma_e5m2_kernel<__nv_bfloat16>
+          <<<grid, kThreads, 0, st>>>((const __nv_bfloat16 *)x, codes, scales_mma, n_blocks, k / 32, k_chunks, tab);
+    else
+      return MXQ_ERR_DTYPE;
+    return check_launch();
+  }
   if (in_dtype == MXQ_F32) {
     const int64_t n_vec = rows * k / 4;
 #define MXQ_PACK(e, f)                                                                                  \

@@ -79,23 +79,29 @@ def options(**fields):
         _TLS.opts = prev
 
 
-_STATIC_B_ONLY = _lib.GemmOptions(flags=_lib.GEMM_STATIC_B)
+_FLAG_ONLY: dict[int, "_lib.GemmOptions"] = {}
 
 
-def _options_ptr(static_b: bool = False):
-    """Address of the options struct of this thread's `options(...)` block (None outside one).  static_b adds
-    MXQ_GEMM_STATIC_B: operand B is a weight packed long ago, which the small-M kernel may fetch ahead of the stream
-    dependency."""
+def _options_ptr(static_b: bool = False, a_e5m2: bool = False):
+    """Address of the options struct of this thread's `options(...)` block (None outside one), with the flags a call
+    adds itself: MXQ_GEMM_STATIC_B (operand B is a weight packed long ago, which the small-M kernel may fetch ahead of
+    the stream dependency) and MXQ_GEMM_A_E5M2 (operand A holds E5M2 bytes)."""
+    extra = (_lib.GEMM_STATIC_B if static_b else 0) | (_lib.GEMM_A_E5M2 if a_e5m2 else 0)
     cur = getattr(_TLS, "opts", None)
-    if not static_b:
+    if not extra:
         return None if cur is None else ctypes.addressof(cur[0])
     if cur is None:
-        return ctypes.addressof(_STATIC_B_ONLY)
-    if len(cur) < 3:
+        opt = _FLAG_ONLY.get(extra)
+        if opt is None:
+            opt = _FLAG_ONLY[extra] = _lib.GemmOptions(flags=extra)
+        return ctypes.addressof(opt)
+    cache = cur[2] if len(cur) > 2 else {}
+    if extra not in cache:
         fields = dict(cur[1])
-        fields["flags"] = fields.get("flags", 0) | _lib.GEMM_STATIC_B
-        cur = _TLS.opts = (cur[0], cur[1], _lib.GemmOptions(**fields))
-    return ctypes.addressof(cur[2])
+        fields["flags"] = fields.get("flags", 0) | extra
+        cache[extra] = _lib.GemmOptions(**fields)
+        cur = _TLS.opts = (cur[0], cur[1], cache)
+    return ctypes.addressof(cache[extra])
 
 
 def _status(device: torch.device) -> Tensor:
@@ -222,22 +228,24 @@ def batched_product(a: Tensor, b: Tensor, out_dtype: torch.dtype | None = None, 
 
 @dataclass
 class MXOperand:
-    """A [rows, K] matrix as tensor-core operands: hardware E4M3 bytes and E8M0 scales in the MMA chunk layout."""
+    """A [rows, K] matrix as tensor-core operands: hardware FP8 bytes and E8M0 scales in the MMA chunk layout."""
 
-    codes: Tensor   # uint8 [rows, K] (E4M3 bytes) or [rows, K / 2] (two E2M1 nibbles per byte, `fp4`)
+    codes: Tensor   # uint8 [rows, K] (E4M3 bytes, or E5M2 bytes with `e5m2`) or [rows, K / 2] (two E2M1 nibbles per byte, `fp4`)
     scales: Tensor  # uint8 [mxq_mma_scale_bytes(rows, K)]
     rows: int
     k: int
     fp4: bool = False  # weights only: MXFP4 codes nibble-packed; the copy engine expands them on the way to the MMA
+    e5m2: bool = False  # MXFP8 with E5M2 elements: hardware E5M2 bytes, every block one scale step up (values halved)
 
     @property
     def format(self) -> int:
-        return _lib.CODES_E2M1X2 if self.fp4 else _lib.CODES_E4M3
+        return _lib.CODES_E2M1X2 if self.fp4 else (_lib.CODES_E5M2 if self.e5m2 else _lib.CODES_E4M3)
 
 
 def mma_supported(exp_bits: int, frac_bits: int, block_size: int, k: int) -> bool:
-    """Formats the block-scaled GEMM can take: every value must be an E4M3 number, blocks of 32 along K."""
-    return block_size == 32 and exp_bits <= 4 and frac_bits <= 3 and k % 32 == 0
+    """Formats the block-scaled GEMM can take, blocks of 32 along K: elements that are E4M3 numbers (E <= 4, F <= 3),
+    or E5M2."""
+    return block_size == 32 and k % 32 == 0 and ((exp_bits <= 4 and frac_bits <= 3) or (exp_bits, frac_bits) == (5, 2))
 
 
 def fp4_supported(exp_bits: int, frac_bits: int, k: int) -> bool:
@@ -254,7 +262,7 @@ def pack_mx_operand(x: Tensor, exp_bits: int, frac_bits: int, fp4: bool = False)
     assert x.dim() == 2
     rows, k = x.shape
     if not mma_supported(exp_bits, frac_bits, 32, k):
-        raise NotImplementedError("block-scaled operands need E <= 4, F <= 3 and K divisible by 32")
+        raise NotImplementedError("block-scaled operands need E <= 4 and F <= 3, or E5M2, and K divisible by 32")
     xc = x.contiguous()
     if xc.data_ptr() % 16:
         xc = xc.clone()
@@ -274,7 +282,7 @@ def pack_mx_operand(x: Tensor, exp_bits: int, frac_bits: int, fp4: bool = False)
         rc = lib.mxq_mxfp_pack_mma(xc.data_ptr(), codes.data_ptr(), scales.data_ptr(), _DT[x.dtype], rows, k, exp_bits,
                                    frac_bits, _floor_tab_ptr(), _stream(x))
     _lib.check(rc, "mxq_mxfp_pack_mma")
-    return MXOperand(codes, scales, rows, k)
+    return MXOperand(codes, scales, rows, k, False, (exp_bits, frac_bits) == (5, 2))
 
 
 def pack_gated_operand(gate: Tensor, up: Tensor, exp_bits: int, frac_bits: int) -> MXOperand:
@@ -287,8 +295,8 @@ def pack_gated_operand(gate: Tensor, up: Tensor, exp_bits: int, frac_bits: int) 
         raise NotImplementedError("pack_gated_operand: gate and up must be bfloat16")
     assert gate.dim() == 2 and gate.shape == up.shape
     rows, k = gate.shape
-    if not mma_supported(exp_bits, frac_bits, 32, k):
-        raise NotImplementedError("block-scaled operands need E <= 4, F <= 3 and K divisible by 32")
+    if not mma_supported(exp_bits, frac_bits, 32, k) or exp_bits > 4:
+        raise NotImplementedError("the fused SiLU*mul pack needs E <= 4, F <= 3 and K divisible by 32")
     ok = lambda t: t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0  # noqa: E731
     if not (ok(gate) and ok(up) and gate.stride(0) == up.stride(0)):
         gate, up = gate.contiguous(), up.contiguous()
@@ -339,14 +347,14 @@ def mx_gemm(a: MXOperand, b: MXOperand, bias: Tensor | None, out_dtype: torch.dt
     """[a.rows, b.rows] = a @ b^T (+ bias) with block-scaled MXFP8 tensor-core MMAs, fp32 accumulation.
     static_b: b was packed before any kernel that may still be running on the stream was launched (a layer's weight);
     never set it for an operand that the stream is still producing."""
-    assert a.k == b.k and not a.fp4, "the first operand is always E4M3 bytes"
+    assert a.k == b.k and not a.fp4, "the first operand holds one byte per element"
     out = torch.empty((a.rows, b.rows), dtype=out_dtype, device=a.codes.device)
     bb, bdt = _bias_args(bias)
     st = _status(a.codes.device)
     with _on_device(a.codes):
         rc = _lib.lib().mxq_gemm_mxf8(a.codes.data_ptr(), a.scales.data_ptr(), b.codes.data_ptr(), b.scales.data_ptr(),
                                       b.format, out.data_ptr(), 0 if bb is None else bb.data_ptr(), _DT[out_dtype], bdt, a.rows,
-                                      b.rows, a.k, st.data_ptr(), _options_ptr(static_b), _stream(a.codes))
+                                      b.rows, a.k, st.data_ptr(), _options_ptr(static_b, a.e5m2), _stream(a.codes))
     _lib.check(rc, "mxq_gemm_mxf8")
     if _CHECK_EVERY_CALL:
         check_status(a.codes.device)

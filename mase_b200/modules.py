@@ -151,7 +151,8 @@ class LinearMXFP(_LinearBase):
         if cached is not None and cached.codes is codes and cached.scales is scales:
             return cached
         fp4 = codes.shape[1] * 2 == self.in_features and codes.shape[1] != self.in_features
-        op = MXOperand(codes, scales, codes.shape[0], self.in_features, fp4)
+        e5m2 = (self.config.get("weight_exponent_width"), self.config.get("weight_frac_width")) == (5, 2)
+        op = MXOperand(codes, scales, codes.shape[0], self.in_features, fp4, e5m2)
         self.__dict__["_mx_operand"] = op
         return op
 
@@ -245,7 +246,7 @@ class LinearMXFP(_LinearBase):
         kernel reads gate and up and writes the quantized tensor-core operand.  Falls back to the plain forward where
         the block-scaled path does not apply."""
         _, x_block, x_exp, x_frac = self._input_format()
-        if gate.dtype == torch.bfloat16 and self._uses_packed_path(gate):
+        if gate.dtype == torch.bfloat16 and self._uses_packed_path(gate) and x_exp <= 4:
             return mx_gated_linear(gate, up, self._packed_weight(), self.bias, x_exp, x_frac, self.output_dtype)
         return self.forward(torch.nn.functional.silu(gate) * up)
 

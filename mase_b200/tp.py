@@ -243,7 +243,9 @@ class RowParallelLinear(nn.Module):
             return False
         inner = self.inner
         rows = like.numel() // like.shape[-1]
-        return (hasattr(inner, "_uses_packed_path") and inner._uses_packed_path(like) and inner.bias is None
+        e5m2 = any((inner.config.get(k + "_exponent_width"), inner.config.get(k + "_frac_width")) == (5, 2)
+                   for k in ("weight", "data_in")) if hasattr(inner, "config") else False
+        return (hasattr(inner, "_uses_packed_path") and inner._uses_packed_path(like) and inner.bias is None and not e5m2
                 and rows % (256 * self.tp.world) == 0 and inner.out_features % 8 == 0
                 and PeerReducer.available(self.tp, like.device))
 

@@ -349,3 +349,37 @@ def test_decode_sized_forward_matches_its_parts(shape, fp4):
     ref = O.mxfp_fake(x, 32, 4, 3).float() @ O.mxfp_fake(w, 32, we, wf, 1).float().t()
     err = float((gemm.mx_linear(xd, wp, None, 4, 3, torch.float32).cpu() - ref).abs().max() / ref.abs().max())
     assert err <= 1e-3, (shape, fp4, err)
+
+
+@pytest.mark.parametrize("which", ["weight", "activation", "both"])
+@pytest.mark.parametrize("shape", [(16, 1024, 512), (256, 512, 384), (1024, 2048, 1024)])
+def test_e5m2_operands_on_the_block_scaled_mma(which, shape):
+    """MXFP8 with E5M2 elements runs on the block-scaled tensor-core MMA.  The hardware reads exponent code 31 as
+    inf / nan, so every block is stored one scale step up with halved values; halving is exact except for elements 30
+    binades below their block's maximum, so the result must equal the fp32 product of the oracle-quantized operands to
+    1e-5 of the largest output (accumulation order), for the small-M, single-CTA and CTA-pair kernels, through the
+    module (fused pack + GEMM) and through separately packed operands."""
+    M, K, N = shape
+    x, w = synthetic.linear_operands(M, K, N, seed=K)
+    x[0, :32] = 0
+    x[1, 32:64] *= 1e-3
+    x[1, 40] = 90.0  # a block that spans 17 binades
+    we, wf = (5, 2) if which in ("weight", "both") else (4, 3)
+    xe, xf = (5, 2) if which in ("activation", "both") else (4, 3)
+    cfg = {"weight_block_size": 32, "weight_exponent_width": we, "weight_frac_width": wf,
+           "data_in_block_size": 32, "data_in_exponent_width": xe, "data_in_frac_width": xf}
+    layer = mb.LinearMXFP(K, N, bias=False, device=DEV, dtype=torch.bfloat16, config=cfg)
+    layer.load_state_dict({"weight": w.to(DEV)}, strict=False)
+    packed = layer._packed_weight()
+    assert packed is not None and packed.e5m2 == (we == 5)
+    assert_bits_equal(layer.weight.data, O.mxfp_fake(w, 32, we, wf, 1), "weight")
+    layer.output_dtype = torch.float32
+    y = layer(x.to(DEV))
+    xp = gemm.pack_mx_operand(x.to(DEV), xe, xf)
+    assert xp.e5m2 == (xe == 5)
+    y2 = gemm.mx_gemm(xp, packed, None, torch.float32)
+    gemm.check_status()
+    ref = O.mxfp_fake(x, 32, xe, xf).float() @ O.mxfp_fake(w, 32, we, wf, 1).float().t()
+    for got, what in ((y, "module"), (y2, "parts")):
+        err = float((got.cpu() - ref).abs().max() / ref.abs().max())
+        assert err <= 1e-5, (which, shape, what, err)
