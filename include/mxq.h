@@ -211,9 +211,11 @@ int64_t mxq_mma_scale_bytes(int64_t rows, int64_t k);
 
 /* Quantize a [rows, k] matrix to MXFP (E, F) with blocks of 32 along k -- the same codes and scales as
  * extract_mxfp_components (chop/nn/quantizers/mxfp/fake.py:12-72) -- and store them as tensor-core operands:
- * hardware E4M3 bytes [rows, k] plus E8M0 scales in 512-byte chunks per 128 rows x 128 columns.  E <= 4, F <= 3.
- * A block that holds the reference's top E4M3 code (480, NaN in hardware) is stored one binade lower with its
- * scale raised by one.  The scale array is padded to whole 256-row tiles; scale bytes of rows past `rows` are left
+ * hardware E4M3 bytes [rows, k] plus E8M0 scales in 512-byte chunks per 128 rows x 128 columns.  E <= 4, F <= 3,
+ * or E = 5, F = 2.  A block that holds the reference's top E4M3 code (480, NaN in hardware) is stored one binade
+ * lower with its scale raised by one.  E = 5, F = 2 writes hardware E5M2 bytes instead, every block one scale step up
+ * with halved values (the reference's top exponent code 31 is inf / nan in hardware); the GEMM is told through
+ * MXQ_CODES_E5M2 (operand B) or MXQ_GEMM_A_E5M2 (operand A).  The scale array is padded to whole 256-row tiles; scale bytes of rows past `rows` are left
  * unset (they only reach accumulator rows that the GEMM never stores), scale bytes of K blocks past `k` are zero. */
 int mxq_mxfp_pack_mma(const void *x, uint8_t *codes, uint8_t *scales_mma, int in_dtype, int64_t rows, int64_t k, int E,
                       int F, const uint8_t *floor_tab_host, void *stream);
