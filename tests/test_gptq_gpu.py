@@ -121,3 +121,20 @@ def test_quantize_tensor_dispatch():
     assert torch.equal(y, mb.mxint_quantizer(x, 32, 4, 1))
     with pytest.raises(ValueError):
         gptq.quantize_tensor(x, 1, "int8", MXINT4, quantile_search=False)
+
+
+def test_run_gptq_with_the_activation_weighted_search():
+    """clip_search_y: the inner clipping search weighs its error by the layer's calibration inputs (the last Linear
+    of each group collects them, as in the reference).  One decoder layer, MXFP4; the weights must come out finite,
+    changed, and with at most 15 distinct values per block."""
+    g = torch.Generator().manual_seed(4)
+    data = [torch.randint(0, 97, (1, 16), generator=g) for _ in range(3)]
+    base = tiny_llama()
+    before = base.model.layers[0].mlp.down_proj.weight.detach().clone()
+    cfg = {"device": DEV, "format": "mxfp", "weight_config": MXFP4, "quantile_search": True, "clip_search_y": True,
+           "cali_batch_size": 2, "calibration_data": data, "max_layers": 1}
+    out = gptq.run_gptq(base, cfg)
+    w = out.model.layers[0].mlp.down_proj.weight.detach().cpu()
+    assert torch.isfinite(w).all() and not torch.equal(w, before)
+    assert max(len(torch.unique(b)) for b in w.reshape(-1, 32)[:128]) <= 15
+    assert torch.equal(out.model.layers[1].mlp.down_proj.weight.cpu(), tiny_llama().model.layers[1].mlp.down_proj.weight)
