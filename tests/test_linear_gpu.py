@@ -383,3 +383,26 @@ def test_e5m2_operands_on_the_block_scaled_mma(which, shape):
     for got, what in ((y, "module"), (y2, "parts")):
         err = float((got.cpu() - ref).abs().max() / ref.abs().max())
         assert err <= 1e-5, (which, shape, what, err)
+
+
+def test_gated_pack_matches_torch_for_every_bf16_gate_value():
+    """The fused SiLU*mul pack evaluates silu with a fast exponential and division where that provably rounds like the
+    exact expression, and with the exact expression elsewhere: every finite bf16 gate pattern, against five up values,
+    must give the codes and scales of packing torch's own `silu(gate) * up`."""
+    pat = torch.arange(0, 65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    pat = pat[torch.isfinite(pat.float())]
+    pad = (-pat.numel()) % 128
+    gate_row = torch.cat([pat, torch.zeros(pad, dtype=torch.bfloat16)])
+    ups = torch.tensor([1.0, -0.37, 3.0, 1e-3, 117.0], dtype=torch.bfloat16)
+    gate = gate_row[None].expand(len(ups), -1).contiguous().to(DEV)
+    up = ups[:, None].expand(-1, gate_row.numel()).contiguous().to(DEV)
+    fused = gemm.pack_gated_operand(gate, up, 4, 3)
+    ref = gemm.pack_mx_operand(torch.nn.functional.silu(gate) * up, 4, 3)
+    torch.cuda.synchronize()
+    assert torch.equal(fused.codes, ref.codes)
+    # scale bytes of the rows that exist (the array is padded to 256-row tiles whose other bytes are never written)
+    rows, k = gate.shape
+    r = torch.arange(rows)[:, None]
+    kb = torch.arange(k // 32)[None]
+    off = ((r >> 7) * (k // 128) + (kb >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (kb & 3)
+    assert torch.equal(fused.scales.cpu()[off], ref.scales.cpu()[off])
