@@ -202,3 +202,37 @@ def test_fused_attention_softmax_vs_composed_oracle(dtype, cols):
             assert same >= 0.97, (in_fmt, out_fmt, cols, same)
     # shapes the kernel does not take are declined, not mangled
     assert F.attention_softmax(scores[..., :20].to(DEV), None, None, None, None, None, None) is None
+
+
+@pytest.mark.parametrize("fmt", ["mxfp", "mxint"])
+def test_decode_step_with_a_cache_matches_the_last_row_of_a_prefill(fmt):
+    """One query row against 96 cached keys (the batched products with M = 1, the softmax kernel with one row per
+    head): the output must be that of the last token of a 96-token prefill through the same cached path."""
+    g = torch.Generator().manual_seed(12)
+    B, S, HID = 2, 96, 256
+    block = CLS[fmt](None, 0, QCFG[fmt], hidden_size=HID, num_heads=4, num_kv_heads=2, device=DEV, dtype=torch.bfloat16)
+    for prm in block.parameters():
+        prm.data.copy_((torch.randn(prm.shape, generator=g) * 0.05).to(DEV))
+    hidden = torch.randn(B, S, HID, generator=g).bfloat16().to(DEV)
+    pos = torch.arange(S, dtype=torch.float32)
+    inv = 1.0 / (10000 ** (torch.arange(0, 64, 2, dtype=torch.float32) / 64))
+    ang = torch.cat([pos[:, None] * inv[None], pos[:, None] * inv[None]], dim=-1)
+    cos, sin = ang.cos()[None].expand(B, S, 64).bfloat16().to(DEV), ang.sin()[None].expand(B, S, 64).bfloat16().to(DEV)
+    causal = torch.zeros(B, 1, S, S, dtype=torch.bfloat16).masked_fill(
+        torch.ones(S, S, dtype=torch.bool).triu(1)[None, None], torch.finfo(torch.bfloat16).min).to(DEV)
+    with torch.no_grad():
+        full, _ = block(hidden, (cos, sin), causal, past_key_value=ListCache())
+        # fill the cache with the first 95 tokens through a twin whose probabilities stay unquantized (95 keys are
+        # not whole blocks of 32, which the reference's quantizer rejects as well); keys and values are cached alike
+        cache = ListCache()
+        twin = CLS[fmt](None, 0, dict(QCFG[fmt], av_matmul={"bypass": True}), hidden_size=HID, num_heads=4, num_kv_heads=2,
+                        device=DEV, dtype=torch.bfloat16)
+        twin.load_state_dict(block.state_dict())
+        twin(hidden[:, : S - 1], (cos[:, : S - 1], sin[:, : S - 1]), causal[:, :, : S - 1, : S - 1], past_key_value=cache)
+        step, probs = block(hidden[:, S - 1:], (cos[:, S - 1:], sin[:, S - 1:]),
+                            torch.zeros(B, 1, 1, S, dtype=torch.bfloat16, device=DEV), past_key_value=cache)
+    gemm.check_status()
+    assert step.shape == (B, 1, HID) and probs.shape == (B, 4, 1, S)
+    ref = full[:, S - 1:].float()
+    err = float((step.float() - ref).abs().max() / ref.abs().max())
+    assert err <= 2e-2, (fmt, err)
