@@ -446,6 +446,20 @@ def attention_extras(device, peaks: dict) -> dict:
         t_qk = 1.0 / quick_gbs(lambda: gemm.batched_product(q, k), 1, calls=10) / 1e9
         t_pv = 1.0 / quick_gbs(lambda: gemm.batched_product(p, vt), 1, calls=10) / 1e9
     flops = 2.0 * B * H * S * S * D
+    # the same block with its projections swapped for MXINT8 layers (what the quantize pass does by name): every
+    # kernel of the forward is then this package's
+    import mase_b200 as mb
+
+    int_cfg = {"weight_block_size": 32, "weight_width": 8, "data_in_block_size": 32, "data_in_width": 8}
+    quant_block = attention.AttentionMXFP.from_attention(block, qc)
+    for name in ("q_proj", "k_proj", "v_proj", "o_proj"):
+        lin = getattr(quant_block, name)
+        q_lin = mb.LinearMXInt(lin.in_features, lin.out_features, bias=False, device=device, dtype=torch.bfloat16, config=int_cfg)
+        q_lin.load_state_dict({"weight": lin.weight.data}, strict=False)
+        setattr(quant_block, name, q_lin)
+    with torch.no_grad():
+        t_quant_block = 1.0 / quick_gbs(lambda: quant_block(hd, (cd, sd), md), 1, calls=5) / 1e9
+    del quant_block
     w = {n: prm.detach().cpu() for n, prm in block.named_parameters()}
     torch.set_num_threads(os.cpu_count() or 1)
     t0 = time.perf_counter()
@@ -455,7 +469,8 @@ def attention_extras(device, peaks: dict) -> dict:
     # bytes each product has to move: both operands once, the result once (bf16)
     qk_bytes = 2.0 * B * H * (S * D + S * D + S * S)
     pv_bytes = 2.0 * B * H * (S * S + D * S + S * D)
-    return {"block_ms": t_block * 1e3, "qk_batched_us": t_qk * 1e6, "pv_batched_us": t_pv * 1e6,
+    return {"block_ms": t_block * 1e3, "block_with_mxint8_projections_ms": t_quant_block * 1e3,
+            "qk_batched_us": t_qk * 1e6, "pv_batched_us": t_pv * 1e6,
             "qk_TFLOPs": flops / t_qk / 1e12, "pv_TFLOPs": flops / t_pv / 1e12,
             "roofline": {"bound": "hbm", "unit": "GB/s", "peak": hbm, "peak_source": f"{hbm_kind} copy bandwidth",
                          "qk_achieved": qk_bytes / t_qk / 1e9, "qk_frac": qk_bytes / t_qk / 1e9 / hbm,
