@@ -2,7 +2,10 @@
 
 Public surface (same names as in `chop.nn.quantizers` / `chop.nn.quantized`):
   quantizers: mxint_quantizer, mxfp_quantizer, block_fp_quantizer, *_quantizer_sim, extract_* / compose_*
-  modules:    LinearMXFP, LinearMXInt, LinearBlockFP, linearBlockFP
+  modules:    LinearMXFP, LinearMXInt, LinearBlockFP, linearBlockFP, EmbeddingMXFP / MXInt, RMSNormMinifloat,
+              AttentionMXFP / MXInt (+ the Qwen3 variants), GatedMLPMX            (mase_b200.attention)
+  functional: matmul / bmm / kv_cache / softmax / silu / rope for mxfp, mxint, minifloat
+  calibration: the clipping search inside *_quantizer_sim(quantile_search=True); GPTQ (mase_b200.gptq)
   patch(chop) registers them in an imported MASE so that its quantize passes pick them up.
 
 All compute goes through libmxq.so (C ABI in include/mxq.h); there is no CPU or eager fallback.
@@ -39,6 +42,9 @@ from .modules import (  # noqa: F401
 from .functional import (  # noqa: F401
     bmm_mxfp, bmm_mxint, kv_cache_mxfp, kv_cache_mxint, matmul_mxfp, matmul_mxint, rope_minifloat, rope_mxfp, rope_mxint,
     silu_minifloat, silu_mxfp, silu_mxint, softmax_minifloat, softmax_mxfp, softmax_mxint,
+)
+from .attention import (  # noqa: F401
+    AttentionMXFP, AttentionMXInt, GatedMLPMX, Qwen3AttentionMXFP, Qwen3AttentionMXInt,
 )
 from .patch import patch  # noqa: F401
 
