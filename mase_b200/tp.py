@@ -432,7 +432,7 @@ def build_tp_gated_mlp(cls, w_gate: Tensor, w_up: Tensor, w_down: Tensor, config
     return TPGatedMLP(None, None, down, gate_up=gate_up)
 
 
-def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, comm_sms: int = 32) -> Tensor:
+def run_mlp_stack(layers: list[TPGatedMLP], x: Tensor, micro_batches: int = 1, comm_sms: int = 16) -> Tensor:
     """x -> layer_1 -> ... -> layer_L.  With micro_batches > 1 the rows are split and the cross-GPU reduction of one
     micro-batch (side stream) overlaps the GEMMs of the next one, within and across layers.  The GEMM kernels are
     persistent and fill every SM, so while the pipeline runs they are capped to leave `comm_sms` SMs to the
