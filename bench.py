@@ -561,9 +561,9 @@ def linear_extras(device, peaks: dict) -> dict:
         xq = mb.mxfp_quantizer(x, 32, 4, 3)
         t_dense = 1.0 / quick_gbs(lambda: gemm.linear_forward(xq, layer.weight, None), 1, calls=calls) / 1e9
         # the same forward replayed from a CUDA graph: device time without the per-call host work.  Small problems are
-        # captured eight to a graph, each on its own copy of the layer (8 x 17 MB of packed weights > L2), so that the
+        # captured sixteen to a graph, each on its own copy of the layer (16 x 17 MB of packed weights > L2), so that the
         # replay's launch cost does not hide a kernel of a few microseconds and the weights stream from HBM every time.
-        reps = 8 if M <= 128 else 1
+        reps = 16 if M <= 128 else 1
         if reps > 1 and len(copies) == 1:
             copies.extend(copy.deepcopy(layer) for _ in range(reps - 1))
         graph = torch.cuda.CUDAGraph()
@@ -585,8 +585,8 @@ def linear_extras(device, peaks: dict) -> dict:
             roof = {"bound": "hbm", "achieved": algo / t_graph / 1e9, "peak": hbm, "unit": "GB/s",
                     "frac": algo / t_graph / 1e9 / hbm, "gemm_only_frac": algo / t_gemm / 1e9 / hbm,
                     "peak_source": f"{hbm_kind} copy bandwidth", "algorithmic_bytes": algo,
-                    "timed": "whole forward (activation pack + GEMM), eight layers with their own weights to a CUDA "
-                             "graph: 140 MB of weights per replay, more than L2"}
+                    "timed": "whole forward (activation pack + GEMM), sixteen layers with their own weights to a CUDA "
+                             "graph: 280 MB of weights per replay, more than L2"}
         else:
             ach = flops / t_graph / 1e12
             roof = {"bound": "tensor", "achieved": ach, "peak": peaks["fp8_used"], "unit": "TFLOP/s",

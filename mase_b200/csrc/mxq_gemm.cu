@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "mxq.h"
 #include "mxq_internal.h"
@@ -1264,7 +1265,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static EncodeTiledFn encode_fn() {
+static EncodeTiledFn driver_encode_fn() {
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void *ptr = nullptr;
@@ -1275,6 +1276,44 @@ static EncodeTiledFn encode_fn() {
   }
   return fn;
 }
+
+// A tensor map is a pure function of the arguments of cuTensorMapEncodeTiled (it holds an address and a geometry, no
+// state), and a serving loop launches the same few problems over and over: every host thread keeps the maps it encoded
+// last, keyed by all arguments, and a launch that finds its map copies 128 bytes instead of calling the driver.
+struct MapKey {
+  uint64_t v[16];
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+constexpr int kMapSlots = 128;
+static CUresult encode_cached(CUtensorMap *map, CUtensorMapDataType dt, cuuint32_t rank, void *ptr, const cuuint64_t *dims,
+                              const cuuint64_t *strides, const cuuint32_t *box, const cuuint32_t *estr,
+                              CUtensorMapInterleave il, CUtensorMapSwizzle sw, CUtensorMapL2promotion promo,
+                              CUtensorMapFloatOOBfill fill) {
+  EncodeTiledFn fn = driver_encode_fn();
+  if (rank < 1 || rank > 3) return fn(map, dt, rank, ptr, dims, strides, box, estr, il, sw, promo, fill);
+  static thread_local MapSlot slots[kMapSlots] = {};
+  MapKey k = {};
+  k.v[0] = reinterpret_cast<uintptr_t>(ptr);
+  k.v[1] = ((uint64_t)dt << 48) | ((uint64_t)rank << 40) | ((uint64_t)il << 32) | ((uint64_t)sw << 24) | ((uint64_t)promo << 16) |
+           (uint64_t)fill;
+  for (cuuint32_t i = 0; i < rank; ++i) k.v[2 + i] = dims[i], k.v[8 + i] = ((uint64_t)box[i] << 32) | estr[i];
+  for (cuuint32_t i = 0; i + 1 < rank; ++i) k.v[5 + i] = strides[i];
+  uint64_t h = 0x9E3779B97F4A7C15ull;
+  for (int i = 0; i < 11; ++i) h = (h ^ k.v[i]) * 0x100000001B3ull;
+  MapSlot &s = slots[(h >> 20) % kMapSlots];
+  if (s.valid && memcmp(&s.key, &k, sizeof(k)) == 0) {
+    *map = s.map;
+    return CUDA_SUCCESS;
+  }
+  const CUresult r = fn(map, dt, rank, ptr, dims, strides, box, estr, il, sw, promo, fill);
+  if (r == CUDA_SUCCESS) s.key = k, s.map = *map, s.valid = true;
+  return r;
+}
+static EncodeTiledFn encode_fn() { return driver_encode_fn() ? &encode_cached : nullptr; }
 
 // tensor map of a K-major matrix [rows, k] with boxes of box_rows x 128 bytes, 128-byte swizzle, zero fill
 static int make_map(CUtensorMap *map, const void *ptr, int kind, int64_t rows, int64_t k, int box_rows) {
